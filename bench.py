@@ -1,0 +1,391 @@
+"""Benchmark of the quantized-weight hot path.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Workload (config.workload "ffn_matvec_set_b1"): the Q4_K_M FFN matvec set at
+batch 1 -- gate and up [12288 x 4096] in Q4_K and down [4096 x 12288] in Q6_K,
+weights N(0, 0.02) before quantization, activations N(0, 1), f32 -- one "step"
+being the three matvecs over ONE of several distinct resident weight
+instances, so that every step streams its weights from HBM rather than L2.
+
+Metric: algorithmic bytes (GGUF block bytes of the three tensors plus the f32
+vectors) per second.  `value` is timed with the activations already on the
+device (a CUDA graph of K steps, CUDA events); `e2e` is timed through the
+C-ABI host-pointer calls with pinned host buffers, copies inside the timed
+region.  `--impl reference` times the CPU restatement of the reference's own
+matvec loops on the host cores for the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+HIDDEN, FFN = 4096, 12288
+Q4_K, Q6_K = 12, 14
+GATE_BYTES = FFN * (HIDDEN // 256) * 144      # 28,311,552
+DOWN_BYTES = HIDDEN * (FFN // 256) * 210      # 41,287,680
+VEC_BYTES = 4 * (HIDDEN + 2 * FFN + FFN + HIDDEN)  # x, gate out, up out, down in, down out
+STEP_BYTES = 2 * GATE_BYTES + DOWN_BYTES + VEC_BYTES  # 98,091,008
+SEED = 0x4C455649
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            return json.load(f), "measured"
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clock and throttle-reason samples during the timed region."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+              "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, device: int):
+        self.device, self.proc, self.lines = device, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if not self.proc:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=2)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            f = [s.strip() for s in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(smax) if smax else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def make_inputs():
+    from leviathan_b200 import quant as Q
+
+    x = Q.normal(SEED ^ 0x100, (HIDDEN,), 1.0)
+    a = Q.normal(SEED ^ 0x101, (FFN,), 1.0)
+    return x, a
+
+
+def make_instance(i: int, device: str):
+    """Quantized gate/up/down of weight instance i (uint8 tensors on device)."""
+    import torch
+
+    from leviathan_b200 import quant as Q
+
+    g = torch.Generator(device=device).manual_seed(SEED + 16 * i)
+    out = []
+    for t, rows, cols in ((Q4_K, FFN, HIDDEN), (Q4_K, FFN, HIDDEN), (Q6_K, HIDDEN, FFN)):
+        w = torch.randn((rows, cols), generator=g, device=device, dtype=torch.float32) * 0.02
+        out.append(Q.quantize(t, w))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# CPU arm: the oracle's threaded matvec (the reference's own CPU loops)
+# ---------------------------------------------------------------------------
+
+def cpu_step_timer(threads: int | None, steps: int, warmup: int):
+    from oracle import oracle as O
+
+    native = None
+    try:
+        native = O.build(native_out=os.path.join(tempfile.gettempdir(), "lev_oracle_native"))
+    except Exception:
+        native = None
+    threads = threads or O.hardware_threads()
+    gate, up, down = [t.numpy() for t in make_instance(0, "cpu")]
+    x, a = make_inputs()
+
+    def step():
+        O.matvec_threaded(Q4_K, gate, FFN, HIDDEN, x, threads, lib_path=native)
+        O.matvec_threaded(Q4_K, up, FFN, HIDDEN, x, threads, lib_path=native)
+        O.matvec_threaded(Q6_K, down, HIDDEN, FFN, a, threads, lib_path=native)
+
+    for _ in range(warmup):
+        step()
+    times = []
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        step()
+        times.append(time.perf_counter() - t0)
+    return times, threads, ("native" if native else "portable")
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    steps = max(1, min(args.steps, 20))
+    times, threads, build = cpu_step_timer(None, steps, max(1, min(args.warmup, 3)))
+    ms = 1000.0 * sum(times) / len(times)
+    value = STEP_BYTES / (ms * 1e-3) / 1e9
+    line = {
+        "impl": "reference", "metric": "Q4/Q6 matvec HBM GB/s", "value": value, "unit": "GB/s",
+        "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "ffn_matvec_set_b1", "gate_up": "Q4_K 12288x4096 x2", "down": "Q6_K 4096x12288",
+                   "columns": 1, "bytes_per_step": STEP_BYTES},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
+                         "sample": f"{steps} full steps of the same three matvecs, oracle C port ({build} build), "
+                                   "row chunks over all host threads"},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+# ---------------------------------------------------------------------------
+# GPU arm
+# ---------------------------------------------------------------------------
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    import leviathan_b200 as lev
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    torch.cuda.set_device(local)
+    dev = f"cuda:{local}"
+    ctx = lev.Context(local)
+
+    # Each rank holds its own weight instances (no data-path collective: the
+    # FFN sets of different ranks are independent objects).
+    n_inst = args.instances
+    inst = []
+    for i in range(n_inst):
+        g, u, d = make_instance(rank * n_inst + i, dev)
+        inst.append((ctx.upload(g, Q4_K, FFN, HIDDEN), ctx.upload(u, Q4_K, FFN, HIDDEN),
+                     ctx.upload(d, Q6_K, HIDDEN, FFN)))
+        del g, u, d
+    torch.cuda.empty_cache()
+    x_h, a_h = make_inputs()
+    x = torch.from_numpy(x_h).to(dev)
+    a = torch.from_numpy(a_h).to(dev)
+    yg = torch.empty(FFN, device=dev)
+    yu = torch.empty(FFN, device=dev)
+    yd = torch.empty(HIDDEN, device=dev)
+
+    def step(i):
+        wg, wu, wd = inst[i % n_inst]
+        ctx.matvec(wg, x, out=yg.view(1, -1))
+        ctx.matvec(wu, x, out=yu.view(1, -1))
+        ctx.matvec(wd, a, out=yd.view(1, -1))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # warm-up (also sizes every scratch buffer before capture)
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    l0 = ctx.launch_count()
+    step(0)
+    launches_per_step = ctx.launch_count() - l0
+
+    # K steps as one CUDA graph on a side stream; timed with events on that stream
+    s = torch.cuda.Stream(device=dev)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(s):
+        with torch.cuda.graph(graph, stream=s):
+            for i in range(args.steps):
+                step(i)
+    with torch.cuda.stream(s):
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+    torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    reps = args.reps
+    e0 = [torch.cuda.Event(enable_timing=True) for _ in range(reps)]
+    e1 = [torch.cuda.Event(enable_timing=True) for _ in range(reps)]
+    barrier()
+    with torch.cuda.stream(s):
+        for r in range(reps):
+            e0[r].record(s)
+            graph.replay()
+            e1[r].record(s)
+    barrier()
+    rep_ms = [a_.elapsed_time(b_) for a_, b_ in zip(e0, e1)]
+    ms_per_step = statistics.median(rep_ms) / args.steps
+
+    # per-kernel launch durations for the roofline: separate graphs of one kernel type
+    def time_kernel(which):
+        g2 = torch.cuda.CUDAGraph()
+        n = 4 * n_inst
+        with torch.cuda.stream(s):
+            with torch.cuda.graph(g2, stream=s):
+                for i in range(n):
+                    wg, wu, wd = inst[i % n_inst]
+                    if which == "q4_k":
+                        ctx.matvec(wg if i % 2 == 0 else wu, x, out=yg.view(1, -1))
+                    else:
+                        ctx.matvec(wd, a, out=yd.view(1, -1))
+            for _ in range(3):
+                g2.replay()
+            ts = []
+            for _ in range(7):
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record(s)
+                g2.replay()
+                a1.record(s)
+                a1.synchronize()
+                ts.append(a0.elapsed_time(a1) / n)
+        return statistics.median(ts)
+
+    k_q4k_ms = time_kernel("q4_k")
+    k_q6k_ms = time_kernel("q6_k")
+    clocks = sampler.stop() if rank == 0 else None
+
+    # e2e: host buffers through the C-ABI host-pointer path, weights resident
+    xp = torch.from_numpy(x_h).pin_memory()
+    ap = torch.from_numpy(a_h).pin_memory()
+    ygp = torch.empty(1, FFN).pin_memory()
+    yup = torch.empty(1, FFN).pin_memory()
+    ydp = torch.empty(1, HIDDEN).pin_memory()
+
+    def e2e_step(i):
+        wg, wu, wd = inst[i % n_inst]
+        ctx.matvec(wg, xp.numpy(), out=ygp.numpy())
+        ctx.matvec(wu, xp.numpy(), out=yup.numpy())
+        ctx.matvec(wd, ap.numpy(), out=ydp.numpy())
+
+    for i in range(3):
+        e2e_step(i)
+    barrier()
+    t0 = time.perf_counter()
+    for i in range(args.steps):
+        e2e_step(i)
+    barrier()
+    e2e_ms = 1000.0 * (time.perf_counter() - t0) / args.steps
+
+    if world > 1:
+        t = torch.tensor([ms_per_step, e2e_ms], device=dev, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_per_step, e2e_ms = t.tolist()
+
+    # parity spot check of what was timed (sampled rows against the oracle)
+    parity = None
+    if rank == 0 and not args.no_check:
+        from oracle import oracle as O
+
+        g_bytes = make_instance(0, dev)
+        rows = 64
+        sub = g_bytes[0][: rows * (HIDDEN // 256) * 144].cpu().numpy()
+        ref = O.q4_k_matvec_f64(sub, rows, HIDDEN, x_h)
+        step(0)
+        torch.cuda.synchronize()
+        subd = g_bytes[2][: rows * (FFN // 256) * 210].cpu().numpy()
+        refd = O.q6_k_matvec_f64(subd, rows, FFN, a_h)
+        parity = {"q4_k_max_rel_err_64_rows": O.max_rel_err(yg[:rows].cpu().numpy(), ref),
+                  "q6_k_max_rel_err_64_rows": O.max_rel_err(yd[:rows].cpu().numpy(), refd)}
+
+    if rank == 0:
+        peaks, peak_kind = _peaks()
+        value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
+        q4k_bytes = GATE_BYTES + 4 * (HIDDEN + FFN)
+        q6k_bytes = DOWN_BYTES + 4 * (HIDDEN + FFN)
+        ach = q4k_bytes / (k_q4k_ms * 1e-3) / 1e9
+        line = {
+            "metric": "Q4/Q6 matvec HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": "ffn_matvec_set_b1", "gate_up": "Q4_K 12288x4096 x2", "down": "Q6_K 4096x12288",
+                       "columns": 1, "bytes_per_step": STEP_BYTES, "weight_instances_per_gpu": n_inst,
+                       "l2": f"inputs larger than L2: {n_inst} distinct instances = {n_inst * STEP_BYTES / 1e6:.0f} MB "
+                             "cycled, one per step", "timing": f"median of {reps} replays of a {args.steps}-step CUDA graph",
+                       "sharding": "independent FFN instances per rank, no collective"},
+            "roofline": {"bound": "hbm", "kernel": ctx.last_evidence()["kernel_name"] + ":q4_k",
+                         "achieved": ach, "peak": peaks["hbm_gbs"], "peak_source": peak_kind, "unit": "GB/s",
+                         "frac": ach / peaks["hbm_gbs"], "traffic": None, "us_per_launch": k_q4k_ms * 1e3,
+                         "algorithmic_bytes_per_launch": q4k_bytes,
+                         "q6_k": {"achieved": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9, "us_per_launch": k_q6k_ms * 1e3,
+                                  "frac": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                  "algorithmic_bytes_per_launch": q6k_bytes}},
+            "e2e": {"value": world * STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": 4 * (HIDDEN + HIDDEN + FFN), "d2h_bytes_per_step": 4 * (FFN + FFN + HIDDEN)},
+            "gpu_launches": launches_per_step * args.steps * reps,
+            "clocks": clocks, "parity": parity,
+        }
+        if not args.no_cpu and world == 1:
+            times, threads, build = cpu_step_timer(None, 11, 3)
+            cms = statistics.median(times)
+            line["cpu_baseline"] = {"value": STEP_BYTES / cms / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
+                                    "sample": f"11 full steps (median) of the same three matvecs, oracle C port "
+                                              f"({build} build), row chunks over all host threads"}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--reps", type=int, default=11)
+    ap.add_argument("--instances", type=int, default=8)
+    ap.add_argument("--impl", default="native", choices=["native", "reference"])
+    ap.add_argument("--no-cpu", action="store_true")
+    ap.add_argument("--no-check", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_gpu(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,274 @@
+/*
+ * libleviathan_cuda.so -- C ABI of the B200 (sm_100a) quantized-weight hot
+ * path of Leviathan: GGUF Q4_0 / Q4_K / Q6_K dequant-fused matvec (decode),
+ * dequant-GEMM (prefill) and the routed-MoE composite.
+ *
+ * Conventions
+ *   - every entry point returns a lev_status; LEV_OK is 0.  Nothing aborts,
+ *     traps or falls back silently.  lev_last_error(ctx) holds the message
+ *     of the most recent failure on that context.
+ *   - shapes are validated on the host before any device work, in the order
+ *     the reference validates them (dimensions, byte counts, input counts,
+ *     finiteness).
+ *   - the caller owns host arrays and the device buffers it passes; the
+ *     library owns what it allocates behind opaque handles.  Weights are
+ *     uploaded once and stay resident, addressed by (handle, row offset)
+ *     the way the reference addresses one resident buffer by byte offset
+ *     (Sources/LeviathanCore/Gemma4.swift:2622-2631).
+ *   - a context is not thread-safe; all work of a context is issued on one
+ *     CUDA stream (lev_cuda_set_stream).  Entry points given device
+ *     pointers are asynchronous on that stream; entry points given host
+ *     pointers (LEV_FLAG_HOST_IO, the *_host conveniences) copy in, run,
+ *     copy out and synchronize before returning.
+ *   - no torch types appear anywhere in this header.
+ */
+#ifndef LEVIATHAN_CUDA_H
+#define LEVIATHAN_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LEV_CUDA_ABI_VERSION 1
+
+/* Status codes.  The first group keeps the names of the reference's typed
+ * errors (Sources/LeviathanCore/Q4.swift:17-31; rust ShapeError,
+ * rust/crates/lev-cpu/src/lib.rs:76-81). */
+typedef enum lev_status {
+    LEV_OK = 0,
+    LEV_BAD_DIMENSIONS = 1,
+    LEV_WRONG_INPUT_COUNT = 2,
+    LEV_NONFINITE_INPUT = 3,
+    LEV_NONFINITE_SCALE = 4,
+    LEV_NONFINITE_OUTPUT = 5,
+    LEV_EXCEEDS_WORKLOAD = 6,
+    LEV_INTEGER_OVERFLOW = 7,
+    LEV_DEVICE_UNAVAILABLE = 8,
+    LEV_KERNEL_FAILED = 9,
+    LEV_TIMEOUT = 10,
+    LEV_NCCL_ERROR = 11,
+    LEV_BAD_ARGUMENT = 12,
+    LEV_OUT_OF_MEMORY = 13,
+    LEV_BAD_OP_SPEC = 14,
+    LEV_UNSUPPORTED = 15
+} lev_status;
+
+/* ggml tensor type ids of the block formats on the path
+ * (Sources/LeviathanCore/GGUF.swift:58-93, rust/crates/lev-gguf/src/lib.rs:94-112) */
+typedef enum lev_ggml_type {
+    LEV_GGML_F32 = 0,
+    LEV_GGML_Q4_0 = 2,  /* 32 values / 18 bytes  */
+    LEV_GGML_Q4_K = 12, /* 256 values / 144 bytes */
+    LEV_GGML_Q6_K = 14  /* 256 values / 210 bytes */
+} lev_ggml_type;
+
+/* Limits restated from Sources/LeviathanCore/Q4.swift:8-15.  The byte cap is
+ * raised from 32 GiB to what one B200 holds; the overflow checks stay. */
+#define LEV_MAX_DIM (1 << 22)
+#define LEV_MAX_WEIGHT_BYTES (160ull << 30)
+#define LEV_MAX_COLUMNS 8    /* activation columns per matvec call */
+#define LEV_MAX_TOP_K 64     /* Sources/LeviathanCore/MoELowering.swift region bound */
+#define LEV_MAX_EXPERTS 1024
+
+/* flags */
+#define LEV_FLAG_CHECK_FINITE 1u /* reject non-finite x and y (synchronizes) */
+#define LEV_FLAG_HOST_IO 2u      /* x / y (and idx, w) are host pointers */
+
+/* Kernel schedules: named, enumerable, shape- and device-derived candidates
+ * with candidate 0 the plain kernel, after Q4ScheduleDeriver.derive
+ * (Sources/LeviathanCore/Q4Lowering.swift:283-362). */
+typedef enum lev_schedule {
+    LEV_SCHEDULE_AUTO = -1,
+    LEV_SCHEDULE_PLAIN = 0,  /* one warp per row, reference block order */
+    LEV_SCHEDULE_STREAM = 1  /* repacked fragment-major stream, tensor-core dot */
+} lev_schedule;
+
+typedef struct lev_ctx lev_ctx;
+typedef struct lev_weights lev_weights;
+typedef struct lev_moe_weights lev_moe_weights;
+typedef struct lev_op lev_op;
+
+/* CUDA analogue of ForgeHardwareProfile (Sources/LeviathanCore/Forge.swift:17-30) */
+typedef struct lev_hw_profile {
+    char device_name[128];
+    int sm_count;
+    int max_threads_per_block;
+    int warp_width;
+    int cc_major, cc_minor;
+    size_t total_memory;
+    size_t free_memory;
+    size_t shared_memory_per_block_optin;
+    size_t l2_bytes;
+} lev_hw_profile;
+
+/* Evidence of one run, after Q4MatvecEvidence
+ * (Sources/LeviathanCore/Q4.swift:117-124) */
+typedef struct lev_evidence {
+    char device_name[128];
+    char kernel_name[64];
+    int64_t out_dim, in_dim;
+    int n_cols;
+    int grid, block;
+    size_t weight_bytes;
+    float gpu_us;        /* device time of the kernel(s), CUDA events */
+    int status;          /* "completed" == LEV_OK */
+} lev_evidence;
+
+/* ---- context ---------------------------------------------------------- */
+int lev_cuda_abi_version(void);
+const char* lev_status_name(int status);
+/* Replaces MTLCreateSystemDefaultDevice + makeCommandQueue
+ * (Sources/LeviathanCore/Q4.swift:193-196). */
+int lev_cuda_init(int device, lev_ctx** out_ctx);
+int lev_cuda_destroy(lev_ctx* ctx);
+const char* lev_last_error(const lev_ctx* ctx);
+int lev_cuda_hardware_profile(lev_ctx* ctx, lev_hw_profile* out);
+/* cuda_stream is a cudaStream_t; NULL restores the context's own stream. */
+int lev_cuda_set_stream(lev_ctx* ctx, void* cuda_stream);
+int lev_cuda_synchronize(lev_ctx* ctx);
+/* Launch counter: kernels launched by this context since creation. */
+int64_t lev_cuda_launch_count(const lev_ctx* ctx);
+int lev_cuda_last_evidence(const lev_ctx* ctx, lev_evidence* out);
+
+/* ---- resident weights --------------------------------------------------
+ * Replaces the resident weightsBuffer + per-tensor byte offsets
+ * (Sources/LeviathanCore/Gemma4.swift:2583-2631).  `bytes` are raw GGUF
+ * block bytes, row-major [rows][cols/block][block bytes]; the byte count is
+ * validated against the geometry (Sources/LeviathanCore/Q4.swift:176-186).
+ * Block scales are checked finite at upload (Q4.swift:43-50, Q6.swift:33-37).
+ * bytes_on_device != 0 means `bytes` is a device pointer. */
+int lev_weights_upload(lev_ctx* ctx, const void* bytes, size_t n_bytes, int ggml_type,
+                       int64_t rows, int64_t cols, int bytes_on_device, lev_weights** out);
+int lev_weights_free(lev_ctx* ctx, lev_weights* w);
+int lev_weights_info(const lev_weights* w, int* ggml_type, int64_t* rows, int64_t* cols,
+                     size_t* gguf_bytes);
+
+/* Block dequantization of rows [row0, row0+rows) to f32 [rows][cols],
+ * bit-exact with Q4_0.decodeBlock (Q4.swift:54-69), Q6_K.decodeBlock
+ * (Q6.swift:24-62) and dequant_block_f32
+ * (rust/crates/lev-cpu/src/lib.rs:110-130). */
+int lev_dequantize(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, float* out,
+                   unsigned flags);
+
+/* ---- decode matvec -----------------------------------------------------
+ * y[c][r] = sum_k W[row0 + r][k] * x[c][k], c < n_cols <= LEV_MAX_COLUMNS.
+ * x is [n_cols][cols], y is [n_cols][rows] (column-major over tokens like
+ * the reference's nb-column kernels, rust/crates/lev-forge/src/q8.rs:196).
+ * Replaces Gemma4Runner.matvec(tensor:extraOffset:x:xCount:y:yCapacity:)
+ * (Sources/LeviathanCore/Gemma4.swift:2583-2638) and Builder::matvec
+ * (rust/crates/lev-model/src/gpu.rs:334-370).  x_count and y_capacity are
+ * element counts and are checked like xCount / yCapacity there. */
+int lev_matvec(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x,
+               int64_t x_count, int n_cols, float* y, int64_t y_capacity, int schedule,
+               unsigned flags);
+
+/* One-shot host conveniences: upload, run, read back, report.  Replace
+ * Q4MetalBackend.matvecReporting (Sources/LeviathanCore/Q4.swift:165-167),
+ * Q6MetalBackend.matvecReporting (Sources/LeviathanCore/Q6.swift:199-201)
+ * and VulkanContext::run_matvec for Q4_K
+ * (rust/crates/lev-vulkan/src/lib.rs:571-582).  Finite checks always on. */
+int lev_q4_0_matvec_host(lev_ctx* ctx, const uint8_t* blocks, size_t n_bytes, int64_t out_dim,
+                         int64_t in_dim, const float* x, int64_t x_count, float* y,
+                         lev_evidence* evidence);
+int lev_q4_k_matvec_host(lev_ctx* ctx, const uint8_t* blocks, size_t n_bytes, int64_t out_dim,
+                         int64_t in_dim, const float* x, int64_t x_count, float* y,
+                         lev_evidence* evidence);
+int lev_q6_k_matvec_host(lev_ctx* ctx, const uint8_t* blocks, size_t n_bytes, int64_t out_dim,
+                         int64_t in_dim, const float* x, int64_t x_count, float* y,
+                         lev_evidence* evidence);
+
+/* ---- prefill dequant-GEMM ----------------------------------------------
+ * Y[t][r] = sum_k bf16(W[r][k]) * X[t][k], f32 accumulate; X is bf16
+ * [tokens][cols], Y is f32 [tokens][rows].  Replaces the act_f16 +
+ * q4k/q6k_gemm_blocked_tokens program of
+ * rust/crates/lev-forge/src/coopmat.rs:49-58, :236-425. */
+int lev_gemm_prefill(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int64_t tokens,
+                     float* y, unsigned flags);
+/* f32 activations -> bf16 (round to nearest even); emit_act_f16's role
+ * (rust/crates/lev-forge/src/coopmat.rs:49-58). */
+int lev_act_bf16(lev_ctx* ctx, const float* x, int64_t n, void* out_bf16);
+
+/* ---- routed MoE composite ----------------------------------------------
+ * Expert weights are the fused gate_up tensor [experts][2*inter][hidden] and
+ * the down tensor [experts][hidden][inter], both Q4_0
+ * (Sources/LeviathanCore/MoESIMDLowering.swift:106-107); router weight is
+ * f32 [experts][hidden].  local_first/local_count select the experts
+ * resident on this GPU (expert parallel); pass 0/experts for all. */
+int lev_moe_weights_upload(lev_ctx* ctx, const float* router_w, const uint8_t* gate_up_q4_0,
+                           size_t gate_up_bytes, const uint8_t* down_q4_0, size_t down_bytes,
+                           int experts, int hidden, int inter, int local_first,
+                           int local_count, int bytes_on_device, lev_moe_weights** out);
+int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w);
+
+/* Router decision for `tokens` rows of x [tokens][hidden]: logits in the
+ * fixed order documented in lev_moe.cu, softmax in f64, top_k by
+ * probability (ties to the lower index), renormalised f32 weights.
+ * Replaces the readback + CPU block of
+ * Sources/LeviathanCore/Gemma4.swift:3794-3810.  scores may be NULL. */
+int lev_moe_route(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens,
+                  int top_k, int32_t* idx, float* weights, float* scores, unsigned flags);
+/* Token->expert grouping: histogram, exclusive scan, stable permutation of
+ * pair ids (token*top_k + rank).  No reference counterpart (the reference
+ * batch is one token; closest analogue MoEModelBinding.offsets,
+ * Sources/LeviathanCore/MoEModelBinding.swift:174-195). */
+int lev_moe_group(lev_ctx* ctx, const int32_t* idx, int64_t tokens, int top_k, int experts,
+                  int32_t* counts, int32_t* offsets, int32_t* perm, unsigned flags);
+/* Expert FFN for every (token, rank): y_slots [tokens][top_k][hidden];
+ * act_out [tokens][top_k][inter] may be NULL.  One grouped launch per stage
+ * driven by the device-side offsets.  Replaces runMoeBatchedRouted
+ * (Sources/LeviathanCore/Gemma4.swift:2073-2176) and
+ * MoEEmittedKernels.runComponent (MoELowering.swift:975). */
+int lev_moe_experts(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens,
+                    int top_k, const int32_t* idx, float* y_slots, float* act_out,
+                    unsigned flags);
+/* out[t] = sum_k weights[t][k] * y_slots[t][k], f32, rank order, from zero
+ * (g4_axpy per slot, Sources/LeviathanCore/Gemma4.swift:4459-4466, :3878). */
+int lev_moe_combine(lev_ctx* ctx, const float* y_slots, const float* weights, int64_t tokens,
+                    int top_k, int hidden, float* out, unsigned flags);
+/* The whole layer.  idx_out / w_out may be NULL. */
+int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens,
+                  int top_k, float* out, int32_t* idx_out, float* w_out, unsigned flags);
+
+/* ---- Forge op-spec surface ---------------------------------------------
+ * Accepts the op JSON of Q4OpIR (Sources/LeviathanCore/Q4Lowering.swift:50-145,
+ * producer tools/q4_lower/q4_op_model.py:76-124) extended with
+ * quant "q4_k" / "q6_k", `columns` and op "<quant>.gemm"; and the region JSON
+ * of MoERegionIR (Sources/LeviathanCore/MoELowering.swift:176-283; scalar
+ * fields and graphSha256, not the graph re-walk).  Unknown fields are
+ * rejected.  Replaces installQ4GeneratedKernel / uninstall
+ * (Sources/LeviathanCore/Gemma4.swift:1022-1110). */
+int lev_op_install_json(lev_ctx* ctx, const char* json, size_t json_len, lev_op** out);
+int lev_op_uninstall(lev_ctx* ctx, lev_op* op);
+/* identity = SHA-256 hex of the sorted-keys JSON (Q4Lowering.swift:176-181) */
+int lev_op_describe(const lev_op* op, char* kind /*32*/, int64_t* in_dim, int64_t* out_dim,
+                    int* ggml_type, int* columns, char* identity_hex /*65*/,
+                    char* kernel_name /*64*/);
+/* does this installed op serve a weights handle of that geometry?
+ * (q4GeneratedServesTensor, Sources/LeviathanCore/Gemma4.swift:989-1012) */
+int lev_op_serves(const lev_op* op, const lev_weights* w, int64_t rows);
+
+/* ---- multi-GPU (one process per GPU, NCCL over NVLink) ------------------ */
+#define LEV_NCCL_ID_BYTES 128
+int lev_dist_unique_id(void* id128);
+int lev_dist_init(lev_ctx* ctx, int rank, int world, const void* id128);
+int lev_dist_destroy(lev_ctx* ctx);
+/* rows of W are split across ranks; each rank computes its slice into
+ * y_full[c][rank*rows_local ...] and the slices are all-gathered. */
+int lev_matvec_rowsplit_allgather(lev_ctx* ctx, const lev_weights* w_local, const float* x,
+                                  int64_t x_count, int n_cols, float* y_full,
+                                  int64_t y_capacity, unsigned flags);
+int lev_gemm_prefill_rowsplit_allgather(lev_ctx* ctx, const lev_weights* w_local,
+                                        const void* x_bf16, int64_t tokens, float* y_full,
+                                        unsigned flags);
+/* expert-parallel layer: tokens are data-parallel (this rank's x rows),
+ * experts are sharded as uploaded; all-to-all dispatch and combine. */
+int lev_moe_layer_ep(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens,
+                     int top_k, float* out, int32_t* idx_out, float* w_out, unsigned flags);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEVIATHAN_CUDA_H */

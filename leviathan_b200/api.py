@@ -1,0 +1,362 @@
+"""Python host layer over the C ABI: contexts, resident weights and the
+operators of the quantized-weight hot path.
+
+numpy arrays are host buffers (the call copies in and out and synchronizes,
+LEV_FLAG_HOST_IO); torch CUDA tensors are device buffers (the call is
+asynchronous on the context's stream).  torch is used for device memory and
+streams only; every operation runs in libleviathan_cuda.so.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from . import _lib as L
+
+
+class LevError(RuntimeError):
+    """A non-zero lev_status; `.name` is the reference's error-case name."""
+
+    def __init__(self, status: int, message: str):
+        super().__init__(f"{L.STATUS.get(status, status)}: {message}")
+        self.status = status
+        self.name = L.STATUS.get(status, str(status))
+        self.message = message
+
+
+def _is_torch(a) -> bool:
+    return type(a).__module__.startswith("torch")
+
+
+def _ptr(a):
+    if a is None:
+        return None
+    if _is_torch(a):
+        return a.data_ptr()
+    return a.ctypes.data
+
+
+class Weights:
+    def __init__(self, ctx: "Context", handle, ggml_type: int, rows: int, cols: int, gguf_bytes: int):
+        self.ctx, self.handle = ctx, handle
+        self.ggml_type, self.rows, self.cols, self.gguf_bytes = ggml_type, rows, cols, gguf_bytes
+
+    def free(self):
+        if self.handle:
+            self.ctx.lib.lev_weights_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class MoEWeights:
+    def __init__(self, ctx: "Context", handle, experts, hidden, inter, local_first, local_count):
+        self.ctx, self.handle = ctx, handle
+        self.experts, self.hidden, self.inter = experts, hidden, inter
+        self.local_first, self.local_count = local_first, local_count
+
+    def free(self):
+        if self.handle:
+            self.ctx.lib.lev_moe_weights_free(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Context:
+    """One device, one stream (lev_ctx).  Not thread-safe."""
+
+    def __init__(self, device: int = 0, follow_torch_stream: bool = True):
+        """follow_torch_stream: before every call that is given torch tensors,
+        issue on torch's current stream for this device, so the usual torch
+        ordering rules hold between this library's kernels and torch's."""
+        self.follow_torch_stream = follow_torch_stream
+        self._stream_seen = None
+        self.lib = L.load()
+        h = C.c_void_p()
+        st = self.lib.lev_cuda_init(device, C.byref(h))
+        if st != L.OK:
+            raise LevError(st, f"lev_cuda_init(device={device})")
+        self.handle = h
+        self.device = device
+
+    # -- plumbing --
+    def _check(self, st: int):
+        if st != L.OK:
+            raise LevError(st, self.lib.lev_last_error(self.handle).decode(errors="replace"))
+
+    def close(self):
+        if self.handle:
+            self.lib.lev_cuda_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def hardware_profile(self) -> dict:
+        p = L.HwProfile()
+        self._check(self.lib.lev_cuda_hardware_profile(self.handle, C.byref(p)))
+        return {k: (getattr(p, k).decode() if k == "device_name" else getattr(p, k)) for k, _ in p._fields_}
+
+    def set_stream(self, cuda_stream: int | None):
+        self._check(self.lib.lev_cuda_set_stream(self.handle, cuda_stream))
+
+    def use_torch_stream(self):
+        import torch
+
+        self.set_stream(torch.cuda.current_stream(self.device).cuda_stream)
+
+    def synchronize(self):
+        self._check(self.lib.lev_cuda_synchronize(self.handle))
+
+    def launch_count(self) -> int:
+        return self.lib.lev_cuda_launch_count(self.handle)
+
+    def last_evidence(self) -> dict:
+        e = L.Evidence()
+        self._check(self.lib.lev_cuda_last_evidence(self.handle, C.byref(e)))
+        return {k: (getattr(e, k).decode() if k.endswith("_name") else getattr(e, k)) for k, _ in e._fields_}
+
+    def _flags(self, host: bool, check_finite: bool) -> int:
+        if not host and self.follow_torch_stream:
+            import torch
+
+            s = torch.cuda.current_stream(self.device).cuda_stream
+            if s != self._stream_seen:
+                self.set_stream(s)
+                self._stream_seen = s
+        return (L.FLAG_HOST_IO if host else 0) | (L.FLAG_CHECK_FINITE if check_finite else 0)
+
+    def _empty_like_io(self, like, shape, dtype_np, dtype_torch_name):
+        if _is_torch(like):
+            import torch
+
+            return torch.empty(shape, dtype=getattr(torch, dtype_torch_name), device=like.device)
+        return np.empty(shape, dtype_np)
+
+    # -- weights --
+    def upload(self, blocks, ggml_type: int, rows: int, cols: int) -> Weights:
+        """lev_weights_upload: raw GGUF block bytes (numpy uint8 or torch uint8 CUDA)."""
+        on_dev = _is_torch(blocks) and blocks.is_cuda
+        if not _is_torch(blocks):
+            blocks = np.ascontiguousarray(blocks, np.uint8)
+            n = blocks.size
+        else:
+            blocks = blocks.contiguous()
+            n = blocks.numel()
+        if on_dev:
+            self._flags(False, False)
+        h = C.c_void_p()
+        self._check(self.lib.lev_weights_upload(self.handle, _ptr(blocks), n, ggml_type, rows, cols,
+                                                1 if on_dev else 0, C.byref(h)))
+        return Weights(self, h, ggml_type, rows, cols, n)
+
+    def dequantize(self, w: Weights, row0: int = 0, rows: int | None = None, device_out=None):
+        rows = w.rows - row0 if rows is None else rows
+        if device_out is not None:
+            self._flags(False, False)
+            self._check(self.lib.lev_dequantize(self.handle, w.handle, row0, rows, _ptr(device_out), 0))
+            return device_out
+        out = np.empty((max(rows, 0), w.cols), np.float32)
+        self._check(self.lib.lev_dequantize(self.handle, w.handle, row0, rows, _ptr(out), L.FLAG_HOST_IO))
+        return out
+
+    # -- decode matvec --
+    def matvec(self, w: Weights, x, row0: int = 0, rows: int | None = None, out=None,
+               schedule: int = L.SCHEDULE_AUTO, check_finite: bool = False):
+        """y[c][r] = W[row0+r] . x[c]; x is [cols] or [n_cols][cols]."""
+        rows = w.rows - row0 if rows is None else rows
+        host = not _is_torch(x)
+        if host:
+            x = np.ascontiguousarray(x, np.float32)
+            x_count = x.size
+        else:
+            x = x.contiguous()
+            x_count = x.numel()
+        one_d = x.ndim == 1
+        n_cols = 1 if one_d else x.shape[0]
+        if out is None:
+            out = self._empty_like_io(x, (n_cols, max(rows, 0)), np.float32, "float32")
+        cap = out.size if host else out.numel()
+        self._check(self.lib.lev_matvec(self.handle, w.handle, row0, rows, _ptr(x), x_count, n_cols, _ptr(out), cap,
+                                        schedule, self._flags(host, check_finite)))
+        return out[0] if one_d else out
+
+    def _matvec_host(self, fn, blocks, out_dim, in_dim, x):
+        blocks = np.ascontiguousarray(blocks, np.uint8)
+        x = np.ascontiguousarray(x, np.float32)
+        y = np.empty(max(out_dim, 0), np.float32)
+        ev = L.Evidence()
+        self._check(fn(self.handle, _ptr(blocks), blocks.size, out_dim, in_dim, _ptr(x), x.size, _ptr(y), C.byref(ev)))
+        evidence = {k: (getattr(ev, k).decode() if k.endswith("_name") else getattr(ev, k)) for k, _ in ev._fields_}
+        evidence["command_status"] = "completed" if ev.status == 0 else L.STATUS.get(ev.status, "?")
+        return y, evidence
+
+    def q4_0_matvec_reporting(self, blocks, out_dim, in_dim, x):
+        """Q4MetalBackend.matvecReporting (Sources/LeviathanCore/Q4.swift:165-167)."""
+        return self._matvec_host(self.lib.lev_q4_0_matvec_host, blocks, out_dim, in_dim, x)
+
+    def q6_k_matvec_reporting(self, blocks, out_dim, in_dim, x):
+        """Q6MetalBackend.matvecReporting (Sources/LeviathanCore/Q6.swift:199-201)."""
+        return self._matvec_host(self.lib.lev_q6_k_matvec_host, blocks, out_dim, in_dim, x)
+
+    def q4_k_matvec_reporting(self, blocks, out_dim, in_dim, x):
+        """VulkanContext::run_matvec for Q4_K (rust/crates/lev-vulkan/src/lib.rs:571-582)."""
+        return self._matvec_host(self.lib.lev_q4_k_matvec_host, blocks, out_dim, in_dim, x)
+
+    # -- prefill --
+    def act_bf16(self, x):
+        import torch
+
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+        self._flags(False, False)
+        self._check(self.lib.lev_act_bf16(self.handle, _ptr(x.contiguous()), x.numel(), _ptr(out)))
+        return out
+
+    def gemm_prefill(self, w: Weights, x_bf16, out=None):
+        """Y[t][r] = sum_k bf16(W[r][k]) X[t][k]; X torch bf16 CUDA [tokens][cols]."""
+        import torch
+
+        x_bf16 = x_bf16.contiguous()
+        tokens = x_bf16.shape[0]
+        if out is None:
+            out = torch.empty((tokens, w.rows), dtype=torch.float32, device=x_bf16.device)
+        self._flags(False, False)
+        self._check(self.lib.lev_gemm_prefill(self.handle, w.handle, _ptr(x_bf16), tokens, _ptr(out), 0))
+        return out
+
+    # -- MoE --
+    def moe_upload(self, router_w, gate_up, down, experts, hidden, inter, local_first=0, local_count=None) -> MoEWeights:
+        local_count = experts if local_count is None else local_count
+        on_dev = _is_torch(gate_up) and gate_up.is_cuda
+        if not on_dev:
+            router_w = np.ascontiguousarray(router_w, np.float32)
+            gate_up = np.ascontiguousarray(gate_up, np.uint8)
+            down = np.ascontiguousarray(down, np.uint8)
+            gb, db = gate_up.size, down.size
+        else:
+            router_w, gate_up, down = router_w.contiguous(), gate_up.contiguous(), down.contiguous()
+            gb, db = gate_up.numel(), down.numel()
+        if on_dev:
+            self._flags(False, False)
+        h = C.c_void_p()
+        self._check(self.lib.lev_moe_weights_upload(self.handle, _ptr(router_w), _ptr(gate_up), gb, _ptr(down), db,
+                                                    experts, hidden, inter, local_first, local_count,
+                                                    1 if on_dev else 0, C.byref(h)))
+        return MoEWeights(self, h, experts, hidden, inter, local_first, local_count)
+
+    def moe_route(self, mw: MoEWeights, x, top_k: int, want_scores: bool = False, check_finite: bool = False):
+        host = not _is_torch(x)
+        x = np.ascontiguousarray(x, np.float32) if host else x.contiguous()
+        tokens = x.shape[0]
+        idx = self._empty_like_io(x, (tokens, top_k), np.int32, "int32")
+        wts = self._empty_like_io(x, (tokens, top_k), np.float32, "float32")
+        scores = self._empty_like_io(x, (tokens, mw.experts), np.float32, "float32") if want_scores else None
+        self._check(self.lib.lev_moe_route(self.handle, mw.handle, _ptr(x), tokens, top_k, _ptr(idx), _ptr(wts),
+                                           _ptr(scores), self._flags(host, check_finite)))
+        return (idx, wts, scores) if want_scores else (idx, wts)
+
+    def moe_group(self, idx, experts: int):
+        host = not _is_torch(idx)
+        idx = np.ascontiguousarray(idx, np.int32) if host else idx.contiguous()
+        tokens, top_k = idx.shape
+        counts = self._empty_like_io(idx, (experts,), np.int32, "int32")
+        offsets = self._empty_like_io(idx, (experts + 1,), np.int32, "int32")
+        perm = self._empty_like_io(idx, (tokens * top_k,), np.int32, "int32")
+        self._check(self.lib.lev_moe_group(self.handle, _ptr(idx), tokens, top_k, experts, _ptr(counts), _ptr(offsets),
+                                           _ptr(perm), self._flags(host, False)))
+        return counts, offsets, perm
+
+    def moe_experts(self, mw: MoEWeights, x, idx, want_act: bool = False):
+        host = not _is_torch(x)
+        x = np.ascontiguousarray(x, np.float32) if host else x.contiguous()
+        idx = np.ascontiguousarray(idx, np.int32) if host else idx.contiguous()
+        tokens, top_k = idx.shape
+        y = self._empty_like_io(x, (tokens, top_k, mw.hidden), np.float32, "float32")
+        act = self._empty_like_io(x, (tokens, top_k, mw.inter), np.float32, "float32") if want_act else None
+        self._check(self.lib.lev_moe_experts(self.handle, mw.handle, _ptr(x), tokens, top_k, _ptr(idx), _ptr(y),
+                                             _ptr(act), self._flags(host, False)))
+        return (y, act) if want_act else y
+
+    def moe_combine(self, y_slots, weights):
+        host = not _is_torch(y_slots)
+        y_slots = np.ascontiguousarray(y_slots, np.float32) if host else y_slots.contiguous()
+        weights = np.ascontiguousarray(weights, np.float32) if host else weights.contiguous()
+        tokens, top_k, hidden = y_slots.shape
+        out = self._empty_like_io(y_slots, (tokens, hidden), np.float32, "float32")
+        self._check(self.lib.lev_moe_combine(self.handle, _ptr(y_slots), _ptr(weights), tokens, top_k, hidden, _ptr(out),
+                                             self._flags(host, False)))
+        return out
+
+    def moe_layer(self, mw: MoEWeights, x, top_k: int, out=None, want_routing: bool = False, check_finite: bool = False,
+                  expert_parallel: bool = False):
+        host = not _is_torch(x)
+        x = np.ascontiguousarray(x, np.float32) if host else x.contiguous()
+        tokens = x.shape[0]
+        if out is None:
+            out = self._empty_like_io(x, (tokens, mw.hidden), np.float32, "float32")
+        idx = self._empty_like_io(x, (tokens, top_k), np.int32, "int32") if want_routing else None
+        wts = self._empty_like_io(x, (tokens, top_k), np.float32, "float32") if want_routing else None
+        fn = self.lib.lev_moe_layer_ep if expert_parallel else self.lib.lev_moe_layer
+        self._check(fn(self.handle, mw.handle, _ptr(x), tokens, top_k, _ptr(out), _ptr(idx), _ptr(wts),
+                       self._flags(host, check_finite)))
+        return (out, idx, wts) if want_routing else out
+
+    # -- op spec --
+    def op_install(self, op_json: str | bytes):
+        data = op_json.encode() if isinstance(op_json, str) else op_json
+        h = C.c_void_p()
+        self._check(self.lib.lev_op_install_json(self.handle, data, len(data), C.byref(h)))
+        return h
+
+    def op_describe(self, op) -> dict:
+        kind = C.create_string_buffer(32)
+        ident = C.create_string_buffer(65)
+        kern = C.create_string_buffer(64)
+        i, o, t, c = C.c_int64(), C.c_int64(), C.c_int(), C.c_int()
+        self._check(self.lib.lev_op_describe(op, kind, C.byref(i), C.byref(o), C.byref(t), C.byref(c), ident, kern))
+        return {"kind": kind.value.decode(), "in_dim": i.value, "out_dim": o.value, "ggml_type": t.value,
+                "columns": c.value, "identity": ident.value.decode(), "kernel_name": kern.value.decode()}
+
+    def op_serves(self, op, w: Weights, rows: int) -> bool:
+        return bool(self.lib.lev_op_serves(op, w.handle, rows))
+
+    def op_uninstall(self, op):
+        self._check(self.lib.lev_op_uninstall(self.handle, op))
+
+    # -- multi-GPU --
+    @staticmethod
+    def dist_unique_id() -> bytes:
+        buf = C.create_string_buffer(L.NCCL_ID_BYTES)
+        st = L.load().lev_dist_unique_id(buf)
+        if st != L.OK:
+            raise LevError(st, "lev_dist_unique_id")
+        return buf.raw
+
+    def dist_init(self, rank: int, world: int, unique_id: bytes):
+        self._check(self.lib.lev_dist_init(self.handle, rank, world, unique_id))
+
+    def matvec_rowsplit_allgather(self, w_local: Weights, x, world: int, out=None):
+        import torch
+
+        x = x.contiguous()
+        one_d = x.ndim == 1
+        n_cols = 1 if one_d else x.shape[0]
+        if out is None:
+            out = torch.empty((n_cols, w_local.rows * world), dtype=torch.float32, device=x.device)
+        self._flags(False, False)
+        self._check(self.lib.lev_matvec_rowsplit_allgather(self.handle, w_local.handle, _ptr(x), x.numel(), n_cols,
+                                                           _ptr(out), out.numel(), 0))
+        return out[0] if one_d else out
+
+    def gemm_prefill_rowsplit_allgather(self, w_local: Weights, x_bf16, world: int, out=None):
+        import torch
+
+        x_bf16 = x_bf16.contiguous()
+        tokens = x_bf16.shape[0]
+        if out is None:
+            out = torch.empty((tokens, w_local.rows * world), dtype=torch.float32, device=x_bf16.device)
+        self._flags(False, False)
+        self._check(self.lib.lev_gemm_prefill_rowsplit_allgather(self.handle, w_local.handle, _ptr(x_bf16), tokens,
+                                                                 _ptr(out), 0))
+        return out

@@ -1,0 +1,113 @@
+// Internal declarations shared by the translation units of libleviathan_cuda.so.
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "leviathan_cuda.h"
+
+#define LEV_Q4_0_VALUES 32
+#define LEV_Q4_0_BYTES 18
+#define LEV_QK_K 256
+#define LEV_Q4_K_BYTES 144
+#define LEV_Q6_K_BYTES 210
+
+// device status word bits (finite checks, bounded waits)
+#define LEV_DEV_NONFINITE_INPUT 1
+#define LEV_DEV_NONFINITE_SCALE 2
+#define LEV_DEV_NONFINITE_OUTPUT 4
+#define LEV_DEV_TIMEOUT 8
+
+struct lev_dist_state;
+
+struct lev_ctx {
+    int device;
+    cudaStream_t own_stream;
+    cudaStream_t stream;
+    cudaDeviceProp prop;
+    char err[512];
+    int64_t launches;
+    lev_evidence ev;
+    // scratch owned by the context, grown on demand, reused across calls
+    void* scratch[8];
+    size_t scratch_bytes[8];
+    int* d_status;   // device status word
+    int* h_status;   // pinned mirror
+    cudaEvent_t ev0, ev1;
+    lev_dist_state* dist;
+};
+
+// Scratch slots (each one buffer; a call may use several at once).
+enum {
+    LEV_SCR_X = 0,       // staged activations (host io) / prepared activations
+    LEV_SCR_Y = 1,       // staged outputs (host io)
+    LEV_SCR_MOE_A = 2,   // router scores, idx, weights
+    LEV_SCR_MOE_B = 3,   // grouping tables
+    LEV_SCR_MOE_C = 4,   // gathered activations / expert intermediates
+    LEV_SCR_MOE_D = 5,   // expert outputs per (token, rank)
+    LEV_SCR_XPREP = 6,   // split activations for the stream schedule
+    LEV_SCR_DIST = 7
+};
+
+struct lev_weights {
+    int type;
+    int64_t rows, cols;
+    int64_t blocks_per_row;
+    size_t gguf_bytes;    // rows * blocks_per_row * block bytes
+    uint8_t* raw;         // GGUF block bytes, row-major (device)
+    // fragment-major repack for the stream schedule (device); NULL if absent
+    uint8_t* packed;
+    size_t packed_bytes;
+    int64_t packed_rows;  // rows rounded up to the 16-row tile
+    int owns_raw;
+};
+
+struct lev_moe_weights {
+    int experts, hidden, inter;
+    int local_first, local_count;
+    float* router_w;          // [experts][hidden]
+    lev_weights* gate_up;     // [local_count * 2*inter][hidden] Q4_0
+    lev_weights* down;        // [local_count * hidden][inter]  Q4_0
+};
+
+static inline int lev_block_values(int type) { return type == LEV_GGML_Q4_0 ? 32 : 256; }
+static inline int lev_block_bytes(int type) {
+    return type == LEV_GGML_Q4_0 ? LEV_Q4_0_BYTES : (type == LEV_GGML_Q4_K ? LEV_Q4_K_BYTES : LEV_Q6_K_BYTES);
+}
+static inline bool lev_type_ok(int type) {
+    return type == LEV_GGML_Q4_0 || type == LEV_GGML_Q4_K || type == LEV_GGML_Q6_K;
+}
+
+int lev_fail(lev_ctx* ctx, int status, const char* fmt, ...);
+int lev_cuda_check(lev_ctx* ctx, cudaError_t e, const char* what);
+int lev_scratch(lev_ctx* ctx, int slot, size_t bytes, void** out);
+// reads the device status word (synchronizes the stream) and clears it
+int lev_read_status(lev_ctx* ctx, int* bits);
+
+#define LEV_CUDA(ctx, call)                                         \
+    do {                                                            \
+        int _st = lev_cuda_check((ctx), (call), #call);             \
+        if (_st) return _st;                                        \
+    } while (0)
+
+#define LEV_TRY(call)                \
+    do {                             \
+        int _st = (call);            \
+        if (_st) return _st;         \
+    } while (0)
+
+// ---- launchers implemented in the kernel translation units ----
+int lev_launch_scale_check(lev_ctx* ctx, const lev_weights* w);
+int lev_launch_finite_check(lev_ctx* ctx, const float* v, int64_t n, int bit);
+int lev_launch_dequantize(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, float* out);
+int lev_launch_matvec_plain(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows,
+                            const float* x, int n_cols, float* y);
+int lev_repack_weights(lev_ctx* ctx, lev_weights* w);
+bool lev_stream_supported(const lev_weights* w, int64_t row0, int64_t rows, int n_cols);
+int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows,
+                             const float* x, int n_cols, float* y);
+
+int lev_weights_create(lev_ctx* ctx, const void* bytes, size_t n_bytes, int type, int64_t rows,
+                       int64_t cols, int on_device, bool repack, lev_weights** out);
