@@ -126,7 +126,8 @@ int lev_cuda_init(int device, lev_ctx** out_ctx);
 int lev_cuda_destroy(lev_ctx* ctx);
 const char* lev_last_error(const lev_ctx* ctx);
 int lev_cuda_hardware_profile(lev_ctx* ctx, lev_hw_profile* out);
-/* cuda_stream is a cudaStream_t; NULL restores the context's own stream. */
+/* cuda_stream is a cudaStream_t; NULL restores the context's own stream (pass
+ * cudaStreamLegacy, not 0, to name the legacy default stream). */
 int lev_cuda_set_stream(lev_ctx* ctx, void* cuda_stream);
 int lev_cuda_synchronize(lev_ctx* ctx);
 /* Launch counter: kernels launched by this context since creation. */

@@ -99,6 +99,10 @@ class Context:
         return {k: (getattr(p, k).decode() if k == "device_name" else getattr(p, k)) for k, _ in p._fields_}
 
     def set_stream(self, cuda_stream: int | None):
+        """cuda_stream: a cudaStream_t value; 0 means the legacy default
+        stream (passed as cudaStreamLegacy), None the context's own stream."""
+        if cuda_stream == 0:
+            cuda_stream = 1  # cudaStreamLegacy
         self._check(self.lib.lev_cuda_set_stream(self.handle, cuda_stream))
 
     def use_torch_stream(self):

@@ -31,8 +31,8 @@ struct lev_ctx {
     int64_t launches;
     lev_evidence ev;
     // scratch owned by the context, grown on demand, reused across calls
-    void* scratch[8];
-    size_t scratch_bytes[8];
+    void* scratch[12];
+    size_t scratch_bytes[12];
     int* d_status;   // device status word
     int* h_status;   // pinned mirror
     cudaEvent_t ev0, ev1;
@@ -48,7 +48,10 @@ enum {
     LEV_SCR_MOE_C = 4,   // gathered activations / expert intermediates
     LEV_SCR_MOE_D = 5,   // expert outputs per (token, rank)
     LEV_SCR_XPREP = 6,   // split activations for the stream schedule
-    LEV_SCR_DIST = 7
+    LEV_SCR_DIST = 7,
+    LEV_SCR_COUNTERS = 8,  // tile counters of the stream schedule, zero between launches
+    LEV_SCR_PARTIALS = 9,  // per-warp partial sums of the stream schedule
+    LEV_SCR_SLOTS = 12
 };
 
 struct lev_weights {
@@ -83,6 +86,8 @@ static inline bool lev_type_ok(int type) {
 int lev_fail(lev_ctx* ctx, int status, const char* fmt, ...);
 int lev_cuda_check(lev_ctx* ctx, cudaError_t e, const char* what);
 int lev_scratch(lev_ctx* ctx, int slot, size_t bytes, void** out);
+// like lev_scratch, and the buffer is zero-filled whenever it is (re)allocated
+int lev_scratch_zeroed(lev_ctx* ctx, int slot, size_t bytes, void** out);
 // reads the device status word (synchronizes the stream) and clears it
 int lev_read_status(lev_ctx* ctx, int* bits);
 

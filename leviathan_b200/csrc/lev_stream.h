@@ -1,0 +1,37 @@
+// Interface of the stream schedule shared by the dense matvec and the
+// grouped expert FFN.
+#pragma once
+
+#include "lev_internal.h"
+
+// where the activation columns of a call come from
+struct lev_stream_source {
+    const float* x;        // source rows
+    int64_t ld;            // elements between source rows
+    const int* rowmap;     // [job][cmax] source row per column (-1 = empty); NULL: row = column
+    const int* njobs_dev;  // device count of jobs; NULL: all `jobs` given to lev_stream_prepare
+    int gelu_inter;        // > 0: value = gelu_tanh(x[e]) * x[gelu_inter + e]
+    float* act_out;        // optional [row][cols] copy of the source values
+};
+
+// which weight rows a call streams and where results go
+struct lev_stream_job {
+    int64_t row0;          // dense: first row (multiple of 16); grouped: 0
+    int64_t rows;          // rows per job
+    int64_t out_ld;        // elements between output columns
+    int max_jobs;          // dense: 1; grouped: upper bound of the device job count
+    const int* njobs_dev;  // grouped: device count of jobs
+    const int* job_slice;  // grouped: [job] slice index (slice = rows consecutive rows of the tensor)
+    const int* outmap;     // grouped: [job][cmax] output column index (-1 = none)
+};
+
+int lev_stream_terms(int n_cols);
+int64_t lev_stream_chunks(const lev_weights* w);
+size_t lev_stream_table_bytes(const lev_weights* w, int cmax, int terms, int jobs, size_t* frag_bytes);
+int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_source& src, int cmax, int terms, int jobs,
+                       void* tables);
+// fused_src != NULL (dense calls whose tables fit shared memory): every CTA builds the
+// tables itself and `tables` is unused
+bool lev_stream_fuses_prepare(const lev_weights* w, int cmax, int terms);
+int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
+                   int terms, float* y, const lev_stream_source* fused_src);

@@ -22,6 +22,10 @@ def random_blocks(t, seed, rows, cols):
     n = rows * cols // bv
     raw = (Q.splitmix64(seed, n * bb) & np.uint64(0xFF)).astype(np.uint8).reshape(n, bb)
     halves = np.array([0x2E66, 0x3000, 0x3266, 0x2800, 0x1C00, 0x3400, 0xAE66, 0xB000], np.uint16)
+    if t == Q.GGML_Q6_K:
+        # int8 sub-scales reach 127 and levels 32: keep d near 2^-9 so that a
+        # row's terms stay O(10) and f32 accumulation noise stays below 1e-4
+        halves = np.array([0x1400, 0x1800, 0x1C00, 0x1A66, 0x9400, 0x9800, 0x9C00, 0x1666], np.uint16)
     pick = (Q.splitmix64(seed ^ 0x5A5A, 2 * n) % np.uint64(8)).astype(np.int64).reshape(n, 2)
     pos = {Q.GGML_Q4_0: [0], Q.GGML_Q4_K: [0, 2], Q.GGML_Q6_K: [208]}[t]
     for k, p in enumerate(pos):
