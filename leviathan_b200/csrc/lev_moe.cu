@@ -1,0 +1,715 @@
+// Routed mixture-of-experts composite: router decision, token->expert
+// grouping, grouped expert FFN over Q4_0 weights, ordered weighted combine.
+//
+// Router logits.  The reference computes them with an f32 GPU kernel
+// (Sources/LeviathanCore/Gemma4.swift:4160-4172) and states no CPU form, so
+// the summation order is fixed here and restated term for term by the CPU
+// oracle: partial p[l] (l = 0..31) accumulates elements l, l+32, l+64, ... in
+// ascending order with a correctly rounded double fma; the 32 partials are
+// combined by an xor butterfly (distance 16, 8, 4, 2, 1) of double adds and
+// the result is rounded once to f32.
+//
+// Router decision (Sources/LeviathanCore/Gemma4.swift:3797-3810): m = max
+// score (f32); e_i = exp(double(s_i -f32 m)); sum in ascending index order;
+// p_i = e_i / sum; order by p descending, ties to the lower index; the first
+// top_k; w_k = float(p_k / sum of selected p).
+//
+// Grouping: stable counting sort of pair ids (token*top_k + rank) by expert,
+// entirely on the device, followed by a job table that cuts every expert's
+// run of pairs into groups of up to `cmax` columns.  The expert FFN is then
+// two grouped launches of the stream schedule (gate_up, down) driven by that
+// table; no host synchronisation happens anywhere in the layer.
+#include <math.h>
+
+#include <new>
+
+#include "lev_internal.h"
+#include "lev_stream.h"
+
+namespace {
+
+__device__ __forceinline__ double warp_butterfly(double v) {
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) v += __shfl_xor_sync(0xffffffffu, v, d);
+    return v;
+}
+
+// one warp per (token, 8 experts); 8 warps of a CTA share the expert rows
+__global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__ rw, const float* __restrict__ x,
+                                                       int64_t tokens, int experts, int hidden,
+                                                       float* __restrict__ scores, int* status) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t tok = (int64_t)blockIdx.y * 8 + warp;
+    const int e0 = blockIdx.x * 8;
+    if (tok >= tokens) return;
+    double acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.0;
+    const float* xr = x + tok * hidden;
+    for (int i = lane; i < hidden; i += 32) {
+        double xv = (double)xr[i];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (e0 + j < experts) acc[j] = fma((double)__ldg(rw + (int64_t)(e0 + j) * hidden + i), xv, acc[j]);
+    }
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        float s = (float)warp_butterfly(acc[j]);
+        if (e0 + j < experts) {
+            bad |= !isfinite(s);
+            if (lane == 0) scores[tok * experts + e0 + j] = s;
+        }
+    }
+    if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
+}
+
+// one warp per token
+__global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ scores, int64_t tokens, int experts,
+                                                     int top_k, const float* __restrict__ expert_scale,
+                                                     int32_t* __restrict__ idx, float* __restrict__ weights) {
+    extern __shared__ double sp[];  // [warps][experts] probabilities; selected ones are set to -1
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int64_t tok = (int64_t)blockIdx.x * 4 + warp;
+    if (tok >= tokens) return;
+    double* p = sp + (size_t)warp * experts;
+    const float* s = scores + tok * experts;
+    float m = -INFINITY;
+    for (int i = lane; i < experts; i += 32) m = fmaxf(m, s[i]);
+#pragma unroll
+    for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+    for (int i = lane; i < experts; i += 32) p[i] = exp((double)(s[i] - m));
+    __syncwarp();
+    double sum = 0.0;
+    if (lane == 0)
+        for (int i = 0; i < experts; i++) sum += p[i];
+    sum = __shfl_sync(0xffffffffu, sum, 0);
+    for (int i = lane; i < experts; i += 32) p[i] = p[i] / sum;
+    __syncwarp();
+    double psel = 0.0, prob_sum = 0.0;  // lane k keeps the k-th selected probability (top_k <= 64: two per lane)
+    double psel2 = 0.0;
+    int isel = -1, isel2 = -1;
+    for (int k = 0; k < top_k; k++) {
+        double best = -1.0;
+        int bi = 0x7fffffff;
+        for (int i = lane; i < experts; i += 32) {
+            double v = p[i];
+            if (v > best) {  // ascending i: the first maximum is the lowest index
+                best = v;
+                bi = i;
+            }
+        }
+#pragma unroll
+        for (int d = 16; d >= 1; d >>= 1) {
+            double ob = __shfl_xor_sync(0xffffffffu, best, d);
+            int oi = __shfl_xor_sync(0xffffffffu, bi, d);
+            if (ob > best || (ob == best && oi < bi)) {
+                best = ob;
+                bi = oi;
+            }
+        }
+        prob_sum += best;  // rank order, like topIdx.reduce
+        if (lane == (k & 31)) {
+            if (k < 32) {
+                psel = best;
+                isel = bi;
+            } else {
+                psel2 = best;
+                isel2 = bi;
+            }
+        }
+        if (lane == 0) p[bi] = -1.0;
+        __syncwarp();
+    }
+    if (lane < top_k) {
+        float sc = expert_scale ? expert_scale[isel] : 1.0f;
+        idx[tok * top_k + lane] = isel;
+        weights[tok * top_k + lane] = __fmul_rn((float)(psel / prob_sum), sc);
+    }
+    if (lane + 32 < top_k) {
+        float sc = expert_scale ? expert_scale[isel2] : 1.0f;
+        idx[tok * top_k + lane + 32] = isel2;
+        weights[tok * top_k + lane + 32] = __fmul_rn((float)(psel2 / prob_sum), sc);
+    }
+}
+
+// Grouping and job table, one CTA.  Experts outside [first, first+count) are
+// not resident on this GPU; their pairs are left out.
+struct GroupArgs {
+    const int32_t* idx;  // [pairs]
+    int pairs, top_k, experts, first, count, cmax;
+    int32_t* counts;     // [experts]
+    int32_t* offsets;    // [experts + 1]
+    int32_t* perm;       // [pairs] pair ids in grouped order
+    // job table (all optional)
+    int* njobs;          // [1]
+    int* job_slice;      // [max_jobs] local expert index
+    int* job_token;      // [max_jobs][cmax] token of each column, -1 = none
+    int* job_pos;        // [max_jobs][cmax] grouped position, -1 = none
+    int* job_pair;       // [max_jobs][cmax] pair id, -1 = none
+    int* status;
+};
+
+__global__ void __launch_bounds__(1024) k_group(GroupArgs G) {
+    extern __shared__ int sh[];  // hist[experts], offs[experts + 1], jobbase[experts + 1]
+    int* hist = sh;
+    int* offs = sh + G.experts;
+    int* jobbase = offs + G.experts + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int e = tid; e < G.experts; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    bool bad = false;
+    for (int i = tid; i < G.pairs; i += blockDim.x) {
+        int e = G.idx[i];
+        if (e < 0 || e >= G.experts) bad = true;
+        else if (e >= G.first && e < G.first + G.count) atomicAdd(&hist[e], 1);
+    }
+    if (bad) atomicOr(G.status, LEV_DEV_NONFINITE_INPUT);
+    __syncthreads();
+    if (warp == 0) {
+        // exclusive scans over experts: each lane owns a contiguous run
+        int per = (G.experts + 31) / 32, b = lane * per, e1 = min(b + per, G.experts);
+        int s = 0, js = 0;
+        for (int e = b; e < e1; e++) {
+            s += hist[e];
+            js += (hist[e] + G.cmax - 1) / G.cmax;
+        }
+        int incl = s, jincl = js;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, d), jv = __shfl_up_sync(0xffffffffu, jincl, d);
+            if (lane >= d) {
+                incl += v;
+                jincl += jv;
+            }
+        }
+        int run = incl - s, jrun = jincl - js;
+        for (int e = b; e < e1; e++) {
+            offs[e] = run;
+            jobbase[e] = jrun;
+            run += hist[e];
+            jrun += (hist[e] + G.cmax - 1) / G.cmax;
+        }
+        if (lane == 31) {
+            offs[G.experts] = incl;
+            jobbase[G.experts] = jincl;
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < G.experts; e += blockDim.x) {
+        G.counts[e] = hist[e];
+        G.offsets[e] = offs[e];
+    }
+    if (tid == 0) {
+        G.offsets[G.experts] = offs[G.experts];
+        if (G.njobs) *G.njobs = jobbase[G.experts];
+    }
+    // stable placement: a warp walks all pairs for one expert at a time
+    for (int e = G.first + warp; e < G.first + G.count; e += nwarps) {
+        if (hist[e] == 0) continue;
+        int base = offs[e], seen = 0;
+        for (int i0 = 0; i0 < G.pairs && seen < hist[e]; i0 += 32) {
+            int i = i0 + lane;
+            bool hit = i < G.pairs && G.idx[i] == e;
+            unsigned mask = __ballot_sync(0xffffffffu, hit);
+            if (hit) {
+                int r = seen + __popc(mask & ((1u << lane) - 1u));
+                int pos = base + r;
+                G.perm[pos] = i;
+                if (G.job_slice) {
+                    int j = jobbase[e] + r / G.cmax, c = r % G.cmax;
+                    G.job_token[j * G.cmax + c] = i / G.top_k;
+                    G.job_pos[j * G.cmax + c] = pos;
+                    G.job_pair[j * G.cmax + c] = i;
+                }
+            }
+            seen += __popc(mask);
+        }
+        if (G.job_slice) {
+            int nj = (hist[e] + G.cmax - 1) / G.cmax;
+            for (int j = lane; j < nj; j += 32) G.job_slice[jobbase[e] + j] = e - G.first;
+            // empty columns of the expert's last job
+            int tail = nj * G.cmax - hist[e];
+            if (lane < tail) {
+                int j = jobbase[e] + nj - 1, c = G.cmax - 1 - lane;
+                G.job_token[j * G.cmax + c] = -1;
+                G.job_pos[j * G.cmax + c] = -1;
+                G.job_pair[j * G.cmax + c] = -1;
+            }
+        }
+    }
+}
+
+// out[t][h] = sum_k w[t][k] * y[t][k][h]: a separate multiply and add per
+// slot in rank order from zero (Sources/LeviathanCore/Gemma4.swift:4459-4466)
+__global__ void k_combine(const float* __restrict__ y, const float* __restrict__ w, int64_t tokens, int top_k,
+                          int hidden, float* __restrict__ out) {
+    int64_t total = tokens * hidden;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t t = i / hidden;
+        int h = (int)(i - t * hidden);
+        float acc = 0.f;
+        for (int k = 0; k < top_k; k++)
+            acc = __fadd_rn(acc, __fmul_rn(w[t * top_k + k], y[(t * top_k + k) * hidden + h]));
+        out[i] = acc;
+    }
+}
+
+int grid_for(lev_ctx* ctx, int64_t n, int block, int per_sm) {
+    int64_t g = (n + block - 1) / block, cap = (int64_t)ctx->prop.multiProcessorCount * per_sm;
+    return (int)(g < 1 ? 1 : (g > cap ? cap : g));
+}
+
+int check_tokens(lev_ctx* ctx, const lev_moe_weights* w, int64_t tokens, int top_k) {
+    if (tokens <= 0 || tokens > (1 << 20)) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "tokens %lld", (long long)tokens);
+    if (top_k <= 0 || top_k > LEV_MAX_TOP_K || top_k > w->experts)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "topK %d with %d experts", top_k, w->experts);
+    return LEV_OK;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// weights
+// ---------------------------------------------------------------------------
+extern "C" int lev_moe_weights_upload(lev_ctx* ctx, const float* router_w, const uint8_t* gu, size_t gu_bytes,
+                                      const uint8_t* dn, size_t dn_bytes, int experts, int hidden, int inter,
+                                      int local_first, int local_count, int on_device, lev_moe_weights** out) {
+    if (!ctx || !out) return LEV_BAD_ARGUMENT;
+    *out = nullptr;
+    // region bounds of Sources/LeviathanCore/MoELowering.swift (dims <= 8192, multiples of 32)
+    if (hidden <= 0 || inter <= 0 || hidden % 32 || inter % 32 || hidden > 8192 || inter > 8192)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "hidden %d, expertIntermediate %d", hidden, inter);
+    if (experts <= 0 || experts > LEV_MAX_EXPERTS || local_first < 0 || local_count <= 0 || local_first + local_count > experts)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "experts %d, local [%d, +%d)", experts, local_first, local_count);
+    size_t gu_stride = (size_t)(2 * inter) * (hidden / 32) * 18, dn_stride = (size_t)hidden * (inter / 32) * 18;
+    if (gu_bytes != gu_stride * local_count || dn_bytes != dn_stride * local_count)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "packed slice sizes do not match the shape (%zu / %zu bytes, need %zu / %zu)",
+                        gu_bytes, dn_bytes, gu_stride * local_count, dn_stride * local_count);
+    if (!router_w || !gu || !dn) return lev_fail(ctx, LEV_BAD_ARGUMENT, "null weights");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    lev_moe_weights* w = new (std::nothrow) lev_moe_weights();
+    if (!w) return lev_fail(ctx, LEV_OUT_OF_MEMORY, "host allocation");
+    memset(w, 0, sizeof *w);
+    w->experts = experts;
+    w->hidden = hidden;
+    w->inter = inter;
+    w->local_first = local_first;
+    w->local_count = local_count;
+    size_t rb = (size_t)experts * hidden * sizeof(float);
+    int st = lev_cuda_check(ctx, cudaMalloc((void**)&w->router_w, rb), "cudaMalloc(router)");
+    if (!st)
+        st = lev_cuda_check(ctx,
+                            cudaMemcpyAsync(w->router_w, router_w, rb,
+                                            on_device ? cudaMemcpyDeviceToDevice : cudaMemcpyHostToDevice, ctx->stream),
+                            "copy router");
+    if (!st) st = lev_weights_create(ctx, gu, gu_bytes, LEV_GGML_Q4_0, (int64_t)local_count * 2 * inter, hidden, on_device, true, &w->gate_up);
+    if (!st) st = lev_weights_create(ctx, dn, dn_bytes, LEV_GGML_Q4_0, (int64_t)local_count * hidden, inter, on_device, true, &w->down);
+    if (!st) st = lev_cuda_check(ctx, cudaStreamSynchronize(ctx->stream), "sync");
+    if (st) {
+        lev_moe_weights_free(ctx, w);
+        return st;
+    }
+    *out = w;
+    return LEV_OK;
+}
+
+extern "C" int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w) {
+    if (!ctx || !w) return LEV_BAD_ARGUMENT;
+    cudaSetDevice(ctx->device);
+    cudaStreamSynchronize(ctx->stream);
+    if (w->router_w) cudaFree(w->router_w);
+    if (w->gate_up) lev_weights_free(ctx, w->gate_up);
+    if (w->down) lev_weights_free(ctx, w->down);
+    delete w;
+    return LEV_OK;
+}
+
+// ---------------------------------------------------------------------------
+// device-pointer stages
+// ---------------------------------------------------------------------------
+static int route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
+                     float* weights, float* scores) {
+    dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
+    k_router_logits<<<grid, 256, 0, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
+    ctx->launches++;
+    LEV_CUDA(ctx, cudaGetLastError());
+    size_t smem = (size_t)4 * w->experts * sizeof(double);
+    k_router_topk<<<(unsigned)((tokens + 3) / 4), 128, smem, ctx->stream>>>(scores, tokens, w->experts, top_k, nullptr, idx, weights);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_router_topk");
+}
+
+struct JobTable {
+    int cmax, max_jobs;
+    int *njobs, *job_slice, *job_token, *job_pos, *job_pair;
+};
+
+static int group_dev(lev_ctx* ctx, const int32_t* idx, int64_t tokens, int top_k, int experts, int first, int count,
+                     int32_t* counts, int32_t* offsets, int32_t* perm, JobTable* jt) {
+    GroupArgs G;
+    G.idx = idx;
+    G.pairs = (int)(tokens * top_k);
+    G.top_k = top_k;
+    G.experts = experts;
+    G.first = first;
+    G.count = count;
+    G.cmax = jt ? jt->cmax : 1;
+    G.counts = counts;
+    G.offsets = offsets;
+    G.perm = perm;
+    G.njobs = jt ? jt->njobs : nullptr;
+    G.job_slice = jt ? jt->job_slice : nullptr;
+    G.job_token = jt ? jt->job_token : nullptr;
+    G.job_pos = jt ? jt->job_pos : nullptr;
+    G.job_pair = jt ? jt->job_pair : nullptr;
+    G.status = ctx->d_status;
+    size_t smem = (size_t)(3 * experts + 2) * sizeof(int);
+    k_group<<<1, 1024, smem, ctx->stream>>>(G);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_group");
+}
+
+static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, const int* total_pos, int64_t pairs,
+                              int inter, float* act);
+
+// expert FFN for the pairs whose experts are resident; y_pairs is [pairs][hidden]
+// indexed by pair id (token*top_k + rank); act_out (optional) likewise [pairs][inter]
+static int experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                       const int32_t* idx, float* y_pairs, float* act_out) {
+    const int64_t pairs = tokens * top_k;
+    const int cmax = pairs <= 2 * (int64_t)w->local_count ? 4 : 8, terms = 2;
+    int64_t mj = (int64_t)w->local_count + pairs / cmax;
+    if (mj > pairs) mj = pairs;
+    const int max_jobs = (int)mj;
+
+    // grouping tables
+    size_t ints = (size_t)w->experts * 2 + 1 + pairs + 1 + max_jobs + (size_t)3 * max_jobs * cmax + 64;
+    void* gb;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_B, ints * sizeof(int), &gb));
+    int* p = (int*)gb;
+    int32_t* counts = p;
+    p += w->experts;
+    int32_t* offsets = p;
+    p += w->experts + 1;
+    int32_t* perm = p;
+    p += pairs;
+    JobTable jt;
+    jt.cmax = cmax;
+    jt.max_jobs = max_jobs;
+    jt.njobs = p;
+    p += 1;
+    jt.job_slice = p;
+    p += max_jobs;
+    jt.job_token = p;
+    p += (size_t)max_jobs * cmax;
+    jt.job_pos = p;
+    p += (size_t)max_jobs * cmax;
+    jt.job_pair = p;
+    LEV_TRY(group_dev(ctx, idx, tokens, top_k, w->experts, w->local_first, w->local_count, counts, offsets, perm, &jt));
+
+    // gate_up: columns = tokens of each job, outputs in grouped order [pos][2*inter]
+    const int64_t gu_rows = 2 * (int64_t)w->inter;
+    size_t tb_gu = lev_stream_table_bytes(w->gate_up, cmax, terms, max_jobs, nullptr);
+    size_t tb_dn = lev_stream_table_bytes(w->down, cmax, terms, max_jobs, nullptr);
+    size_t tb = tb_gu > tb_dn ? tb_gu : tb_dn;
+    size_t gu_bytes = ((size_t)pairs * gu_rows * sizeof(float) + 255) & ~(size_t)255;
+    void* cb;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_C, gu_bytes + tb + 256, &cb));
+    float* gu = (float*)cb;
+    void* tables = (char*)cb + gu_bytes;
+
+    lev_stream_source src = {};
+    src.x = x;
+    src.ld = w->hidden;
+    src.rowmap = jt.job_token;
+    src.njobs_dev = jt.njobs;
+    LEV_TRY(lev_stream_prepare(ctx, w->gate_up, src, cmax, terms, max_jobs, tables));
+    lev_stream_job J = {};
+    J.rows = gu_rows;
+    J.out_ld = gu_rows;
+    J.max_jobs = max_jobs;
+    J.njobs_dev = jt.njobs;
+    J.job_slice = jt.job_slice;
+    J.outmap = jt.job_pos;
+    LEV_TRY(lev_stream_run(ctx, w->gate_up, J, tables, cmax, terms, gu, nullptr));
+
+    // down: columns = gelu_tanh(gate) * up of each grouped position, outputs by pair id
+    lev_stream_source src2 = {};
+    src2.x = gu;
+    src2.ld = gu_rows;
+    src2.rowmap = jt.job_pos;
+    src2.njobs_dev = jt.njobs;
+    src2.gelu_inter = w->inter;
+    LEV_TRY(lev_stream_prepare(ctx, w->down, src2, cmax, terms, max_jobs, tables));
+    lev_stream_job J2 = {};
+    J2.rows = w->hidden;
+    J2.out_ld = w->hidden;
+    J2.max_jobs = max_jobs;
+    J2.njobs_dev = jt.njobs;
+    J2.job_slice = jt.job_slice;
+    J2.outmap = jt.job_pair;
+    LEV_TRY(lev_stream_run(ctx, w->down, J2, tables, cmax, terms, y_pairs, nullptr));
+    if (act_out) {
+        // activations by pair id, recomputed from the gate_up outputs (diagnostic output)
+        LEV_TRY(lev_moe_launch_act(ctx, gu, perm, offsets + w->experts, pairs, w->inter, act_out));
+    }
+    return LEV_OK;
+}
+
+namespace {
+__device__ __forceinline__ float gelu_tanh_up_f32(float g, float u) {
+    float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    float e = expf(-2.0f * fabsf(inner));
+    float th = copysignf((1.0f - e) / (1.0f + e), inner);
+    return 0.5f * g * (1.0f + th) * u;
+}
+// act[pair id][i] from gu[grouped position][2*inter]; positions beyond the grouped count are skipped
+__global__ void k_act(const float* __restrict__ gu, const int* __restrict__ perm, const int* __restrict__ total_pos,
+                      int64_t pairs, int inter, float* __restrict__ act) {
+    int64_t n = (int64_t)(*total_pos) * inter;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        int64_t pos = i / inter;
+        int k = (int)(i - pos * inter);
+        const float* r = gu + pos * 2 * inter;
+        act[(int64_t)perm[pos] * inter + k] = gelu_tanh_up_f32(r[k], r[inter + k]);
+    }
+}
+}  // namespace
+
+static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, const int* total_pos, int64_t pairs,
+                              int inter, float* act) {
+    k_act<<<grid_for(ctx, pairs * inter, 256, 8), 256, 0, ctx->stream>>>(gu, perm, total_pos, pairs, inter, act);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_act");
+}
+
+static int combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out) {
+    k_combine<<<grid_for(ctx, tokens * hidden, 256, 8), 256, 0, ctx->stream>>>(y, wts, tokens, top_k, hidden, out);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_combine");
+}
+
+// ---------------------------------------------------------------------------
+// host-buffer staging helpers
+// ---------------------------------------------------------------------------
+namespace {
+struct Stage {
+    lev_ctx* ctx;
+    char* base = nullptr;
+    size_t cap = 0, off = 0;
+    int init(lev_ctx* c, size_t bytes) {
+        ctx = c;
+        void* p;
+        int st = lev_scratch(c, LEV_SCR_X, bytes + 4096, &p);
+        base = (char*)p;
+        cap = bytes + 4096;
+        return st;
+    }
+    void* take(size_t bytes) {
+        void* p = base + off;
+        off += (bytes + 255) & ~(size_t)255;
+        return p;
+    }
+};
+int status_to_error(lev_ctx* ctx, unsigned flags, bool sync) {
+    if (flags & LEV_FLAG_CHECK_FINITE) {
+        int bits = 0;
+        LEV_TRY(lev_read_status(ctx, &bits));
+        if (bits & LEV_DEV_TIMEOUT) return lev_fail(ctx, LEV_TIMEOUT, "a bounded device wait ran out");
+        if (bits & LEV_DEV_NONFINITE_INPUT) return lev_fail(ctx, LEV_NONFINITE_INPUT, "activation vector");
+        if (bits & LEV_DEV_NONFINITE_OUTPUT) return lev_fail(ctx, LEV_NONFINITE_OUTPUT, "router scores or outputs");
+    } else if (sync) {
+        LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return LEV_OK;
+}
+}  // namespace
+
+extern "C" int lev_moe_route(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                             int32_t* idx, float* weights, float* scores, unsigned flags) {
+    if (!ctx || !w || !x || !idx || !weights) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_tokens(ctx, w, tokens, top_k));
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool host = flags & LEV_FLAG_HOST_IO;
+    size_t xb = (size_t)tokens * w->hidden * 4, ib = (size_t)tokens * top_k * 4, sb = (size_t)tokens * w->experts * 4;
+    Stage S;
+    LEV_TRY(S.init(ctx, (host ? xb + 2 * ib : 0) + sb + 2048));
+    const float* dx = x;
+    int32_t* didx = idx;
+    float* dw = weights;
+    float* dscores = (scores && !host) ? scores : (float*)S.take(sb);
+    if (host) {
+        if (flags & LEV_FLAG_CHECK_FINITE)
+            for (int64_t i = 0; i < tokens * w->hidden; i++)
+                if (!isfinite(x[i])) return lev_fail(ctx, LEV_NONFINITE_INPUT, "activation vector");
+        float* px = (float*)S.take(xb);
+        LEV_CUDA(ctx, cudaMemcpyAsync(px, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+        dx = px;
+        didx = (int32_t*)S.take(ib);
+        dw = (float*)S.take(ib);
+    } else if (flags & LEV_FLAG_CHECK_FINITE) {
+        LEV_TRY(lev_launch_finite_check(ctx, dx, tokens * w->hidden, LEV_DEV_NONFINITE_INPUT));
+    }
+    LEV_TRY(route_dev(ctx, w, dx, tokens, top_k, didx, dw, dscores));
+    if (host) {
+        LEV_CUDA(ctx, cudaMemcpyAsync(idx, didx, ib, cudaMemcpyDeviceToHost, ctx->stream));
+        LEV_CUDA(ctx, cudaMemcpyAsync(weights, dw, ib, cudaMemcpyDeviceToHost, ctx->stream));
+        if (scores) LEV_CUDA(ctx, cudaMemcpyAsync(scores, dscores, sb, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return status_to_error(ctx, flags, host);
+}
+
+extern "C" int lev_moe_group(lev_ctx* ctx, const int32_t* idx, int64_t tokens, int top_k, int experts, int32_t* counts,
+                             int32_t* offsets, int32_t* perm, unsigned flags) {
+    if (!ctx || !idx || !counts || !offsets || !perm) return LEV_BAD_ARGUMENT;
+    if (tokens <= 0 || top_k <= 0 || top_k > LEV_MAX_TOP_K || experts <= 0 || experts > LEV_MAX_EXPERTS ||
+        tokens * top_k > (1 << 24))
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "tokens %lld, topK %d, experts %d", (long long)tokens, top_k, experts);
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool host = flags & LEV_FLAG_HOST_IO;
+    size_t pb = (size_t)tokens * top_k * 4, eb = (size_t)(experts + 1) * 4;
+    const int32_t* didx = idx;
+    int32_t *dc = counts, *dof = offsets, *dp = perm;
+    Stage S;
+    if (host) {
+        for (int64_t i = 0; i < tokens * top_k; i++)
+            if (idx[i] < 0 || idx[i] >= experts) return lev_fail(ctx, LEV_BAD_ARGUMENT, "expert index %d outside 0..%d", idx[i], experts - 1);
+        LEV_TRY(S.init(ctx, 2 * pb + 2 * eb + 2048));
+        int32_t* pi = (int32_t*)S.take(pb);
+        LEV_CUDA(ctx, cudaMemcpyAsync(pi, idx, pb, cudaMemcpyHostToDevice, ctx->stream));
+        didx = pi;
+        dc = (int32_t*)S.take(eb);
+        dof = (int32_t*)S.take(eb);
+        dp = (int32_t*)S.take(pb);
+    }
+    LEV_TRY(group_dev(ctx, didx, tokens, top_k, experts, 0, experts, dc, dof, dp, nullptr));
+    if (host) {
+        LEV_CUDA(ctx, cudaMemcpyAsync(counts, dc, (size_t)experts * 4, cudaMemcpyDeviceToHost, ctx->stream));
+        LEV_CUDA(ctx, cudaMemcpyAsync(offsets, dof, eb, cudaMemcpyDeviceToHost, ctx->stream));
+        LEV_CUDA(ctx, cudaMemcpyAsync(perm, dp, pb, cudaMemcpyDeviceToHost, ctx->stream));
+        LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return LEV_OK;
+}
+
+extern "C" int lev_moe_experts(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                               const int32_t* idx, float* y_slots, float* act_out, unsigned flags) {
+    if (!ctx || !w || !x || !idx || !y_slots) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_tokens(ctx, w, tokens, top_k));
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool host = flags & LEV_FLAG_HOST_IO;
+    const int64_t pairs = tokens * top_k;
+    size_t xb = (size_t)tokens * w->hidden * 4, ib = (size_t)pairs * 4, yb = (size_t)pairs * w->hidden * 4,
+           ab = (size_t)pairs * w->inter * 4;
+    const float* dx = x;
+    const int32_t* didx = idx;
+    float *dy = y_slots, *da = act_out;
+    Stage S;
+    if (host) {
+        for (int64_t i = 0; i < pairs; i++)
+            if (idx[i] < 0 || idx[i] >= w->experts) return lev_fail(ctx, LEV_BAD_ARGUMENT, "expert index %d outside 0..%d", idx[i], w->experts - 1);
+        LEV_TRY(S.init(ctx, xb + ib + yb + (act_out ? ab : 0) + 2048));
+        float* px = (float*)S.take(xb);
+        int32_t* pi = (int32_t*)S.take(ib);
+        LEV_CUDA(ctx, cudaMemcpyAsync(px, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+        LEV_CUDA(ctx, cudaMemcpyAsync(pi, idx, ib, cudaMemcpyHostToDevice, ctx->stream));
+        dx = px;
+        didx = pi;
+        dy = (float*)S.take(yb);
+        if (act_out) da = (float*)S.take(ab);
+    }
+    if (w->local_count != w->experts) LEV_CUDA(ctx, cudaMemsetAsync(dy, 0, yb, ctx->stream));  // pairs of absent experts stay zero
+    LEV_TRY(experts_dev(ctx, w, dx, tokens, top_k, didx, dy, da));
+    if (host) {
+        LEV_CUDA(ctx, cudaMemcpyAsync(y_slots, dy, yb, cudaMemcpyDeviceToHost, ctx->stream));
+        if (act_out) LEV_CUDA(ctx, cudaMemcpyAsync(act_out, da, ab, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return status_to_error(ctx, flags, host);
+}
+
+extern "C" int lev_moe_combine(lev_ctx* ctx, const float* y_slots, const float* weights, int64_t tokens, int top_k,
+                               int hidden, float* out, unsigned flags) {
+    if (!ctx || !y_slots || !weights || !out) return LEV_BAD_ARGUMENT;
+    if (tokens <= 0 || top_k <= 0 || top_k > LEV_MAX_TOP_K || hidden <= 0)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "tokens %lld, topK %d, hidden %d", (long long)tokens, top_k, hidden);
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool host = flags & LEV_FLAG_HOST_IO;
+    size_t yb = (size_t)tokens * top_k * hidden * 4, wb = (size_t)tokens * top_k * 4, ob = (size_t)tokens * hidden * 4;
+    const float *dy = y_slots, *dw = weights;
+    float* dout = out;
+    Stage S;
+    if (host) {
+        // merge coefficients are checked finite before use (Sources/LeviathanCore/Gemma4.swift:2101-2106)
+        for (int64_t i = 0; i < tokens * top_k; i++)
+            if (!isfinite(weights[i])) return lev_fail(ctx, LEV_NONFINITE_INPUT, "routed merge weights must be finite");
+        LEV_TRY(S.init(ctx, yb + wb + ob + 2048));
+        float* py = (float*)S.take(yb);
+        float* pw = (float*)S.take(wb);
+        LEV_CUDA(ctx, cudaMemcpyAsync(py, y_slots, yb, cudaMemcpyHostToDevice, ctx->stream));
+        LEV_CUDA(ctx, cudaMemcpyAsync(pw, weights, wb, cudaMemcpyHostToDevice, ctx->stream));
+        dy = py;
+        dw = pw;
+        dout = (float*)S.take(ob);
+    }
+    LEV_TRY(combine_dev(ctx, dy, dw, tokens, top_k, hidden, dout));
+    if (host) {
+        LEV_CUDA(ctx, cudaMemcpyAsync(out, dout, ob, cudaMemcpyDeviceToHost, ctx->stream));
+        LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    }
+    return LEV_OK;
+}
+
+int lev_moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, float* out,
+                         int32_t* idx_out, float* w_out) {
+    const int64_t pairs = tokens * top_k;
+    size_t ib = ((size_t)pairs * 4 + 255) & ~(size_t)255, sb = ((size_t)tokens * w->experts * 4 + 255) & ~(size_t)255;
+    void* a;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_A, 2 * ib + sb + 256, &a));
+    int32_t* idx = idx_out ? idx_out : (int32_t*)a;
+    float* wts = w_out ? w_out : (float*)((char*)a + ib);
+    float* scores = (float*)((char*)a + 2 * ib);
+    void* d;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_D, (size_t)pairs * w->hidden * 4 + 256, &d));
+    LEV_TRY(route_dev(ctx, w, x, tokens, top_k, idx, wts, scores));
+    LEV_TRY(experts_dev(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr));
+    return combine_dev(ctx, (const float*)d, wts, tokens, top_k, w->hidden, out);
+}
+
+extern "C" int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                             float* out, int32_t* idx_out, float* w_out, unsigned flags) {
+    if (!ctx || !w || !x || !out) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_tokens(ctx, w, tokens, top_k));
+    if (w->local_count != w->experts)
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "experts are sharded on this context: use lev_moe_layer_ep");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool host = flags & LEV_FLAG_HOST_IO;
+    size_t xb = (size_t)tokens * w->hidden * 4, ib = (size_t)tokens * top_k * 4;
+    const float* dx = x;
+    float* dout = out;
+    int32_t* didx = idx_out;
+    float* dw = w_out;
+    Stage S;
+    if (host) {
+        if (flags & LEV_FLAG_CHECK_FINITE)
+            for (int64_t i = 0; i < tokens * w->hidden; i++)
+                if (!isfinite(x[i])) return lev_fail(ctx, LEV_NONFINITE_INPUT, "activation vector");
+        LEV_TRY(S.init(ctx, 2 * xb + 2 * ib + 2048));
+        float* px = (float*)S.take(xb);
+        LEV_CUDA(ctx, cudaMemcpyAsync(px, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+        dx = px;
+        dout = (float*)S.take(xb);
+        didx = (int32_t*)S.take(ib);
+        dw = (float*)S.take(ib);
+    } else if (flags & LEV_FLAG_CHECK_FINITE) {
+        LEV_TRY(lev_launch_finite_check(ctx, dx, tokens * w->hidden, LEV_DEV_NONFINITE_INPUT));
+    }
+    LEV_TRY(lev_moe_layer_device(ctx, w, dx, tokens, top_k, dout, didx, dw));
+    if (flags & LEV_FLAG_CHECK_FINITE) LEV_TRY(lev_launch_finite_check(ctx, dout, tokens * w->hidden, LEV_DEV_NONFINITE_OUTPUT));
+    if (host) {
+        LEV_CUDA(ctx, cudaMemcpyAsync(out, dout, xb, cudaMemcpyDeviceToHost, ctx->stream));
+        if (idx_out) LEV_CUDA(ctx, cudaMemcpyAsync(idx_out, didx, ib, cudaMemcpyDeviceToHost, ctx->stream));
+        if (w_out) LEV_CUDA(ctx, cudaMemcpyAsync(w_out, dw, ib, cudaMemcpyDeviceToHost, ctx->stream));
+    }
+    return status_to_error(ctx, flags, host);
+}

@@ -5,13 +5,6 @@
 
 extern "C" int lev_gemm_prefill(lev_ctx* ctx, const lev_weights*, const void*, int64_t, float*, unsigned) { return NOT_YET(ctx, "lev_gemm_prefill"); }
 extern "C" int lev_act_bf16(lev_ctx* ctx, const float*, int64_t, void*) { return NOT_YET(ctx, "lev_act_bf16"); }
-extern "C" int lev_moe_weights_upload(lev_ctx* ctx, const float*, const uint8_t*, size_t, const uint8_t*, size_t, int, int, int, int, int, int, lev_moe_weights**) { return NOT_YET(ctx, "lev_moe_weights_upload"); }
-extern "C" int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights*) { return NOT_YET(ctx, "lev_moe_weights_free"); }
-extern "C" int lev_moe_route(lev_ctx* ctx, const lev_moe_weights*, const float*, int64_t, int, int32_t*, float*, float*, unsigned) { return NOT_YET(ctx, "lev_moe_route"); }
-extern "C" int lev_moe_group(lev_ctx* ctx, const int32_t*, int64_t, int, int, int32_t*, int32_t*, int32_t*, unsigned) { return NOT_YET(ctx, "lev_moe_group"); }
-extern "C" int lev_moe_experts(lev_ctx* ctx, const lev_moe_weights*, const float*, int64_t, int, const int32_t*, float*, float*, unsigned) { return NOT_YET(ctx, "lev_moe_experts"); }
-extern "C" int lev_moe_combine(lev_ctx* ctx, const float*, const float*, int64_t, int, int, float*, unsigned) { return NOT_YET(ctx, "lev_moe_combine"); }
-extern "C" int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights*, const float*, int64_t, int, float*, int32_t*, float*, unsigned) { return NOT_YET(ctx, "lev_moe_layer"); }
 extern "C" int lev_op_install_json(lev_ctx* ctx, const char*, size_t, lev_op**) { return NOT_YET(ctx, "lev_op_install_json"); }
 extern "C" int lev_op_uninstall(lev_ctx* ctx, lev_op*) { return NOT_YET(ctx, "lev_op_uninstall"); }
 extern "C" int lev_op_describe(const lev_op*, char*, int64_t*, int64_t*, int*, int*, char*, char*) { return LEV_UNSUPPORTED; }
