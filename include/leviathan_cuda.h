@@ -181,6 +181,23 @@ int lev_q6_k_matvec_host(lev_ctx* ctx, const uint8_t* blocks, size_t n_bytes, in
                          int64_t in_dim, const float* x, int64_t x_count, float* y,
                          lev_evidence* evidence);
 
+/* No counterpart in the reference.  The same matvec as lev_matvec on the stream
+ * schedule, for callers that cannot allocate device memory when they call:
+ * loops whose memory budget was fixed at start-up, processes whose own
+ * allocator holds the whole device, threads that must not take the driver's
+ * allocation lock.  x and y are device pointers; all work buffers sit in a
+ * fixed array inside the library (lev_static_scratch_bytes() bytes on every GPU
+ * that loads it, until the process ends), so nothing is allocated or freed.
+ * Calls whose buffers would not fit return LEV_EXCEEDS_WORKLOAD; tensors the
+ * stream schedule does not serve return LEV_UNSUPPORTED.  All calls on a
+ * device share the array: do not let two of them overlap on the GPU.  The
+ * first call on a device resolves the array's address and configures the
+ * kernel; make it before any stream capture begins. */
+int lev_matvec_static_scratch(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows,
+                              const float* x, int64_t x_count, int n_cols, float* y,
+                              int64_t y_capacity);
+size_t lev_static_scratch_bytes(void);
+
 /* ---- prefill dequant-GEMM ----------------------------------------------
  * Y[t][r] = sum_k bf16(W[r][k]) * X[t][k], f32 accumulate; X is bf16
  * [tokens][cols], Y is f32 [tokens][rows].  Replaces the act_f16 +

@@ -65,6 +65,8 @@ SIGNATURES = {
     "lev_q4_0_matvec_host": (_I, [_P, _P, _Z, _L, _L, _P, _L, _P, C.POINTER(Evidence)]),
     "lev_q4_k_matvec_host": (_I, [_P, _P, _Z, _L, _L, _P, _L, _P, C.POINTER(Evidence)]),
     "lev_q6_k_matvec_host": (_I, [_P, _P, _Z, _L, _L, _P, _L, _P, C.POINTER(Evidence)]),
+    "lev_matvec_static_scratch": (_I, [_P, _P, _L, _L, _P, _L, _I, _P, _L]),
+    "lev_static_scratch_bytes": (_Z, []),
     "lev_gemm_prefill": (_I, [_P, _P, _P, _L, _P, _U]),
     "lev_act_bf16": (_I, [_P, _P, _L, _P]),
     "lev_moe_weights_upload": (_I, [_P, _P, _P, _Z, _P, _Z, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),

@@ -186,6 +186,22 @@ class Context:
                                         schedule, self._flags(host, check_finite)))
         return out[0] if one_d else out
 
+    def matvec_static_scratch(self, w: Weights, x, row0: int = 0, rows: int | None = None, out=None):
+        """lev_matvec_static_scratch: the stream-schedule matvec that allocates
+        nothing (torch CUDA tensors only); see include/leviathan_cuda.h."""
+        import torch
+
+        rows = w.rows - row0 if rows is None else rows
+        x = x.contiguous()
+        one_d = x.ndim == 1
+        n_cols = 1 if one_d else x.shape[0]
+        if out is None:
+            out = torch.empty((n_cols, max(rows, 0)), dtype=torch.float32, device=x.device)
+        self._flags(False, False)
+        self._check(self.lib.lev_matvec_static_scratch(self.handle, w.handle, row0, rows, _ptr(x), x.numel(), n_cols,
+                                                       _ptr(out), out.numel()))
+        return out[0] if one_d else out
+
     def _matvec_host(self, fn, blocks, out_dim, in_dim, x):
         blocks = np.ascontiguousarray(blocks, np.uint8)
         x = np.ascontiguousarray(x, np.float32)

@@ -761,8 +761,34 @@ bool lev_stream_fuses_prepare(const lev_weights* w, int cmax, int terms) {
     return (size_t)kWarpsPerCta * kDepth * kStepBytes + tb <= 110 * 1024;
 }
 
+// sizes of the two work buffers a call needs: per-warp partial sums and per-tile counters
+void lev_stream_workspace_bytes(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, int cmax,
+                                size_t* partial_bytes, size_t* counter_bytes) {
+    const int64_t steps = lev_stream_chunks(w) / 4, tiles_per_job = (J.rows + 15) / 16;
+    const int64_t max_steps = (int64_t)J.max_jobs * tiles_per_job * steps;
+    int ctas_per_sm = env_int("LEV_STREAM_CTAS_PER_SM", 2);
+    ctas_per_sm = ctas_per_sm < 1 ? 1 : (ctas_per_sm > 2 ? 2 : ctas_per_sm);
+    int grid = ctx->prop.multiProcessorCount * ctas_per_sm;
+    int64_t need_warps = (max_steps + 1) / 2;
+    if ((int64_t)grid * kWarpsPerCta > need_warps) grid = (int)((need_warps + kWarpsPerCta - 1) / kWarpsPerCta);
+    if (grid < 1) grid = 1;
+    *partial_bytes = (size_t)grid * kWarpsPerCta * 2 * cmax * 16 * sizeof(float);
+    *counter_bytes = (size_t)(J.max_jobs * tiles_per_job + 2) * sizeof(int);
+}
+
 int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, const void* tables, int cmax, int terms,
                    float* y, const lev_stream_source* fused_src) {
+    size_t pb, cb;
+    lev_stream_workspace_bytes(ctx, w, J, cmax, &pb, &cb);
+    void *pbuf, *counters;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_PARTIALS, pb, &pbuf));
+    LEV_TRY(lev_scratch_zeroed(ctx, LEV_SCR_COUNTERS, cb, &counters));
+    return lev_stream_run_ws(ctx, w, J, tables, cmax, terms, y, fused_src, pbuf, counters);
+}
+
+// the launch itself, on caller-provided work buffers (counters zero on entry; left zero on exit)
+int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, const void* tables, int cmax, int terms,
+                      float* y, const lev_stream_source* fused_src, void* pbuf, void* counters) {
     const int glt = cmax * terms, ntiles = (glt + 7) / 8;
     const int64_t chunks = lev_stream_chunks(w), steps = chunks / 4;
     const bool grouped = J.njobs_dev != nullptr;
@@ -784,10 +810,6 @@ int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, 
     size_t ring = (size_t)kWarpsPerCta * kDepth * kStepBytes;
     // stage the tables in shared memory when the call is dense and two CTAs still fit
     bool xs = !grouped && ring + tb <= 110 * 1024;
-
-    void *pbuf, *counters;
-    LEV_TRY(lev_scratch(ctx, LEV_SCR_PARTIALS, (size_t)max_warps * 2 * cmax * 16 * sizeof(float), &pbuf));
-    LEV_TRY(lev_scratch_zeroed(ctx, LEV_SCR_COUNTERS, (size_t)(J.max_jobs * tiles_per_job + 2) * sizeof(int), &counters));
 
     size_t fb_all;
     lev_stream_table_bytes(w, cmax, terms, J.max_jobs, &fb_all);

@@ -35,3 +35,7 @@ int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_sour
 bool lev_stream_fuses_prepare(const lev_weights* w, int cmax, int terms);
 int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
                    int terms, float* y, const lev_stream_source* fused_src);
+void lev_stream_workspace_bytes(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, int cmax,
+                                size_t* partial_bytes, size_t* counter_bytes);
+int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
+                      int terms, float* y, const lev_stream_source* fused_src, void* partials, void* counters);
