@@ -116,3 +116,10 @@ int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, i
 
 int lev_weights_create(lev_ctx* ctx, const void* bytes, size_t n_bytes, int type, int64_t rows,
                        int64_t cols, int on_device, bool repack, lev_weights** out);
+
+// device-pointer stages of the MoE composite (lev_moe.cu), shared with the expert-parallel layer
+int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
+                      float* weights, float* scores);
+int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                        const int32_t* idx, float* y_pairs, float* act_out);
+int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out);

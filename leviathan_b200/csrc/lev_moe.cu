@@ -328,7 +328,7 @@ extern "C" int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w) {
 // ---------------------------------------------------------------------------
 // device-pointer stages
 // ---------------------------------------------------------------------------
-static int route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
+int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
                      float* weights, float* scores) {
     dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
     k_router_logits<<<grid, 256, 0, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
@@ -375,7 +375,7 @@ static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, co
 
 // expert FFN for the pairs whose experts are resident; y_pairs is [pairs][hidden]
 // indexed by pair id (token*top_k + rank); act_out (optional) likewise [pairs][inter]
-static int experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
                        const int32_t* idx, float* y_pairs, float* act_out) {
     const int64_t pairs = tokens * top_k;
     const int cmax = pairs <= 2 * (int64_t)w->local_count ? 4 : 8, terms = 2;
@@ -484,7 +484,7 @@ static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, co
     return lev_cuda_check(ctx, cudaGetLastError(), "k_act");
 }
 
-static int combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out) {
+int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out) {
     k_combine<<<grid_for(ctx, tokens * hidden, 256, 8), 256, 0, ctx->stream>>>(y, wts, tokens, top_k, hidden, out);
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_combine");
@@ -551,7 +551,7 @@ extern "C" int lev_moe_route(lev_ctx* ctx, const lev_moe_weights* w, const float
     } else if (flags & LEV_FLAG_CHECK_FINITE) {
         LEV_TRY(lev_launch_finite_check(ctx, dx, tokens * w->hidden, LEV_DEV_NONFINITE_INPUT));
     }
-    LEV_TRY(route_dev(ctx, w, dx, tokens, top_k, didx, dw, dscores));
+    LEV_TRY(lev_moe_route_dev(ctx, w, dx, tokens, top_k, didx, dw, dscores));
     if (host) {
         LEV_CUDA(ctx, cudaMemcpyAsync(idx, didx, ib, cudaMemcpyDeviceToHost, ctx->stream));
         LEV_CUDA(ctx, cudaMemcpyAsync(weights, dw, ib, cudaMemcpyDeviceToHost, ctx->stream));
@@ -620,7 +620,7 @@ extern "C" int lev_moe_experts(lev_ctx* ctx, const lev_moe_weights* w, const flo
         if (act_out) da = (float*)S.take(ab);
     }
     if (w->local_count != w->experts) LEV_CUDA(ctx, cudaMemsetAsync(dy, 0, yb, ctx->stream));  // pairs of absent experts stay zero
-    LEV_TRY(experts_dev(ctx, w, dx, tokens, top_k, didx, dy, da));
+    LEV_TRY(lev_moe_experts_dev(ctx, w, dx, tokens, top_k, didx, dy, da));
     if (host) {
         LEV_CUDA(ctx, cudaMemcpyAsync(y_slots, dy, yb, cudaMemcpyDeviceToHost, ctx->stream));
         if (act_out) LEV_CUDA(ctx, cudaMemcpyAsync(act_out, da, ab, cudaMemcpyDeviceToHost, ctx->stream));
@@ -652,7 +652,7 @@ extern "C" int lev_moe_combine(lev_ctx* ctx, const float* y_slots, const float* 
         dw = pw;
         dout = (float*)S.take(ob);
     }
-    LEV_TRY(combine_dev(ctx, dy, dw, tokens, top_k, hidden, dout));
+    LEV_TRY(lev_moe_combine_dev(ctx, dy, dw, tokens, top_k, hidden, dout));
     if (host) {
         LEV_CUDA(ctx, cudaMemcpyAsync(out, dout, ob, cudaMemcpyDeviceToHost, ctx->stream));
         LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
@@ -671,9 +671,9 @@ int lev_moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x,
     float* scores = (float*)((char*)a + 2 * ib);
     void* d;
     LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_D, (size_t)pairs * w->hidden * 4 + 256, &d));
-    LEV_TRY(route_dev(ctx, w, x, tokens, top_k, idx, wts, scores));
-    LEV_TRY(experts_dev(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr));
-    return combine_dev(ctx, (const float*)d, wts, tokens, top_k, w->hidden, out);
+    LEV_TRY(lev_moe_route_dev(ctx, w, x, tokens, top_k, idx, wts, scores));
+    LEV_TRY(lev_moe_experts_dev(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr));
+    return lev_moe_combine_dev(ctx, (const float*)d, wts, tokens, top_k, w->hidden, out);
 }
 
 extern "C" int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,

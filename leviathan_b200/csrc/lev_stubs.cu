@@ -9,9 +9,3 @@ extern "C" int lev_op_install_json(lev_ctx* ctx, const char*, size_t, lev_op**) 
 extern "C" int lev_op_uninstall(lev_ctx* ctx, lev_op*) { return NOT_YET(ctx, "lev_op_uninstall"); }
 extern "C" int lev_op_describe(const lev_op*, char*, int64_t*, int64_t*, int*, int*, char*, char*) { return LEV_UNSUPPORTED; }
 extern "C" int lev_op_serves(const lev_op*, const lev_weights*, int64_t) { return 0; }
-extern "C" int lev_dist_unique_id(void*) { return LEV_UNSUPPORTED; }
-extern "C" int lev_dist_init(lev_ctx* ctx, int, int, const void*) { return NOT_YET(ctx, "lev_dist_init"); }
-extern "C" int lev_dist_destroy(lev_ctx*) { return LEV_OK; }
-extern "C" int lev_matvec_rowsplit_allgather(lev_ctx* ctx, const lev_weights*, const float*, int64_t, int, float*, int64_t, unsigned) { return NOT_YET(ctx, "lev_matvec_rowsplit_allgather"); }
-extern "C" int lev_gemm_prefill_rowsplit_allgather(lev_ctx* ctx, const lev_weights*, const void*, int64_t, float*, unsigned) { return NOT_YET(ctx, "lev_gemm_prefill_rowsplit_allgather"); }
-extern "C" int lev_moe_layer_ep(lev_ctx* ctx, const lev_moe_weights*, const float*, int64_t, int, float*, int32_t*, float*, unsigned) { return NOT_YET(ctx, "lev_moe_layer_ep"); }
