@@ -3,8 +3,6 @@
 
 #define NOT_YET(ctx, what) lev_fail((ctx), LEV_UNSUPPORTED, what " is not built yet")
 
-extern "C" int lev_gemm_prefill(lev_ctx* ctx, const lev_weights*, const void*, int64_t, float*, unsigned) { return NOT_YET(ctx, "lev_gemm_prefill"); }
-extern "C" int lev_act_bf16(lev_ctx* ctx, const float*, int64_t, void*) { return NOT_YET(ctx, "lev_act_bf16"); }
 extern "C" int lev_op_install_json(lev_ctx* ctx, const char*, size_t, lev_op**) { return NOT_YET(ctx, "lev_op_install_json"); }
 extern "C" int lev_op_uninstall(lev_ctx* ctx, lev_op*) { return NOT_YET(ctx, "lev_op_uninstall"); }
 extern "C" int lev_op_describe(const lev_op*, char*, int64_t*, int64_t*, int*, int*, char*, char*) { return LEV_UNSUPPORTED; }
