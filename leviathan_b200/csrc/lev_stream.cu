@@ -15,10 +15,9 @@
 // 2047), so two LOP3 per 32-bit word turn packed nibbles into A fragments
 // with no integer->float conversion; nibbles sitting at bits 4..7 come out
 // multiplied by 16 and the matching activations are pre-divided by 16.  The
-// f32 activations are split exactly into fp16 terms (x = h0 + h1*2^-11
-// + h2*2^-22; three terms while 3*columns <= 8, else two) that occupy
-// separate mma columns, so the tensor-core products are exact and the only
-// rounding is the f32 accumulation.  Block scales are applied to the f32
+// f32 activations are split into two fp16 terms (x = h0 + h1*2^-11, exact to
+// 2^-22 relative) that occupy separate mma columns, so the tensor-core
+// products are exact and the remaining rounding is the f32 accumulation.  Block scales are applied to the f32
 // accumulators per sub-block; the Q4_0 "-8" offset enters as the accumulator
 // initial value and the Q4_K min term is accumulated on CUDA cores.
 //
@@ -44,9 +43,11 @@
 namespace {
 
 constexpr float kHiScale = 0.0625f;  // activations of k-slots fed by nibbles at bits 4..7
-constexpr int kDepth = 4;            // ring stages per warp
-constexpr int kStepBytes = 2304;
-constexpr int kWarpsPerCta = 8;
+constexpr int kStepBytesQ4 = 2304;  // one K-step of a 16-row tile: Q4_K block / four Q4_0 chunks
+constexpr int kStepBytesQ6 = 3360;  // one Q6_K block of 16 rows
+__host__ __device__ constexpr int step_bytes(int type) { return type == LEV_GGML_Q6_K ? kStepBytesQ6 : kStepBytesQ4; }
+constexpr int kWarpsPerCta = 8;   // grouped and large calls
+constexpr int kWarpsWide = 24;    // dense calls: one CTA per SM
 constexpr unsigned kWaitPolls = 1u << 24;  // bound of every mbarrier wait
 
 __device__ __forceinline__ void mma16816(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
@@ -82,14 +83,18 @@ __device__ __forceinline__ float byte_to_float(unsigned w, unsigned k) {
 //         (columns = byte index), mma 2,3 high nibbles (columns 32 + byte).
 //   Q4_0: the chunk is two 32-value blocks; bytes 4t..4t+3 of each block;
 //         mma 0,1 = block 0 low / high nibbles, mma 2,3 = block 1.
+//   Q6_K: mma m covers the 16-value sub-block 4*chunk + m; lane t holds its elements
+//         4t..4t+3 (register r, half h -> element 4t + 2r + h); mma 2,3 use levels
+//         stored 16x (in bits 4..9), so their activations are pre-divided by 16.
 template <int TYPE>
 __device__ __forceinline__ int chunk_col(int t, int m, int r, int h) {
     if (TYPE == LEV_GGML_Q4_K) return (m >> 1) * 32 + 8 * t + 4 * (m & 1) + r + 2 * h;
+    if (TYPE == LEV_GGML_Q6_K) return 16 * m + 4 * t + 2 * r + h;
     return (m >> 1) * 32 + (m & 1) * 16 + 4 * t + r + 2 * h;
 }
 template <int TYPE>
 __device__ __forceinline__ bool chunk_hi(int m) {
-    return TYPE == LEV_GGML_Q4_K ? (m >> 1) : (m & 1);
+    return TYPE == LEV_GGML_Q4_0 ? (m & 1) : (m >> 1);
 }
 
 // term `term` of the exact fp16 split of v: v = h0 + h1*2^-11 + h2*2^-22.
@@ -163,10 +168,12 @@ __device__ __forceinline__ bool prep_frag(const PrepArgs& P, int job, int chunk,
     return bad;
 }
 
-// one 32-column sum by a whole warp: lane i holds element i, xor butterfly (fixed order).
-// Q4_K: which = activation column c, sums the true x of sub-block sb of the chunk.
-// Q4_0: which = mma column, sums what the tensor core sees of block sb: low-nibble
-//       slots carry term(x), high-nibble slots term(x/16) against nibbles worth 16x.
+// One sum of a chunk's activations by a whole warp (xor butterfly, fixed order).
+// Q4_K: which = activation column c; the true x of the 32-value sub-block sb (0, 1).
+// Q4_0: which = mma column; what the tensor core sees of block sb (0, 1), times -8 * 2^-24:
+//       low-nibble slots carry term(x), high-nibble slots term(x/16) against nibbles worth 16x.
+// Q6_K: which = mma column; the same for the two 16-value sub-blocks 2*sb, 2*sb+1 (lanes
+//       0..15 / 16..31), times -32 * 2^-24; the result of sub-block 2*sb + (lane >> 4).
 template <int TYPE>
 __device__ __forceinline__ float prep_sum32(const PrepArgs& P, int job, int chunk, int sb, int which, int lane) {
     const int c = TYPE == LEV_GGML_Q4_K ? which : which / P.terms;
@@ -176,27 +183,12 @@ __device__ __forceinline__ float prep_sum32(const PrepArgs& P, int job, int chun
     float xv = prep_src(P, row, e);
     if (P.act_out && term == 0 && row >= 0 && e < P.cols) P.act_out[(int64_t)row * P.cols + e] = xv;
     float s = xv;
-    if (TYPE != LEV_GGML_Q4_K) s = lane < 16 ? split_term(xv, term) : 16.0f * split_term(xv * kHiScale, term);
+    if (TYPE == LEV_GGML_Q4_0) s = lane < 16 ? split_term(xv, term) : 16.0f * split_term(xv * kHiScale, term);
+    if (TYPE == LEV_GGML_Q6_K) s = sb == 0 ? split_term(xv, term) : 16.0f * split_term(xv * kHiScale, term);
 #pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
-    return TYPE == LEV_GGML_Q4_K ? s : -8.0f * 5.9604644775390625e-08f * s;
-}
-
-// the same sum by one thread (four interleaved partial sums, fixed order), for the fused path
-template <int TYPE>
-__device__ __forceinline__ float prep_sum32_serial(const PrepArgs& P, int chunk, int sb, int which) {
-    const int c = TYPE == LEV_GGML_Q4_K ? which : which / P.terms;
-    const int term = TYPE == LEV_GGML_Q4_K ? 0 : which - c * P.terms;
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 32; i++) {
-        float xv = prep_src(P, c, (int64_t)chunk * 64 + sb * 32 + i);
-        float s = xv;
-        if (TYPE != LEV_GGML_Q4_K) s = i < 16 ? split_term(xv, term) : 16.0f * split_term(xv * kHiScale, term);
-        acc[i & 3] += s;
-    }
-    float s = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-    return TYPE == LEV_GGML_Q4_K ? s : -8.0f * 5.9604644775390625e-08f * s;
+    for (int d = (TYPE == LEV_GGML_Q6_K ? 8 : 16); d >= 1; d >>= 1) s += __shfl_xor_sync(0xffffffffu, s, d);
+    if (TYPE == LEV_GGML_Q4_K) return s;
+    return (TYPE == LEV_GGML_Q6_K ? -32.0f : -8.0f) * 5.9604644775390625e-08f * s;
 }
 
 // grid (chunks, jobs); one warp per 8 mma columns
@@ -218,6 +210,17 @@ __global__ void k_prepare_x(PrepArgs P) {
                     float s = prep_sum32<TYPE>(P, job, chunk, sb, c, lane);
                     if (lane == 0) P.aux[(((int64_t)job * P.chunks + chunk) * 2 + sb) * P.cmax + c] = s;
                 }
+    } else if (TYPE == LEV_GGML_Q6_K) {
+        for (int cc = 0; cc < 8; cc++) {
+            const int col2 = nt * 8 + cc;  // uniform across the warp
+            if (col2 >= P.glt) break;
+#pragma unroll
+            for (int half = 0; half < 2; half++) {  // sub-blocks 2*half, 2*half+1 of the chunk
+                float s = prep_sum32<TYPE>(P, job, chunk, half, col2, lane);
+                if ((lane & 15) == 0)
+                    P.aux[(((int64_t)job * P.chunks + chunk) * 4 + 2 * half + (lane >> 4)) * P.glt + col2] = s;
+            }
+        }
     } else {
         for (int cc = 0; cc < 8; cc++) {
             const int col2 = nt * 8 + cc;  // uniform across the warp
@@ -306,6 +309,81 @@ __global__ void k_repack_q40(const uint8_t* __restrict__ raw, int64_t rows, int6
     }
 }
 
+// Q6_K: per (tile, block) 210 units of 16 B:
+//   [0, 16)    the 16 int8 sub-block scales of each row (row order)
+//   [16, 18)   the fp16 d of the 16 rows
+//   [18, 146)  per chunk c (64 columns) 32 lane units: the low 4 bits of the levels; lane (g, t)
+//              holds 8 B of row g then 8 B of row g+8.  In a row's two words W0, W1, the level of
+//              element 16m + 4t + j of the chunk sits in word m&1, low (m<2) or high (m>=2)
+//              nibble of byte {0, 2, 1, 3}[j]  -- the order the A-fragment masks pick them up.
+//   [146, 210) per chunk 32 lane units of 8 B: the high 2 bits, one word per row; the field of
+//              (m, j) sits at bit {4, 6, 2, 0, 8, 10, 12, 14}[2m + (j >> 1)] + 16 * (j & 1).
+__device__ __forceinline__ unsigned q6k_level(const uint8_t* blk, int e) {  // stored 6-bit level of element e (0..255)
+    int hb = e >> 7, rem = e & 127, grp = rem >> 5, l = rem & 31;
+    unsigned ql = blk[64 * hb + ((grp & 1) ? 32 : 0) + l];
+    unsigned lo = (grp & 2) ? (ql >> 4) : (ql & 15u);
+    unsigned hi = (blk[128 + 32 * hb + l] >> (2 * grp)) & 3u;
+    return lo | (hi << 4);
+}
+__global__ void k_repack_q6k(const uint8_t* __restrict__ raw, int64_t rows, int64_t bpr, int64_t tiles,
+                             uint4* __restrict__ out) {
+    int64_t total = tiles * bpr * 210;
+    for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < total; u += (int64_t)gridDim.x * blockDim.x) {
+        int64_t tb = u / 210;
+        int k = (int)(u - tb * 210);
+        int64_t tile = tb / bpr, b = tb - tile * bpr;
+        unsigned w[4] = {0, 0, 0, 0};
+        if (k < 16) {
+            int64_t row = tile * 16 + k;
+            if (row < rows) {
+                const uint8_t* p = raw + (row * bpr + b) * LEV_Q6_K_BYTES + 192;
+                for (int i = 0; i < 16; i++) w[i >> 2] |= (unsigned)p[i] << (8 * (i & 3));
+            }
+        } else if (k < 18) {
+            for (int i = 0; i < 8; i++) {
+                int64_t row = tile * 16 + (k - 16) * 8 + i;
+                unsigned d = 0;
+                if (row < rows) {
+                    const uint8_t* p = raw + (row * bpr + b) * LEV_Q6_K_BYTES + 208;
+                    d = (unsigned)p[0] | ((unsigned)p[1] << 8);
+                }
+                w[i >> 1] |= d << (16 * (i & 1));
+            }
+        } else if (k < 146) {
+            int c = (k - 18) >> 5, lane = (k - 18) & 31, g = lane >> 2, t = lane & 3;
+            for (int rr = 0; rr < 2; rr++) {
+                int64_t row = tile * 16 + g + 8 * rr;
+                if (row >= rows) continue;
+                const uint8_t* blk = raw + (row * bpr + b) * LEV_Q6_K_BYTES;
+                for (int m = 0; m < 4; m++)
+                    for (int j = 0; j < 4; j++) {
+                        unsigned lv = q6k_level(blk, 64 * c + 16 * m + 4 * t + j) & 15u;
+                        const int byte = j == 0 ? 0 : (j == 1 ? 2 : (j == 2 ? 1 : 3));
+                        w[2 * rr + (m & 1)] |= lv << (8 * byte + ((m & 2) ? 4 : 0));
+                    }
+            }
+        } else {
+            // two lanes per 16-byte unit
+            int idx = (k - 146) * 2;
+            for (int hl = 0; hl < 2; hl++) {
+                int c = (idx + hl) >> 5, lane = (idx + hl) & 31, g = lane >> 2, t = lane & 3;
+                for (int rr = 0; rr < 2; rr++) {
+                    int64_t row = tile * 16 + g + 8 * rr;
+                    if (row >= rows) continue;
+                    const uint8_t* blk = raw + (row * bpr + b) * LEV_Q6_K_BYTES;
+                    for (int m = 0; m < 4; m++)
+                        for (int j = 0; j < 4; j++) {
+                            unsigned hv = q6k_level(blk, 64 * c + 16 * m + 4 * t + j) >> 4;
+                            const int pos[8] = {4, 6, 2, 0, 8, 10, 12, 14};
+                            w[2 * hl + rr] |= hv << (pos[2 * m + (j >> 1)] + 16 * (j & 1));
+                        }
+                }
+            }
+        }
+        out[u] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // ---------------------------------------------------------------------------
 // streaming kernel
 // ---------------------------------------------------------------------------
@@ -313,24 +391,22 @@ struct StreamArgs {
     const uint4* wp;        // packed weights: first tile of this call (dense) or of the tensor (grouped)
     int steps_per_tile;     // K-steps per tile
     int tiles_per_job;      // tiles of one job (one expert slice; the whole call when dense)
-    int max_warps;          // warps of the grid
-    int total_steps;        // dense: tiles * steps_per_tile
+    int tiles_per_group;    // tiles one CTA works on at a time, their K-steps split over its warps
+    int total_tiles;        // dense: tiles of the call
     const int* njobs_dev;   // grouped: device count of jobs (total steps = jobs * tiles_per_job * steps_per_tile)
     const int* job_slice;   // grouped: [job] index of the expert slice, in units of tiles_per_job tiles
     const int* outmap;      // grouped: [job][cmax] output row of each column, -1 = none; NULL: column index
     int64_t rows;           // rows of one job
     int64_t out_ld;         // elements between output columns
+    int out_cols;           // output columns that exist (dense: the call's n_cols)
     int chunks;             // padded 64-column chunks of the activation tables
     const uint4* frag;      // [job][chunk][glt][4] x 32 B
     const float* aux;       // Q4_K: [job][sub-block][cmax] ; Q4_0: [job][chunk][2][glt]
     int cmax, terms, glt;
-    float* partials;        // [warp][2][cmax][16]
-    int* tile_count;        // [job tiles], zero between launches
     int* status;            // device status word
     float* y;
     int debug;              // bit 0: skip the arithmetic (data-movement timing only)
-    int fused_prep;         // XS only: build the activation tables in shared memory from prep.x
-    PrepArgs prep;
+    int depth;              // ring stages per warp
 };
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -358,226 +434,305 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
     return false;
 }
 
-// address of K-step s of the global stream
-__device__ __forceinline__ const unsigned char* step_src(const StreamArgs& A, int s) {
-    int gt = s / A.steps_per_tile, k = s - gt * A.steps_per_tile;
-    int64_t tile = gt;
-    if (A.job_slice) {
-        int job = gt / A.tiles_per_job;
-        tile = (int64_t)A.job_slice[job] * A.tiles_per_job + (gt - job * A.tiles_per_job);
-    }
-    return reinterpret_cast<const unsigned char*>(A.wp) + (tile * A.steps_per_tile + k) * (int64_t)kStepBytes;
-}
+// CMAX: activation columns per job (compile time, so that every table index
+// is a constant multiple); XS: the tables of the (single) job are staged in
+// shared memory; OCC: CTAs per SM the register budget is sized for.
+template <int CMAX>
+struct StreamDims {
+    static constexpr int kTerms = 2;
+    static constexpr int kGlt = CMAX * kTerms;        // live mma columns
+    static constexpr int kNT = (kGlt + 7) / 8;        // n-tiles of 8 columns
+};
 
-// XS: activation tables of the (single) job are staged in shared memory
-template <int TYPE, int NT, bool XS>
-__global__ void __launch_bounds__(kWarpsPerCta * 32, 2) k_stream(StreamArgs A) {
-    constexpr int kMaxC = 4 * NT;  // 8*NT mma columns hold at most 4*NT activation columns
+// W: warps per CTA; OCC: CTAs per SM the register budget is sized for
+template <int TYPE, int CMAX, bool XS, int W, int OCC>
+__global__ void __launch_bounds__(W * 32, OCC) k_stream(StreamArgs A) {
+    using D = StreamDims<CMAX>;
+    constexpr int NT = D::kNT, GLT = D::kGlt, TERMS = D::kTerms;
+    constexpr int kWarpsPerCta = W;
+    constexpr int kStepBytes = step_bytes(TYPE);
+    constexpr int kAuxPerChunk = TYPE == LEV_GGML_Q4_K ? 2 * CMAX : (TYPE == LEV_GGML_Q6_K ? 4 * GLT : 2 * GLT);
+    const int kDepth = A.depth;  // ring stages per warp (1..4)
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[kWarpsPerCta][kDepth];
+    __shared__ __align__(8) unsigned long long bars[W][4];
+    __shared__ float rec[W][2][CMAX][16];  // partial sums of tiles a warp shares with its neighbours
+    __shared__ int rec_tile[W][2];         // group-local tile of each record, -1 = none
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int spt = A.steps_per_tile, tpg = A.tiles_per_group;
+    const int total_tiles = A.njobs_dev ? *A.njobs_dev * A.tiles_per_job : A.total_tiles;
+    const int groups = (total_tiles + tpg - 1) / tpg;
 
-    const int total = A.njobs_dev ? *A.njobs_dev * A.tiles_per_job * A.steps_per_tile : A.total_steps;
-    int range = (total + A.max_warps - 1) / A.max_warps;
-    if (range < 2) range = 2;
-    const int gw = blockIdx.x * kWarpsPerCta + warp;
-    const int s0 = gw * range;
-    const int n = (s0 + range <= total ? s0 + range : total) - s0;
+    // K-step range of this warp inside group grp: the group's steps are split evenly over the warps
+    auto warp_range = [&](int grp, int& s, int& e, int& per) {
+        int nt_here = total_tiles - grp * tpg < tpg ? total_tiles - grp * tpg : tpg;
+        int nst = nt_here * spt;
+        per = (nst + kWarpsPerCta - 1) / kWarpsPerCta;
+        s = warp * per;
+        e = s + per < nst ? s + per : nst;
+        if (s > e) s = e;
+    };
 
     unsigned char* ring = smem_raw + (size_t)warp * kDepth * kStepBytes;
     const unsigned ring_s = smem_u32(ring), bar_s = smem_u32(&bars[warp][0]);
-    if (lane == 0 && n > 0) {
-#pragma unroll
+    // fetch cursor (used by lane 0): walks this warp's K-steps over all of the CTA's groups
+    int f_grp = blockIdx.x, f_s = 0, f_e = 0, f_gt = 0, f_k = 0;
+    auto fetch_seek = [&]() {  // position on the first step of group f_grp
+        int per;
+        warp_range(f_grp, f_s, f_e, per);
+        f_gt = f_grp * tpg + f_s / spt;
+        f_k = f_s - (f_s / spt) * spt;
+    };
+    auto fetch_next = [&]() -> const unsigned char* {  // address of the next K-step, nullptr when done
+        while (f_grp < groups && f_s >= f_e) {
+            f_grp += gridDim.x;
+            if (f_grp < groups) fetch_seek();
+        }
+        if (f_grp >= groups) return nullptr;
+        int64_t tile = f_gt;
+        if (A.job_slice) {
+            int job = f_gt / A.tiles_per_job;
+            tile = (int64_t)A.job_slice[job] * A.tiles_per_job + (f_gt - job * A.tiles_per_job);
+        }
+        const unsigned char* p = reinterpret_cast<const unsigned char*>(A.wp) + (tile * spt + f_k) * (int64_t)kStepBytes;
+        f_s++;
+        if (++f_k == spt) {
+            f_k = 0;
+            f_gt++;
+        }
+        return p;
+    };
+    if (lane == 0) {
         for (int d = 0; d < kDepth; d++) mbar_init(bar_s + 8 * d, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-#pragma unroll
-        for (int d = 0; d < kDepth; d++)
-            if (d < n) bulk_load(ring_s + d * kStepBytes, step_src(A, s0 + d), kStepBytes, bar_s + 8 * d);
+        if (f_grp < groups) fetch_seek();
+        for (int d = 0; d < kDepth; d++) {
+            const unsigned char* p = fetch_next();
+            if (p) bulk_load(ring_s + d * kStepBytes, p, kStepBytes, bar_s + 8 * d);
+        }
     }
-    // dense calls stage the activation tables once per CTA while the first
-    // weight bytes are on their way
-    const uint4* sfrag = nullptr;
-    const float* saux = nullptr;
+    // dense calls stage the activation tables once per CTA while the first weight bytes are on their way
+    const uint4* jfrag = A.frag;
+    const float* jaux = A.aux;
     if (XS) {
         uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)kWarpsPerCta * kDepth * kStepBytes);
-        const int nfrag = A.chunks * A.glt * 8;  // uint4 units
-        const int naux = TYPE == LEV_GGML_Q4_K ? A.chunks * 2 * A.cmax : A.chunks * 2 * A.glt;
+        const int nfrag = A.chunks * GLT * 8;  // uint4 units
+        const int naux = A.chunks * kAuxPerChunk;
         float* sa = reinterpret_cast<float*>(xs + nfrag);
-        if (A.fused_prep) {
-            // each CTA splits the activations itself while its first weight
-            // bytes are in flight: no separate preparation launch
-            bool bad = false;
-            for (int i = threadIdx.x; i < A.chunks * A.glt * 4; i += blockDim.x) {
-                int tt = i & 3, col = (i >> 2) % A.glt, chunk = (i >> 2) / A.glt;
-                bad |= prep_frag<TYPE>(A.prep, 0, chunk, col, tt, xs + (size_t)i * 2);
-            }
-            // 32-column sums, one thread each so that the loads of all sums are in flight together
-            const int per = TYPE == LEV_GGML_Q4_K ? A.cmax : A.glt;
-            for (int i = threadIdx.x; i < naux; i += blockDim.x)
-                sa[i] = prep_sum32_serial<TYPE>(A.prep, i / (2 * per), (i / per) & 1, i % per);
-            if (bad && blockIdx.x == 0) atomicOr(A.status, LEV_DEV_NONFINITE_INPUT);
-        } else {
-            for (int i = threadIdx.x; i < nfrag; i += blockDim.x) xs[i] = __ldg(A.frag + i);
-            for (int i = threadIdx.x; i < naux; i += blockDim.x) sa[i] = __ldg(A.aux + i);
-        }
-        __syncthreads();
-        sfrag = xs;
-        saux = sa;
+        for (int i = threadIdx.x; i < nfrag; i += blockDim.x) xs[i] = __ldg(A.frag + i);
+        for (int i = threadIdx.x; i < naux; i += blockDim.x) sa[i] = __ldg(A.aux + i);
+        jfrag = xs;
+        jaux = sa;
     }
-    if (n <= 0) return;  // no block-wide barrier below this line
-    __syncwarp();
+    __syncthreads();
 
-    int gt = s0 / A.steps_per_tile;        // global tile index (job * tiles_per_job + tile)
-    int k = s0 - gt * A.steps_per_tile;    // K-step inside the tile
-    int seg_k0 = k;                        // where this warp's segment of the tile began
-    int pend_tile[2] = {-1, -1};           // global tiles with a partials record of this warp
-    const int first_gt = gt;
+    // per-lane table offsets.  A chunk's fragments are [GLT columns][4 t] x 32 B, so lane (g, t) of
+    // n-tile nt reads entry nt*32 + lane; lanes beyond the live columns read a valid entry whose
+    // values land in accumulator columns nobody reads.
+    int xoff[NT], boff0[NT], boff1[NT];
+#pragma unroll
+    for (int nt = 0; nt < NT; nt++) {
+        int e = nt * 32 + lane;
+        xoff[nt] = (e < GLT * 4 ? e : lane % (GLT * 4 < 32 ? GLT * 4 : 32)) * 2;
+        int c0 = nt * 8 + 2 * t;  // Q4_0: columns 2t, 2t+1 of the bias rows, clamped the same way
+        boff0[nt] = c0 < GLT ? c0 : 0;
+        boff1[nt] = c0 + 1 < GLT ? c0 + 1 : 0;
+    }
 
     float yacc[NT][4];
-    float mina[kMaxC], minb[kMaxC];
-#pragma unroll
-    for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-        for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
-#pragma unroll
-    for (int c = 0; c < kMaxC; c++) mina[c] = minb[c] = 0.f;
+    float mina[CMAX], minb[CMAX];
+    int slot = 0;          // ring stage of the next K-step
+    unsigned phase = 0;    // its mbarrier phase parity
+    bool dead = false;   // a bounded wait ran out: skip the work, keep meeting the barriers
 
-    int job = gt / A.tiles_per_job;
-    const uint4* jfrag = XS ? sfrag : A.frag + (int64_t)job * A.chunks * A.glt * 8;
-    const float* jaux = XS ? saux
-                           : A.aux + (int64_t)job * (TYPE == LEV_GGML_Q4_K ? A.chunks * 2 * A.cmax : A.chunks * 2 * A.glt);
-
-    for (int i = 0; i < n; i++) {
-        const int slot = i % kDepth;
-        if (!mbar_wait(bar_s + 8 * slot, (unsigned)(i / kDepth) & 1u)) {
-            if (lane == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
-            return;
+    for (int grp = blockIdx.x; grp < groups; grp += gridDim.x) {
+        int s, e, per;
+        warp_range(grp, s, e, per);
+        if (lane < 2) rec_tile[warp][lane] = -1;
+        int tl = s / spt;            // group-local tile
+        int k = s - tl * spt;        // K-step inside the tile
+        int seg_k0 = k;
+        const int first_tl = tl;
+        int job = (grp * tpg + tl) / A.tiles_per_job;
+        if (!XS) {
+            jfrag = A.frag + (int64_t)job * A.chunks * GLT * 8;
+            jaux = A.aux + (int64_t)job * A.chunks * kAuxPerChunk;
         }
-        const uint4* st = reinterpret_cast<const uint4*>(ring + slot * kStepBytes);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
+#pragma unroll
+        for (int c = 0; c < CMAX; c++) mina[c] = minb[c] = 0.f;
 
-        if (!(A.debug & 1))
-#pragma unroll
-        for (int c = 0; c < 4; c++) {
-            // ---- activation fragments of this chunk ----
-            const int ch = k * 4 + c;
-            uint4 x0[NT], x1[NT];
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++) {
-                x0[nt] = make_uint4(0, 0, 0, 0);
-                x1[nt] = x0[nt];
-                if (nt * 8 + g < A.glt) {
-                    const uint4* p = jfrag + ((ch * A.glt + nt * 8 + g) * 4 + t) * 2;
-                    x0[nt] = XS ? p[0] : __ldg(p);
-                    x1[nt] = XS ? p[1] : __ldg(p + 1);
-                }
+        for (int i = s; i < e && !dead; i++) {
+            if (!mbar_wait(bar_s + 8 * slot, phase)) {
+                if (lane == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
+                dead = true;
+                break;
             }
-            if (TYPE == LEV_GGML_Q4_K) {
-                const uint4 q = st[16 + c * 32 + lane];
-                // 6-bit scales of sub-blocks 2c, 2c+1 of rows g (h0) and g+8 (h1)
-                // (rust/crates/lev-cpu/src/lib.rs:64-74), four per word
-                const uint4 h0 = st[g], h1 = st[8 + g];
-                unsigned sa = c < 2 ? (h0.y & 0x3F3F3F3Fu) : ((h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u));
-                unsigned sb = c < 2 ? (h1.y & 0x3F3F3F3Fu) : ((h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u));
-                float dA = h2f_bits(h0.x & 0xffffu) * 16777216.0f, dB = h2f_bits(h1.x & 0xffffu) * 16777216.0f;  // d * 2^24
-                float sA_lo = dA * byte_to_float(sa, 2 * (c & 1)), sA_hi = dA * byte_to_float(sa, 2 * (c & 1) + 1);
-                float sB_lo = dB * byte_to_float(sb, 2 * (c & 1)), sB_hi = dB * byte_to_float(sb, 2 * (c & 1) + 1);
-                unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
-                unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+            const uint4* st = reinterpret_cast<const uint4*>(ring + slot * kStepBytes);
+            const uint4* xchunk = jfrag + k * (4 * GLT * 8);
+            const float* achunk = jaux + k * (4 * kAuxPerChunk);
+
+            if (!(A.debug & 1)) {
+                if (TYPE == LEV_GGML_Q4_K) {
+                    const uint4 h0 = st[g], h1 = st[8 + g];
+                    // 6-bit scales of the 8 sub-blocks of rows g (h0) and g+8 (h1), four per word
+                    // (rust/crates/lev-cpu/src/lib.rs:64-74)
+                    const unsigned sa_lo = h0.y & 0x3F3F3F3Fu, sa_hi = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
+                    const unsigned sb_lo = h1.y & 0x3F3F3F3Fu, sb_hi = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
+                    const float dA = h2f_bits(h0.x & 0xffffu) * 16777216.0f, dB = h2f_bits(h1.x & 0xffffu) * 16777216.0f;  // d * 2^24
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    float lo[4], hi[4];
-                    mma16816_z(lo, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0[nt].x, x0[nt].y);
-                    mma16816(lo, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x0[nt].z, x0[nt].w);
-                    mma16816_z(hi, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x1[nt].x, x1[nt].y);
-                    mma16816(hi, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1[nt].z, x1[nt].w);
-                    yacc[nt][0] = fmaf(sA_lo, lo[0], fmaf(sA_hi, hi[0], yacc[nt][0]));
-                    yacc[nt][1] = fmaf(sA_lo, lo[1], fmaf(sA_hi, hi[1], yacc[nt][1]));
-                    yacc[nt][2] = fmaf(sB_lo, lo[2], fmaf(sB_hi, hi[2], yacc[nt][2]));
-                    yacc[nt][3] = fmaf(sB_lo, lo[3], fmaf(sB_hi, hi[3], yacc[nt][3]));
-                }
-            } else {
-                const uint2 sc = reinterpret_cast<const uint2*>(st + c * 36)[g];
-                const uint4 q = st[c * 36 + 4 + lane];
-                // d * 2^24 for (row g, blk0), (row g, blk1), (row g+8, blk0), (row g+8, blk1)
-                float dA0 = h2f_bits(sc.x & 0xffffu) * 16777216.0f, dA1 = h2f_bits(sc.x >> 16) * 16777216.0f;
-                float dB0 = h2f_bits(sc.y & 0xffffu) * 16777216.0f, dB1 = h2f_bits(sc.y >> 16) * 16777216.0f;
-                unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
-                unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+                    for (int c = 0; c < 4; c++) {
+                        const uint4 q = st[16 + c * 32 + lane];
+                        const unsigned sa = c < 2 ? sa_lo : sa_hi, sb = c < 2 ? sb_lo : sb_hi;
+                        const float sA_lo = dA * byte_to_float(sa, 2 * (c & 1)), sA_hi = dA * byte_to_float(sa, 2 * (c & 1) + 1);
+                        const float sB_lo = dB * byte_to_float(sb, 2 * (c & 1)), sB_hi = dB * byte_to_float(sb, 2 * (c & 1) + 1);
+                        const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+                        const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
 #pragma unroll
-                for (int nt = 0; nt < NT; nt++) {
-                    // accumulators start at -8 * 2^-24 * (sum of the block's activations)
-                    float k00 = 0.f, k01 = 0.f, k10 = 0.f, k11 = 0.f;
-                    const int cb = nt * 8 + 2 * t;
-                    const float* bp = jaux + (ch * 2) * A.glt + cb;
-                    if (cb < A.glt) {
-                        k00 = XS ? bp[0] : __ldg(bp);
-                        k10 = XS ? bp[A.glt] : __ldg(bp + A.glt);
+                        for (int nt = 0; nt < NT; nt++) {
+                            const uint4* xp = xchunk + c * (GLT * 8) + xoff[nt];
+                            const uint4 x0 = XS ? xp[0] : __ldg(xp), x1 = XS ? xp[1] : __ldg(xp + 1);
+                            float lo[4], hi[4];
+                            mma16816_z(lo, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
+                            mma16816(lo, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x0.z, x0.w);
+                            mma16816_z(hi, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x1.x, x1.y);
+                            mma16816(hi, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1.z, x1.w);
+                            yacc[nt][0] = fmaf(sA_lo, lo[0], fmaf(sA_hi, hi[0], yacc[nt][0]));
+                            yacc[nt][1] = fmaf(sA_lo, lo[1], fmaf(sA_hi, hi[1], yacc[nt][1]));
+                            yacc[nt][2] = fmaf(sB_lo, lo[2], fmaf(sB_hi, hi[2], yacc[nt][2]));
+                            yacc[nt][3] = fmaf(sB_lo, lo[3], fmaf(sB_hi, hi[3], yacc[nt][3]));
+                        }
                     }
-                    if (cb + 1 < A.glt) {
-                        k01 = XS ? bp[1] : __ldg(bp + 1);
-                        k11 = XS ? bp[A.glt + 1] : __ldg(bp + A.glt + 1);
+                    // min term: this lane owns sub-blocks 2t, 2t+1 of its two rows
+                    const unsigned ma = t < 2 ? (h0.z & 0x3F3F3F3Fu) : (((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u));
+                    const unsigned mb = t < 2 ? (h1.z & 0x3F3F3F3Fu) : (((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u));
+                    const unsigned mab = t & 1 ? (ma >> 16) : ma, mbb = t & 1 ? (mb >> 16) : mb;
+                    const float dminA = h2f_bits(h0.x >> 16), dminB = h2f_bits(h1.x >> 16);
+                    const float mA0 = dminA * byte_to_float(mab, 0), mA1 = dminA * byte_to_float(mab, 1);
+                    const float mB0 = dminB * byte_to_float(mbb, 0), mB1 = dminB * byte_to_float(mbb, 1);
+                    const float* sx0 = achunk + 2 * t * CMAX;  // sums of sub-blocks 2t, 2t+1: [sub-block][CMAX]
+#pragma unroll
+                    for (int c = 0; c < CMAX; c++) {
+                        const float x0 = XS ? sx0[c] : __ldg(sx0 + c), x1 = XS ? sx0[CMAX + c] : __ldg(sx0 + CMAX + c);
+                        mina[c] = fmaf(mA0, x0, fmaf(mA1, x1, mina[c]));
+                        minb[c] = fmaf(mB0, x0, fmaf(mB1, x1, minb[c]));
                     }
-                    float a0[4] = {k00, k01, k00, k01}, a1[4] = {k10, k11, k10, k11};
-                    mma16816(a0, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0[nt].x, x0[nt].y);
-                    mma16816(a0, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x0[nt].z, x0[nt].w);
-                    mma16816(a1, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x1[nt].x, x1[nt].y);
-                    mma16816(a1, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1[nt].z, x1[nt].w);
-                    yacc[nt][0] = fmaf(dA0, a0[0], fmaf(dA1, a1[0], yacc[nt][0]));
-                    yacc[nt][1] = fmaf(dA0, a0[1], fmaf(dA1, a1[1], yacc[nt][1]));
-                    yacc[nt][2] = fmaf(dB0, a0[2], fmaf(dB1, a1[2], yacc[nt][2]));
-                    yacc[nt][3] = fmaf(dB0, a0[3], fmaf(dB1, a1[3], yacc[nt][3]));
-                }
-            }
-        }
-        if (TYPE == LEV_GGML_Q4_K && !(A.debug & 1)) {
-            // min term: this lane owns sub-blocks 2t, 2t+1 of its two rows
-            const uint4 h0 = st[g], h1 = st[8 + g];
-            unsigned ma = t < 2 ? (h0.z & 0x3F3F3F3Fu) : (((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u));
-            unsigned mb = t < 2 ? (h1.z & 0x3F3F3F3Fu) : (((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u));
-            int sh = 16 * (t & 1);
-            float dminA = h2f_bits(h0.x >> 16), dminB = h2f_bits(h1.x >> 16);
-            float mA0 = dminA * (float)((ma >> sh) & 0xffu), mA1 = dminA * (float)((ma >> (sh + 8)) & 0xffu);
-            float mB0 = dminB * (float)((mb >> sh) & 0xffu), mB1 = dminB * (float)((mb >> (sh + 8)) & 0xffu);
-            const float* sx0 = jaux + (k * 8 + 2 * t) * A.cmax;
+                } else if (TYPE == LEV_GGML_Q6_K) {
+                    // int8 scales of the 16 sub-blocks of rows g and g+8, fp16 d of both rows
+                    const uint4 sa4 = st[g], sb4 = st[8 + g];
+                    const unsigned short* dp = reinterpret_cast<const unsigned short*>(st + 16);
+                    const float dA = h2f_bits(dp[g]) * 16777216.0f, dB = h2f_bits(dp[g + 8]) * 16777216.0f;  // d * 2^24
+                    const unsigned scA[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, scB[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
 #pragma unroll
-            for (int c = 0; c < kMaxC; c++) {
-                if (c < A.cmax) {
-                    float x0 = XS ? sx0[c] : __ldg(sx0 + c), x1 = XS ? sx0[A.cmax + c] : __ldg(sx0 + A.cmax + c);
-                    mina[c] = fmaf(mA0, x0, fmaf(mA1, x1, mina[c]));
-                    minb[c] = fmaf(mB0, x0, fmaf(mB1, x1, minb[c]));
-                }
-            }
-        }
-
-        // every lane has consumed its shared-memory reads of this stage: refill it
-        __syncwarp();
-        if (lane == 0 && i + kDepth < n)
-            bulk_load(ring_s + slot * kStepBytes, step_src(A, s0 + i + kDepth), kStepBytes, bar_s + 8 * slot);
-
-        k++;
-        if (k == A.steps_per_tile || i == n - 1) {
-            // ---- this warp's segment of the tile ends: fold to one f32 per (row, column) ----
-            const bool whole = seg_k0 == 0 && k == A.steps_per_tile;
-            const int rec = gt == first_gt ? 0 : 1;
-            const int tile_in_job = gt - job * A.tiles_per_job;
-            float* pbuf = A.partials + ((int64_t)(gw * 2 + rec) * A.cmax) * 16;
+                    for (int c = 0; c < 4; c++) {
+                        const uint4 q = st[18 + c * 32 + lane];
+                        const uint2 hq = reinterpret_cast<const uint2*>(st + 146)[c * 32 + lane];
+                        // row g: words q.x, q.y + high bits hq.x ; row g+8: q.z, q.w + hq.y
+                        const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+                        const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+                        const unsigned ha = hq.x, hb = hq.y;
+                        // the 2-bit fields, shifted so that each register's pair lands on bits 4,5 / 20,21
+                        // (low-nibble registers) or 8,9 / 24,25 (high-nibble registers)
+                        const unsigned ha_r2 = ha >> 2, ha_l2 = ha << 2, ha_l4 = ha << 4, ha_r4 = ha >> 4, ha_r6 = ha >> 6;
+                        const unsigned hb_r2 = hb >> 2, hb_l2 = hb << 2, hb_l4 = hb << 4, hb_r4 = hb >> 4, hb_r6 = hb >> 6;
+                        // A fragments {row g k-lo, row g+8 k-lo, row g k-hi, row g+8 k-hi} of the four sub-blocks
+                        const unsigned a[4][4] = {
+                            {(w0 & 0x000F000Fu) | (ha & 0x00300030u), (w2 & 0x000F000Fu) | (hb & 0x00300030u),
+                             (w0s & 0x000F000Fu) | (ha_r2 & 0x00300030u), (w2s & 0x000F000Fu) | (hb_r2 & 0x00300030u)},
+                            {(w1 & 0x000F000Fu) | (ha_l2 & 0x00300030u), (w3 & 0x000F000Fu) | (hb_l2 & 0x00300030u),
+                             (w1s & 0x000F000Fu) | (ha_l4 & 0x00300030u), (w3s & 0x000F000Fu) | (hb_l4 & 0x00300030u)},
+                            {(w0 & 0x00F000F0u) | (ha & 0x03000300u), (w2 & 0x00F000F0u) | (hb & 0x03000300u),
+                             (w0s & 0x00F000F0u) | (ha_r2 & 0x03000300u), (w2s & 0x00F000F0u) | (hb_r2 & 0x03000300u)},
+                            {(w1 & 0x00F000F0u) | (ha_r4 & 0x03000300u), (w3 & 0x00F000F0u) | (hb_r4 & 0x03000300u),
+                             (w1s & 0x00F000F0u) | (ha_r6 & 0x03000300u), (w3s & 0x00F000F0u) | (hb_r6 & 0x03000300u)}};
+                        const float* bchunk = achunk + c * (4 * GLT);
 #pragma unroll
-            for (int c = 0; c < kMaxC; c++) {
-                if (c < A.cmax) {
-                    float va = 0.f, vb = 0.f;
+                        for (int nt = 0; nt < NT; nt++) {
+                            const uint4* xp = xchunk + c * (GLT * 8) + xoff[nt];
+                            const uint4 x0 = XS ? xp[0] : __ldg(xp), x1 = XS ? xp[1] : __ldg(xp + 1);
+                            const unsigned xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
 #pragma unroll
-                    for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                        for (int jj = 0; jj < 2; jj++) {
-                            int col = nt * 8 + 2 * t + jj;
-                            int xc = col / A.terms, term = col - xc * A.terms;
-                            float sc = term == 0 ? 1.0f : (term == 1 ? 4.8828125e-4f : 2.384185791015625e-7f);
-                            if (xc == c) {
-                                va = fmaf(yacc[nt][jj], sc, va);
-                                vb = fmaf(yacc[nt][2 + jj], sc, vb);
+                            for (int m = 0; m < 4; m++) {
+                                // accumulator starts at -32 * 2^-24 * (sum of the sub-block's activations)
+                                const float k0 = XS ? bchunk[m * GLT + boff0[nt]] : __ldg(bchunk + m * GLT + boff0[nt]);
+                                const float k1 = XS ? bchunk[m * GLT + boff1[nt]] : __ldg(bchunk + m * GLT + boff1[nt]);
+                                float acc[4] = {k0, k1, k0, k1};
+                                mma16816(acc, a[m][0], a[m][1], a[m][2], a[m][3], xb[2 * m], xb[2 * m + 1]);
+                                const float sA = dA * (float)(int)(signed char)(scA[c] >> (8 * m));
+                                const float sB = dB * (float)(int)(signed char)(scB[c] >> (8 * m));
+                                yacc[nt][0] = fmaf(sA, acc[0], yacc[nt][0]);
+                                yacc[nt][1] = fmaf(sA, acc[1], yacc[nt][1]);
+                                yacc[nt][2] = fmaf(sB, acc[2], yacc[nt][2]);
+                                yacc[nt][3] = fmaf(sB, acc[3], yacc[nt][3]);
                             }
                         }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 4; c++) {
+                        const uint2 sc = reinterpret_cast<const uint2*>(st + c * 36)[g];
+                        const uint4 q = st[c * 36 + 4 + lane];
+                        // d * 2^24 for (row g, blk0), (row g, blk1), (row g+8, blk0), (row g+8, blk1)
+                        const float dA0 = h2f_bits(sc.x & 0xffffu) * 16777216.0f, dA1 = h2f_bits(sc.x >> 16) * 16777216.0f;
+                        const float dB0 = h2f_bits(sc.y & 0xffffu) * 16777216.0f, dB1 = h2f_bits(sc.y >> 16) * 16777216.0f;
+                        const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+                        const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+                        const float* bchunk = achunk + c * (2 * GLT);
+#pragma unroll
+                        for (int nt = 0; nt < NT; nt++) {
+                            const uint4* xp = xchunk + c * (GLT * 8) + xoff[nt];
+                            const uint4 x0 = XS ? xp[0] : __ldg(xp), x1 = XS ? xp[1] : __ldg(xp + 1);
+                            // accumulators start at -8 * 2^-24 * (sum of the block's activations)
+                            const float k00 = XS ? bchunk[boff0[nt]] : __ldg(bchunk + boff0[nt]);
+                            const float k01 = XS ? bchunk[boff1[nt]] : __ldg(bchunk + boff1[nt]);
+                            const float k10 = XS ? bchunk[GLT + boff0[nt]] : __ldg(bchunk + GLT + boff0[nt]);
+                            const float k11 = XS ? bchunk[GLT + boff1[nt]] : __ldg(bchunk + GLT + boff1[nt]);
+                            float a0[4] = {k00, k01, k00, k01}, a1[4] = {k10, k11, k10, k11};
+                            mma16816(a0, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
+                            mma16816(a0, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x0.z, x0.w);
+                            mma16816(a1, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x1.x, x1.y);
+                            mma16816(a1, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1.z, x1.w);
+                            yacc[nt][0] = fmaf(dA0, a0[0], fmaf(dA1, a1[0], yacc[nt][0]));
+                            yacc[nt][1] = fmaf(dA0, a0[1], fmaf(dA1, a1[1], yacc[nt][1]));
+                            yacc[nt][2] = fmaf(dB0, a0[2], fmaf(dB1, a1[2], yacc[nt][2]));
+                            yacc[nt][3] = fmaf(dB0, a0[3], fmaf(dB1, a1[3], yacc[nt][3]));
+                        }
+                    }
+                }
+            }
+
+            // every lane has consumed its shared-memory reads of this stage: refill it
+            __syncwarp();
+            if (lane == 0) {
+                const unsigned char* p = fetch_next();
+                if (p) bulk_load(ring_s + slot * kStepBytes, p, kStepBytes, bar_s + 8 * slot);
+            }
+            if (++slot == kDepth) {
+                slot = 0;
+                phase ^= 1u;
+            }
+
+            k++;
+            if (k == spt || i == e - 1) {
+                // ---- this warp's segment of the tile ends: fold to one f32 per (row, column) ----
+                const bool whole = seg_k0 == 0 && k == spt;
+                const int r = tl == first_tl ? 0 : 1;
+                const int gt = grp * tpg + tl;
+                const int tile_in_job = gt - job * A.tiles_per_job;
+#pragma unroll
+                for (int c = 0; c < CMAX; c++) {
+                    float va = 0.f, vb = 0.f;
+#pragma unroll
+                    for (int term = 0; term < TERMS; term++) {
+                        constexpr float kScale[3] = {1.0f, 4.8828125e-4f, 2.384185791015625e-7f};  // 2^0, 2^-11, 2^-22
+                        const int col = c * TERMS + term, nt = col / 8, jj = col & 1;
+                        const bool mine = t == (col % 8) / 2;
+                        va = fmaf(mine ? yacc[nt][jj] : 0.f, kScale[term], va);
+                        vb = fmaf(mine ? yacc[nt][2 + jj] : 0.f, kScale[term], vb);
+                    }
                     if (TYPE == LEV_GGML_Q4_K) {
                         va -= mina[c];
                         vb -= minb[c];
@@ -588,65 +743,53 @@ __global__ void __launch_bounds__(kWarpsPerCta * 32, 2) k_stream(StreamArgs A) {
                     vb += __shfl_xor_sync(0xffffffffu, vb, 2);
                     if (t == 0) {
                         if (whole) {
-                            const int oc = A.outmap ? A.outmap[job * A.cmax + c] : c;
-                            int64_t r = (int64_t)tile_in_job * 16 + g;
-                            if (oc >= 0) {
-                                if (r < A.rows) A.y[(int64_t)oc * A.out_ld + r] = va;
-                                if (r + 8 < A.rows) A.y[(int64_t)oc * A.out_ld + r + 8] = vb;
+                            const int oc = A.outmap ? A.outmap[job * CMAX + c] : c;
+                            const int64_t row = (int64_t)tile_in_job * 16 + g;
+                            if (oc >= 0 && oc < A.out_cols) {
+                                if (row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = va;
+                                if (row + 8 < A.rows) A.y[(int64_t)oc * A.out_ld + row + 8] = vb;
                             }
                         } else {
-                            __stcg(pbuf + c * 16 + g, va);
-                            __stcg(pbuf + c * 16 + g + 8, vb);
+                            rec[warp][r][c][g] = va;
+                            rec[warp][r][c][g + 8] = vb;
                         }
                     }
                 }
-            }
-            if (!whole) pend_tile[rec] = gt;
+                if (!whole && lane == 0) rec_tile[warp][r] = tl;
 #pragma unroll
-            for (int nt = 0; nt < NT; nt++)
+                for (int nt = 0; nt < NT; nt++)
 #pragma unroll
-                for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
+                    for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
 #pragma unroll
-            for (int c = 0; c < kMaxC; c++) mina[c] = minb[c] = 0.f;
-            gt++;
-            k = 0;
-            seg_k0 = 0;
-            if (!XS && gt - job * A.tiles_per_job >= A.tiles_per_job) {
-                job++;
-                jfrag = A.frag + (int64_t)job * A.chunks * A.glt * 8;
-                jaux = A.aux + (int64_t)job * (TYPE == LEV_GGML_Q4_K ? A.chunks * 2 * A.cmax : A.chunks * 2 * A.glt);
-            }
-        }
-    }
-
-    // ---- tiles shared with other warps: the last arriver adds the records in warp order ----
-#pragma unroll
-    for (int rec = 0; rec < 2; rec++) {
-        const int pt = pend_tile[rec];
-        if (pt < 0) continue;
-        __threadfence();
-        __syncwarp();
-        const int w_first = (pt * A.steps_per_tile) / range;
-        const int w_last = (pt * A.steps_per_tile + A.steps_per_tile - 1) / range;
-        int prev = 0;
-        if (lane == 0) prev = atomicAdd(A.tile_count + pt, 1);
-        prev = __shfl_sync(0xffffffffu, prev, 0);
-        if (prev == w_last - w_first) {
-            __threadfence();
-            const int pjob = pt / A.tiles_per_job, ptile = pt - pjob * A.tiles_per_job;
-            for (int idx = lane; idx < A.cmax * 16; idx += 32) {
-                float acc = 0.f;
-                for (int w = w_first; w <= w_last; w++) {
-                    int wrec = (w * range) / A.steps_per_tile == pt ? 0 : 1;
-                    acc += __ldcg(A.partials + ((int64_t)(w * 2 + wrec) * A.cmax) * 16 + idx);
+                for (int c = 0; c < CMAX; c++) mina[c] = minb[c] = 0.f;
+                tl++;
+                k = 0;
+                seg_k0 = 0;
+                if (!XS && grp * tpg + tl - job * A.tiles_per_job >= A.tiles_per_job) {
+                    job++;
+                    jfrag = A.frag + (int64_t)job * A.chunks * GLT * 8;
+                    jaux = A.aux + (int64_t)job * A.chunks * kAuxPerChunk;
                 }
-                const int c = idx >> 4;
-                const int oc = A.outmap ? A.outmap[pjob * A.cmax + c] : c;
-                int64_t r = (int64_t)ptile * 16 + (idx & 15);
-                if (oc >= 0 && r < A.rows) A.y[(int64_t)oc * A.out_ld + r] = acc;
             }
-            if (lane == 0) A.tile_count[pt] = 0;
         }
+        __syncthreads();
+        // ---- tiles shared between warps: add the warps' records in warp order ----
+        {
+            const int nt_here = total_tiles - grp * tpg < tpg ? total_tiles - grp * tpg : tpg;
+            for (int item = threadIdx.x; item < nt_here * CMAX * 16; item += blockDim.x) {
+                const int tile = item / (CMAX * 16), idx = item - tile * (CMAX * 16);
+                const int w_first = (tile * spt) / per, w_last = (tile * spt + spt - 1) / per;
+                if (w_first == w_last) continue;  // one warp had the whole tile and wrote it
+                float acc = 0.f;
+                for (int w = w_first; w <= w_last; w++) acc += rec[w][rec_tile[w][0] == tile ? 0 : 1][0][idx];
+                const int gt = grp * tpg + tile, pjob = gt / A.tiles_per_job, ptile = gt - pjob * A.tiles_per_job;
+                const int c = idx >> 4;
+                const int oc = A.outmap ? A.outmap[pjob * CMAX + c] : c;
+                const int64_t row = (int64_t)ptile * 16 + (idx & 15);
+                if (oc >= 0 && oc < A.out_cols && row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = acc;
+            }
+        }
+        __syncthreads();
     }
 }
 
@@ -655,15 +798,40 @@ int grid_cap(lev_ctx* ctx, int64_t work, int block, int per_sm) {
     return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
-template <int TYPE, int NT, bool XS>
+template <int TYPE, int CMAX, bool XS, int W, int OCC>
 int launch_stream(lev_ctx* ctx, int grid, size_t smem, const StreamArgs& A) {
     static size_t configured[16] = {};  // per device: largest dynamic shared memory opted in so far
     if (configured[ctx->device & 15] < smem) {
-        LEV_CUDA(ctx, cudaFuncSetAttribute(k_stream<TYPE, NT, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_stream<TYPE, CMAX, XS, W, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[ctx->device & 15] = smem;
     }
-    k_stream<TYPE, NT, XS><<<grid, kWarpsPerCta * 32, smem, ctx->stream>>>(A);
+    k_stream<TYPE, CMAX, XS, W, OCC><<<grid, W * 32, smem, ctx->stream>>>(A);
     return LEV_OK;
+}
+
+// variant 0: eight warps, two CTAs per SM, tables read from global memory (grouped / oversized tables)
+// variant 1: eight warps, two CTAs per SM, tables in shared memory
+// variant 2: twenty-four warps, one CTA per SM, tables in shared memory
+template <int TYPE, int CMAX>
+int launch_stream_variant(lev_ctx* ctx, int grid, size_t smem, const StreamArgs& A, int variant) {
+    if (variant == 0) return launch_stream<TYPE, CMAX, false, kWarpsPerCta, 2>(ctx, grid, smem, A);
+    if (variant == 2 && CMAX <= 4) return launch_stream<TYPE, (CMAX <= 4 ? CMAX : 1), true, kWarpsWide, 1>(ctx, grid, smem, A);
+    return launch_stream<TYPE, CMAX, true, kWarpsPerCta, 2>(ctx, grid, smem, A);
+}
+
+template <int TYPE>
+int launch_stream_cmax(lev_ctx* ctx, int cmax, int grid, size_t smem, const StreamArgs& A, int variant) {
+    switch (cmax) {
+        case 1: return launch_stream_variant<TYPE, 1>(ctx, grid, smem, A, variant);
+        case 2: return launch_stream_variant<TYPE, 2>(ctx, grid, smem, A, variant);
+        case 3: return launch_stream_variant<TYPE, 3>(ctx, grid, smem, A, variant);
+        case 4: return launch_stream_variant<TYPE, 4>(ctx, grid, smem, A, variant);
+        case 5: return launch_stream_variant<TYPE, 5>(ctx, grid, smem, A, variant);
+        case 6: return launch_stream_variant<TYPE, 6>(ctx, grid, smem, A, variant);
+        case 7: return launch_stream_variant<TYPE, 7>(ctx, grid, smem, A, variant);
+        case 8: return launch_stream_variant<TYPE, 8>(ctx, grid, smem, A, variant);
+    }
+    return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d", cmax);
 }
 
 int env_int(const char* name, int fallback) {
@@ -673,7 +841,10 @@ int env_int(const char* name, int fallback) {
 
 }  // namespace
 
-int lev_stream_terms(int n_cols) { return 3 * n_cols <= 8 ? 3 : 2; }
+int lev_stream_terms(int n_cols) {
+    (void)n_cols;
+    return 2;
+}
 
 // 64-column chunks of the activation tables; Q4_0 rows are padded with zero
 // blocks to whole K-steps of four chunks
@@ -683,16 +854,17 @@ int64_t lev_stream_chunks(const lev_weights* w) {
 }
 
 int lev_repack_weights(lev_ctx* ctx, lev_weights* w) {
-    if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0) return LEV_OK;  // other types: plain schedule
     int64_t tiles = (w->rows + 15) / 16;
     int64_t steps = lev_stream_chunks(w) / 4;
-    size_t bytes = (size_t)tiles * steps * kStepBytes;
+    size_t bytes = (size_t)tiles * steps * step_bytes(w->type);
     LEV_CUDA(ctx, cudaMalloc((void**)&w->packed, bytes + 256));
     w->packed_bytes = bytes;
     w->packed_rows = tiles * 16;
     int grid = grid_cap(ctx, (int64_t)(bytes / 16), 256, 16);
     if (w->type == LEV_GGML_Q4_K)
         k_repack_q4k<<<grid, 256, 0, ctx->stream>>>(w->raw, w->rows, w->blocks_per_row, tiles, (uint4*)w->packed);
+    else if (w->type == LEV_GGML_Q6_K)
+        k_repack_q6k<<<grid, 256, 0, ctx->stream>>>(w->raw, w->rows, w->blocks_per_row, tiles, (uint4*)w->packed);
     else
         k_repack_q40<<<grid, 256, 0, ctx->stream>>>(w->raw, w->rows, w->blocks_per_row, tiles, lev_stream_chunks(w),
                                                     (uint4*)w->packed);
@@ -713,8 +885,9 @@ size_t lev_stream_table_bytes(const lev_weights* w, int cmax, int terms, int job
     int64_t chunks = lev_stream_chunks(w);
     int glt = cmax * terms;
     size_t fb = ((size_t)jobs * chunks * glt * 4 * 32 + 255) & ~(size_t)255;
-    size_t ab = w->type == LEV_GGML_Q4_K ? (size_t)jobs * chunks * 2 * cmax * sizeof(float)
-                                         : (size_t)jobs * chunks * 2 * glt * sizeof(float);
+    size_t ab = w->type == LEV_GGML_Q4_K   ? (size_t)jobs * chunks * 2 * cmax * sizeof(float)
+                : w->type == LEV_GGML_Q6_K ? (size_t)jobs * chunks * 4 * glt * sizeof(float)
+                                           : (size_t)jobs * chunks * 2 * glt * sizeof(float);
     ab = (ab + 255) & ~(size_t)255;
     if (frag_bytes) *frag_bytes = fb;
     return fb + ab;
@@ -729,6 +902,7 @@ int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_sour
     int ntiles = (P.glt + 7) / 8;
     dim3 grid((unsigned)P.chunks, (unsigned)jobs);
     if (w->type == LEV_GGML_Q4_K) k_prepare_x<LEV_GGML_Q4_K><<<grid, 32 * ntiles, 0, ctx->stream>>>(P);
+    else if (w->type == LEV_GGML_Q6_K) k_prepare_x<LEV_GGML_Q6_K><<<grid, 32 * ntiles, 0, ctx->stream>>>(P);
     else k_prepare_x<LEV_GGML_Q4_0><<<grid, 32 * ntiles, 0, ctx->stream>>>(P);
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_prepare_x");
@@ -756,18 +930,13 @@ static PrepArgs make_prep(lev_ctx* ctx, const lev_weights* w, const lev_stream_s
     return P;
 }
 
-bool lev_stream_fuses_prepare(const lev_weights* w, int cmax, int terms) {
-    size_t tb = lev_stream_table_bytes(w, cmax, terms, 1, nullptr);
-    return (size_t)kWarpsPerCta * kDepth * kStepBytes + tb <= 110 * 1024;
-}
-
 // sizes of the two work buffers a call needs: per-warp partial sums and per-tile counters
 void lev_stream_workspace_bytes(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, int cmax,
                                 size_t* partial_bytes, size_t* counter_bytes) {
     const int64_t steps = lev_stream_chunks(w) / 4, tiles_per_job = (J.rows + 15) / 16;
     const int64_t max_steps = (int64_t)J.max_jobs * tiles_per_job * steps;
-    int ctas_per_sm = env_int("LEV_STREAM_CTAS_PER_SM", 2);
-    ctas_per_sm = ctas_per_sm < 1 ? 1 : (ctas_per_sm > 2 ? 2 : ctas_per_sm);
+    int ctas_per_sm = env_int("LEV_STREAM_CTAS_PER_SM", 3);
+    ctas_per_sm = ctas_per_sm < 1 ? 1 : (ctas_per_sm > 3 ? 3 : ctas_per_sm);
     int grid = ctx->prop.multiProcessorCount * ctas_per_sm;
     int64_t need_warps = (max_steps + 1) / 2;
     if ((int64_t)grid * kWarpsPerCta > need_warps) grid = (int)((need_warps + kWarpsPerCta - 1) / kWarpsPerCta);
@@ -789,36 +958,58 @@ int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, 
 // the launch itself, on caller-provided work buffers (counters zero on entry; left zero on exit)
 int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, const void* tables, int cmax, int terms,
                       float* y, const lev_stream_source* fused_src, void* pbuf, void* counters) {
-    const int glt = cmax * terms, ntiles = (glt + 7) / 8;
+    const int glt = cmax * terms;
     const int64_t chunks = lev_stream_chunks(w), steps = chunks / 4;
     const bool grouped = J.njobs_dev != nullptr;
     const int64_t tiles_per_job = (J.rows + 15) / 16;
     const int64_t max_steps = (int64_t)J.max_jobs * tiles_per_job * steps;
     if (max_steps > 0x7fffffff / 4) return lev_fail(ctx, LEV_EXCEEDS_WORKLOAD, "stream schedule: too many K-steps");
+    if (fused_src) return lev_fail(ctx, LEV_UNSUPPORTED, "in-kernel activation preparation is not built");
+    if (terms != lev_stream_terms(cmax)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "stream schedule: %d terms with %d columns", terms, cmax);
 
-    int ctas_per_sm = env_int("LEV_STREAM_CTAS_PER_SM", 2);
-    ctas_per_sm = ctas_per_sm < 1 ? 1 : (ctas_per_sm > 2 ? 2 : ctas_per_sm);
-    int grid = ctx->prop.multiProcessorCount * ctas_per_sm;
-    // a call with little work uses fewer warps, each with at least two K-steps
-    int64_t need_warps = (max_steps + 1) / 2;
-    if ((int64_t)grid * kWarpsPerCta > need_warps) grid = (int)((need_warps + kWarpsPerCta - 1) / kWarpsPerCta);
+    const size_t kStepBytes = step_bytes(w->type);
+    size_t tb = lev_stream_table_bytes(w, cmax, terms, 1, nullptr);
+    const int64_t total_tiles = (int64_t)J.max_jobs * tiles_per_job;
+    const int sms = ctx->prop.multiProcessorCount;
+    const size_t smem_cap = 200 * 1024;
+    // Variant and ring depth.  Dense calls with small tables run one CTA of 24 warps per SM: the
+    // tables are staged once per SM and the ring is as deep as shared memory allows, so that for
+    // decode-sized tensors every byte is requested at kernel start.  Everything else runs two
+    // CTAs of eight warps per SM with a four-stage ring.
+    int variant = grouped ? 0 : 1, warps = kWarpsPerCta, occ = 2, depth = 4;
+    if (!grouped && cmax <= 4 && !env_int("LEV_STREAM_NARROW", 0) && (size_t)kWarpsWide * kStepBytes + tb <= smem_cap) {
+        variant = 2;
+        warps = kWarpsWide;
+        occ = 1;
+    }
+    if (variant == 1 && (size_t)kWarpsPerCta * 4 * kStepBytes + tb > 110 * 1024) variant = 0;
+    // Tiles are handed to CTAs in groups whose K-steps the warps split evenly; every reduction
+    // then stays inside one CTA.  A dense call sizes the groups so that the whole tensor is one
+    // resident wave; a grouped call, whose tile count only the device knows, uses the smallest
+    // useful group and lets the CTAs stride over them.
+    const int resident = sms * occ;
+    int tpg = (int)((2 * warps + steps - 1) / steps);  // at least two K-steps per warp
+    if (!grouped && (total_tiles + resident - 1) / resident > tpg) tpg = (int)((total_tiles + resident - 1) / resident);
+    int64_t ngroups = (total_tiles + tpg - 1) / tpg;
+    int grid = (int)(ngroups < resident ? ngroups : resident);
     if (grid < 1) grid = 1;
-    const int max_warps = grid * kWarpsPerCta;
-
-    size_t fb;
-    size_t tb = lev_stream_table_bytes(w, cmax, terms, 1, &fb);
-    size_t ring = (size_t)kWarpsPerCta * kDepth * kStepBytes;
-    // stage the tables in shared memory when the call is dense and two CTAs still fit
-    bool xs = !grouped && ring + tb <= 110 * 1024;
+    if (variant == 2) {
+        int64_t per_warp = ((int64_t)tpg * steps + warps - 1) / warps;
+        int fit = (int)((smem_cap - tb) / ((size_t)warps * kStepBytes));
+        depth = (int)(per_warp < fit ? per_warp : fit);
+        depth = depth < 1 ? 1 : (depth > 4 ? 4 : depth);
+    }
+    size_t ring = (size_t)warps * depth * kStepBytes;
+    const bool xs = variant != 0;
 
     size_t fb_all;
     lev_stream_table_bytes(w, cmax, terms, J.max_jobs, &fb_all);
     StreamArgs A;
-    A.wp = (const uint4*)w->packed + (J.row0 / 16) * steps * 144;
+    A.wp = (const uint4*)w->packed + (J.row0 / 16) * steps * (kStepBytes / 16);
     A.steps_per_tile = (int)steps;
     A.tiles_per_job = (int)tiles_per_job;
-    A.max_warps = max_warps;
-    A.total_steps = (int)max_steps;
+    A.tiles_per_group = tpg;
+    A.total_tiles = (int)total_tiles;
     A.njobs_dev = J.njobs_dev;
     A.job_slice = J.job_slice;
     A.outmap = J.outmap;
@@ -830,30 +1021,21 @@ int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& 
     A.cmax = cmax;
     A.terms = terms;
     A.glt = glt;
-    A.partials = (float*)pbuf;
-    A.tile_count = (int*)counters;
+    (void)pbuf;      // reductions stay inside a CTA: the global work buffers are no longer touched
+    (void)counters;
     A.status = ctx->d_status;
     A.y = y;
     A.debug = env_int("LEV_STREAM_DEBUG", 0);
-    A.fused_prep = 0;
-    if (fused_src) {
-        if (!xs) return lev_fail(ctx, LEV_BAD_ARGUMENT, "stream schedule: tables do not fit shared memory");
-        A.fused_prep = 1;
-        A.prep = make_prep(ctx, w, *fused_src, cmax, terms, nullptr, 1);
-    } else {
-        A.prep = PrepArgs();
-    }
+    A.out_cols = J.outmap ? 0x7fffffff : cmax;
     size_t smem = ring + (xs ? tb : 0);
-    int st;
-#define LEV_PICK(T)                                                                                          \
-    (ntiles == 1 ? (xs ? launch_stream<T, 1, true>(ctx, grid, smem, A) : launch_stream<T, 1, false>(ctx, grid, smem, A)) \
-                 : (xs ? launch_stream<T, 2, true>(ctx, grid, smem, A) : launch_stream<T, 2, false>(ctx, grid, smem, A)))
-    st = w->type == LEV_GGML_Q4_K ? LEV_PICK(LEV_GGML_Q4_K) : LEV_PICK(LEV_GGML_Q4_0);
-#undef LEV_PICK
+    A.depth = depth;
+    int st = w->type == LEV_GGML_Q4_K   ? launch_stream_cmax<LEV_GGML_Q4_K>(ctx, cmax, grid, smem, A, variant)
+             : w->type == LEV_GGML_Q6_K ? launch_stream_cmax<LEV_GGML_Q6_K>(ctx, cmax, grid, smem, A, variant)
+                                        : launch_stream_cmax<LEV_GGML_Q4_0>(ctx, cmax, grid, smem, A, variant);
     if (st) return st;
     ctx->launches++;
     ctx->ev.grid = grid;
-    ctx->ev.block = kWarpsPerCta * 32;
+    ctx->ev.block = warps * 32;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_stream");
 }
 
@@ -868,12 +1050,10 @@ int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, i
     J.rows = rows;
     J.out_ld = rows;
     J.max_jobs = 1;
-    // building the tables inside every CTA is available but measured slower than the
-    // separate preparation launch, so it is opt-in
-    if (lev_stream_fuses_prepare(w, n_cols, terms) && getenv("LEV_STREAM_FUSED_PREP"))
-        return lev_stream_run(ctx, w, J, nullptr, n_cols, terms, y, &src);
     void* tables;
     LEV_TRY(lev_scratch(ctx, LEV_SCR_XPREP, lev_stream_table_bytes(w, n_cols, terms, 1, nullptr) + 256, &tables));
-    LEV_TRY(lev_stream_prepare(ctx, w, src, n_cols, terms, 1, tables));
+    const int dbg = env_int("LEV_STREAM_DEBUG", 0);  // timing aids: bit 1 no main launch, bit 2 no preparation launch
+    if (!(dbg & 4)) LEV_TRY(lev_stream_prepare(ctx, w, src, n_cols, terms, 1, tables));
+    if (dbg & 2) return LEV_OK;
     return lev_stream_run(ctx, w, J, tables, n_cols, terms, y, nullptr);
 }

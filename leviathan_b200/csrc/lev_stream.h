@@ -32,7 +32,6 @@ int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_sour
                        void* tables);
 // fused_src != NULL (dense calls whose tables fit shared memory): every CTA builds the
 // tables itself and `tables` is unused
-bool lev_stream_fuses_prepare(const lev_weights* w, int cmax, int terms);
 int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
                    int terms, float* y, const lev_stream_source* fused_src);
 void lev_stream_workspace_bytes(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, int cmax,

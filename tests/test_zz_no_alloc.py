@@ -36,11 +36,11 @@ def test_static_scratch_refuses_what_does_not_fit_or_is_not_served():
     ctx = lev.Context(0)
     lib = ctx.lib
     assert lib.lev_static_scratch_bytes() == 4 << 20
-    # Q6_K is not on the stream schedule
-    w6 = H.quantized(Q.GGML_Q6_K, 3, 16, 256)
-    h6 = ctx.upload(w6, Q.GGML_Q6_K, 16, 256)
+    # an odd row offset is not served by the stream schedule
+    w6 = H.quantized(Q.GGML_Q6_K, 3, 32, 256)
+    h6 = ctx.upload(w6, Q.GGML_Q6_K, 32, 256)
     with pytest.raises(lev.LevError) as e:
-        ctx.matvec_static_scratch(h6, torch.zeros(256, device="cuda"))
+        ctx.matvec_static_scratch(h6, torch.zeros(256, device="cuda"), row0=3, rows=16)
     assert e.value.name == "unsupported"
     h6.free()
     # eight columns of a million-wide row need 33 MB of split-activation tables
