@@ -192,8 +192,17 @@ __device__ __forceinline__ float prep_sum32(const PrepArgs& P, int job, int chun
 }
 
 // grid (chunks, jobs); one warp per 8 mma columns
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor drains.  launch_dependents lets the successor start early;
+// wait blocks until every predecessor grid has completed and its writes are visible.  Both are
+// no-ops under an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
 template <int TYPE>
 __global__ void k_prepare_x(PrepArgs P) {
+    pdl_launch_dependents();
+    pdl_wait();  // x may be the previous kernel's output, and that kernel may still read the tables
     const int chunk = blockIdx.x, job = blockIdx.y;
     if (P.njobs_dev && job >= *P.njobs_dev) return;
     const int lane = threadIdx.x & 31, nt = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
@@ -511,6 +520,8 @@ __global__ void __launch_bounds__(W * 32, OCC) k_stream(StreamArgs A) {
             if (p) bulk_load(ring_s + d * kStepBytes, p, kStepBytes, bar_s + 8 * d);
         }
     }
+    pdl_launch_dependents();
+    pdl_wait();  // the weight requests above are already in flight; the tables come from the preceding launch
     // dense calls stage the activation tables once per CTA while the first weight bytes are on their way
     const uint4* jfrag = A.frag;
     const float* jaux = A.aux;
@@ -798,6 +809,25 @@ int grid_cap(lev_ctx* ctx, int64_t work, int block, int per_sm) {
     return (int)(g < 1 ? 1 : (g > cap ? cap : g));
 }
 
+int env_int(const char* name, int fallback);
+
+// launch with the programmatic-stream-serialization attribute (see pdl_wait)
+template <class Kernel, class Args>
+cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Args& args) {
+    static const int enabled = env_int("LEV_PDL", 1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args);
+}
+
 template <int TYPE, int CMAX, bool XS, int W, int OCC>
 int launch_stream(lev_ctx* ctx, int grid, size_t smem, const StreamArgs& A) {
     static size_t configured[16] = {};  // per device: largest dynamic shared memory opted in so far
@@ -805,7 +835,7 @@ int launch_stream(lev_ctx* ctx, int grid, size_t smem, const StreamArgs& A) {
         LEV_CUDA(ctx, cudaFuncSetAttribute(k_stream<TYPE, CMAX, XS, W, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[ctx->device & 15] = smem;
     }
-    k_stream<TYPE, CMAX, XS, W, OCC><<<grid, W * 32, smem, ctx->stream>>>(A);
+    LEV_CUDA(ctx, launch_pdl(k_stream<TYPE, CMAX, XS, W, OCC>, dim3(grid), dim3(W * 32), smem, ctx->stream, A));
     return LEV_OK;
 }
 
@@ -901,9 +931,10 @@ int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_sour
     PrepArgs P = make_prep(ctx, w, src, cmax, terms, tables, jobs);
     int ntiles = (P.glt + 7) / 8;
     dim3 grid((unsigned)P.chunks, (unsigned)jobs);
-    if (w->type == LEV_GGML_Q4_K) k_prepare_x<LEV_GGML_Q4_K><<<grid, 32 * ntiles, 0, ctx->stream>>>(P);
-    else if (w->type == LEV_GGML_Q6_K) k_prepare_x<LEV_GGML_Q6_K><<<grid, 32 * ntiles, 0, ctx->stream>>>(P);
-    else k_prepare_x<LEV_GGML_Q4_0><<<grid, 32 * ntiles, 0, ctx->stream>>>(P);
+    dim3 block(32 * ntiles);
+    if (w->type == LEV_GGML_Q4_K) LEV_CUDA(ctx, launch_pdl(k_prepare_x<LEV_GGML_Q4_K>, grid, block, 0, ctx->stream, P));
+    else if (w->type == LEV_GGML_Q6_K) LEV_CUDA(ctx, launch_pdl(k_prepare_x<LEV_GGML_Q6_K>, grid, block, 0, ctx->stream, P));
+    else LEV_CUDA(ctx, launch_pdl(k_prepare_x<LEV_GGML_Q4_0>, grid, block, 0, ctx->stream, P));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_prepare_x");
 }
