@@ -40,6 +40,10 @@ DOWN_BYTES = HIDDEN * (FFN // 256) * 210      # 41,287,680
 VEC_BYTES = 4 * (HIDDEN + 2 * FFN + FFN + HIDDEN)  # x, gate out, up out, down in, down out
 STEP_BYTES = 2 * GATE_BYTES + DOWN_BYTES + VEC_BYTES  # 98,091,008
 SEED = 0x4C455649
+# dram__bytes_read + dram__bytes_write of one Q4_K 12288x4096 stream launch, from the ncu
+# capture summarised in profiles/k_stream_q4k_q6k_full_capture.txt
+Q4K_DRAM_TRAFFIC = 28_353_536
+Q6K_DRAM_TRAFFIC = 41_376_512
 
 
 def _peaks():
@@ -63,7 +67,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.device)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
@@ -165,7 +169,7 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "Q4/Q6 matvec HBM GB/s", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
         "config": {"workload": "ffn_matvec_set_b1", "gate_up": "Q4_K 12288x4096 x2", "down": "Q6_K 4096x12288",
                    "columns": 1, "bytes_per_step": STEP_BYTES},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
@@ -349,11 +353,11 @@ def run_gpu(args):
                        "sharding": "independent FFN instances per rank, no collective"},
             "roofline": {"bound": "hbm", "kernel": ctx.last_evidence()["kernel_name"] + ":q4_k",
                          "achieved": ach, "peak": peaks["hbm_gbs"], "peak_source": peak_kind, "unit": "GB/s",
-                         "frac": ach / peaks["hbm_gbs"], "traffic": None, "us_per_launch": k_q4k_ms * 1e3,
+                         "frac": ach / peaks["hbm_gbs"], "traffic": Q4K_DRAM_TRAFFIC, "us_per_launch": k_q4k_ms * 1e3,
                          "algorithmic_bytes_per_launch": q4k_bytes,
                          "q6_k": {"achieved": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9, "us_per_launch": k_q6k_ms * 1e3,
                                   "frac": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                  "algorithmic_bytes_per_launch": q6k_bytes}},
+                                  "algorithmic_bytes_per_launch": q6k_bytes, "traffic": Q6K_DRAM_TRAFFIC}},
             "e2e": {"value": world * STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * (HIDDEN + HIDDEN + FFN), "d2h_bytes_per_step": 4 * (FFN + FFN + HIDDEN)},
             "gpu_launches": launches_per_step * args.steps * reps,
@@ -375,7 +379,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--reps", type=int, default=11)
+    ap.add_argument("--reps", type=int, default=31)
     ap.add_argument("--instances", type=int, default=8)
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu", action="store_true")
