@@ -1,0 +1,319 @@
+// Device code shared by the stream-schedule kernels: tensor-core fragment helpers, the exact
+// fp16 split of activations, bulk-copy / mbarrier wrappers with bounded waits, programmatic
+// dependent launch, and the arithmetic of one K-step for the three block formats.
+#pragma once
+#include <cuda_fp16.h>
+#include <stdlib.h>
+
+#include "lev_internal.h"
+
+namespace {
+
+constexpr float kHiScale = 0.0625f;  // activations of k-slots fed by nibbles at bits 4..7
+constexpr int kStepBytesQ4 = 2304;  // one K-step of a 16-row tile: Q4_K block / four Q4_0 chunks
+constexpr int kStepBytesQ6 = 3360;  // one Q6_K block of 16 rows
+__host__ __device__ constexpr int step_bytes(int type) { return type == LEV_GGML_Q6_K ? kStepBytesQ6 : kStepBytesQ4; }
+constexpr int kWarpsPerCta = 8;   // grouped and large calls
+constexpr int kWarpsWide = 24;    // dense calls: one CTA per SM
+constexpr unsigned kWaitPolls = 1u << 24;  // bound of every mbarrier wait
+
+__device__ __forceinline__ void mma16816(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void mma16816_z(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3, unsigned b0,
+                                           unsigned b1) {
+    // zero accumulator input: lets the compiler use the zero register for C
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};\n"
+        : "=f"(d[0]), "=f"(d[1]), "=f"(d[2]), "=f"(d[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+
+__device__ __forceinline__ float h2f_bits(unsigned bits) {
+    return __half2float(__ushort_as_half((unsigned short)bits));
+}
+// float(byte k of w) without the conversion unit: 2^23 + byte, minus 2^23
+__device__ __forceinline__ float byte_to_float(unsigned w, unsigned k) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u + k)) - 8388608.0f;
+}
+
+// ---------------------------------------------------------------------------
+// activation preparation
+// ---------------------------------------------------------------------------
+// Column element of k-slot pair for lane t, mma m (0..3), register r (0: b0,
+// 1: b1), half h (0, 1) inside a 64-column chunk.
+//   Q4_K: bytes 8t..8t+7 of the chunk's 32 bytes; mma 0,1 take low nibbles
+//         (columns = byte index), mma 2,3 high nibbles (columns 32 + byte).
+//   Q4_0: the chunk is two 32-value blocks; bytes 4t..4t+3 of each block;
+//         mma 0,1 = block 0 low / high nibbles, mma 2,3 = block 1.
+//   Q6_K: mma m covers the 16-value sub-block 4*chunk + m; lane t holds its elements
+//         4t..4t+3 (register r, half h -> element 4t + 2r + h); mma 2,3 use levels
+//         stored 16x (in bits 4..9), so their activations are pre-divided by 16.
+template <int TYPE>
+__device__ __forceinline__ int chunk_col(int t, int m, int r, int h) {
+    if (TYPE == LEV_GGML_Q4_K) return (m >> 1) * 32 + 8 * t + 4 * (m & 1) + r + 2 * h;
+    if (TYPE == LEV_GGML_Q6_K) return 16 * m + 4 * t + 2 * r + h;
+    return (m >> 1) * 32 + (m & 1) * 16 + 4 * t + r + 2 * h;
+}
+template <int TYPE>
+__device__ __forceinline__ bool chunk_hi(int m) {
+    return TYPE == LEV_GGML_Q4_0 ? (m & 1) : (m >> 1);
+}
+
+// term `term` of the exact fp16 split of v: v = h0 + h1*2^-11 + h2*2^-22.
+// The 1/16 of the high-nibble slots is applied BEFORE the split so that every
+// term is exactly representable even when it lands in the fp16 subnormals.
+__device__ __forceinline__ float split_term(float v, int term) {
+    float h0 = __half2float(__float2half_rn(v));
+    if (term == 0) return h0;
+    float r1 = (v - h0) * 2048.0f;
+    float h1 = __half2float(__float2half_rn(r1));
+    if (term == 1) return h1;
+    return __half2float(__float2half_rn((r1 - h1) * 2048.0f));
+}
+
+// gelu_tanh(gate) * up in f32 exactly as the reference kernel states it
+// (Sources/LeviathanCore/Gemma4.swift:4364-4377): tanh through exp(-2|x|)
+__device__ __forceinline__ float gelu_tanh_up(float g, float u) {
+    float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    float e = expf(-2.0f * fabsf(inner));
+    float th = copysignf((1.0f - e) / (1.0f + e), inner);
+    float gelu = 0.5f * g * (1.0f + th);
+    return gelu * u;
+}
+
+// Programmatic dependent launch: a kernel launched with the stream-serialization attribute may
+// start while its predecessor drains.  launch_dependents lets the successor start early;
+// wait blocks until every predecessor grid has completed and its writes are visible.  Both are
+// no-ops under an ordinary launch.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;\n"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
+// bounded wait: false when the phase did not complete within kWaitPolls polls
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
+    for (unsigned i = 0; i < kWaitPolls; i++) {
+        unsigned ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+// CMAX: activation columns per job (compile time, so that every table index
+// is a constant multiple); XS: the tables of the (single) job are staged in
+// shared memory; OCC: CTAs per SM the register budget is sized for.
+template <int CMAX>
+struct StreamDims {
+    static constexpr int kTerms = 2;
+    static constexpr int kGlt = CMAX * kTerms;        // live mma columns
+    static constexpr int kNT = (kGlt + 7) / 8;        // n-tiles of 8 columns
+};
+
+
+// Per-lane table offsets of a kernel instance.  A chunk's fragments are [GLT columns][4 t] x 32 B,
+// so lane (g, t) of n-tile nt reads entry nt*32 + lane; lanes beyond the live columns read a valid
+// entry whose values land in accumulator columns nobody reads.
+template <int CMAX>
+struct LaneOffsets {
+    static constexpr int NT = StreamDims<CMAX>::kNT, GLT = StreamDims<CMAX>::kGlt;
+    int xoff[NT], boff0[NT], boff1[NT];
+    __device__ __forceinline__ void init(int lane) {
+        const int t = lane & 3;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            int e = nt * 32 + lane;
+            xoff[nt] = (e < GLT * 4 ? e : lane % (GLT * 4 < 32 ? GLT * 4 : 32)) * 2;
+            int c0 = nt * 8 + 2 * t;  // Q4_0 / Q6_K: columns 2t, 2t+1 of the bias rows, clamped the same way
+            boff0[nt] = c0 < GLT ? c0 : 0;
+            boff1[nt] = c0 + 1 < GLT ? c0 + 1 : 0;
+        }
+    }
+};
+
+// The arithmetic of one K-step: `st` is the step's bytes in shared memory, `xchunk` / `achunk` the
+// activation fragments and auxiliary sums of the step's four chunks (SM: in shared memory, else
+// global and read through the read-only path).  Adds into yacc (per mma column) and, for Q4_K,
+// into the min-term sums mina / minb (rows g / g+8, per activation column).
+template <int TYPE, int CMAX, bool SM>
+__device__ __forceinline__ void stream_step(const uint4* st, const uint4* xchunk, const float* achunk, int lane,
+                                            const LaneOffsets<CMAX>& O, float (*yacc)[4], float* mina, float* minb) {
+    using D = StreamDims<CMAX>;
+    constexpr int NT = D::kNT, GLT = D::kGlt;
+    constexpr bool XS = SM;
+    const int g = lane >> 2, t = lane & 3;
+    const int* xoff = O.xoff;
+    const int* boff0 = O.boff0;
+    const int* boff1 = O.boff1;
+    (void)g; (void)t; (void)boff0; (void)boff1; (void)mina; (void)minb;
+if (TYPE == LEV_GGML_Q4_K) {
+    const uint4 h0 = st[g], h1 = st[8 + g];
+    // 6-bit scales of the 8 sub-blocks of rows g (h0) and g+8 (h1), four per word
+    // (rust/crates/lev-cpu/src/lib.rs:64-74)
+    const unsigned sa_lo = h0.y & 0x3F3F3F3Fu, sa_hi = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
+    const unsigned sb_lo = h1.y & 0x3F3F3F3Fu, sb_hi = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
+    const float dA = h2f_bits(h0.x & 0xffffu) * 16777216.0f, dB = h2f_bits(h1.x & 0xffffu) * 16777216.0f;  // d * 2^24
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint4 q = st[16 + c * 32 + lane];
+        const unsigned sa = c < 2 ? sa_lo : sa_hi, sb = c < 2 ? sb_lo : sb_hi;
+        const float sA_lo = dA * byte_to_float(sa, 2 * (c & 1)), sA_hi = dA * byte_to_float(sa, 2 * (c & 1) + 1);
+        const float sB_lo = dB * byte_to_float(sb, 2 * (c & 1)), sB_hi = dB * byte_to_float(sb, 2 * (c & 1) + 1);
+        const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+        const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const uint4* xp = xchunk + c * (GLT * 8) + xoff[nt];
+            const uint4 x0 = XS ? xp[0] : __ldg(xp), x1 = XS ? xp[1] : __ldg(xp + 1);
+            float lo[4], hi[4];
+            mma16816_z(lo, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
+            mma16816(lo, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x0.z, x0.w);
+            mma16816_z(hi, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x1.x, x1.y);
+            mma16816(hi, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1.z, x1.w);
+            yacc[nt][0] = fmaf(sA_lo, lo[0], fmaf(sA_hi, hi[0], yacc[nt][0]));
+            yacc[nt][1] = fmaf(sA_lo, lo[1], fmaf(sA_hi, hi[1], yacc[nt][1]));
+            yacc[nt][2] = fmaf(sB_lo, lo[2], fmaf(sB_hi, hi[2], yacc[nt][2]));
+            yacc[nt][3] = fmaf(sB_lo, lo[3], fmaf(sB_hi, hi[3], yacc[nt][3]));
+        }
+    }
+    // min term: this lane owns sub-blocks 2t, 2t+1 of its two rows
+    const unsigned ma = t < 2 ? (h0.z & 0x3F3F3F3Fu) : (((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u));
+    const unsigned mb = t < 2 ? (h1.z & 0x3F3F3F3Fu) : (((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u));
+    const unsigned mab = t & 1 ? (ma >> 16) : ma, mbb = t & 1 ? (mb >> 16) : mb;
+    const float dminA = h2f_bits(h0.x >> 16), dminB = h2f_bits(h1.x >> 16);
+    const float mA0 = dminA * byte_to_float(mab, 0), mA1 = dminA * byte_to_float(mab, 1);
+    const float mB0 = dminB * byte_to_float(mbb, 0), mB1 = dminB * byte_to_float(mbb, 1);
+    const float* sx0 = achunk + 2 * t * CMAX;  // sums of sub-blocks 2t, 2t+1: [sub-block][CMAX]
+#pragma unroll
+    for (int c = 0; c < CMAX; c++) {
+        const float x0 = XS ? sx0[c] : __ldg(sx0 + c), x1 = XS ? sx0[CMAX + c] : __ldg(sx0 + CMAX + c);
+        mina[c] = fmaf(mA0, x0, fmaf(mA1, x1, mina[c]));
+        minb[c] = fmaf(mB0, x0, fmaf(mB1, x1, minb[c]));
+    }
+} else if (TYPE == LEV_GGML_Q6_K) {
+    // int8 scales of the 16 sub-blocks of rows g and g+8, fp16 d of both rows
+    const uint4 sa4 = st[g], sb4 = st[8 + g];
+    const unsigned short* dp = reinterpret_cast<const unsigned short*>(st + 16);
+    const float dA = h2f_bits(dp[g]) * 16777216.0f, dB = h2f_bits(dp[g + 8]) * 16777216.0f;  // d * 2^24
+    const unsigned scA[4] = {sa4.x, sa4.y, sa4.z, sa4.w}, scB[4] = {sb4.x, sb4.y, sb4.z, sb4.w};
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint4 q = st[18 + c * 32 + lane];
+        const uint2 hq = reinterpret_cast<const uint2*>(st + 146)[c * 32 + lane];
+        // row g: words q.x, q.y + high bits hq.x ; row g+8: q.z, q.w + hq.y
+        const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+        const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+        const unsigned ha = hq.x, hb = hq.y;
+        // the 2-bit fields, shifted so that each register's pair lands on bits 4,5 / 20,21
+        // (low-nibble registers) or 8,9 / 24,25 (high-nibble registers)
+        const unsigned ha_r2 = ha >> 2, ha_l2 = ha << 2, ha_l4 = ha << 4, ha_r4 = ha >> 4, ha_r6 = ha >> 6;
+        const unsigned hb_r2 = hb >> 2, hb_l2 = hb << 2, hb_l4 = hb << 4, hb_r4 = hb >> 4, hb_r6 = hb >> 6;
+        // A fragments {row g k-lo, row g+8 k-lo, row g k-hi, row g+8 k-hi} of the four sub-blocks
+        const unsigned a[4][4] = {
+            {(w0 & 0x000F000Fu) | (ha & 0x00300030u), (w2 & 0x000F000Fu) | (hb & 0x00300030u),
+             (w0s & 0x000F000Fu) | (ha_r2 & 0x00300030u), (w2s & 0x000F000Fu) | (hb_r2 & 0x00300030u)},
+            {(w1 & 0x000F000Fu) | (ha_l2 & 0x00300030u), (w3 & 0x000F000Fu) | (hb_l2 & 0x00300030u),
+             (w1s & 0x000F000Fu) | (ha_l4 & 0x00300030u), (w3s & 0x000F000Fu) | (hb_l4 & 0x00300030u)},
+            {(w0 & 0x00F000F0u) | (ha & 0x03000300u), (w2 & 0x00F000F0u) | (hb & 0x03000300u),
+             (w0s & 0x00F000F0u) | (ha_r2 & 0x03000300u), (w2s & 0x00F000F0u) | (hb_r2 & 0x03000300u)},
+            {(w1 & 0x00F000F0u) | (ha_r4 & 0x03000300u), (w3 & 0x00F000F0u) | (hb_r4 & 0x03000300u),
+             (w1s & 0x00F000F0u) | (ha_r6 & 0x03000300u), (w3s & 0x00F000F0u) | (hb_r6 & 0x03000300u)}};
+        const float* bchunk = achunk + c * (4 * GLT);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const uint4* xp = xchunk + c * (GLT * 8) + xoff[nt];
+            const uint4 x0 = XS ? xp[0] : __ldg(xp), x1 = XS ? xp[1] : __ldg(xp + 1);
+            const unsigned xb[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+#pragma unroll
+            for (int m = 0; m < 4; m++) {
+                // accumulator starts at -32 * 2^-24 * (sum of the sub-block's activations)
+                const float k0 = XS ? bchunk[m * GLT + boff0[nt]] : __ldg(bchunk + m * GLT + boff0[nt]);
+                const float k1 = XS ? bchunk[m * GLT + boff1[nt]] : __ldg(bchunk + m * GLT + boff1[nt]);
+                float acc[4] = {k0, k1, k0, k1};
+                mma16816(acc, a[m][0], a[m][1], a[m][2], a[m][3], xb[2 * m], xb[2 * m + 1]);
+                const float sA = dA * (float)(int)(signed char)(scA[c] >> (8 * m));
+                const float sB = dB * (float)(int)(signed char)(scB[c] >> (8 * m));
+                yacc[nt][0] = fmaf(sA, acc[0], yacc[nt][0]);
+                yacc[nt][1] = fmaf(sA, acc[1], yacc[nt][1]);
+                yacc[nt][2] = fmaf(sB, acc[2], yacc[nt][2]);
+                yacc[nt][3] = fmaf(sB, acc[3], yacc[nt][3]);
+            }
+        }
+    }
+} else {
+#pragma unroll
+    for (int c = 0; c < 4; c++) {
+        const uint2 sc = reinterpret_cast<const uint2*>(st + c * 36)[g];
+        const uint4 q = st[c * 36 + 4 + lane];
+        // d * 2^24 for (row g, blk0), (row g, blk1), (row g+8, blk0), (row g+8, blk1)
+        const float dA0 = h2f_bits(sc.x & 0xffffu) * 16777216.0f, dA1 = h2f_bits(sc.x >> 16) * 16777216.0f;
+        const float dB0 = h2f_bits(sc.y & 0xffffu) * 16777216.0f, dB1 = h2f_bits(sc.y >> 16) * 16777216.0f;
+        const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+        const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+        const float* bchunk = achunk + c * (2 * GLT);
+#pragma unroll
+        for (int nt = 0; nt < NT; nt++) {
+            const uint4* xp = xchunk + c * (GLT * 8) + xoff[nt];
+            const uint4 x0 = XS ? xp[0] : __ldg(xp), x1 = XS ? xp[1] : __ldg(xp + 1);
+            // accumulators start at -8 * 2^-24 * (sum of the block's activations)
+            const float k00 = XS ? bchunk[boff0[nt]] : __ldg(bchunk + boff0[nt]);
+            const float k01 = XS ? bchunk[boff1[nt]] : __ldg(bchunk + boff1[nt]);
+            const float k10 = XS ? bchunk[GLT + boff0[nt]] : __ldg(bchunk + GLT + boff0[nt]);
+            const float k11 = XS ? bchunk[GLT + boff1[nt]] : __ldg(bchunk + GLT + boff1[nt]);
+            float a0[4] = {k00, k01, k00, k01}, a1[4] = {k10, k11, k10, k11};
+            mma16816(a0, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
+            mma16816(a0, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x0.z, x0.w);
+            mma16816(a1, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x1.x, x1.y);
+            mma16816(a1, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1.z, x1.w);
+            yacc[nt][0] = fmaf(dA0, a0[0], fmaf(dA1, a1[0], yacc[nt][0]));
+            yacc[nt][1] = fmaf(dA0, a0[1], fmaf(dA1, a1[1], yacc[nt][1]));
+            yacc[nt][2] = fmaf(dB0, a0[2], fmaf(dB1, a1[2], yacc[nt][2]));
+            yacc[nt][3] = fmaf(dB0, a0[3], fmaf(dB1, a1[3], yacc[nt][3]));
+        }
+    }
+}
+}
+
+int env_int(const char* name, int fallback);
+
+// launch with the programmatic-stream-serialization attribute (see pdl_wait)
+template <class Kernel, class Args>
+cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Args& args) {
+    static const int enabled = env_int("LEV_PDL", 1);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = enabled ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kernel, args);
+}
+
+inline int env_int(const char* name, int fallback) {
+    const char* v = getenv(name);
+    return v && *v ? atoi(v) : fallback;
+}
+
+}  // namespace
