@@ -21,6 +21,14 @@ namespace {
 
 constexpr int kMaxDepth = 8;
 
+#ifdef LEV_TIMELINE
+// development aid (not compiled into the product): per-warp clock stamps of the last launch
+__device__ long long lev_tl[160][24][32];
+#define TL(i) do { if (lane == 0 && (i) < 32) lev_tl[blockIdx.x][warp][(i)] = clock64(); } while (0)
+#else
+#define TL(i) do {} while (0)
+#endif
+
 struct DenseArgs {
     const uint4* wp;   // first tile of the call
     int spt;           // K-steps per tile
@@ -35,6 +43,7 @@ struct DenseArgs {
     int64_t rows, out_ld;
     int* status;
     int depth;         // ring stages per warp
+    int sps;           // K-steps per stage
     int debug;         // bit 0: skip the arithmetic
 };
 
@@ -46,9 +55,8 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     constexpr int kAuxPerChunk = TYPE == LEV_GGML_Q4_K ? 2 * CMAX : (TYPE == LEV_GGML_Q6_K ? 4 * GLT : 2 * GLT);
     static_assert(W % 4 == 0 && TERMS == 2, "warps are dealt to the four schedulers in equal shares");
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ __align__(8) unsigned long long bars[W][kMaxDepth];
+    __shared__ __align__(8) unsigned long long bars[W][kMaxDepth];  // stage filled (bulk copy landed)
     __shared__ float rec[W][2][CMAX][16];  // partial sums of tiles a warp shares with its neighbours
-    __shared__ int rec_tile[W][2];         // CTA-local tile of each record, -1 = none
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     // logical position of this warp in the CTA's run: warps of one scheduler (warp % 4) are
     // neighbours, so shares that differ by one step spread evenly over the schedulers
@@ -60,105 +68,142 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     const int nst = ntiles * spt;
     const int s = (int)((int64_t)nst * lw / W), e = (int)((int64_t)nst * (lw + 1) / W);
 
-    unsigned char* ring = smem_raw + (size_t)warp * depth * kStepBytes;
+    TL(0);
+    const int sps = A.sps;  // K-steps per ring stage (one bulk copy, one barrier wait)
+    const unsigned stage_bytes = (unsigned)sps * kStepBytes;
+
+    unsigned char* ring = smem_raw + (size_t)warp * depth * stage_bytes;
     const unsigned ring_s = smem_u32(ring), bar_s = smem_u32(&bars[warp][0]);
+    // fetch side (lane 0): this warp's share is one contiguous byte range
     const unsigned char* f_ptr = reinterpret_cast<const unsigned char*>(A.wp) + ((int64_t)tile0 * spt + s) * kStepBytes;
-    int f_left = e - s;
-    if (lane < 2) rec_tile[warp][lane] = -1;
+    int f_left = e - s;  // K-steps not yet requested
     if (lane == 0) {
         for (int d = 0; d < depth; d++) mbar_init(bar_s + 8 * d, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        for (int d = 0; d < depth && f_left > 0; d++, f_left--, f_ptr += kStepBytes)
-            bulk_load(ring_s + d * kStepBytes, f_ptr, kStepBytes, bar_s + 8 * d);
+        for (int d = 0; d < depth && f_left > 0; d++) {
+            const int n = f_left < sps ? f_left : sps;
+            bulk_load(ring_s + d * stage_bytes, f_ptr, n * kStepBytes, bar_s + 8 * d);
+            f_ptr += n * kStepBytes;
+            f_left -= n;
+        }
     }
+    LaneOffsets<CMAX> O;
+    O.init(lane);
+    int tl = s / spt;    // CTA-local tile
+    int k = s - tl * spt;
+    TL(1);
     pdl_launch_dependents();
     pdl_wait();  // weights are immutable and already on their way; x and y belong to the launches before
 
+    TL(2);
     // ---- activation tables, built by every CTA for itself ----
-    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)W * depth * kStepBytes);
+    // One item = (chunk, activation column, lane-of-quad tt): the 16 activations that feed lane
+    // tt's B fragments of the chunk's four mma, both split terms.
+    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)W * depth * stage_bytes);
     float* sa = reinterpret_cast<float*>(xs + A.chunks * GLT * 8);
     {
-        const int entries = A.chunks * GLT * 4, rounded = (entries + 31) & ~31;
+        const int items = A.chunks * CMAX * 4;  // a multiple of 4: quads stay whole
         bool bad = false;
-        for (int idx = threadIdx.x; idx < rounded; idx += W * 32) {
-            const bool live = idx < entries;
-            const int ii = live ? idx : entries - 1;
-            const int chunk = ii / (GLT * 4), rem = ii - chunk * (GLT * 4), col = rem >> 2, tt = rem & 3;
-            const int c = col >> 1, term = col & 1;
-            const float* xr = A.x + (int64_t)(c < A.n_cols ? c : 0) * A.x_ld;
+        for (int idx0 = warp * 32; idx0 < items; idx0 += W * 32) {
+            const int idx = idx0 + lane;
+            const bool live = idx < items;
+            const int ii = live ? idx : items - 1;
+            const int chunk = ii / (CMAX * 4), rem = ii - chunk * (CMAX * 4), c = rem >> 2, tt = rem & 3;
+            const bool has = c < A.n_cols;
+            const float* xr = A.x + (int64_t)(has ? c : 0) * A.x_ld;
+            // the four elements of one mma are consecutive in x (component r + 2h, Q6_K: 2r + h)
             float xv[4][2][2];
 #pragma unroll
-            for (int m = 0; m < 4; m++)
+            for (int m = 0; m < 4; m++) {
+                const int el = chunk * 64 + chunk_col<TYPE>(tt, m, 0, 0);
+                const float4 v = __ldg(reinterpret_cast<const float4*>(xr + (el < A.cols ? el : 0)));
+                const bool in = el < A.cols && has;
+                const float q[4] = {in ? v.x : 0.f, in ? v.y : 0.f, in ? v.z : 0.f, in ? v.w : 0.f};
 #pragma unroll
                 for (int r = 0; r < 2; r++)
 #pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const int el = chunk * 64 + chunk_col<TYPE>(tt, m, r, h);
-                        const float v = __ldg(xr + (el < A.cols ? el : 0));
-                        xv[m][r][h] = (el < A.cols && c < A.n_cols) ? v : 0.f;
-                    }
-            unsigned regs[8];
-            float seen[4];  // what the tensor core sees of each mma's four elements, summed
-            float plain[2] = {0.f, 0.f};
+                    for (int h = 0; h < 2; h++) xv[m][r][h] = q[chunk_col<TYPE>(tt, m, r, h) - chunk_col<TYPE>(tt, m, 0, 0)];
+            }
+            unsigned r0[8], r1[8];         // fragment registers of term 0 / term 1
+            float seen0[4], seen1[4];      // what the tensor core sees of each mma's four elements, summed
+            float plain[2] = {0.f, 0.f};   // true activations of the chunk's two halves
 #pragma unroll
             for (int m = 0; m < 4; m++) {
-                seen[m] = 0.f;
+                seen0[m] = seen1[m] = 0.f;
 #pragma unroll
                 for (int r = 0; r < 2; r++) {
-                    float v[2];
-#pragma unroll
-                    for (int h = 0; h < 2; h++) {
-                        const float sv = split_term(chunk_hi<TYPE>(m) ? xv[m][r][h] * kHiScale : xv[m][r][h], term);
-                        bad |= !isfinite(sv);
-                        v[h] = sv;
-                        seen[m] += chunk_hi<TYPE>(m) ? 16.0f * sv : sv;
-                        plain[m >> 1] += xv[m][r][h];
-                    }
-                    __half2 hv = __floats2half2_rn(v[0], v[1]);
-                    regs[m * 2 + r] = *reinterpret_cast<unsigned*>(&hv);
+                    const float sc = chunk_hi<TYPE>(m) ? kHiScale : 1.0f;
+                    const float v0 = xv[m][r][0] * sc, v1 = xv[m][r][1] * sc;
+                    // x = h0 + h1 * 2^-11, both exactly representable in fp16
+                    const __half2 p0 = __floats2half2_rn(v0, v1);
+                    const float2 f0 = __half22float2(p0);
+                    const __half2 p1 = __floats2half2_rn((v0 - f0.x) * 2048.0f, (v1 - f0.y) * 2048.0f);
+                    const float2 f1 = __half22float2(p1);
+                    bad |= !isfinite(f0.x) | !isfinite(f0.y);
+                    r0[m * 2 + r] = *reinterpret_cast<const unsigned*>(&p0);
+                    r1[m * 2 + r] = *reinterpret_cast<const unsigned*>(&p1);
+                    seen0[m] += f0.x + f0.y;
+                    seen1[m] += f1.x + f1.y;
+                    plain[m >> 1] += xv[m][r][0] + xv[m][r][1];
                 }
             }
             if (live) {
-                xs[ii * 2] = make_uint4(regs[0], regs[1], regs[2], regs[3]);
-                xs[ii * 2 + 1] = make_uint4(regs[4], regs[5], regs[6], regs[7]);
+                uint4* e0 = xs + (((chunk * GLT + 2 * c) * 4 + tt) * 2);
+                e0[0] = make_uint4(r0[0], r0[1], r0[2], r0[3]);
+                e0[1] = make_uint4(r0[4], r0[5], r0[6], r0[7]);
+                e0[8] = make_uint4(r1[0], r1[1], r1[2], r1[3]);  // column 2c+1: four lanes x two units further
+                e0[9] = make_uint4(r1[4], r1[5], r1[6], r1[7]);
             }
             // sums over the quad (the four tt of one chunk and column)
             if (TYPE == LEV_GGML_Q4_K) {
-                // true activations of the chunk's two 32-value sub-blocks
 #pragma unroll
                 for (int hf = 0; hf < 2; hf++) {
                     float v = plain[hf];
                     v += __shfl_xor_sync(0xffffffffu, v, 1);
                     v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    if (live && tt == 0 && term == 0) sa[(chunk * 2 + hf) * CMAX + c] = v;
+                    if (live && tt == 0) sa[(chunk * 2 + hf) * CMAX + c] = v;
                 }
             } else if (TYPE == LEV_GGML_Q6_K) {
-                // -32 * 2^-24 * (sum seen by the tensor core) of each 16-value sub-block
+                // -32 * 2^-24 * (sum seen by the tensor core) of each 16-value sub-block; levels of
+                // mma 2, 3 sit 16x high against activations divided by 16
 #pragma unroll
                 for (int m = 0; m < 4; m++) {
-                    float v = seen[m];
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    if (live && tt == 0) sa[(chunk * 4 + m) * GLT + col] = -32.0f * 5.9604644775390625e-08f * v;
+                    const float k = (chunk_hi<TYPE>(m) ? 16.0f : 1.0f) * -32.0f * 5.9604644775390625e-08f;
+                    float v0 = seen0[m], v1 = seen1[m];
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+                    if (live && tt == 0) {
+                        sa[(chunk * 4 + m) * GLT + 2 * c] = k * v0;
+                        sa[(chunk * 4 + m) * GLT + 2 * c + 1] = k * v1;
+                    }
                 }
             } else {
-                // -8 * 2^-24 * (sum seen by the tensor core) of each 32-value block
+                // -8 * 2^-24 * (sum seen by the tensor core) of each 32-value block (mma 2b: low
+                // nibbles, mma 2b+1: high nibbles, worth 16x against activations divided by 16)
 #pragma unroll
                 for (int blk = 0; blk < 2; blk++) {
-                    float v = seen[2 * blk] + seen[2 * blk + 1];
-                    v += __shfl_xor_sync(0xffffffffu, v, 1);
-                    v += __shfl_xor_sync(0xffffffffu, v, 2);
-                    if (live && tt == 0) sa[(chunk * 2 + blk) * GLT + col] = -8.0f * 5.9604644775390625e-08f * v;
+                    const float k = -8.0f * 5.9604644775390625e-08f;
+                    float v0 = seen0[2 * blk] + 16.0f * seen0[2 * blk + 1], v1 = seen1[2 * blk] + 16.0f * seen1[2 * blk + 1];
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 1);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 1);
+                    v0 += __shfl_xor_sync(0xffffffffu, v0, 2);
+                    v1 += __shfl_xor_sync(0xffffffffu, v1, 2);
+                    if (live && tt == 0) {
+                        sa[(chunk * 2 + blk) * GLT + 2 * c] = k * v0;
+                        sa[(chunk * 2 + blk) * GLT + 2 * c + 1] = k * v1;
+                    }
                 }
             }
         }
         if (bad) atomicOr(A.status, LEV_DEV_NONFINITE_INPUT);
     }
+    TL(3);
     __syncthreads();
+    TL(4);
 
-    LaneOffsets<CMAX> O;
-    O.init(lane);
     float yacc[NT][4];
     float mina[CMAX], minb[CMAX];
 #pragma unroll
@@ -168,103 +213,113 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
 #pragma unroll
     for (int c = 0; c < CMAX; c++) mina[c] = minb[c] = 0.f;
 
-    int slot = 0;        // ring stage of the next K-step
+    int slot = 0;        // ring stage in use
     unsigned phase = 0;  // its mbarrier phase parity
-    int tl = s / spt;    // CTA-local tile
-    int k = s - tl * spt;
     int seg_k0 = k;
     const int first_tl = tl;
-    for (int i = s; i < e; i++) {
+    for (int i0 = s; i0 < e; i0 += sps) {
         if (!mbar_wait(bar_s + 8 * slot, phase)) {
             if (lane == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
             break;
         }
-        const uint4* st = reinterpret_cast<const uint4*>(ring + slot * kStepBytes);
-        if (!(A.debug & 1))
-            stream_step<TYPE, CMAX, true>(st, xs + k * (4 * GLT * 8), sa + k * (4 * kAuxPerChunk), lane, O, yacc, mina, minb);
+        const int i1 = i0 + sps < e ? i0 + sps : e;
+        for (int i = i0; i < i1; i++) {
+            TL(5 + 2 * (i - s));
+            const uint4* st = reinterpret_cast<const uint4*>(ring + slot * stage_bytes + (i - i0) * kStepBytes);
+            if (!(A.debug & 1))
+                stream_step<TYPE, CMAX, true>(st, xs + k * (4 * GLT * 8), sa + k * (4 * kAuxPerChunk), lane, O, yacc, mina, minb);
+            TL(6 + 2 * (i - s));
+            k++;
+            if (k == spt || i == e - 1) {
+                // ---- this warp's segment of the tile ends: fold to one f32 per (row, column) ----
+                const bool whole = seg_k0 == 0 && k == spt;
+                const int r = tl == first_tl ? 0 : 1;
+#pragma unroll
+                for (int c = 0; c < CMAX; c++) {
+                    float va = 0.f, vb = 0.f;
+#pragma unroll
+                    for (int term = 0; term < TERMS; term++) {
+                        constexpr float kScale[2] = {1.0f, 4.8828125e-4f};  // 2^0, 2^-11
+                        const int col = c * TERMS + term, nt = col / 8, jj = col & 1;
+                        const bool mine = t == (col % 8) / 2;
+                        va = fmaf(mine ? yacc[nt][jj] : 0.f, kScale[term], va);
+                        vb = fmaf(mine ? yacc[nt][2 + jj] : 0.f, kScale[term], vb);
+                    }
+                    if (TYPE == LEV_GGML_Q4_K) {
+                        va -= mina[c];
+                        vb -= minb[c];
+                    }
+                    va += __shfl_xor_sync(0xffffffffu, va, 1);
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 1);
+                    va += __shfl_xor_sync(0xffffffffu, va, 2);
+                    vb += __shfl_xor_sync(0xffffffffu, vb, 2);
+                    if (t == 0) {
+                        if (whole) {
+                            const int64_t row = (int64_t)(tile0 + tl) * 16 + g;
+                            if (c < A.n_cols) {
+                                if (row < A.rows) A.y[(int64_t)c * A.out_ld + row] = va;
+                                if (row + 8 < A.rows) A.y[(int64_t)c * A.out_ld + row + 8] = vb;
+                            }
+                        } else {
+                            rec[warp][r][c][g] = va;
+                            rec[warp][r][c][g + 8] = vb;
+                        }
+                    }
+                }
+#pragma unroll
+                for (int nt = 0; nt < NT; nt++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
+#pragma unroll
+                for (int c = 0; c < CMAX; c++) mina[c] = minb[c] = 0.f;
+                tl++;
+                k = 0;
+                seg_k0 = 0;
+            }
+        }
         // every lane has consumed its shared-memory reads of this stage: refill it
         __syncwarp();
         if (lane == 0 && f_left > 0) {
-            bulk_load(ring_s + slot * kStepBytes, f_ptr, kStepBytes, bar_s + 8 * slot);
-            f_ptr += kStepBytes;
-            f_left--;
+            const int n = f_left < sps ? f_left : sps;
+            bulk_load(ring_s + slot * stage_bytes, f_ptr, n * kStepBytes, bar_s + 8 * slot);
+            f_ptr += n * kStepBytes;
+            f_left -= n;
         }
         if (++slot == depth) {
             slot = 0;
             phase ^= 1u;
         }
-        k++;
-        if (k == spt || i == e - 1) {
-            // ---- this warp's segment of the tile ends: fold to one f32 per (row, column) ----
-            const bool whole = seg_k0 == 0 && k == spt;
-            const int r = tl == first_tl ? 0 : 1;
-#pragma unroll
-            for (int c = 0; c < CMAX; c++) {
-                float va = 0.f, vb = 0.f;
-#pragma unroll
-                for (int term = 0; term < TERMS; term++) {
-                    constexpr float kScale[2] = {1.0f, 4.8828125e-4f};  // 2^0, 2^-11
-                    const int col = c * TERMS + term, nt = col / 8, jj = col & 1;
-                    const bool mine = t == (col % 8) / 2;
-                    va = fmaf(mine ? yacc[nt][jj] : 0.f, kScale[term], va);
-                    vb = fmaf(mine ? yacc[nt][2 + jj] : 0.f, kScale[term], vb);
-                }
-                if (TYPE == LEV_GGML_Q4_K) {
-                    va -= mina[c];
-                    vb -= minb[c];
-                }
-                va += __shfl_xor_sync(0xffffffffu, va, 1);
-                vb += __shfl_xor_sync(0xffffffffu, vb, 1);
-                va += __shfl_xor_sync(0xffffffffu, va, 2);
-                vb += __shfl_xor_sync(0xffffffffu, vb, 2);
-                if (t == 0) {
-                    if (whole) {
-                        const int64_t row = (int64_t)(tile0 + tl) * 16 + g;
-                        if (c < A.n_cols) {
-                            if (row < A.rows) A.y[(int64_t)c * A.out_ld + row] = va;
-                            if (row + 8 < A.rows) A.y[(int64_t)c * A.out_ld + row + 8] = vb;
-                        }
-                    } else {
-                        rec[warp][r][c][g] = va;
-                        rec[warp][r][c][g + 8] = vb;
-                    }
-                }
-            }
-            if (!whole && lane == 0) rec_tile[warp][r] = tl;
-#pragma unroll
-            for (int nt = 0; nt < NT; nt++)
-#pragma unroll
-                for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
-#pragma unroll
-            for (int c = 0; c < CMAX; c++) mina[c] = minb[c] = 0.f;
-            tl++;
-            k = 0;
-            seg_k0 = 0;
-        }
     }
+    TL(29);
     __syncthreads();
+    TL(30);
     // ---- tiles shared between warps: add the warps' records in the order of their ranges ----
+    // logical warp l owns steps [nst*l/W, nst*(l+1)/W); the one holding step q is ((q+1)*W - 1) / nst
     for (int item = threadIdx.x; item < ntiles * CMAX * 16; item += W * 32) {
         const int tile = item / (CMAX * 16), idx = item - tile * (CMAX * 16);
+        const int l_first = ((tile * spt + 1) * W - 1) / nst, l_last = ((tile * spt + spt) * W - 1) / nst;
+        if (l_first == l_last) continue;  // one warp had the whole tile and wrote it
         float acc = 0.f;
-        int found = 0;
-#pragma unroll 1
-        for (int l2 = 0; l2 < W; l2++) {
+        for (int l2 = l_first; l2 <= l_last; l2++) {
             const int pw = (l2 % (W / 4)) * 4 + l2 / (W / 4);  // the warp whose logical position is l2
-            if (rec_tile[pw][0] == tile) {
-                acc += rec[pw][0][0][idx];
-                found++;
-            } else if (rec_tile[pw][1] == tile) {
-                acc += rec[pw][1][0][idx];
-                found++;
-            }
+            const int s2 = (int)((int64_t)nst * l2 / W), e2 = (int)((int64_t)nst * (l2 + 1) / W);
+            if (s2 == e2) continue;  // more warps than K-steps: this one had nothing
+            acc += rec[pw][tile == s2 / spt ? 0 : 1][0][idx];
         }
-        if (!found) continue;  // one warp had the whole tile and wrote it
         const int c = idx >> 4;
         const int64_t row = (int64_t)(tile0 + tile) * 16 + (idx & 15);
         if (c < A.n_cols && row < A.rows) A.y[(int64_t)c * A.out_ld + row] = acc;
     }
+    TL(31);
 }
+
+#ifdef LEV_TIMELINE
+}  // namespace
+extern "C" int lev_debug_timeline(long long* out) {
+    return (int)cudaMemcpyFromSymbol(out, lev_tl, sizeof(lev_tl));
+}
+namespace {
+#endif
 
 template <int TYPE, int CMAX, int W>
 int launch_dense(lev_ctx* ctx, int grid, size_t smem, const DenseArgs& A) {
@@ -297,7 +352,7 @@ int launch_dense_c(lev_ctx* ctx, int cmax, int warps, int grid, size_t smem, con
 }
 
 struct DensePlan {
-    int warps, depth, grid;
+    int warps, depth, sps, grid;
     size_t smem;
 };
 
@@ -308,8 +363,8 @@ bool dense_plan(lev_ctx* ctx, const lev_weights* w, int64_t rows, int n_cols, De
     const size_t tb = lev_stream_table_bytes(w, n_cols, 2, 1, nullptr);
     const int64_t tiles = (rows + 15) / 16, spt = lev_stream_chunks(w) / 4;
     if (tiles < 1 || tiles * spt > 0x7fffffff / 64) return false;
-    int warps = env_int("LEV_DENSE_WARPS", 12);
-    if (warps != 8 && warps != 12 && warps != 16 && warps != 24) warps = 12;
+    int warps = env_int("LEV_DENSE_WARPS", 8);
+    if (warps != 8 && warps != 12 && warps != 16 && warps != 24) warps = 8;
     // half of an SM's shared memory unless one CTA takes the SM
     size_t cap = (size_t)env_int("LEV_DENSE_SMEM_KB", warps <= 16 ? 108 : 200) * 1024;
     const int sms = ctx->prop.multiProcessorCount;
@@ -321,30 +376,37 @@ bool dense_plan(lev_ctx* ctx, const lev_weights* w, int64_t rows, int n_cols, De
         cap = 200 * 1024;
         if (tb + (size_t)warps * step > cap) return false;
     }
-    int64_t depth = (int64_t)((cap - tb) / ((size_t)warps * step));
-    if (depth > per_warp) depth = per_warp;
+    // K-steps one warp can hold in shared memory, cut into stages of sps steps
+    int64_t room = (int64_t)((cap - tb) / ((size_t)warps * step));
+    if (room > per_warp) room = per_warp;
+    int sps = env_int("LEV_DENSE_SPS", 2);
+    if (sps < 1) sps = 1;
+    if (sps * 2 > room) sps = room >= 2 ? (int)(room / 2) : 1;  // at least two stages when there is room
+    int64_t depth = room / sps;
     if (depth > kMaxDepth) depth = kMaxDepth;
     const int forced = env_int("LEV_DENSE_DEPTH", 0);
     if (forced > 0 && forced < depth) depth = forced;
     if (depth < 1) depth = 1;
     P->warps = warps;
     P->depth = (int)depth;
+    P->sps = sps;
     P->grid = grid;
-    P->smem = (size_t)warps * depth * step + tb;
+    P->smem = (size_t)warps * depth * sps * step + tb;
     return true;
 }
 
 }  // namespace
 
-bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, int n_cols) {
+bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols) {
     DensePlan P;
-    return w->packed && row0 % 16 == 0 && dense_plan(ctx, w, rows, n_cols, &P);
+    // x is read in 16-byte vectors
+    return w->packed && row0 % 16 == 0 && ((uintptr_t)x & 15) == 0 && dense_plan(ctx, w, rows, n_cols, &P);
 }
 
 // x: [n_cols][w->cols] device, y: [n_cols][rows] device.  No work buffers.
 int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y) {
     DensePlan P;
-    if (!w->packed || row0 % 16 != 0 || !dense_plan(ctx, w, rows, n_cols, &P))
+    if (!w->packed || row0 % 16 != 0 || ((uintptr_t)x & 15) != 0 || !dense_plan(ctx, w, rows, n_cols, &P))
         return lev_fail(ctx, LEV_UNSUPPORTED, "dense stream kernel: shape not served");
     const int64_t tiles = (rows + 15) / 16, chunks = lev_stream_chunks(w), spt = chunks / 4;
     const size_t step = step_bytes(w->type);
@@ -363,6 +425,7 @@ int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows
     A.out_ld = rows;
     A.status = ctx->d_status;
     A.depth = P.depth;
+    A.sps = P.sps;
     A.debug = env_int("LEV_STREAM_DEBUG", 0);
     int st = w->type == LEV_GGML_Q4_K   ? launch_dense_c<LEV_GGML_Q4_K>(ctx, n_cols, P.warps, P.grid, P.smem, A)
              : w->type == LEV_GGML_Q6_K ? launch_dense_c<LEV_GGML_Q6_K>(ctx, n_cols, P.warps, P.grid, P.smem, A)

@@ -67,7 +67,7 @@ extern "C" int lev_matvec_static_scratch(lev_ctx* ctx, const lev_weights* w, int
         return lev_fail(ctx, LEV_UNSUPPORTED, "the stream schedule does not serve this tensor or row window");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
     // the one-launch kernel builds its tables in shared memory and needs no work buffers at all
-    if (lev_dense_supported(ctx, w, row0, rows, n_cols)) return lev_dense_run(ctx, w, row0, rows, x, n_cols, y);
+    if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) return lev_dense_run(ctx, w, row0, rows, x, n_cols, y);
 
     const int terms = lev_stream_terms(n_cols);
     lev_stream_job J = {};

@@ -796,7 +796,7 @@ int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& 
 
 int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols,
                              float* y) {
-    if (lev_dense_supported(ctx, w, row0, rows, n_cols)) return lev_dense_run(ctx, w, row0, rows, x, n_cols, y);
+    if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) return lev_dense_run(ctx, w, row0, rows, x, n_cols, y);
     const int terms = lev_stream_terms(n_cols);
     lev_stream_source src = {};
     src.x = x;

@@ -40,5 +40,5 @@ int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& 
                       int terms, float* y, const lev_stream_source* fused_src, void* partials, void* counters);
 
 // one-launch dense matvec (lev_dense.cu): n_cols <= 4 and tables that fit shared memory
-bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, int n_cols);
+bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols);
 int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y);

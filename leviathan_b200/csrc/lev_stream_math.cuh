@@ -15,7 +15,7 @@ constexpr int kStepBytesQ6 = 3360;  // one Q6_K block of 16 rows
 __host__ __device__ constexpr int step_bytes(int type) { return type == LEV_GGML_Q6_K ? kStepBytesQ6 : kStepBytesQ4; }
 constexpr int kWarpsPerCta = 8;   // grouped and large calls
 constexpr int kWarpsWide = 24;    // dense calls: one CTA per SM
-constexpr unsigned kWaitPolls = 1u << 24;  // bound of every mbarrier wait
+constexpr long long kWaitCycles = 2000000000LL;  // bound of every wait on a barrier: about one second of SM clocks
 
 __device__ __forceinline__ void mma16816(float* d, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -104,9 +104,23 @@ __device__ __forceinline__ void bulk_load(unsigned dst, const void* src, unsigne
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
 }
-// bounded wait: false when the phase did not complete within kWaitPolls polls
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+// non-blocking: has the phase with this parity completed?
+__device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n .reg .pred p;\n mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// bounded wait: false when the phase did not complete within kWaitCycles SM clocks (about a second)
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
-    for (unsigned i = 0; i < kWaitPolls; i++) {
+    long long t_start = 0;
+    for (unsigned i = 1;; i++) {
         unsigned ok;
         asm volatile(
             "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
@@ -114,8 +128,12 @@ __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
             : "r"(bar), "r"(parity)
             : "memory");
         if (ok) return true;
+        if ((i & 63u) == 0) {
+            const long long now = clock64();
+            if (t_start == 0) t_start = now;
+            else if (now - t_start > kWaitCycles) return false;
+        }
     }
-    return false;
 }
 
 // CMAX: activation columns per job (compile time, so that every table index
@@ -164,6 +182,50 @@ __device__ __forceinline__ void stream_step(const uint4* st, const uint4* xchunk
     const int* boff0 = O.boff0;
     const int* boff1 = O.boff1;
     (void)g; (void)t; (void)boff0; (void)boff1; (void)mina; (void)minb;
+#ifdef LEV_SIM_LEAN
+if (TYPE == LEV_GGML_Q4_K) {
+    const uint4 h0 = st[g], h1 = st[8 + g];
+    const unsigned sa_lo = h0.y & 0x3F3F3F3Fu, sa_hi = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
+    const unsigned sb_lo = h1.y & 0x3F3F3F3Fu, sb_hi = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
+    const float dA = h2f_bits(h0.x & 0xffffu), dB = h2f_bits(h1.x & 0xffffu);
+#pragma unroll
+    for (int G = 0; G < 2; G++) {
+        float acc[4];
+#pragma unroll
+        for (int cc = 0; cc < 2; cc++) {
+            const int c = 2 * G + cc;
+            const uint4 q = st[16 + c * 32 + lane];
+            const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
+            const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
+            const uint4* xp = xchunk + c * (GLT * 8) + xoff[0];
+            const uint4 x0 = xp[0], x1 = xp[1];
+            if (cc == 0) mma16816_z(acc, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
+            else mma16816(acc, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
+            mma16816(acc, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x0.z, x0.w);
+            mma16816(acc, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x1.x, x1.y);
+            mma16816(acc, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1.z, x1.w);
+        }
+        const float sA = dA * (__uint_as_float(__byte_perm(G ? sa_hi : sa_lo, 0x4B000000u, 0x7650u + t)) - 8388608.0f);
+        const float sB = dB * (__uint_as_float(__byte_perm(G ? sb_hi : sb_lo, 0x4B000000u, 0x7650u + t)) - 8388608.0f);
+        yacc[0][0] = fmaf(sA, acc[0], yacc[0][0]);
+        yacc[0][1] = fmaf(sA, acc[1], yacc[0][1]);
+        yacc[0][2] = fmaf(sB, acc[2], yacc[0][2]);
+        yacc[0][3] = fmaf(sB, acc[3], yacc[0][3]);
+    }
+    const unsigned ma = t < 2 ? (h0.z & 0x3F3F3F3Fu) : (((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u));
+    const unsigned mb = t < 2 ? (h1.z & 0x3F3F3F3Fu) : (((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u));
+    const unsigned mab = t & 1 ? (ma >> 16) : ma, mbb = t & 1 ? (mb >> 16) : mb;
+    const float dminA = h2f_bits(h0.x >> 16), dminB = h2f_bits(h1.x >> 16);
+    const float mA0 = dminA * byte_to_float(mab, 0), mA1 = dminA * byte_to_float(mab, 1);
+    const float mB0 = dminB * byte_to_float(mbb, 0), mB1 = dminB * byte_to_float(mbb, 1);
+    const float* sx0 = achunk + 2 * t * CMAX;
+#pragma unroll
+    for (int c = 0; c < CMAX; c++) {
+        mina[c] = fmaf(mA0, sx0[c], fmaf(mA1, sx0[CMAX + c], mina[c]));
+        minb[c] = fmaf(mB0, sx0[c], fmaf(mB1, sx0[CMAX + c], minb[c]));
+    }
+} else
+#endif
 if (TYPE == LEV_GGML_Q4_K) {
     const uint4 h0 = st[g], h1 = st[8 + g];
     // 6-bit scales of the 8 sub-blocks of rows g (h0) and g+8 (h1), four per word
