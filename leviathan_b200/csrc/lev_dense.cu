@@ -326,6 +326,10 @@ int launch_dense(lev_ctx* ctx, int grid, size_t smem, const DenseArgs& A) {
     static size_t configured[16] = {};  // per device: largest dynamic shared memory opted in so far
     if (configured[ctx->device & 15] < smem) {
         LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // every instance asks for the same (largest) shared-memory carve-out: an SM whose split
+        // would have to change between two launches cannot hold CTAs of both at once
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                           (int)cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 15] = smem;
     }
     LEV_CUDA(ctx, launch_pdl(k_dense<TYPE, CMAX, W>, dim3(grid), dim3(W * 32), smem, ctx->stream, A));
