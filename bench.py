@@ -41,9 +41,9 @@ VEC_BYTES = 4 * (HIDDEN + 2 * FFN + FFN + HIDDEN)  # x, gate out, up out, down i
 STEP_BYTES = 2 * GATE_BYTES + DOWN_BYTES + VEC_BYTES  # 98,091,008
 SEED = 0x4C455649
 # dram__bytes_read + dram__bytes_write of one Q4_K 12288x4096 stream launch, from the ncu
-# capture summarised in profiles/k_stream_q4k_q6k_full_capture.txt
-Q4K_DRAM_TRAFFIC = 28_353_536
-Q6K_DRAM_TRAFFIC = 41_376_512
+# capture summarised in profiles/k_dense_q4k_q6k_full_capture.txt
+Q4K_DRAM_TRAFFIC = 28_353_280
+Q6K_DRAM_TRAFFIC = 41_372_672
 
 
 def _peaks():

@@ -370,7 +370,7 @@ bool dense_plan(lev_ctx* ctx, const lev_weights* w, int64_t rows, int n_cols, De
     int warps = env_int("LEV_DENSE_WARPS", 8);
     if (warps != 8 && warps != 12 && warps != 16 && warps != 24) warps = 8;
     // half of an SM's shared memory unless one CTA takes the SM
-    size_t cap = (size_t)env_int("LEV_DENSE_SMEM_KB", warps <= 16 ? 108 : 200) * 1024;
+    size_t cap = (size_t)env_int("LEV_DENSE_SMEM_KB", warps <= 16 ? 110 : 200) * 1024;
     const int sms = ctx->prop.multiProcessorCount;
     const int grid = (int)(tiles < sms ? tiles : sms);
     const int64_t per_cta = ((tiles + grid - 1) / grid) * spt;
