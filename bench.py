@@ -315,6 +315,10 @@ def run_gpu(args):
     barrier()
     e2e_ms = 1000.0 * (time.perf_counter() - t0) / args.steps
 
+    extras = None
+    if not args.no_extras:
+        extras = run_extras(ctx, inst[0][0], dev, s, world, rank)
+
     if world > 1:
         t = torch.tensor([ms_per_step, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -361,7 +365,7 @@ def run_gpu(args):
             "e2e": {"value": world * STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * (HIDDEN + HIDDEN + FFN), "d2h_bytes_per_step": 4 * (FFN + FFN + HIDDEN)},
             "gpu_launches": launches_per_step * args.steps * reps,
-            "clocks": clocks, "parity": parity,
+            "clocks": clocks, "parity": parity, "extras": extras,
         }
         if not args.no_cpu and world == 1:
             times, threads, build = cpu_step_timer(None, 11, 3)
@@ -374,6 +378,109 @@ def run_gpu(args):
         dist.destroy_process_group()
 
 
+# ---------------------------------------------------------------------------
+# side measurements (not part of `value`): prefill dequant-GEMM and the routed MoE layer
+# ---------------------------------------------------------------------------
+
+MOE_EXPERTS, MOE_HIDDEN, MOE_INTER, MOE_TOPK = 128, 2816, 704, 8
+MOE_EXPERT_BYTES = (2 * MOE_INTER * (MOE_HIDDEN // 32) + MOE_HIDDEN * (MOE_INTER // 32)) * 18  # 3,345,408
+MOE_ROUTER_BYTES = MOE_EXPERTS * MOE_HIDDEN * 4
+
+
+def _graph_time(torch, stream, fn, iters, reps=7):
+    """Median milliseconds per call of fn(i), i = 0..iters-1 captured as one CUDA graph."""
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        for i in range(min(iters, 3)):
+            fn(i)
+        stream.synchronize()
+        with torch.cuda.graph(g, stream=stream):
+            for i in range(iters):
+                fn(i)
+        for _ in range(3):
+            g.replay()
+        ts = []
+        for _ in range(reps):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            g.replay()
+            a1.record(stream)
+            a1.synchronize()
+            ts.append(a0.elapsed_time(a1) / iters)
+    return statistics.median(ts)
+
+
+def run_extras(ctx, w_gate, dev, stream, world, rank):
+    """Prefill GEMM (512 tokens x the Q4_K gate tensor) and the 128-expert top-8 MoE layer at
+    1 / 32 / 512 tokens; with more than one rank the experts are sharded and the layer runs
+    expert-parallel.  Every rank takes part, rank 0 reports."""
+    import torch
+
+    from leviathan_b200 import quant as Q
+
+    peaks, _ = _peaks()
+    out = {}
+    if world == 1:
+        g = torch.Generator(device=dev).manual_seed(SEED ^ 0x300)
+        xs = [torch.randn((512, HIDDEN), generator=g, device=dev).to(torch.bfloat16) for _ in range(4)]
+        y = torch.empty((512, FFN), device=dev)
+        ms = _graph_time(torch, stream, lambda i: ctx.gemm_prefill(w_gate, xs[i % 4], out=y), 8)
+        flop = 2.0 * 512 * HIDDEN * FFN
+        out["prefill_gemm"] = {"workload": "X bf16 [512x4096] x Q4_K [12288x4096]", "ms": ms,
+                               "tflops": flop / ms / 1e9, "peak_tflops_sustained": peaks["bf16_tflops_sustained"],
+                               "tensor_frac": flop / ms / 1e9 / peaks["bf16_tflops_sustained"]}
+    # MoE layer
+    if world > 1:
+        from leviathan_b200 import dist as lev_dist
+
+        lev_dist.init_from_torch(ctx)
+    g = torch.Generator(device=dev).manual_seed(SEED ^ 0x400)
+    first, count = (0, MOE_EXPERTS) if world == 1 else (rank * (MOE_EXPERTS // world), MOE_EXPERTS // world)
+    gu, dn = [], []
+    for e in range(MOE_EXPERTS):  # every rank draws all experts so that shards agree, keeps its own
+        wgu = torch.randn((2 * MOE_INTER, MOE_HIDDEN), generator=g, device=dev) * 0.02
+        wdn = torch.randn((MOE_HIDDEN, MOE_INTER), generator=g, device=dev) * 0.02
+        if first <= e < first + count:
+            gu.append(Q.quantize(2, wgu))
+            dn.append(Q.quantize(2, wdn))
+    router = torch.randn((MOE_EXPERTS, MOE_HIDDEN), generator=g, device=dev) * 0.02
+    mw = ctx.moe_upload(router, torch.cat(gu), torch.cat(dn), MOE_EXPERTS, MOE_HIDDEN, MOE_INTER, first, count)
+    del gu, dn
+    moe = {}
+    for tokens in (1, 32, 512):
+        xt = [torch.randn((tokens, MOE_HIDDEN), generator=g, device=dev) for _ in range(8)]
+        yo = torch.empty((tokens, MOE_HIDDEN), device=dev)
+        if world > 1:
+            fn = lambda i: ctx.moe_layer(mw, xt[i % 8], MOE_TOPK, out=yo, expert_parallel=True)  # noqa: E731
+            # collectives are not captured: time eager calls with events
+            for i in range(3):
+                fn(i)
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for i in range(16):
+                fn(i)
+            a1.record()
+            a1.synchronize()
+            ms = a0.elapsed_time(a1) / 16
+            import torch.distributed as dist
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
+        else:
+            ms = _graph_time(torch, stream, lambda i: ctx.moe_layer(mw, xt[i % 8], MOE_TOPK, out=yo), 8)
+        idx = ctx.moe_route(mw, xt[0], MOE_TOPK)[0]
+        distinct = int(torch.unique(idx).numel())
+        byts = MOE_ROUTER_BYTES + distinct * MOE_EXPERT_BYTES
+        moe[f"T{tokens}"] = {"ms_per_layer": ms, "tokens_per_s": tokens / (ms * 1e-3), "distinct_experts": distinct,
+                             "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
+                             "hbm_frac": byts / ms / 1e6 / peaks["hbm_gbs"]}
+    out["moe_layer"] = {"workload": "128 experts Q4_0 (GU 1408x2816, DN 2816x704), top-8, hidden 2816",
+                        "parallelism": "single GPU" if world == 1 else f"expert-parallel over {world} GPUs", **moe}
+    mw.free()
+    return out if rank == 0 else None
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -384,6 +491,7 @@ def main():
     ap.add_argument("--impl", default="native", choices=["native", "reference"])
     ap.add_argument("--no-cpu", action="store_true")
     ap.add_argument("--no-check", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the prefill GEMM and MoE layer side measurements")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

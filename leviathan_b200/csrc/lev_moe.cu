@@ -34,10 +34,14 @@ __device__ __forceinline__ double warp_butterfly(double v) {
     return v;
 }
 
-// one warp per (token, 8 experts); 8 warps of a CTA share the expert rows
-__global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__ rw, const float* __restrict__ x,
-                                                       int64_t tokens, int experts, int hidden,
-                                                       float* __restrict__ scores, int* status) {
+// Router logits.  Summation order (the oracle states the same): lane l of a warp adds the
+// products of elements l, l+32, l+64, ... in ascending order as double FMAs starting from zero,
+// the 32 lane sums meet in an xor butterfly (16, 8, 4, 2, 1), one rounding to f32.
+//
+// Plain form: one warp per (token, 8 experts), operands straight from global memory.
+__global__ void __launch_bounds__(256) k_router_logits_plain(const float* __restrict__ rw, const float* __restrict__ x,
+                                                             int64_t tokens, int experts, int hidden,
+                                                             float* __restrict__ scores, int* status) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t tok = (int64_t)blockIdx.y * 8 + warp;
     const int e0 = blockIdx.x * 8;
@@ -59,6 +63,85 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
         if (e0 + j < experts) {
             bad |= !isfinite(s);
             if (lane == 0) scores[tok * experts + e0 + j] = s;
+        }
+    }
+    if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
+}
+
+// Staged form: a CTA of 8 warps takes 8 experts x 8 tokens; every warp brings its expert's row
+// and one token's activations into shared memory with one bulk copy each (all 16 rows are in
+// flight at once: the plain form is bound by the latency of 88 dependent rounds of loads), then
+// warp w computes expert w against the 8 tokens.  Needs 16-byte aligned rows.
+__global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__ rw, const float* __restrict__ x,
+                                                       int64_t tokens, int experts, int hidden,
+                                                       float* __restrict__ scores, int* status) {
+    extern __shared__ __align__(128) unsigned char rsm[];
+    __shared__ __align__(8) unsigned long long bar;
+    float* ws = reinterpret_cast<float*>(rsm);      // [8][hidden]
+    float* xs = ws + (size_t)8 * hidden;            // [8][hidden]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e = blockIdx.x * 8 + warp;
+    const int64_t t0 = (int64_t)blockIdx.y * 8;
+    const int ntok = (int)(tokens - t0 < 8 ? tokens - t0 : 8);
+    const unsigned bar_s = (unsigned)__cvta_generic_to_shared(&bar);
+    const unsigned row_bytes = (unsigned)hidden * 4u;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar_s), "r"(8));
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    __syncthreads();
+    if (lane == 0) {
+        const unsigned bytes = (e < experts ? row_bytes : 0u) + (warp < ntok ? row_bytes : 0u);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_s), "r"(bytes) : "memory");
+        if (e < experts)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                             (unsigned)__cvta_generic_to_shared(ws + (size_t)warp * hidden)),
+                         "l"(rw + (int64_t)e * hidden), "r"(row_bytes), "r"(bar_s)
+                         : "memory");
+        if (warp < ntok)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                             (unsigned)__cvta_generic_to_shared(xs + (size_t)warp * hidden)),
+                         "l"(x + (t0 + warp) * hidden), "r"(row_bytes), "r"(bar_s)
+                         : "memory");
+    }
+    // bounded wait for the 16 rows
+    bool landed = false;
+    {
+        const long long t_start = clock64();
+        for (unsigned i = 1; !landed; i++) {
+            unsigned ok;
+            asm volatile(
+                "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                : "=r"(ok)
+                : "r"(bar_s), "r"(0)
+                : "memory");
+            landed = ok != 0;
+            if (!landed && (i & 63u) == 0 && clock64() - t_start > 2000000000LL) break;
+        }
+    }
+    if (!landed) {
+        if (threadIdx.x == 0) atomicOr(status, LEV_DEV_TIMEOUT);
+        return;
+    }
+    if (e >= experts) return;
+    double acc[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) acc[j] = 0.0;
+    const float* wr = ws + (size_t)warp * hidden;
+    for (int i = lane; i < hidden; i += 32) {
+        const double wv = (double)wr[i];
+#pragma unroll
+        for (int j = 0; j < 8; j++)
+            if (j < ntok) acc[j] = fma(wv, (double)xs[(size_t)j * hidden + i], acc[j]);
+    }
+    bool bad = false;
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        if (j < ntok) {
+            float sv = (float)warp_butterfly(acc[j]);
+            bad |= !isfinite(sv);
+            if (lane == 0) scores[(t0 + j) * experts + e] = sv;
         }
     }
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
@@ -240,6 +323,113 @@ __global__ void __launch_bounds__(1024) k_group(GroupArgs G) {
     }
 }
 
+// Same result as k_group for pair counts whose per-chunk histograms fit shared memory: pairs are
+// cut into chunks of 32 in index order; chunk histograms, a scan over chunks per expert, then
+// every pair finds its stable position as offset[expert] + pairs of that expert in earlier
+// chunks + earlier lanes of its own chunk.  No pass over all pairs per expert.
+__global__ void __launch_bounds__(1024) k_group_fast(GroupArgs G, int nchunks) {
+    extern __shared__ int sh[];  // hist[experts], offs[experts + 1], jobbase[experts + 1], ch[nchunks][experts]
+    int* hist = sh;
+    int* offs = sh + G.experts;
+    int* jobbase = offs + G.experts + 1;
+    int* ch = jobbase + G.experts + 1;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
+    for (int e = tid; e < G.experts; e += blockDim.x) hist[e] = 0;
+    for (int i = tid; i < nchunks * G.experts; i += blockDim.x) ch[i] = 0;
+    __syncthreads();
+    bool bad = false;
+    for (int c = warp; c < nchunks; c += nwarps) {
+        const int i = c * 32 + lane;
+        if (i < G.pairs) {
+            const int e = G.idx[i];
+            if (e < 0 || e >= G.experts) bad = true;
+            else if (e >= G.first && e < G.first + G.count) {
+                atomicAdd(&ch[c * G.experts + e], 1);
+                atomicAdd(&hist[e], 1);
+            }
+        }
+    }
+    if (bad) atomicOr(G.status, LEV_DEV_NONFINITE_INPUT);
+    __syncthreads();
+    if (warp == 0) {
+        int per = (G.experts + 31) / 32, b = lane * per, e1 = min(b + per, G.experts);
+        int s = 0, js = 0;
+        for (int e = b; e < e1; e++) {
+            s += hist[e];
+            js += (hist[e] + G.cmax - 1) / G.cmax;
+        }
+        int incl = s, jincl = js;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            int v = __shfl_up_sync(0xffffffffu, incl, d), jv = __shfl_up_sync(0xffffffffu, jincl, d);
+            if (lane >= d) {
+                incl += v;
+                jincl += jv;
+            }
+        }
+        int run = incl - s, jrun = jincl - js;
+        for (int e = b; e < e1; e++) {
+            offs[e] = run;
+            jobbase[e] = jrun;
+            run += hist[e];
+            jrun += (hist[e] + G.cmax - 1) / G.cmax;
+        }
+        if (lane == 31) {
+            offs[G.experts] = incl;
+            jobbase[G.experts] = jincl;
+        }
+    } else {
+        // exclusive scan over chunks, one thread per expert
+        for (int e = tid - 32; e < G.experts; e += blockDim.x - 32) {
+            int run = 0;
+            for (int c = 0; c < nchunks; c++) {
+                const int v = ch[c * G.experts + e];
+                ch[c * G.experts + e] = run;
+                run += v;
+            }
+        }
+    }
+    __syncthreads();
+    for (int e = tid; e < G.experts; e += blockDim.x) {
+        G.counts[e] = hist[e];
+        G.offsets[e] = offs[e];
+        if (G.job_slice && e >= G.first && e < G.first + G.count) {
+            const int nj = (hist[e] + G.cmax - 1) / G.cmax;
+            for (int j = 0; j < nj; j++) G.job_slice[jobbase[e] + j] = e - G.first;
+            for (int r = hist[e]; r < nj * G.cmax; r++) {  // empty columns of the expert's last job
+                const int q = (jobbase[e] + nj - 1) * G.cmax + (r - (nj - 1) * G.cmax);
+                G.job_token[q] = -1;
+                G.job_pos[q] = -1;
+                G.job_pair[q] = -1;
+            }
+        }
+    }
+    if (tid == 0) {
+        G.offsets[G.experts] = offs[G.experts];
+        if (G.njobs) *G.njobs = jobbase[G.experts];
+    }
+    for (int c = warp; c < nchunks; c += nwarps) {
+        const int i = c * 32 + lane;
+        int e = -1 - lane;  // lanes without a resident pair match nobody
+        if (i < G.pairs) {
+            const int v = G.idx[i];
+            if (v >= G.first && v < G.first + G.count && v < G.experts) e = v;
+        }
+        const unsigned same = __match_any_sync(0xffffffffu, e);
+        if (e >= 0) {
+            const int r = ch[c * G.experts + e] + __popc(same & ((1u << lane) - 1u));
+            const int pos = offs[e] + r;
+            G.perm[pos] = i;
+            if (G.job_slice) {
+                const int q = (jobbase[e] + r / G.cmax) * G.cmax + r % G.cmax;
+                G.job_token[q] = i / G.top_k;
+                G.job_pos[q] = pos;
+                G.job_pair[q] = i;
+            }
+        }
+    }
+}
+
 // out[t][h] = sum_k w[t][k] * y[t][k][h]: a separate multiply and add per
 // slot in rank order from zero (Sources/LeviathanCore/Gemma4.swift:4459-4466)
 __global__ void k_combine(const float* __restrict__ y, const float* __restrict__ w, int64_t tokens, int top_k,
@@ -331,7 +521,17 @@ extern "C" int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w) {
 int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
                      float* weights, float* scores) {
     dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
-    k_router_logits<<<grid, 256, 0, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
+    const size_t stage = (size_t)16 * w->hidden * sizeof(float);
+    if (stage <= 200 * 1024 && w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0) {
+        static bool configured[16] = {};
+        if (!configured[ctx->device & 15]) {
+            LEV_CUDA(ctx, cudaFuncSetAttribute(k_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            configured[ctx->device & 15] = true;
+        }
+        k_router_logits<<<grid, 256, stage, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
+    } else {
+        k_router_logits_plain<<<grid, 256, 0, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
+    }
     ctx->launches++;
     LEV_CUDA(ctx, cudaGetLastError());
     size_t smem = (size_t)4 * w->experts * sizeof(double);
@@ -365,7 +565,18 @@ static int group_dev(lev_ctx* ctx, const int32_t* idx, int64_t tokens, int top_k
     G.job_pair = jt ? jt->job_pair : nullptr;
     G.status = ctx->d_status;
     size_t smem = (size_t)(3 * experts + 2) * sizeof(int);
-    k_group<<<1, 1024, smem, ctx->stream>>>(G);
+    const int nchunks = (G.pairs + 31) / 32;
+    const size_t fast = smem + (size_t)nchunks * experts * sizeof(int);
+    if (nchunks > 0 && fast <= 160 * 1024) {
+        static bool configured[16] = {};
+        if (!configured[ctx->device & 15]) {
+            LEV_CUDA(ctx, cudaFuncSetAttribute(k_group_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+            configured[ctx->device & 15] = true;
+        }
+        k_group_fast<<<1, 1024, fast, ctx->stream>>>(G, nchunks);
+    } else {
+        k_group<<<1, 1024, smem, ctx->stream>>>(G);
+    }
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_group");
 }
