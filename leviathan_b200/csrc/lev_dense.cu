@@ -45,10 +45,22 @@ struct DenseArgs {
     int depth;         // ring stages per warp
     int sps;           // K-steps per stage
     int debug;         // bit 0: skip the arithmetic
+    // sliced form (JOBS): the call is a device-side list of jobs, each one activation column
+    // against one slice (expert) of the tensor
+    const int* njobs_dev;   // [1] jobs in the list
+    const int* job_slice;   // [job] slice index, in units of tiles_per_job tiles
+    const int* job_src;     // [job] source row of the job's activations, -1 = none
+    const int* job_out;     // [job] output row, -1 = none
+    int tiles_per_job;
+    int gelu_inter;         // > 0: activation e = gelu_tanh(src[e]) * src[gelu_inter + e]
+    int table_stride;       // bytes between the tables of consecutive jobs in shared memory
 };
 
-template <int TYPE, int CMAX, int W>
+constexpr int kMaxJobTables = 3;  // jobs whose tables one CTA of the sliced form can hold
+
+template <int TYPE, int CMAX, int W, bool JOBS>
 __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) {
+    static_assert(!JOBS || CMAX == 1, "the sliced form takes one column per job");
     using D = StreamDims<CMAX>;
     constexpr int NT = D::kNT, GLT = D::kGlt, TERMS = D::kTerms;
     constexpr int kStepBytes = step_bytes(TYPE);
@@ -63,8 +75,22 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     const int lw = (warp & 3) * (W / 4) + (warp >> 2);
     const int spt = A.spt, depth = A.depth;
     const int cta = blockIdx.x;
-    const int tile0 = cta * A.tiles_base + (cta < A.tiles_rem ? cta : A.tiles_rem);
-    const int ntiles = A.tiles_base + (cta < A.tiles_rem ? 1 : 0);
+    int tiles_base = A.tiles_base, tiles_rem = A.tiles_rem;
+    const int tpj = JOBS ? A.tiles_per_job : 1;
+    if (JOBS) {  // the job count is only known on the device (written by a launch that has completed)
+        const int total = *A.njobs_dev * tpj;
+        tiles_base = total / (int)gridDim.x;
+        tiles_rem = total - tiles_base * (int)gridDim.x;
+    }
+    const int tile0 = cta * tiles_base + (cta < tiles_rem ? cta : tiles_rem);
+    const int ntiles = tiles_base + (cta < tiles_rem ? 1 : 0);
+    if (ntiles == 0) return;
+    const int job0 = JOBS ? tile0 / tpj : 0;
+    const int njobs_here = JOBS ? (tile0 + ntiles - 1) / tpj - job0 + 1 : 1;
+    if (JOBS && njobs_here > kMaxJobTables) {
+        if (threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
+        return;
+    }
     const int nst = ntiles * spt;
     const int s = (int)((int64_t)nst * lw / W), e = (int)((int64_t)nst * (lw + 1) / W);
 
@@ -77,14 +103,23 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     // fetch side (lane 0): this warp's share is one contiguous byte range
     const unsigned char* f_ptr = reinterpret_cast<const unsigned char*>(A.wp) + ((int64_t)tile0 * spt + s) * kStepBytes;
     int f_left = e - s;  // K-steps not yet requested
+    int f_q = s;         // sliced form: CTA-local index of the next K-step to request (one per stage)
+    // sliced form: a tile's bytes sit in the slice its job names
+    auto step_src = [&](int q) -> const unsigned char* {
+        const int gt = tile0 + q / spt, k = q - (q / spt) * spt;
+        const int job = gt / tpj, tij = gt - job * tpj;
+        return reinterpret_cast<const unsigned char*>(A.wp) +
+               (((int64_t)A.job_slice[job] * tpj + tij) * spt + k) * (int64_t)kStepBytes;
+    };
     if (lane == 0) {
         for (int d = 0; d < depth; d++) mbar_init(bar_s + 8 * d, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
         for (int d = 0; d < depth && f_left > 0; d++) {
             const int n = f_left < sps ? f_left : sps;
-            bulk_load(ring_s + d * stage_bytes, f_ptr, n * kStepBytes, bar_s + 8 * d);
+            bulk_load(ring_s + d * stage_bytes, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar_s + 8 * d);
             f_ptr += n * kStepBytes;
+            f_q += n;
             f_left -= n;
         }
     }
@@ -100,24 +135,36 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     // ---- activation tables, built by every CTA for itself ----
     // One item = (chunk, activation column, lane-of-quad tt): the 16 activations that feed lane
     // tt's B fragments of the chunk's four mma, both split terms.
-    uint4* xs = reinterpret_cast<uint4*>(smem_raw + (size_t)W * depth * stage_bytes);
-    float* sa = reinterpret_cast<float*>(xs + A.chunks * GLT * 8);
+    unsigned char* tables0 = smem_raw + (size_t)W * depth * stage_bytes;
     {
-        const int items = A.chunks * CMAX * 4;  // a multiple of 4: quads stay whole
+        uint4* xs = reinterpret_cast<uint4*>(tables0);
+        float* sa = reinterpret_cast<float*>(xs + A.chunks * GLT * 8);
+        const int per_job = A.chunks * CMAX * 4;  // a multiple of 4: quads stay whole
+        const int items = per_job * njobs_here;
         bool bad = false;
         for (int idx0 = warp * 32; idx0 < items; idx0 += W * 32) {
             const int idx = idx0 + lane;
             const bool live = idx < items;
-            const int ii = live ? idx : items - 1;
+            const int i2 = live ? idx : items - 1;
+            const int jj = JOBS ? i2 / per_job : 0, ii = i2 - jj * per_job;
             const int chunk = ii / (CMAX * 4), rem = ii - chunk * (CMAX * 4), c = rem >> 2, tt = rem & 3;
-            const bool has = c < A.n_cols;
-            const float* xr = A.x + (int64_t)(has ? c : 0) * A.x_ld;
+            const int src_row = JOBS ? A.job_src[job0 + jj] : c;
+            const bool has = JOBS ? src_row >= 0 : c < A.n_cols;
+            const float* xr = A.x + (int64_t)(has ? src_row : 0) * A.x_ld;
+            if (JOBS) {
+                xs = reinterpret_cast<uint4*>(tables0 + (size_t)jj * A.table_stride);
+                sa = reinterpret_cast<float*>(xs + A.chunks * GLT * 8);
+            }
             // the four elements of one mma are consecutive in x (component r + 2h, Q6_K: 2r + h)
             float xv[4][2][2];
 #pragma unroll
             for (int m = 0; m < 4; m++) {
                 const int el = chunk * 64 + chunk_col<TYPE>(tt, m, 0, 0);
-                const float4 v = __ldg(reinterpret_cast<const float4*>(xr + (el < A.cols ? el : 0)));
+                float4 v = __ldg(reinterpret_cast<const float4*>(xr + (el < A.cols ? el : 0)));
+                if (JOBS && A.gelu_inter > 0) {
+                    const float4 u = __ldg(reinterpret_cast<const float4*>(xr + A.gelu_inter + (el < A.cols ? el : 0)));
+                    v = make_float4(gelu_tanh_up(v.x, u.x), gelu_tanh_up(v.y, u.y), gelu_tanh_up(v.z, u.z), gelu_tanh_up(v.w, u.w));
+                }
                 const bool in = el < A.cols && has;
                 const float q[4] = {in ? v.x : 0.f, in ? v.y : 0.f, in ? v.z : 0.f, in ? v.w : 0.f};
 #pragma unroll
@@ -217,6 +264,22 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     unsigned phase = 0;  // its mbarrier phase parity
     int seg_k0 = k;
     const int first_tl = tl;
+    // tables, output row and tile-in-job of the tile being worked on
+    const uint4* xs = reinterpret_cast<const uint4*>(tables0);
+    const float* sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
+    int job = 0, tij = tile0 + tl, orow = 0;
+    auto enter_tile = [&]() {
+        if (JOBS) {
+            job = (tile0 + tl) / tpj;
+            tij = tile0 + tl - job * tpj;
+            xs = reinterpret_cast<const uint4*>(tables0 + (size_t)(job - job0) * A.table_stride);
+            sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
+            orow = A.job_out[job];
+        } else {
+            tij = tile0 + tl;
+        }
+    };
+    if (s < e) enter_tile();
     for (int i0 = s; i0 < e; i0 += sps) {
         if (!mbar_wait(bar_s + 8 * slot, phase)) {
             if (lane == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
@@ -255,10 +318,11 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
                     vb += __shfl_xor_sync(0xffffffffu, vb, 2);
                     if (t == 0) {
                         if (whole) {
-                            const int64_t row = (int64_t)(tile0 + tl) * 16 + g;
-                            if (c < A.n_cols) {
-                                if (row < A.rows) A.y[(int64_t)c * A.out_ld + row] = va;
-                                if (row + 8 < A.rows) A.y[(int64_t)c * A.out_ld + row + 8] = vb;
+                            const int64_t row = (int64_t)tij * 16 + g;
+                            const int oc = JOBS ? orow : c;
+                            if (JOBS ? orow >= 0 : c < A.n_cols) {
+                                if (row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = va;
+                                if (row + 8 < A.rows) A.y[(int64_t)oc * A.out_ld + row + 8] = vb;
                             }
                         } else {
                             rec[warp][r][c][g] = va;
@@ -275,14 +339,16 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
                 tl++;
                 k = 0;
                 seg_k0 = 0;
+                if (i + 1 < e) enter_tile();
             }
         }
         // every lane has consumed its shared-memory reads of this stage: refill it
         __syncwarp();
         if (lane == 0 && f_left > 0) {
             const int n = f_left < sps ? f_left : sps;
-            bulk_load(ring_s + slot * stage_bytes, f_ptr, n * kStepBytes, bar_s + 8 * slot);
+            bulk_load(ring_s + slot * stage_bytes, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar_s + 8 * slot);
             f_ptr += n * kStepBytes;
+            f_q += n;
             f_left -= n;
         }
         if (++slot == depth) {
@@ -307,8 +373,14 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
             acc += rec[pw][tile == s2 / spt ? 0 : 1][0][idx];
         }
         const int c = idx >> 4;
-        const int64_t row = (int64_t)(tile0 + tile) * 16 + (idx & 15);
-        if (c < A.n_cols && row < A.rows) A.y[(int64_t)c * A.out_ld + row] = acc;
+        if (JOBS) {
+            const int pjob = (tile0 + tile) / tpj, ptij = tile0 + tile - pjob * tpj, oc = A.job_out[pjob];
+            const int64_t row = (int64_t)ptij * 16 + (idx & 15);
+            if (oc >= 0 && row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = acc;
+        } else {
+            const int64_t row = (int64_t)(tile0 + tile) * 16 + (idx & 15);
+            if (c < A.n_cols && row < A.rows) A.y[(int64_t)c * A.out_ld + row] = acc;
+        }
     }
     TL(31);
 }
@@ -321,18 +393,18 @@ extern "C" int lev_debug_timeline(long long* out) {
 namespace {
 #endif
 
-template <int TYPE, int CMAX, int W>
+template <int TYPE, int CMAX, int W, bool JOBS = false>
 int launch_dense(lev_ctx* ctx, int grid, size_t smem, const DenseArgs& A) {
     static size_t configured[16] = {};  // per device: largest dynamic shared memory opted in so far
     if (configured[ctx->device & 15] < smem) {
-        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W, JOBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         // every instance asks for the same (largest) shared-memory carve-out: an SM whose split
         // would have to change between two launches cannot hold CTAs of both at once
-        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W, JOBS>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                            (int)cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 15] = smem;
     }
-    LEV_CUDA(ctx, launch_pdl(k_dense<TYPE, CMAX, W>, dim3(grid), dim3(W * 32), smem, ctx->stream, A));
+    LEV_CUDA(ctx, launch_pdl(k_dense<TYPE, CMAX, W, JOBS>, dim3(grid), dim3(W * 32), smem, ctx->stream, A));
     return LEV_OK;
 }
 
@@ -414,7 +486,7 @@ int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows
         return lev_fail(ctx, LEV_UNSUPPORTED, "dense stream kernel: shape not served");
     const int64_t tiles = (rows + 15) / 16, chunks = lev_stream_chunks(w), spt = chunks / 4;
     const size_t step = step_bytes(w->type);
-    DenseArgs A;
+    DenseArgs A = {};
     A.wp = (const uint4*)w->packed + (row0 / 16) * spt * (int64_t)(step / 16);
     A.spt = (int)spt;
     A.tiles_base = (int)(tiles / P.grid);
@@ -439,4 +511,67 @@ int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows
     ctx->ev.grid = P.grid;
     ctx->ev.block = P.warps * 32;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_dense");
+}
+
+// Sliced form: a device-side list of up to max_jobs jobs, job j = one activation column (row
+// job_src[j] of x, optionally through gelu_tanh(gate) * up) against slice job_slice[j] of the
+// tensor (slice = rows_per_job consecutive rows), result to row job_out[j] of y.
+bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, const float* x,
+                              int64_t x_ld) {
+    if (!w->packed || rows_per_job % 16 != 0 || max_jobs < 1 || env_int("LEV_DENSE", 1) == 0) return false;
+    if (((uintptr_t)x & 15) != 0 || x_ld % 4 != 0) return false;
+    if (max_jobs > ctx->prop.multiProcessorCount) return false;  // keeps a CTA within kMaxJobTables jobs
+    const size_t stride = (lev_stream_table_bytes(w, 1, 2, 1, nullptr) + 255) & ~(size_t)255;
+    return kMaxJobTables * stride + 8 * 2 * (size_t)step_bytes(w->type) <= 110 * 1024;
+}
+
+int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, const int* njobs_dev,
+                       const int* job_slice, const int* job_src, const int* job_out, const float* x, int64_t x_ld,
+                       int gelu_inter, float* y, int64_t out_ld) {
+    if (!lev_dense_jobs_supported(ctx, w, rows_per_job, max_jobs, x, x_ld))
+        return lev_fail(ctx, LEV_UNSUPPORTED, "sliced dense kernel: shape not served");
+    constexpr int W = 8;
+    const int64_t tpj = rows_per_job / 16, chunks = lev_stream_chunks(w), spt = chunks / 4;
+    const size_t step = step_bytes(w->type);
+    const size_t stride = (lev_stream_table_bytes(w, 1, 2, 1, nullptr) + 255) & ~(size_t)255;
+    const size_t cap = 110 * 1024;
+    const int sms = ctx->prop.multiProcessorCount;
+    const int64_t max_tiles = (int64_t)max_jobs * tpj;
+    const int grid = (int)(max_tiles < sms ? max_tiles : sms);
+    const int64_t per_warp = (((max_tiles + grid - 1) / grid) * spt + W - 1) / W;
+    int64_t depth = (int64_t)((cap - kMaxJobTables * stride) / ((size_t)W * step));
+    if (depth > per_warp) depth = per_warp;
+    if (depth > kMaxDepth) depth = kMaxDepth;
+    if (depth < 1) depth = 1;
+    DenseArgs A = {};
+    A.wp = (const uint4*)w->packed;
+    A.spt = (int)spt;
+    A.x = x;
+    A.x_ld = x_ld;
+    A.cols = (int)w->cols;
+    A.chunks = (int)chunks;
+    A.n_cols = 1;
+    A.y = y;
+    A.rows = rows_per_job;
+    A.out_ld = out_ld;
+    A.status = ctx->d_status;
+    A.depth = (int)depth;
+    A.sps = 1;
+    A.debug = env_int("LEV_STREAM_DEBUG", 0);
+    A.njobs_dev = njobs_dev;
+    A.job_slice = job_slice;
+    A.job_src = job_src;
+    A.job_out = job_out;
+    A.tiles_per_job = (int)tpj;
+    A.gelu_inter = gelu_inter;
+    A.table_stride = (int)stride;
+    const size_t smem = (size_t)W * depth * step + kMaxJobTables * stride;
+    int st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 1, W, true>(ctx, grid, smem, A)
+             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 1, W, true>(ctx, grid, smem, A)
+                                        : launch_dense<LEV_GGML_Q4_0, 1, W, true>(ctx, grid, smem, A);
+    if (st) return st;
+    ctx->launches++;
+    ctx->ev.grid = grid;
+    ctx->ev.block = W * 32;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_dense (sliced)");
 }

@@ -589,7 +589,12 @@ static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, co
 int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
                        const int32_t* idx, float* y_pairs, float* act_out) {
     const int64_t pairs = tokens * top_k;
-    const int cmax = pairs <= 2 * (int64_t)w->local_count ? 4 : 8, terms = 2;
+    const int64_t gu_rows_ = 2 * (int64_t)w->inter;
+    // decode-sized calls: one job per (token, slot) pair on the one-launch kernel, whose CTAs
+    // build their activation tables themselves (no preparation launches, no table memory)
+    const bool sliced = pairs <= 64 && lev_dense_jobs_supported(ctx, w->gate_up, gu_rows_, (int)pairs, x, w->hidden) &&
+                        lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)pairs, x, gu_rows_);
+    const int cmax = sliced ? 1 : (pairs <= 2 * (int64_t)w->local_count ? 4 : 8), terms = 2;
     int64_t mj = (int64_t)w->local_count + pairs / cmax;
     if (mj > pairs) mj = pairs;
     const int max_jobs = (int)mj;
@@ -629,6 +634,14 @@ int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, 
     LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_C, gu_bytes + tb + 256, &cb));
     float* gu = (float*)cb;
     void* tables = (char*)cb + gu_bytes;
+    if (sliced) {
+        LEV_TRY(lev_dense_jobs_run(ctx, w->gate_up, gu_rows, max_jobs, jt.njobs, jt.job_slice, jt.job_token, jt.job_pos, x,
+                                   w->hidden, 0, gu, gu_rows));
+        LEV_TRY(lev_dense_jobs_run(ctx, w->down, w->hidden, max_jobs, jt.njobs, jt.job_slice, jt.job_pos, jt.job_pair, gu,
+                                   gu_rows, w->inter, y_pairs, w->hidden));
+        if (act_out) LEV_TRY(lev_moe_launch_act(ctx, gu, perm, offsets + w->experts, pairs, w->inter, act_out));
+        return LEV_OK;
+    }
 
     lev_stream_source src = {};
     src.x = x;
