@@ -17,6 +17,10 @@
 
 #include "lev_internal.h"
 
+// tensor-memory form (lev_gemm_tc.cu)
+bool lev_gemm_tc_supported(const lev_weights* w, const void* x_bf16, int64_t tokens);
+int lev_gemm_tc_run(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int64_t tokens, float* y);
+
 namespace {
 
 constexpr int kTileM = 64, kTileN = 64, kTileK = 32, kPad = 8;  // row stride 40 bf16 = 80 B: conflict-free fragment loads
@@ -172,6 +176,10 @@ extern "C" int lev_gemm_prefill(lev_ctx* ctx, const lev_weights* w, const void* 
     if (tokens <= 0 || tokens > (1 << 20)) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "tokens %lld", (long long)tokens);
     if (w->cols % 32) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "inDim %lld", (long long)w->cols);
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (lev_gemm_tc_supported(w, x_bf16, tokens)) {
+        snprintf(ctx->ev.kernel_name, sizeof ctx->ev.kernel_name, "lev_gemm_prefill_tcgen05");
+        return lev_gemm_tc_run(ctx, w, x_bf16, tokens, y);
+    }
     dim3 grid((unsigned)((w->rows + kTileM - 1) / kTileM), (unsigned)((tokens + kTileN - 1) / kTileN));
     int64_t row_bytes = w->blocks_per_row * lev_block_bytes(w->type);
     k_gemm_prefill<<<grid, 128, 0, ctx->stream>>>(w->raw, w->type, row_bytes, w->rows, w->cols,

@@ -1,0 +1,395 @@
+// Prefill dequant-GEMM on the fifth-generation tensor cores (tcgen05 + TMEM), sm_100a.
+//
+//   Y[t][r] = sum_k bf16(W[r][k]) * X[t][k],  f32 accumulate in tensor memory
+//
+// Same operand rounding as the mma.sync form in lev_gemm.cu (weights decoded bit-exactly
+// as the block decoders form them, then one rounding to bf16; activations are bf16 already;
+// rust/crates/lev-forge/src/coopmat.rs:236-425, oracle rust/crates/lev-cli/src/main.rs:1201-1217).
+//
+// One CTA computes a tile of 256 tokens x 192 weight rows over the whole K:
+//   * warp 0 (one thread): TMA loads of the activation tile, two boxes of 128 tokens x 64 k
+//     (128-byte rows, hardware 128B swizzle) per K-step into a 3-stage ring;
+//   * warps 2..9 (256 threads): decode the K-step's 192 x 64 weights from the GGUF blocks in
+//     global memory and store them as bf16 into the same K-major 128B-swizzled layout, then
+//     publish them to the async proxy (fence.proxy.async) and arrive on the stage's barrier;
+//   * warp 1 (one thread): for each K-step 4 x 2 tcgen05.mma (M = 128 tokens, N = 192 rows,
+//     K = 16) from shared-memory descriptors into two TMEM accumulators (384 of 512 columns),
+//     tcgen05.commit hands the stage back to the producers;
+//   * epilogue: warps 2..9 read the accumulators with tcgen05.ld (warp w owns TMEM lanes
+//     32*(w%4)...) and store Y rows with 16-byte stores.
+// Every wait is bounded by about a second of SM clocks; on a timeout the CTA sets
+// LEV_DEV_TIMEOUT, skips the remaining work, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "lev_internal.h"
+
+namespace {
+
+constexpr int TM = 256;      // tokens per CTA tile (two MMA tiles of 128)
+constexpr int RN = 192;      // weight rows per CTA tile (MMA N)
+constexpr int KS = 64;       // k per pipeline stage (one 128-byte swizzle row of bf16)
+constexpr int STAGES = 3;
+constexpr int kDequantWarps = 8;
+constexpr int kThreads = (2 + kDequantWarps) * 32;
+constexpr int kXHalfBytes = 128 * KS * 2;             // 16384: one TMA box
+constexpr int kXStageBytes = 2 * kXHalfBytes;         // 32768
+constexpr int kWStageBytes = RN * KS * 2;             // 24576
+constexpr int kStageBytes = kXStageBytes + kWStageBytes;
+constexpr int kTmemCols = 512;
+constexpr long long kWaitCycles = 2000000000LL;
+
+struct GemmTcArgs {
+    const uint8_t* raw;   // GGUF blocks, row-major
+    int type;
+    int64_t row_bytes;
+    int64_t rows, cols;
+    int tokens;
+    float* y;             // [tokens][rows]
+    int y_vec;            // rows of y start on 16-byte boundaries
+    int* status;
+};
+
+__device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ float h2f(unsigned bits) { return __half2float(__ushort_as_half((unsigned short)bits)); }
+
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+// bounded wait; false on timeout or when another thread of the CTA has already given up
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
+    long long t_start = 0;
+    for (unsigned i = 1;; i++) {
+        unsigned ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+            : "=r"(ok)
+            : "r"(bar), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((i & 63u) == 0) {
+            if (*abort_flag) return false;
+            const long long now = clock64();
+            if (t_start == 0) t_start = now;
+            else if (now - t_start > kWaitCycles) {
+                *abort_flag = 1;
+                return false;
+            }
+        }
+    }
+}
+
+__device__ __forceinline__ void tma_load_2d(unsigned dst, const CUtensorMap* map, int x, int y, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n" ::"r"(dst),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+
+// shared-memory matrix descriptor: K-major, 128-byte swizzle, 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t umma_desc(unsigned smem_addr) {
+    return (uint64_t)((smem_addr >> 4) & 0x3FFFu) | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+// instruction descriptor: D f32, A and B bf16, both K-major, M = 128, N = RN
+constexpr unsigned kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(RN >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+
+__device__ __forceinline__ void umma_bf16(unsigned d_tmem, uint64_t adesc, uint64_t bdesc, unsigned accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(kInstrDesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void umma_commit(unsigned bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void q4k_scale_min(const unsigned char* s, int j, unsigned* sc, unsigned* mn) {
+    if (j < 4) {
+        *sc = s[j] & 63u;
+        *mn = s[j + 4] & 63u;
+    } else {
+        *sc = (s[j + 4] & 0x0Fu) | ((unsigned)(s[j - 4] >> 6) << 4);
+        *mn = (unsigned)(s[j + 4] >> 4) | ((unsigned)(s[j] >> 6) << 4);
+    }
+}
+
+__device__ __forceinline__ uint4 pack8(const float* v) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
+    return make_uint4(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b), *reinterpret_cast<unsigned*>(&c),
+                      *reinterpret_cast<unsigned*>(&d));
+}
+// byte offset of 16-byte chunk ch (0..7) of row r inside a K-major 128B-swizzled tile
+__device__ __forceinline__ unsigned swz(int r, int ch) { return (unsigned)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4)); }
+
+// The K-step's slice of one row: tid4 = 0..3 picks 8 of the 32 stored bytes; both nibble halves
+// of those bytes are decoded, giving two 16-byte chunks of bf16.
+template <int TYPE>
+__device__ __forceinline__ void decode_pair(const uint8_t* row, int it, int j, bool valid, unsigned char* wtile, int r) {
+    float lo[8], hi[8];
+    int ch_lo, ch_hi;
+    if (TYPE == LEV_GGML_Q4_K) {
+        // K-step = chunk c of block b: low nibbles of qs[32c..32c+32) are columns 0..31, high nibbles 32..63
+        const int b = it >> 2, c = it & 3;
+        ch_lo = j;
+        ch_hi = j + 4;
+        if (valid) {
+            const uint8_t* blk = row + (int64_t)b * LEV_Q4_K_BYTES;
+            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(blk));
+            const uint2 q = __ldg(reinterpret_cast<const uint2*>(blk + 16 + 32 * c + 8 * j));
+            const float d = h2f(hd.x & 0xffffu), dmin = h2f(hd.x >> 16);
+            unsigned char sb[12];
+            *reinterpret_cast<unsigned*>(sb) = hd.y;
+            *reinterpret_cast<unsigned*>(sb + 4) = hd.z;
+            *reinterpret_cast<unsigned*>(sb + 8) = hd.w;
+            unsigned sc0, mn0, sc1, mn1;
+            q4k_scale_min(sb, 2 * c, &sc0, &mn0);
+            q4k_scale_min(sb, 2 * c + 1, &sc1, &mn1);
+            const float d0 = __fmul_rn(d, (float)sc0), m0 = __fmul_rn(dmin, (float)mn0);
+            const float d1 = __fmul_rn(d, (float)sc1), m1 = __fmul_rn(dmin, (float)mn1);
+            const unsigned w[2] = {q.x, q.y};
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const unsigned byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+                lo[i] = __fsub_rn(__fmul_rn(d0, (float)(byte & 15u)), m0);
+                hi[i] = __fsub_rn(__fmul_rn(d1, (float)(byte >> 4)), m1);
+            }
+        }
+    } else {
+        // Q4_0: K-step = two 32-value blocks; j>>1 picks the block, j&1 the byte half;
+        // low nibbles are values 0..15, high nibbles 16..31 of the block
+        const int bi = j >> 1, hb = j & 1;
+        ch_lo = bi * 4 + hb;
+        ch_hi = bi * 4 + hb + 2;
+        if (valid) {
+            const uint8_t* blk = row + (int64_t)(2 * it + bi) * LEV_Q4_0_BYTES;
+            const unsigned short* p16 = reinterpret_cast<const unsigned short*>(blk);
+            const float d = h2f(__ldg(p16));
+            unsigned short w16[4];
+#pragma unroll
+            for (int i = 0; i < 4; i++) w16[i] = __ldg(p16 + 1 + 4 * hb + i);
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const unsigned byte = (w16[i >> 1] >> (8 * (i & 1))) & 0xffu;
+                lo[i] = __fmul_rn(d, (float)(byte & 15u) - 8.0f);
+                hi[i] = __fmul_rn(d, (float)(byte >> 4) - 8.0f);
+            }
+        }
+    }
+    if (!valid) {
+#pragma unroll
+        for (int i = 0; i < 8; i++) lo[i] = hi[i] = 0.f;
+    }
+    *reinterpret_cast<uint4*>(wtile + swz(r, ch_lo)) = pack8(lo);
+    *reinterpret_cast<uint4*>(wtile + swz(r, ch_hi)) = pack8(hi);
+}
+
+template <int TYPE>
+__global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, GemmTcArgs A) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) unsigned long long full_x[STAGES], full_w[STAGES], empty[STAGES], accum_full;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    // the swizzled tiles need 1024-byte alignment
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    const int64_t r0 = (int64_t)blockIdx.x * RN;
+    const int t0 = blockIdx.y * TM;
+    const int halves = A.tokens - t0 > 128 ? 2 : 1;
+    const int kt = (int)(A.cols / KS);
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < STAGES; s++) {
+            mbar_init(s32(&full_x[s]), 1);
+            mbar_init(s32(&full_w[s]), kDequantWarps);
+            mbar_init(s32(&empty[s]), 1);
+        }
+        mbar_init(s32(&accum_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_s;
+    volatile int* abort_flag = &abort_s;
+
+    if (warp == 0) {
+        // ---- activation tiles by TMA ----
+        if (lane == 0) {
+            for (int it = 0; it < kt; it++) {
+                const int s = it % STAGES;
+                if (it >= STAGES && !mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag)) break;
+                const unsigned dst = s32(smem + (size_t)s * kStageBytes);
+                mbar_expect_tx(s32(&full_x[s]), halves * kXHalfBytes);
+                tma_load_2d(dst, &xmap, it * KS, t0, s32(&full_x[s]));
+                if (halves == 2) tma_load_2d(dst + kXHalfBytes, &xmap, it * KS, t0 + 128, s32(&full_x[s]));
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < kt && ok; it++) {
+                const int s = it % STAGES;
+                const unsigned ph = (it / STAGES) & 1;
+                ok = mbar_wait(s32(&full_x[s]), ph, abort_flag) && mbar_wait(s32(&full_w[s]), ph, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned xs = s32(smem + (size_t)s * kStageBytes), ws = xs + kXStageBytes;
+#pragma unroll
+                for (int kk = 0; kk < KS / 16; kk++) {
+                    const uint64_t bdesc = umma_desc(ws + kk * 32);
+                    for (int h = 0; h < halves; h++)
+                        umma_bf16(tmem_base + h * RN, umma_desc(xs + h * kXHalfBytes + kk * 32), bdesc, (it | kk) ? 1u : 0u);
+                }
+                umma_commit(s32(&empty[s]));  // the stage may be refilled when these MMAs have read it
+            }
+            umma_commit(s32(&accum_full));
+        }
+    } else {
+        // ---- weight decode: thread = (3 rows 64 apart) x (byte group j) ----
+        const int td = threadIdx.x - 64, j = td & 3, rb = td >> 2;
+        bool ok = true;
+        for (int it = 0; it < kt && ok; it++) {
+            const int s = it % STAGES;
+            if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
+#pragma unroll
+            for (int i = 0; i < RN / 64; i++) {
+                const int r = rb + 64 * i;
+                const bool valid = r0 + r < A.rows;
+                decode_pair<TYPE>(A.raw + (r0 + (valid ? r : 0)) * A.row_bytes, it, j, valid, wtile, r);
+            }
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s32(&full_w[s]));
+        }
+        // ---- epilogue: TMEM -> Y ----
+        if (ok && mbar_wait(s32(&accum_full), 0, abort_flag)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int quarter = warp & 3, half = (warp - 2) >> 2;
+            if (half < halves) {
+                const int token = t0 + half * 128 + quarter * 32 + lane;
+                float* yrow = A.y + (int64_t)token * A.rows + r0;
+#pragma unroll 1
+                for (int c = 0; c < RN; c += 32) {
+                    unsigned v[32];
+                    const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)(half * RN + c);
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                    if (token < A.tokens) {
+                        if (r0 + c + 32 <= A.rows && A.y_vec) {
+#pragma unroll
+                            for (int q = 0; q < 32; q += 4)
+                                *reinterpret_cast<uint4*>(yrow + c + q) = make_uint4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+                        } else {
+#pragma unroll
+                            for (int q = 0; q < 32; q++)
+                                if (r0 + c + q < A.rows) yrow[c + q] = __uint_as_float(v[q]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (abort_s && threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encode_tiled() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+template <int TYPE>
+int launch_tc(lev_ctx* ctx, const CUtensorMap& map, const GemmTcArgs& A, dim3 grid, size_t smem) {
+    static bool configured[16] = {};
+    if (!configured[ctx->device & 15]) {
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[ctx->device & 15] = true;
+    }
+    k_gemm_tc<TYPE><<<grid, kThreads, smem, ctx->stream>>>(map, A);
+    return LEV_OK;
+}
+
+}  // namespace
+
+// shapes the tensor-memory kernel serves: Q4_K and Q4_0 rows whose K is a multiple of 64,
+// 16-byte aligned activations
+bool lev_gemm_tc_supported(const lev_weights* w, const void* x_bf16, int64_t tokens) {
+    if (getenv("LEV_GEMM_TC") && atoi(getenv("LEV_GEMM_TC")) == 0) return false;
+    if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0) return false;
+    if (w->cols % KS != 0 || ((uintptr_t)x_bf16 & 15) != 0 || tokens < 1) return false;
+    return encode_tiled() != nullptr;
+}
+
+int lev_gemm_tc_run(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int64_t tokens, float* y) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return lev_fail(ctx, LEV_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)w->cols, (cuuint64_t)tokens};
+    const cuuint64_t gstride[1] = {(cuuint64_t)w->cols * 2};
+    const cuuint32_t box[2] = {KS, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x_bf16), gdim, gstride, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return lev_fail(ctx, LEV_KERNEL_FAILED, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    GemmTcArgs A;
+    A.raw = w->raw;
+    A.type = w->type;
+    A.row_bytes = w->blocks_per_row * lev_block_bytes(w->type);
+    A.rows = w->rows;
+    A.cols = w->cols;
+    A.tokens = (int)tokens;
+    A.y = y;
+    A.y_vec = ((uintptr_t)y & 15) == 0 && (w->rows & 3) == 0;
+    A.status = ctx->d_status;
+    dim3 grid((unsigned)((w->rows + RN - 1) / RN), (unsigned)((tokens + TM - 1) / TM));
+    const size_t smem = (size_t)STAGES * kStageBytes + 1024;
+    int st = w->type == LEV_GGML_Q4_K ? launch_tc<LEV_GGML_Q4_K>(ctx, map, A, grid, smem)
+                                      : launch_tc<LEV_GGML_Q4_0>(ctx, map, A, grid, smem);
+    if (st) return st;
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc");
+}

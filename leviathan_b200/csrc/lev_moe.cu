@@ -25,6 +25,7 @@
 
 #include "lev_internal.h"
 #include "lev_stream.h"
+#include "lev_stream_math.cuh"
 
 namespace {
 
@@ -99,6 +100,11 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
                              (unsigned)__cvta_generic_to_shared(ws + (size_t)warp * hidden)),
                          "l"(rw + (int64_t)e * hidden), "r"(row_bytes), "r"(bar_s)
                          : "memory");
+    }
+    // the router rows are constants and already on their way; the activations belong to the launch before
+    pdl_launch_dependents();
+    pdl_wait();
+    if (lane == 0) {
         if (warp < ntok)
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
                              (unsigned)__cvta_generic_to_shared(xs + (size_t)warp * hidden)),
@@ -152,6 +158,8 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
                                                      int top_k, const float* __restrict__ expert_scale,
                                                      int32_t* __restrict__ idx, float* __restrict__ weights) {
     extern __shared__ double sp[];  // [warps][experts] probabilities; selected ones are set to -1
+    pdl_launch_dependents();
+    pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t tok = (int64_t)blockIdx.x * 4 + warp;
     if (tok >= tokens) return;
@@ -434,6 +442,8 @@ __global__ void __launch_bounds__(1024) k_group_fast(GroupArgs G, int nchunks) {
 // slot in rank order from zero (Sources/LeviathanCore/Gemma4.swift:4459-4466)
 __global__ void k_combine(const float* __restrict__ y, const float* __restrict__ w, int64_t tokens, int top_k,
                           int hidden, float* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
     int64_t total = tokens * hidden;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
         int64_t t = i / hidden;
@@ -528,14 +538,16 @@ int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, in
             LEV_CUDA(ctx, cudaFuncSetAttribute(k_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
             configured[ctx->device & 15] = true;
         }
-        k_router_logits<<<grid, 256, stage, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
+        LEV_CUDA(ctx, launch_pdl(k_router_logits, grid, dim3(256), stage, ctx->stream, (const float*)w->router_w, x, tokens,
+                                 (int)w->experts, (int)w->hidden, scores, ctx->d_status));
     } else {
         k_router_logits_plain<<<grid, 256, 0, ctx->stream>>>(w->router_w, x, tokens, w->experts, w->hidden, scores, ctx->d_status);
     }
     ctx->launches++;
     LEV_CUDA(ctx, cudaGetLastError());
     size_t smem = (size_t)4 * w->experts * sizeof(double);
-    k_router_topk<<<(unsigned)((tokens + 3) / 4), 128, smem, ctx->stream>>>(scores, tokens, w->experts, top_k, nullptr, idx, weights);
+    LEV_CUDA(ctx, launch_pdl(k_router_topk, dim3((unsigned)((tokens + 3) / 4)), dim3(128), smem, ctx->stream, (const float*)scores,
+                             tokens, (int)w->experts, top_k, (const float*)nullptr, idx, weights));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_router_topk");
 }
@@ -709,7 +721,8 @@ static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, co
 }
 
 int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out) {
-    k_combine<<<grid_for(ctx, tokens * hidden, 256, 8), 256, 0, ctx->stream>>>(y, wts, tokens, top_k, hidden, out);
+    LEV_CUDA(ctx, launch_pdl(k_combine, dim3(grid_for(ctx, tokens * hidden, 256, 8)), dim3(256), (size_t)0, ctx->stream, y, wts,
+                             tokens, top_k, hidden, out));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_combine");
 }

@@ -357,8 +357,8 @@ if (TYPE == LEV_GGML_Q4_K) {
 int env_int(const char* name, int fallback);
 
 // launch with the programmatic-stream-serialization attribute (see pdl_wait)
-template <class Kernel, class Args>
-cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Args& args) {
+template <class Kernel, class... Args>
+cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Args&... args) {
     static const int enabled = env_int("LEV_PDL", 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -370,7 +370,7 @@ cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaSt
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = enabled ? 1 : 0;
-    return cudaLaunchKernelEx(&cfg, kernel, args);
+    return cudaLaunchKernelEx(&cfg, kernel, args...);
 }
 
 inline int env_int(const char* name, int fallback) {
