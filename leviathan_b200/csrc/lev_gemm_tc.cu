@@ -110,16 +110,6 @@ __device__ __forceinline__ void umma_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
-__device__ __forceinline__ void q4k_scale_min(const unsigned char* s, int j, unsigned* sc, unsigned* mn) {
-    if (j < 4) {
-        *sc = s[j] & 63u;
-        *mn = s[j + 4] & 63u;
-    } else {
-        *sc = (s[j + 4] & 0x0Fu) | ((unsigned)(s[j - 4] >> 6) << 4);
-        *mn = (unsigned)(s[j + 4] >> 4) | ((unsigned)(s[j] >> 6) << 4);
-    }
-}
-
 __device__ __forceinline__ uint4 pack8(const float* v) {
     __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
     __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
@@ -129,63 +119,120 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 // byte offset of 16-byte chunk ch (0..7) of row r inside a K-major 128B-swizzled tile
 __device__ __forceinline__ unsigned swz(int r, int ch) { return (unsigned)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4)); }
 
-// The K-step's slice of one row: tid4 = 0..3 picks 8 of the 32 stored bytes; both nibble halves
-// of those bytes are decoded, giving two 16-byte chunks of bf16.
+// 8 bytes from a 2-byte aligned address
+__device__ __forceinline__ uint2 load8_u16(const uint8_t* p) {
+    const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
+    const unsigned a = __ldg(q), b = __ldg(q + 1), c = __ldg(q + 2), d = __ldg(q + 3);
+    return make_uint2(a | (b << 16), c | (d << 16));
+}
+
+// What one decode thread needs of one row for one K-step (64 columns): it is thread j = 0..3 of
+// the four that share the row and produces two 16-byte chunks (8 bf16 each) of the tile row.
+//   Q4_K: K-step = chunk c of block b; bytes qs[32c + 8j ..+8): low nibbles -> chunk j (sub-block
+//         2c), high nibbles -> chunk j+4 (sub-block 2c+1); the block header every fourth step.
+//   Q4_0: K-step = two blocks; j>>1 picks the block, j&1 the byte half; low nibbles are values
+//         0..15, high nibbles 16..31 of the block -> chunks 4*(j>>1) + (j&1) and + 2.
+//   Q6_K: K-step = two 32-value groups (2*(it&1), +1) of half c = (it&3)>>1 of block b; thread j
+//         takes values 8j..8j+7 of both groups -> chunks j and j+4.
 template <int TYPE>
-__device__ __forceinline__ void decode_pair(const uint8_t* row, int it, int j, bool valid, unsigned char* wtile, int r) {
-    float lo[8], hi[8];
-    int ch_lo, ch_hi;
+struct RowRaw {
+    uint4 hdr;  // Q4_K: d, dmin, 12 scale bytes.  Q4_0: .x = d bits.  Q6_K: .x = d bits, .y = two int8 scales
+    uint2 q0;   // nibble bytes (Q6_K: of the first group)
+    uint2 q1;   // Q6_K: nibble bytes of the second group
+    uint2 qh;   // Q6_K: high-bit bytes
+};
+
+template <int TYPE>
+__device__ __forceinline__ void load_raw(const uint8_t* row, int it, int j, bool valid, RowRaw<TYPE>& R) {
+    if (!valid) return;
     if (TYPE == LEV_GGML_Q4_K) {
-        // K-step = chunk c of block b: low nibbles of qs[32c..32c+32) are columns 0..31, high nibbles 32..63
-        const int b = it >> 2, c = it & 3;
-        ch_lo = j;
-        ch_hi = j + 4;
-        if (valid) {
-            const uint8_t* blk = row + (int64_t)b * LEV_Q4_K_BYTES;
-            const uint4 hd = __ldg(reinterpret_cast<const uint4*>(blk));
-            const uint2 q = __ldg(reinterpret_cast<const uint2*>(blk + 16 + 32 * c + 8 * j));
-            const float d = h2f(hd.x & 0xffffu), dmin = h2f(hd.x >> 16);
-            unsigned char sb[12];
-            *reinterpret_cast<unsigned*>(sb) = hd.y;
-            *reinterpret_cast<unsigned*>(sb + 4) = hd.z;
-            *reinterpret_cast<unsigned*>(sb + 8) = hd.w;
-            unsigned sc0, mn0, sc1, mn1;
-            q4k_scale_min(sb, 2 * c, &sc0, &mn0);
-            q4k_scale_min(sb, 2 * c + 1, &sc1, &mn1);
-            const float d0 = __fmul_rn(d, (float)sc0), m0 = __fmul_rn(dmin, (float)mn0);
-            const float d1 = __fmul_rn(d, (float)sc1), m1 = __fmul_rn(dmin, (float)mn1);
-            const unsigned w[2] = {q.x, q.y};
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const unsigned byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
-                lo[i] = __fsub_rn(__fmul_rn(d0, (float)(byte & 15u)), m0);
-                hi[i] = __fsub_rn(__fmul_rn(d1, (float)(byte >> 4)), m1);
-            }
-        }
+        const uint8_t* blk = row + (int64_t)(it >> 2) * LEV_Q4_K_BYTES;
+        if ((it & 3) == 0) R.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
+        R.q0 = __ldg(reinterpret_cast<const uint2*>(blk + 16 + 32 * (it & 3) + 8 * j));
+    } else if (TYPE == LEV_GGML_Q4_0) {
+        const uint8_t* blk = row + (int64_t)(2 * it + (j >> 1)) * LEV_Q4_0_BYTES;
+        R.hdr.x = __ldg(reinterpret_cast<const unsigned short*>(blk));
+        R.q0 = load8_u16(blk + 2 + 8 * (j & 1));
     } else {
-        // Q4_0: K-step = two 32-value blocks; j>>1 picks the block, j&1 the byte half;
-        // low nibbles are values 0..15, high nibbles 16..31 of the block
-        const int bi = j >> 1, hb = j & 1;
-        ch_lo = bi * 4 + hb;
-        ch_hi = bi * 4 + hb + 2;
-        if (valid) {
-            const uint8_t* blk = row + (int64_t)(2 * it + bi) * LEV_Q4_0_BYTES;
-            const unsigned short* p16 = reinterpret_cast<const unsigned short*>(blk);
-            const float d = h2f(__ldg(p16));
-            unsigned short w16[4];
-#pragma unroll
-            for (int i = 0; i < 4; i++) w16[i] = __ldg(p16 + 1 + 4 * hb + i);
-#pragma unroll
-            for (int i = 0; i < 8; i++) {
-                const unsigned byte = (w16[i >> 1] >> (8 * (i & 1))) & 0xffu;
-                lo[i] = __fmul_rn(d, (float)(byte & 15u) - 8.0f);
-                hi[i] = __fmul_rn(d, (float)(byte >> 4) - 8.0f);
-            }
-        }
+        const uint8_t* blk = row + (int64_t)(it >> 2) * LEV_Q6_K_BYTES;
+        const int c = (it & 3) >> 1, g0 = 2 * (it & 1);
+        R.q0 = load8_u16(blk + 64 * c + 8 * j);
+        R.q1 = load8_u16(blk + 64 * c + 32 + 8 * j);
+        R.qh = load8_u16(blk + 128 + 32 * c + 8 * j);
+        R.hdr.x = __ldg(reinterpret_cast<const unsigned short*>(blk + 208));
+        // int8 scales of the two groups for values 8j..8j+7: index 8c + 2*grp + (j >> 1)
+        const unsigned s0 = blk[192 + 8 * c + 2 * g0 + (j >> 1)], s1 = blk[192 + 8 * c + 2 * (g0 + 1) + (j >> 1)];
+        R.hdr.y = s0 | (s1 << 8);
     }
+}
+
+// scale and min of Q4_K sub-block sb from the 12 packed bytes held in three words
+// (rust/crates/lev-cpu/src/lib.rs:64-74)
+__device__ __forceinline__ void q4k_scale_min_w(unsigned w0, unsigned w1, unsigned w2, int sb, unsigned* sc, unsigned* mn) {
+    const unsigned long long lo = (unsigned long long)w0 | ((unsigned long long)w1 << 32);
+    auto byte = [&](int i) -> unsigned { return i < 8 ? (unsigned)(lo >> (8 * i)) & 0xffu : (w2 >> (8 * (i - 8))) & 0xffu; };
+    if (sb < 4) {
+        *sc = byte(sb) & 63u;
+        *mn = byte(sb + 4) & 63u;
+    } else {
+        *sc = (byte(sb + 4) & 0x0Fu) | ((byte(sb - 4) >> 6) << 4);
+        *mn = (byte(sb + 4) >> 4) | ((byte(sb) >> 6) << 4);
+    }
+}
+
+template <int TYPE>
+__device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int j, bool valid, unsigned char* wtile, int r) {
+    float lo[8], hi[8];
+    int ch_lo = j, ch_hi = j + 4;
     if (!valid) {
 #pragma unroll
         for (int i = 0; i < 8; i++) lo[i] = hi[i] = 0.f;
+        if (TYPE == LEV_GGML_Q4_0) {
+            ch_lo = (j >> 1) * 4 + (j & 1);
+            ch_hi = ch_lo + 2;
+        }
+    } else if (TYPE == LEV_GGML_Q4_K) {
+        const int c = it & 3;
+        const float d = h2f(R.hdr.x & 0xffffu), dmin = h2f(R.hdr.x >> 16);
+        unsigned sc0, mn0, sc1, mn1;
+        q4k_scale_min_w(R.hdr.y, R.hdr.z, R.hdr.w, 2 * c, &sc0, &mn0);
+        q4k_scale_min_w(R.hdr.y, R.hdr.z, R.hdr.w, 2 * c + 1, &sc1, &mn1);
+        const float d0 = __fmul_rn(d, (float)sc0), m0 = __fmul_rn(dmin, (float)mn0);
+        const float d1 = __fmul_rn(d, (float)sc1), m1 = __fmul_rn(dmin, (float)mn1);
+        const unsigned w[2] = {R.q0.x, R.q0.y};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const unsigned byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            lo[i] = __fsub_rn(__fmul_rn(d0, (float)(byte & 15u)), m0);
+            hi[i] = __fsub_rn(__fmul_rn(d1, (float)(byte >> 4)), m1);
+        }
+    } else if (TYPE == LEV_GGML_Q4_0) {
+        ch_lo = (j >> 1) * 4 + (j & 1);
+        ch_hi = ch_lo + 2;
+        const float d = h2f(R.hdr.x);
+        const unsigned w[2] = {R.q0.x, R.q0.y};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const unsigned byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            lo[i] = __fmul_rn(d, (float)(byte & 15u) - 8.0f);
+            hi[i] = __fmul_rn(d, (float)(byte >> 4) - 8.0f);
+        }
+    } else {
+        // Q6_K (Sources/LeviathanCore/Q6.swift:10-62): level = nibble | (two high bits << 4), value = d*scale*(level-32)
+        const int g0 = 2 * (it & 1);
+        const float d = h2f(R.hdr.x);
+        const float ds0 = __fmul_rn(d, (float)(int)(signed char)(R.hdr.y & 0xffu));
+        const float ds1 = __fmul_rn(d, (float)(int)(signed char)((R.hdr.y >> 8) & 0xffu));
+        const unsigned a[2] = {R.q0.x, R.q0.y}, b[2] = {R.q1.x, R.q1.y}, h[2] = {R.qh.x, R.qh.y};
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const unsigned ba = (a[i >> 2] >> (8 * (i & 3))) & 0xffu, bb = (b[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            const unsigned bh = (h[i >> 2] >> (8 * (i & 3))) & 0xffu;
+            const unsigned na = g0 ? (ba >> 4) : (ba & 15u), nb = g0 ? (bb >> 4) : (bb & 15u);
+            const unsigned ha = (bh >> (2 * g0)) & 3u, hb = (bh >> (2 * g0 + 2)) & 3u;
+            lo[i] = __fmul_rn(ds0, (float)((int)(na | (ha << 4)) - 32));
+            hi[i] = __fmul_rn(ds1, (float)((int)(nb | (hb << 4)) - 32));
+        }
     }
     *reinterpret_cast<uint4*>(wtile + swz(r, ch_lo)) = pack8(lo);
     *reinterpret_cast<uint4*>(wtile + swz(r, ch_hi)) = pack8(hi);
@@ -261,23 +308,39 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             umma_commit(s32(&accum_full));
         }
     } else {
-        // ---- weight decode: thread = (3 rows 64 apart) x (byte group j) ----
+        // ---- weight decode: thread = (3 rows 64 apart) x (byte group j); the raw bytes of the
+        // next K-step are requested before this one is decoded ----
         const int td = threadIdx.x - 64, j = td & 3, rb = td >> 2;
+        constexpr int NR = RN / 64;
+        RowRaw<TYPE> cur[NR], nxt[NR];
+        const uint8_t* rowp[NR];
+        bool valid[NR];
+#pragma unroll
+        for (int i = 0; i < NR; i++) {
+            valid[i] = r0 + rb + 64 * i < A.rows;
+            rowp[i] = A.raw + (r0 + (valid[i] ? rb + 64 * i : 0)) * A.row_bytes;
+            load_raw<TYPE>(rowp[i], 0, j, valid[i], cur[i]);
+        }
         bool ok = true;
         for (int it = 0; it < kt && ok; it++) {
             const int s = it % STAGES;
+            if (it + 1 < kt) {
+#pragma unroll
+                for (int i = 0; i < NR; i++) {
+                    nxt[i] = cur[i];  // keeps the block header that is reloaded only every fourth step
+                    load_raw<TYPE>(rowp[i], it + 1, j, valid[i], nxt[i]);
+                }
+            }
             if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
             if (!ok) break;
             unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
 #pragma unroll
-            for (int i = 0; i < RN / 64; i++) {
-                const int r = rb + 64 * i;
-                const bool valid = r0 + r < A.rows;
-                decode_pair<TYPE>(A.raw + (r0 + (valid ? r : 0)) * A.row_bytes, it, j, valid, wtile, r);
-            }
+            for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + 64 * i);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(s32(&full_w[s]));
+#pragma unroll
+            for (int i = 0; i < NR; i++) cur[i] = nxt[i];
         }
         // ---- epilogue: TMEM -> Y ----
         if (ok && mbar_wait(s32(&accum_full), 0, abort_flag)) {
@@ -354,11 +417,11 @@ int launch_tc(lev_ctx* ctx, const CUtensorMap& map, const GemmTcArgs& A, dim3 gr
 
 }  // namespace
 
-// shapes the tensor-memory kernel serves: Q4_K and Q4_0 rows whose K is a multiple of 64,
+// shapes the tensor-memory kernel serves: rows whose K is a multiple of 64,
 // 16-byte aligned activations
 bool lev_gemm_tc_supported(const lev_weights* w, const void* x_bf16, int64_t tokens) {
     if (getenv("LEV_GEMM_TC") && atoi(getenv("LEV_GEMM_TC")) == 0) return false;
-    if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0) return false;
+    if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0 && w->type != LEV_GGML_Q6_K) return false;
     if (w->cols % KS != 0 || ((uintptr_t)x_bf16 & 15) != 0 || tokens < 1) return false;
     return encode_tiled() != nullptr;
 }
@@ -387,8 +450,9 @@ int lev_gemm_tc_run(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int6
     A.status = ctx->d_status;
     dim3 grid((unsigned)((w->rows + RN - 1) / RN), (unsigned)((tokens + TM - 1) / TM));
     const size_t smem = (size_t)STAGES * kStageBytes + 1024;
-    int st = w->type == LEV_GGML_Q4_K ? launch_tc<LEV_GGML_Q4_K>(ctx, map, A, grid, smem)
-                                      : launch_tc<LEV_GGML_Q4_0>(ctx, map, A, grid, smem);
+    int st = w->type == LEV_GGML_Q4_K   ? launch_tc<LEV_GGML_Q4_K>(ctx, map, A, grid, smem)
+             : w->type == LEV_GGML_Q6_K ? launch_tc<LEV_GGML_Q6_K>(ctx, map, A, grid, smem)
+                                        : launch_tc<LEV_GGML_Q4_0>(ctx, map, A, grid, smem);
     if (st) return st;
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc");
