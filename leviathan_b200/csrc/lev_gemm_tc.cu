@@ -9,7 +9,7 @@
 // One CTA computes a tile of 256 tokens x 192 weight rows over the whole K:
 //   * warp 0 (one thread): TMA loads of the activation tile, two boxes of 128 tokens x 64 k
 //     (128-byte rows, hardware 128B swizzle) per K-step into a 3-stage ring;
-//   * warps 2..9 (256 threads): decode the K-step's 192 x 64 weights from the GGUF blocks in
+//   * warps 2..13 (384 threads): decode the K-step's 192 x 64 weights from the GGUF blocks in
 //     global memory and store them as bf16 into the same K-major 128B-swizzled layout, then
 //     publish them to the async proxy (fence.proxy.async) and arrive on the stage's barrier;
 //   * warp 1 (one thread): for each K-step 4 x 2 tcgen05.mma (M = 128 tokens, N = 192 rows,
@@ -31,7 +31,7 @@ constexpr int TM = 256;      // tokens per CTA tile (two MMA tiles of 128)
 constexpr int RN = 192;      // weight rows per CTA tile (MMA N)
 constexpr int KS = 64;       // k per pipeline stage (one 128-byte swizzle row of bf16)
 constexpr int STAGES = 3;
-constexpr int kDequantWarps = 8;
+constexpr int kDequantWarps = 12;
 constexpr int kThreads = (2 + kDequantWarps) * 32;
 constexpr int kXHalfBytes = 128 * KS * 2;             // 16384: one TMA box
 constexpr int kXStageBytes = 2 * kXHalfBytes;         // 32768
@@ -39,6 +39,15 @@ constexpr int kWStageBytes = RN * KS * 2;             // 24576
 constexpr int kStageBytes = kXStageBytes + kWStageBytes;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 2000000000LL;
+
+#ifdef LEV_TIMELINE
+__device__ long long lev_gemm_tl[16];  // development aid: cycle sums of CTA 0
+#define GTL_ADD(i, v) do { if (blockIdx.x == 0 && blockIdx.y == 0) lev_gemm_tl[i] += (v); } while (0)
+#define GTL_NOW() clock64()
+#else
+#define GTL_ADD(i, v) do {} while (0)
+#define GTL_NOW() 0ll
+#endif
 
 struct GemmTcArgs {
     const uint8_t* raw;   // GGUF blocks, row-major
@@ -110,6 +119,9 @@ __device__ __forceinline__ void umma_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
 
+// float(n) for 0 <= n < 2^23 without the conversion unit: 2^23 + n as bits, minus 2^23
+__device__ __forceinline__ float u2f(unsigned n) { return __uint_as_float(0x4B000000u | n) - 8388608.0f; }
+
 __device__ __forceinline__ uint4 pack8(const float* v) {
     __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
     __nv_bfloat162 c = __floats2bfloat162_rn(v[4], v[5]), d = __floats2bfloat162_rn(v[6], v[7]);
@@ -119,11 +131,31 @@ __device__ __forceinline__ uint4 pack8(const float* v) {
 // byte offset of 16-byte chunk ch (0..7) of row r inside a K-major 128B-swizzled tile
 __device__ __forceinline__ unsigned swz(int r, int ch) { return (unsigned)((r >> 3) * 1024 + (r & 7) * 128 + ((ch ^ (r & 7)) << 4)); }
 
+// Loads of weight bytes as volatile asm: they are issued where they are written (one K-step ahead
+// of their use) instead of being sunk to the first use.
+__device__ __forceinline__ uint4 ldg16(const void* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ uint2 ldg8(const void* p) {
+    uint2 v;
+    asm volatile("ld.global.nc.v2.u32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p));
+    return v;
+}
+__device__ __forceinline__ unsigned ldg2(const void* p) {
+    unsigned short v;
+    asm volatile("ld.global.nc.u16 %0, [%1];\n" : "=h"(v) : "l"(p));
+    return v;
+}
 // 8 bytes from a 2-byte aligned address
 __device__ __forceinline__ uint2 load8_u16(const uint8_t* p) {
-    const unsigned short* q = reinterpret_cast<const unsigned short*>(p);
-    const unsigned a = __ldg(q), b = __ldg(q + 1), c = __ldg(q + 2), d = __ldg(q + 3);
+    const unsigned a = ldg2(p), b = ldg2(p + 2), c = ldg2(p + 4), d = ldg2(p + 6);
     return make_uint2(a | (b << 16), c | (d << 16));
+}
+// float(byte k of w) without the conversion unit: the byte lands in the mantissa of 2^23
+__device__ __forceinline__ float byte_f(unsigned w, unsigned k) {
+    return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u + k)) - 8388608.0f;
 }
 
 // What one decode thread needs of one row for one K-step (64 columns): it is thread j = 0..3 of
@@ -147,11 +179,11 @@ __device__ __forceinline__ void load_raw(const uint8_t* row, int it, int j, bool
     if (!valid) return;
     if (TYPE == LEV_GGML_Q4_K) {
         const uint8_t* blk = row + (int64_t)(it >> 2) * LEV_Q4_K_BYTES;
-        if ((it & 3) == 0) R.hdr = __ldg(reinterpret_cast<const uint4*>(blk));
-        R.q0 = __ldg(reinterpret_cast<const uint2*>(blk + 16 + 32 * (it & 3) + 8 * j));
+        if ((it & 3) == 0) R.hdr = ldg16(blk);
+        R.q0 = ldg8(blk + 16 + 32 * (it & 3) + 8 * j);
     } else if (TYPE == LEV_GGML_Q4_0) {
         const uint8_t* blk = row + (int64_t)(2 * it + (j >> 1)) * LEV_Q4_0_BYTES;
-        R.hdr.x = __ldg(reinterpret_cast<const unsigned short*>(blk));
+        R.hdr.x = ldg2(blk);
         R.q0 = load8_u16(blk + 2 + 8 * (j & 1));
     } else {
         const uint8_t* blk = row + (int64_t)(it >> 2) * LEV_Q6_K_BYTES;
@@ -159,7 +191,7 @@ __device__ __forceinline__ void load_raw(const uint8_t* row, int it, int j, bool
         R.q0 = load8_u16(blk + 64 * c + 8 * j);
         R.q1 = load8_u16(blk + 64 * c + 32 + 8 * j);
         R.qh = load8_u16(blk + 128 + 32 * c + 8 * j);
-        R.hdr.x = __ldg(reinterpret_cast<const unsigned short*>(blk + 208));
+        R.hdr.x = ldg2(blk + 208);
         // int8 scales of the two groups for values 8j..8j+7: index 8c + 2*grp + (j >> 1)
         const unsigned s0 = blk[192 + 8 * c + 2 * g0 + (j >> 1)], s1 = blk[192 + 8 * c + 2 * (g0 + 1) + (j >> 1)];
         R.hdr.y = s0 | (s1 << 8);
@@ -194,17 +226,22 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
     } else if (TYPE == LEV_GGML_Q4_K) {
         const int c = it & 3;
         const float d = h2f(R.hdr.x & 0xffffu), dmin = h2f(R.hdr.x >> 16);
-        unsigned sc0, mn0, sc1, mn1;
-        q4k_scale_min_w(R.hdr.y, R.hdr.z, R.hdr.w, 2 * c, &sc0, &mn0);
-        q4k_scale_min_w(R.hdr.y, R.hdr.z, R.hdr.w, 2 * c + 1, &sc1, &mn1);
-        const float d0 = __fmul_rn(d, (float)sc0), m0 = __fmul_rn(dmin, (float)mn0);
-        const float d1 = __fmul_rn(d, (float)sc1), m1 = __fmul_rn(dmin, (float)mn1);
+        // 6-bit scales / mins of sub-blocks 0..3 and 4..7, one byte each
+        // (rust/crates/lev-cpu/src/lib.rs:64-74)
+        const unsigned sc_w = c < 2 ? (R.hdr.y & 0x3F3F3F3Fu) : ((R.hdr.w & 0x0F0F0F0Fu) | ((R.hdr.y >> 2) & 0x30303030u));
+        const unsigned mn_w = c < 2 ? (R.hdr.z & 0x3F3F3F3Fu) : (((R.hdr.w >> 4) & 0x0F0F0F0Fu) | ((R.hdr.z >> 2) & 0x30303030u));
+        const unsigned k0 = 2u * (c & 1);
+        const float d0 = __fmul_rn(d, byte_f(sc_w, k0)), m0 = __fmul_rn(dmin, byte_f(mn_w, k0));
+        const float d1 = __fmul_rn(d, byte_f(sc_w, k0 + 1)), m1 = __fmul_rn(dmin, byte_f(mn_w, k0 + 1));
         const unsigned w[2] = {R.q0.x, R.q0.y};
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const unsigned byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
-            lo[i] = __fsub_rn(__fmul_rn(d0, (float)(byte & 15u)), m0);
-            hi[i] = __fsub_rn(__fmul_rn(d1, (float)(byte >> 4)), m1);
+        for (int h = 0; h < 2; h++) {
+            const unsigned l4 = w[h] & 0x0F0F0F0Fu, h4 = (w[h] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                lo[4 * h + i] = __fsub_rn(__fmul_rn(d0, byte_f(l4, i)), m0);
+                hi[4 * h + i] = __fsub_rn(__fmul_rn(d1, byte_f(h4, i)), m1);
+            }
         }
     } else if (TYPE == LEV_GGML_Q4_0) {
         ch_lo = (j >> 1) * 4 + (j & 1);
@@ -212,10 +249,13 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
         const float d = h2f(R.hdr.x);
         const unsigned w[2] = {R.q0.x, R.q0.y};
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const unsigned byte = (w[i >> 2] >> (8 * (i & 3))) & 0xffu;
-            lo[i] = __fmul_rn(d, (float)(byte & 15u) - 8.0f);
-            hi[i] = __fmul_rn(d, (float)(byte >> 4) - 8.0f);
+        for (int h = 0; h < 2; h++) {
+            const unsigned l4 = w[h] & 0x0F0F0F0Fu, h4 = (w[h] >> 4) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                lo[4 * h + i] = __fmul_rn(d, __uint_as_float(__byte_perm(l4, 0x4B000000u, 0x7650u + i)) - 8388616.0f);
+                hi[4 * h + i] = __fmul_rn(d, __uint_as_float(__byte_perm(h4, 0x4B000000u, 0x7650u + i)) - 8388616.0f);
+            }
         }
     } else {
         // Q6_K (Sources/LeviathanCore/Q6.swift:10-62): level = nibble | (two high bits << 4), value = d*scale*(level-32)
@@ -230,8 +270,8 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
             const unsigned bh = (h[i >> 2] >> (8 * (i & 3))) & 0xffu;
             const unsigned na = g0 ? (ba >> 4) : (ba & 15u), nb = g0 ? (bb >> 4) : (bb & 15u);
             const unsigned ha = (bh >> (2 * g0)) & 3u, hb = (bh >> (2 * g0 + 2)) & 3u;
-            lo[i] = __fmul_rn(ds0, (float)((int)(na | (ha << 4)) - 32));
-            hi[i] = __fmul_rn(ds1, (float)((int)(nb | (hb << 4)) - 32));
+            lo[i] = __fmul_rn(ds0, __uint_as_float(0x4B000000u | na | (ha << 4)) - 8388640.0f);
+            hi[i] = __fmul_rn(ds1, __uint_as_float(0x4B000000u | nb | (hb << 4)) - 8388640.0f);
         }
     }
     *reinterpret_cast<uint4*>(wtile + swz(r, ch_lo)) = pack8(lo);
@@ -240,6 +280,7 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
 
 template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, GemmTcArgs A) {
+    const long long k_start = GTL_NOW();
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) unsigned long long full_x[STAGES], full_w[STAGES], empty[STAGES], accum_full;
     __shared__ unsigned tmem_base_s;
@@ -273,6 +314,9 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = tmem_base_s;
     volatile int* abort_flag = &abort_s;
+    long long e0 = 0;  // development timing only
+    (void)e0;
+    if (threadIdx.x == 64) GTL_ADD(8, GTL_NOW() - k_start);
 
     if (warp == 0) {
         // ---- activation tiles by TMA ----
@@ -293,7 +337,13 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             for (int it = 0; it < kt && ok; it++) {
                 const int s = it % STAGES;
                 const unsigned ph = (it / STAGES) & 1;
-                ok = mbar_wait(s32(&full_x[s]), ph, abort_flag) && mbar_wait(s32(&full_w[s]), ph, abort_flag);
+                const long long c0 = GTL_NOW();
+                ok = mbar_wait(s32(&full_x[s]), ph, abort_flag);
+                const long long c1 = GTL_NOW();
+                ok = ok && mbar_wait(s32(&full_w[s]), ph, abort_flag);
+                const long long c2 = GTL_NOW();
+                GTL_ADD(0, c1 - c0);
+                GTL_ADD(1, c2 - c1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned xs = s32(smem + (size_t)s * kStageBytes), ws = xs + kXStageBytes;
@@ -306,19 +356,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 umma_commit(s32(&empty[s]));  // the stage may be refilled when these MMAs have read it
             }
             umma_commit(s32(&accum_full));
+            GTL_ADD(2, 1);
         }
     } else {
         // ---- weight decode: thread = (3 rows 64 apart) x (byte group j); the raw bytes of the
         // next K-step are requested before this one is decoded ----
         const int td = threadIdx.x - 64, j = td & 3, rb = td >> 2;
-        constexpr int NR = RN / 64;
+        constexpr int kRowStep = kDequantWarps * 8;   // rows covered by one pass of the decode threads
+        constexpr int NR = RN / kRowStep;
+        static_assert(RN % kRowStep == 0, "decode threads tile the weight rows evenly");
         RowRaw<TYPE> cur[NR], nxt[NR];
         const uint8_t* rowp[NR];
         bool valid[NR];
 #pragma unroll
         for (int i = 0; i < NR; i++) {
-            valid[i] = r0 + rb + 64 * i < A.rows;
-            rowp[i] = A.raw + (r0 + (valid[i] ? rb + 64 * i : 0)) * A.row_bytes;
+            valid[i] = r0 + rb + kRowStep * i < A.rows;
+            rowp[i] = A.raw + (r0 + (valid[i] ? rb + kRowStep * i : 0)) * A.row_bytes;
             load_raw<TYPE>(rowp[i], 0, j, valid[i], cur[i]);
         }
         bool ok = true;
@@ -331,24 +384,29 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                     load_raw<TYPE>(rowp[i], it + 1, j, valid[i], nxt[i]);
                 }
             }
+            const long long d0 = GTL_NOW();
             if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
+            const long long d1 = GTL_NOW();
+            if (threadIdx.x == 64) GTL_ADD(3, d1 - d0);
             if (!ok) break;
             unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
 #pragma unroll
-            for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + 64 * i);
+            for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + kRowStep * i);
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(s32(&full_w[s]));
+            if (threadIdx.x == 64) GTL_ADD(4, GTL_NOW() - d1);
 #pragma unroll
             for (int i = 0; i < NR; i++) cur[i] = nxt[i];
         }
         // ---- epilogue: TMEM -> Y ----
-        if (ok && mbar_wait(s32(&accum_full), 0, abort_flag)) {
+        e0 = GTL_NOW();
+        if (ok && warp < 10 && mbar_wait(s32(&accum_full), 0, abort_flag)) {
+            if (threadIdx.x == 64) GTL_ADD(5, GTL_NOW() - e0);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int quarter = warp & 3, half = (warp - 2) >> 2;
             if (half < halves) {
-                const int token = t0 + half * 128 + quarter * 32 + lane;
-                float* yrow = A.y + (int64_t)token * A.rows + r0;
+                unsigned* stg = reinterpret_cast<unsigned*>(smem) + (warp - 2) * (32 * 36);
 #pragma unroll 1
                 for (int c = 0; c < RN; c += 32) {
                     unsigned v[32];
@@ -364,21 +422,37 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                         : "r"(taddr)
                         : "memory");
                     asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-                    if (token < A.tokens) {
-                        if (r0 + c + 32 <= A.rows && A.y_vec) {
+                    // transpose through shared memory (the pipeline stages are idle now) so that every
+                    // store instruction writes whole 128-byte lines of four token rows
+                    __syncwarp();
 #pragma unroll
-                            for (int q = 0; q < 32; q += 4)
-                                *reinterpret_cast<uint4*>(yrow + c + q) = make_uint4(v[q], v[q + 1], v[q + 2], v[q + 3]);
-                        } else {
+                    for (int q = 0; q < 32; q += 4)
+                        *reinterpret_cast<uint4*>(stg + lane * 36 + q) = make_uint4(v[q], v[q + 1], v[q + 2], v[q + 3]);
+                    __syncwarp();
+                    const int col4 = (lane & 7) * 4;
 #pragma unroll
-                            for (int q = 0; q < 32; q++)
-                                if (r0 + c + q < A.rows) yrow[c + q] = __uint_as_float(v[q]);
+                    for (int i = 0; i < 8; i++) {
+                        const int tl = i * 4 + (lane >> 3);
+                        const int tok = t0 + half * 128 + quarter * 32 + tl;
+                        const uint4 o = *reinterpret_cast<const uint4*>(stg + tl * 36 + col4);
+                        if (tok < A.tokens) {
+                            float* dst = A.y + (int64_t)tok * A.rows + r0 + c + col4;
+                            if (r0 + c + col4 + 4 <= A.rows && A.y_vec) {
+                                *reinterpret_cast<uint4*>(dst) = o;
+                            } else {
+                                const unsigned ov[4] = {o.x, o.y, o.z, o.w};
+#pragma unroll
+                                for (int q = 0; q < 4; q++)
+                                    if (r0 + c + col4 + q < A.rows) dst[q] = __uint_as_float(ov[q]);
+                            }
                         }
                     }
                 }
             }
         }
     }
+    if (threadIdx.x == 64) GTL_ADD(6, GTL_NOW() - e0);
+    if (threadIdx.x == 64) GTL_ADD(7, GTL_NOW() - k_start);
     if (abort_s && threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -387,6 +461,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(kTmemCols) : "memory");
     }
 }
+
+#ifdef LEV_TIMELINE
+}  // namespace
+extern "C" int lev_debug_gemm_timeline(long long* out, int reset) {
+    if (reset) {
+        long long z[16] = {};
+        return (int)cudaMemcpyToSymbol(lev_gemm_tl, z, sizeof z);
+    }
+    return (int)cudaMemcpyFromSymbol(out, lev_gemm_tl, sizeof(long long) * 16);
+}
+namespace {
+#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
