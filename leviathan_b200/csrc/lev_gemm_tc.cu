@@ -359,9 +359,12 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             GTL_ADD(2, 1);
         }
     } else {
-        // ---- weight decode: thread = (3 rows 64 apart) x (byte group j); the raw bytes of the
+        // ---- weight decode: thread = (2 rows 96 apart) x (byte group j); the raw bytes of the
         // next K-step are requested before this one is decoded ----
-        const int td = threadIdx.x - 64, j = td & 3, rb = td >> 2;
+        // lanes 0..7 of a warp take byte group 0 of eight consecutive rows, lanes 8..15 group 1, ...:
+        // the eight 16-byte stores of one shared-memory wavefront then fall into eight different
+        // bank groups of the swizzled tile
+        const int j = lane >> 3, rb = (warp - 2) * 8 + (lane & 7);
         constexpr int kRowStep = kDequantWarps * 8;   // rows covered by one pass of the decode threads
         constexpr int NR = RN / kRowStep;
         static_assert(RN % kRowStep == 0, "decode threads tile the weight rows evenly");
