@@ -45,7 +45,7 @@ __device__ long long lev_gemm_tl[16];  // development aid: cycle sums of CTA 0
 #define GTL_ADD(i, v) do { if (blockIdx.x == 0 && blockIdx.y == 0) lev_gemm_tl[i] += (v); } while (0)
 #define GTL_NOW() clock64()
 #else
-#define GTL_ADD(i, v) do {} while (0)
+#define GTL_ADD(i, v) do { (void)(v); } while (0)
 #define GTL_NOW() 0ll
 #endif
 
@@ -118,9 +118,6 @@ __device__ __forceinline__ void umma_bf16(unsigned d_tmem, uint64_t adesc, uint6
 __device__ __forceinline__ void umma_commit(unsigned bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(bar) : "memory");
 }
-
-// float(n) for 0 <= n < 2^23 without the conversion unit: 2^23 + n as bits, minus 2^23
-__device__ __forceinline__ float u2f(unsigned n) { return __uint_as_float(0x4B000000u | n) - 8388608.0f; }
 
 __device__ __forceinline__ uint4 pack8(const float* v) {
     __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
@@ -195,20 +192,6 @@ __device__ __forceinline__ void load_raw(const uint8_t* row, int it, int j, bool
         // int8 scales of the two groups for values 8j..8j+7: index 8c + 2*grp + (j >> 1)
         const unsigned s0 = blk[192 + 8 * c + 2 * g0 + (j >> 1)], s1 = blk[192 + 8 * c + 2 * (g0 + 1) + (j >> 1)];
         R.hdr.y = s0 | (s1 << 8);
-    }
-}
-
-// scale and min of Q4_K sub-block sb from the 12 packed bytes held in three words
-// (rust/crates/lev-cpu/src/lib.rs:64-74)
-__device__ __forceinline__ void q4k_scale_min_w(unsigned w0, unsigned w1, unsigned w2, int sb, unsigned* sc, unsigned* mn) {
-    const unsigned long long lo = (unsigned long long)w0 | ((unsigned long long)w1 << 32);
-    auto byte = [&](int i) -> unsigned { return i < 8 ? (unsigned)(lo >> (8 * i)) & 0xffu : (w2 >> (8 * (i - 8))) & 0xffu; };
-    if (sb < 4) {
-        *sc = byte(sb) & 63u;
-        *mn = byte(sb + 4) & 63u;
-    } else {
-        *sc = (byte(sb + 4) & 0x0Fu) | ((byte(sb - 4) >> 6) << 4);
-        *mn = (byte(sb + 4) >> 4) | ((byte(sb) >> 6) << 4);
     }
 }
 
