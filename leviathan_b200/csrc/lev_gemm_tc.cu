@@ -448,6 +448,235 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     }
 }
 
+// ---------------------------------------------------------------------------
+// Grouped form for the routed MoE at prefill-sized token counts: operands swapped, so that the
+// weight rows are the MMA's M (128) and the tokens of one expert its N (16..256 in steps of 16;
+// experts rarely see many tokens and a padded M would waste most of the tensor work).
+//   job j (device-side table) = up to 256 consecutive grouped positions of one expert;
+//   CTA (rt, j): rows [128*rt, +128) of the job's expert slice x the job's tokens, whole K.
+//   X rows come from a position-ordered bf16 buffer (TMA, 128 rows per box);
+//   D[row][position] is stored as out[out_row(position)][row]: a warp writes 32 consecutive rows.
+// ---------------------------------------------------------------------------
+constexpr int GR_STAGES = 4;
+constexpr int GR_DECODE_WARPS = 8;
+constexpr int GR_THREADS = (2 + GR_DECODE_WARPS) * 32;
+constexpr int GR_W_BYTES = 128 * KS * 2;               // 16384
+constexpr int GR_STAGE_BYTES = GR_W_BYTES + kXStageBytes;  // 49152
+constexpr int GR_TMEM_COLS = 256;
+constexpr int GR_JOB_TOKENS = 256;
+
+struct GroupedArgs {
+    const uint8_t* raw;      // expert-stacked tensor, row-major GGUF blocks
+    int64_t row_bytes;
+    int rows_per_expert;
+    int cols;                // K
+    const int* njobs;        // [1]
+    const int* job_slice;    // [job] local expert
+    const int* job_pos;      // [job][GR_JOB_TOKENS] grouped positions (first entry = first position)
+    const int* offsets;      // [experts + 1] grouped offsets by global expert id
+    int first_expert;        // global id of local expert 0
+    const int* out_row;      // [position] row of `out` for that position, NULL: the position itself
+    float* out;              // [rows of out][out_ld]
+    int64_t out_ld;
+    int* status;
+};
+
+template <int TYPE>
+__global__ void __launch_bounds__(GR_THREADS, 1) k_gemm_tc_grouped(const __grid_constant__ CUtensorMap xmap, GroupedArgs A) {
+    const int job = blockIdx.y;
+    if (job >= *A.njobs) return;  // whole CTA leaves before touching barriers or tensor memory
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) unsigned long long full_x[GR_STAGES], full_w[GR_STAGES], empty[GR_STAGES], accum_full;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    const int e = A.job_slice[job];
+    const int pos0 = A.job_pos[(int64_t)job * GR_JOB_TOKENS];
+    int cnt = A.offsets[A.first_expert + e + 1] - pos0;
+    cnt = cnt > GR_JOB_TOKENS ? GR_JOB_TOKENS : cnt;
+    const int n_pad = (cnt + 15) & ~15;           // MMA N
+    const int boxes = cnt > 128 ? 2 : 1;
+    const int row0 = blockIdx.x * 128;            // first row inside the expert slice
+    const int kt = A.cols / KS;
+    const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_pad >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < GR_STAGES; s++) {
+            mbar_init(s32(&full_x[s]), 1);
+            mbar_init(s32(&full_w[s]), GR_DECODE_WARPS);
+            mbar_init(s32(&empty[s]), 1);
+        }
+        mbar_init(s32(&accum_full), 1);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(GR_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_s;
+    volatile int* abort_flag = &abort_s;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int it = 0; it < kt; it++) {
+                const int s = it % GR_STAGES;
+                if (it >= GR_STAGES && !mbar_wait(s32(&empty[s]), ((it / GR_STAGES) & 1) ^ 1, abort_flag)) break;
+                const unsigned dst = s32(smem + (size_t)s * GR_STAGE_BYTES + GR_W_BYTES);
+                mbar_expect_tx(s32(&full_x[s]), boxes * kXHalfBytes);
+                tma_load_2d(dst, &xmap, it * KS, pos0, s32(&full_x[s]));
+                if (boxes == 2) tma_load_2d(dst + kXHalfBytes, &xmap, it * KS, pos0 + 128, s32(&full_x[s]));
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            bool ok = true;
+            for (int it = 0; it < kt && ok; it++) {
+                const int s = it % GR_STAGES;
+                const unsigned ph = (it / GR_STAGES) & 1;
+                ok = mbar_wait(s32(&full_x[s]), ph, abort_flag) && mbar_wait(s32(&full_w[s]), ph, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const unsigned ws = s32(smem + (size_t)s * GR_STAGE_BYTES), xs = ws + GR_W_BYTES;
+#pragma unroll
+                for (int kk = 0; kk < KS / 16; kk++) {
+                    const uint64_t adesc = umma_desc(ws + kk * 32), bdesc = umma_desc(xs + kk * 32);
+                    const unsigned acc = (it | kk) ? 1u : 0u;
+                    asm volatile(
+                        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n" ::"r"(
+                            tmem_base),
+                        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+                        : "memory");
+                }
+                umma_commit(s32(&empty[s]));
+            }
+            umma_commit(s32(&accum_full));
+        }
+    } else {
+        // ---- weight decode: thread = (2 rows 64 apart) x (byte group j) ----
+        const int j = lane >> 3, rb = (warp - 2) * 8 + (lane & 7);
+        constexpr int NR = 2;
+        RowRaw<TYPE> cur[NR], nxt[NR];
+        const uint8_t* rowp[NR];
+        bool valid[NR];
+#pragma unroll
+        for (int i = 0; i < NR; i++) {
+            const int r = row0 + rb + 64 * i;
+            valid[i] = r < A.rows_per_expert;
+            rowp[i] = A.raw + ((int64_t)e * A.rows_per_expert + (valid[i] ? r : 0)) * A.row_bytes;
+            load_raw<TYPE>(rowp[i], 0, j, valid[i], cur[i]);
+        }
+        bool ok = true;
+        for (int it = 0; it < kt && ok; it++) {
+            const int s = it % GR_STAGES;
+            if (it + 1 < kt) {
+#pragma unroll
+                for (int i = 0; i < NR; i++) {
+                    nxt[i] = cur[i];
+                    load_raw<TYPE>(rowp[i], it + 1, j, valid[i], nxt[i]);
+                }
+            }
+            if (it >= GR_STAGES) ok = mbar_wait(s32(&empty[s]), ((it / GR_STAGES) & 1) ^ 1, abort_flag);
+            if (!ok) break;
+            unsigned char* wtile = smem + (size_t)s * GR_STAGE_BYTES;
+#pragma unroll
+            for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + 64 * i);
+            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(s32(&full_w[s]));
+#pragma unroll
+            for (int i = 0; i < NR; i++) cur[i] = nxt[i];
+        }
+        // ---- epilogue: lane = weight row, TMEM columns = positions ----
+        if (ok && mbar_wait(s32(&accum_full), 0, abort_flag)) {
+            asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+            const int quarter = warp & 3, chalf = (warp - 2) >> 2;
+            const int row = row0 + quarter * 32 + lane;
+#pragma unroll 1
+            for (int c = 32 * chalf; c < n_pad; c += 64) {
+                unsigned v[32];
+                const unsigned taddr = tmem_base + ((unsigned)(quarter * 32) << 16) + (unsigned)c;
+                // n_pad is a multiple of 16: the last chunk may hold 16 columns only
+                if (c + 32 <= n_pad) {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                          "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                          "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                        : "r"(taddr)
+                        : "memory");
+                } else {
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                          "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                        : "r"(taddr)
+                        : "memory");
+#pragma unroll
+                    for (int q = 16; q < 32; q++) v[q] = 0u;
+                }
+                asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                if (row < A.rows_per_expert) {
+#pragma unroll
+                    for (int q = 0; q < 32; q++) {
+                        if (c + q < cnt) {
+                            const int pos = pos0 + c + q;
+                            const int orow = A.out_row ? A.out_row[pos] : pos;
+                            A.out[(int64_t)orow * A.out_ld + row] = __uint_as_float(v[q]);
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (abort_s && threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(GR_TMEM_COLS) : "memory");
+    }
+}
+
+// x f32 [tokens][cols] -> position-ordered bf16 rows: row pos = token of pair perm[pos]
+__global__ void k_gather_bf16(const float* __restrict__ x, const int* __restrict__ perm, const int* __restrict__ total_pos,
+                              int top_k, int cols, __nv_bfloat16* __restrict__ out) {
+    const int64_t n = (int64_t)(*total_pos) * (cols / 4);
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pos = i / (cols / 4);
+        const int c4 = (int)(i - pos * (cols / 4));
+        const float4 v = __ldg(reinterpret_cast<const float4*>(x + (int64_t)(perm[pos] / top_k) * cols) + c4);
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        reinterpret_cast<uint2*>(out + pos * cols)[c4] = make_uint2(*reinterpret_cast<unsigned*>(&a), *reinterpret_cast<unsigned*>(&b));
+    }
+}
+
+// gu f32 [pos][2*inter] -> bf16 [pos][inter] of gelu_tanh(gate) * up
+// (Sources/LeviathanCore/Gemma4.swift:4364-4377)
+__global__ void k_act_grouped_bf16(const float* __restrict__ gu, const int* __restrict__ total_pos, int inter,
+                                   __nv_bfloat16* __restrict__ out) {
+    const int64_t n = (int64_t)(*total_pos) * inter;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t pos = i / inter;
+        const int k = (int)(i - pos * inter);
+        const float g = gu[pos * 2 * inter + k], u = gu[pos * 2 * inter + inter + k];
+        const float inner = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+        const float ex = expf(-2.0f * fabsf(inner));
+        const float th = copysignf((1.0f - ex) / (1.0f + ex), inner);
+        out[i] = __float2bfloat16_rn(0.5f * g * (1.0f + th) * u);
+    }
+}
+
 #ifdef LEV_TIMELINE
 }  // namespace
 extern "C" int lev_debug_gemm_timeline(long long* out, int reset) {
@@ -528,4 +757,80 @@ int lev_gemm_tc_run(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int6
     if (st) return st;
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc");
+}
+
+// ---------------------------------------------------------------------------
+// grouped form: host side
+// ---------------------------------------------------------------------------
+bool lev_gemm_grouped_supported(const lev_weights* w, int rows_per_expert) {
+    if (getenv("LEV_GEMM_TC") && atoi(getenv("LEV_GEMM_TC")) == 0) return false;
+    if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0 && w->type != LEV_GGML_Q6_K) return false;
+    if (w->cols % KS != 0 || rows_per_expert < 1) return false;
+    return encode_tiled() != nullptr;
+}
+
+int lev_gemm_grouped_job_tokens(void) { return GR_JOB_TOKENS; }
+
+// xg: bf16 [capacity_rows][w->cols], rows in grouped-position order.
+int lev_gemm_grouped_run(lev_ctx* ctx, const lev_weights* w, int rows_per_expert, const void* xg_bf16, int64_t capacity_rows,
+                         int max_jobs, const int* njobs, const int* job_slice, const int* job_pos, const int* offsets,
+                         int first_expert, const int* out_row, float* out, int64_t out_ld) {
+    EncodeTiledFn enc = encode_tiled();
+    if (!enc) return lev_fail(ctx, LEV_UNSUPPORTED, "cuTensorMapEncodeTiled is not available");
+    if (((uintptr_t)xg_bf16 & 15) != 0) return lev_fail(ctx, LEV_BAD_ARGUMENT, "grouped activations must be 16-byte aligned");
+    CUtensorMap map;
+    const cuuint64_t gdim[2] = {(cuuint64_t)w->cols, (cuuint64_t)capacity_rows};
+    const cuuint64_t gstride[1] = {(cuuint64_t)w->cols * 2};
+    const cuuint32_t box[2] = {KS, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xg_bf16), gdim, gstride, box, estr,
+                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (cr != CUDA_SUCCESS) return lev_fail(ctx, LEV_KERNEL_FAILED, "cuTensorMapEncodeTiled failed (%d)", (int)cr);
+    GroupedArgs A;
+    A.raw = w->raw;
+    A.row_bytes = w->blocks_per_row * lev_block_bytes(w->type);
+    A.rows_per_expert = rows_per_expert;
+    A.cols = (int)w->cols;
+    A.njobs = njobs;
+    A.job_slice = job_slice;
+    A.job_pos = job_pos;
+    A.offsets = offsets;
+    A.first_expert = first_expert;
+    A.out_row = out_row;
+    A.out = out;
+    A.out_ld = out_ld;
+    A.status = ctx->d_status;
+    dim3 grid((unsigned)((rows_per_expert + 127) / 128), (unsigned)max_jobs);
+    const size_t smem = (size_t)GR_STAGES * GR_STAGE_BYTES + 1024;
+    static bool configured[3][16] = {};
+    const int ti = w->type == LEV_GGML_Q4_K ? 0 : (w->type == LEV_GGML_Q6_K ? 1 : 2);
+    if (!configured[ti][ctx->device & 15]) {
+        if (ti == 0) LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc_grouped<LEV_GGML_Q4_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (ti == 1) LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc_grouped<LEV_GGML_Q6_K>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        if (ti == 2) LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc_grouped<LEV_GGML_Q4_0>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        configured[ti][ctx->device & 15] = true;
+    }
+    if (ti == 0) k_gemm_tc_grouped<LEV_GGML_Q4_K><<<grid, GR_THREADS, smem, ctx->stream>>>(map, A);
+    if (ti == 1) k_gemm_tc_grouped<LEV_GGML_Q6_K><<<grid, GR_THREADS, smem, ctx->stream>>>(map, A);
+    if (ti == 2) k_gemm_tc_grouped<LEV_GGML_Q4_0><<<grid, GR_THREADS, smem, ctx->stream>>>(map, A);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc_grouped");
+}
+
+int lev_gather_bf16(lev_ctx* ctx, const float* x, const int* perm, const int* total_pos, int64_t max_pos, int top_k, int cols,
+                    void* out_bf16) {
+    int64_t g = (max_pos * (cols / 4) + 255) / 256, cap = (int64_t)ctx->prop.multiProcessorCount * 8;
+    k_gather_bf16<<<(unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), 256, 0, ctx->stream>>>(x, perm, total_pos, top_k, cols,
+                                                                                        (__nv_bfloat16*)out_bf16);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_gather_bf16");
+}
+
+int lev_act_grouped_bf16(lev_ctx* ctx, const float* gu, const int* total_pos, int64_t max_pos, int inter, void* out_bf16) {
+    int64_t g = (max_pos * inter + 255) / 256, cap = (int64_t)ctx->prop.multiProcessorCount * 8;
+    k_act_grouped_bf16<<<(unsigned)(g > cap ? cap : (g < 1 ? 1 : g)), 256, 0, ctx->stream>>>(gu, total_pos, inter,
+                                                                                              (__nv_bfloat16*)out_bf16);
+    ctx->launches++;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_act_grouped_bf16");
 }

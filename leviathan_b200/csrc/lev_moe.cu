@@ -552,6 +552,16 @@ int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, in
     return lev_cuda_check(ctx, cudaGetLastError(), "k_router_topk");
 }
 
+// grouped dequant-GEMM on the tensor cores (lev_gemm_tc.cu)
+bool lev_gemm_grouped_supported(const lev_weights* w, int rows_per_expert);
+int lev_gemm_grouped_job_tokens(void);
+int lev_gemm_grouped_run(lev_ctx* ctx, const lev_weights* w, int rows_per_expert, const void* xg_bf16, int64_t capacity_rows,
+                         int max_jobs, const int* njobs, const int* job_slice, const int* job_pos, const int* offsets,
+                         int first_expert, const int* out_row, float* out, int64_t out_ld);
+int lev_gather_bf16(lev_ctx* ctx, const float* x, const int* perm, const int* total_pos, int64_t max_pos, int top_k, int cols,
+                    void* out_bf16);
+int lev_act_grouped_bf16(lev_ctx* ctx, const float* gu, const int* total_pos, int64_t max_pos, int inter, void* out_bf16);
+
 struct JobTable {
     int cmax, max_jobs;
     int *njobs, *job_slice, *job_token, *job_pos, *job_pair;
@@ -606,7 +616,13 @@ int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, 
     // build their activation tables themselves (no preparation launches, no table memory)
     const bool sliced = pairs <= 64 && lev_dense_jobs_supported(ctx, w->gate_up, gu_rows_, (int)pairs, x, w->hidden) &&
                         lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)pairs, x, gu_rows_);
-    const int cmax = sliced ? 1 : (pairs <= 2 * (int64_t)w->local_count ? 4 : 8), terms = 2;
+    // prefill-sized calls: grouped dequant-GEMM on the tensor cores (bf16 operands, f32 accumulate;
+    // the 2e-2 bar of tensor-core prefill applies to this form)
+    const char* mp = getenv("LEV_MOE_GEMM_MIN_PAIRS");
+    const int64_t min_pairs = mp && *mp ? atoll(mp) : 512;
+    const bool tensor = !sliced && pairs >= min_pairs && w->hidden % 4 == 0 && lev_gemm_grouped_supported(w->gate_up, (int)gu_rows_) &&
+                        lev_gemm_grouped_supported(w->down, w->hidden);
+    const int cmax = sliced ? 1 : tensor ? lev_gemm_grouped_job_tokens() : (pairs <= 2 * (int64_t)w->local_count ? 4 : 8), terms = 2;
     int64_t mj = (int64_t)w->local_count + pairs / cmax;
     if (mj > pairs) mj = pairs;
     const int max_jobs = (int)mj;
@@ -642,10 +658,24 @@ int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, 
     size_t tb_dn = lev_stream_table_bytes(w->down, cmax, terms, max_jobs, nullptr);
     size_t tb = tb_gu > tb_dn ? tb_gu : tb_dn;
     size_t gu_bytes = ((size_t)pairs * gu_rows * sizeof(float) + 255) & ~(size_t)255;
+    if (tensor) tb = (((size_t)pairs * w->hidden * 2 + 255) & ~(size_t)255) + (((size_t)pairs * w->inter * 2 + 255) & ~(size_t)255);
     void* cb;
     LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_C, gu_bytes + tb + 256, &cb));
     float* gu = (float*)cb;
     void* tables = (char*)cb + gu_bytes;
+    if (tensor) {
+        void* xg = tables;
+        void* actg = (char*)tables + (((size_t)pairs * w->hidden * 2 + 255) & ~(size_t)255);
+        const int* total_pos = offsets + w->experts;
+        LEV_TRY(lev_gather_bf16(ctx, x, perm, total_pos, pairs, top_k, w->hidden, xg));
+        LEV_TRY(lev_gemm_grouped_run(ctx, w->gate_up, (int)gu_rows, xg, pairs, max_jobs, jt.njobs, jt.job_slice, jt.job_pos, offsets,
+                                     w->local_first, nullptr, gu, gu_rows));
+        LEV_TRY(lev_act_grouped_bf16(ctx, gu, total_pos, pairs, w->inter, actg));
+        LEV_TRY(lev_gemm_grouped_run(ctx, w->down, w->hidden, actg, pairs, max_jobs, jt.njobs, jt.job_slice, jt.job_pos, offsets,
+                                     w->local_first, perm, y_pairs, w->hidden));
+        if (act_out) LEV_TRY(lev_moe_launch_act(ctx, gu, perm, offsets + w->experts, pairs, w->inter, act_out));
+        return LEV_OK;
+    }
     if (sliced) {
         LEV_TRY(lev_dense_jobs_run(ctx, w->gate_up, gu_rows, max_jobs, jt.njobs, jt.job_slice, jt.job_token, jt.job_pos, x,
                                    w->hidden, 0, gu, gu_rows));
