@@ -450,20 +450,22 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 
 // ---------------------------------------------------------------------------
 // Grouped form for the routed MoE at prefill-sized token counts: operands swapped, so that the
-// weight rows are the MMA's M (128) and the tokens of one expert its N (16..256 in steps of 16;
+// weight rows are the MMA's M (128) and the tokens of one expert its N (16..128 in steps of 16;
 // experts rarely see many tokens and a padded M would waste most of the tensor work).
-//   job j (device-side table) = up to 256 consecutive grouped positions of one expert;
+//   job j (device-side table) = up to 128 consecutive grouped positions of one expert;
 //   CTA (rt, j): rows [128*rt, +128) of the job's expert slice x the job's tokens, whole K.
 //   X rows come from a position-ordered bf16 buffer (TMA, 128 rows per box);
 //   D[row][position] is stored as out[out_row(position)][row]: a warp writes 32 consecutive rows.
 // ---------------------------------------------------------------------------
-constexpr int GR_STAGES = 4;
+// The kernel is bound by the weight decode (an expert's weights are decoded for a few dozen tokens
+// only), so two CTAs share an SM: 3 stages x (16 KB weights + 16 KB tokens) and 128 TMEM columns each.
+constexpr int GR_STAGES = 3;
 constexpr int GR_DECODE_WARPS = 8;
 constexpr int GR_THREADS = (2 + GR_DECODE_WARPS) * 32;
 constexpr int GR_W_BYTES = 128 * KS * 2;               // 16384
-constexpr int GR_STAGE_BYTES = GR_W_BYTES + kXStageBytes;  // 49152
-constexpr int GR_TMEM_COLS = 256;
-constexpr int GR_JOB_TOKENS = 256;
+constexpr int GR_STAGE_BYTES = GR_W_BYTES + kXHalfBytes;   // 32768
+constexpr int GR_TMEM_COLS = 128;
+constexpr int GR_JOB_TOKENS = 128;
 
 struct GroupedArgs {
     const uint8_t* raw;      // expert-stacked tensor, row-major GGUF blocks
@@ -482,7 +484,7 @@ struct GroupedArgs {
 };
 
 template <int TYPE>
-__global__ void __launch_bounds__(GR_THREADS, 1) k_gemm_tc_grouped(const __grid_constant__ CUtensorMap xmap, GroupedArgs A) {
+__global__ void __launch_bounds__(GR_THREADS, 2) k_gemm_tc_grouped(const __grid_constant__ CUtensorMap xmap, GroupedArgs A) {
     const int job = blockIdx.y;
     if (job >= *A.njobs) return;  // whole CTA leaves before touching barriers or tensor memory
     extern __shared__ unsigned char smem_dyn[];
@@ -496,7 +498,6 @@ __global__ void __launch_bounds__(GR_THREADS, 1) k_gemm_tc_grouped(const __grid_
     int cnt = A.offsets[A.first_expert + e + 1] - pos0;
     cnt = cnt > GR_JOB_TOKENS ? GR_JOB_TOKENS : cnt;
     const int n_pad = (cnt + 15) & ~15;           // MMA N
-    const int boxes = cnt > 128 ? 2 : 1;
     const int row0 = blockIdx.x * 128;            // first row inside the expert slice
     const int kt = A.cols / KS;
     const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_pad >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
@@ -529,9 +530,8 @@ __global__ void __launch_bounds__(GR_THREADS, 1) k_gemm_tc_grouped(const __grid_
                 const int s = it % GR_STAGES;
                 if (it >= GR_STAGES && !mbar_wait(s32(&empty[s]), ((it / GR_STAGES) & 1) ^ 1, abort_flag)) break;
                 const unsigned dst = s32(smem + (size_t)s * GR_STAGE_BYTES + GR_W_BYTES);
-                mbar_expect_tx(s32(&full_x[s]), boxes * kXHalfBytes);
+                mbar_expect_tx(s32(&full_x[s]), kXHalfBytes);
                 tma_load_2d(dst, &xmap, it * KS, pos0, s32(&full_x[s]));
-                if (boxes == 2) tma_load_2d(dst + kXHalfBytes, &xmap, it * KS, pos0 + 128, s32(&full_x[s]));
             }
         }
     } else if (warp == 1) {

@@ -404,7 +404,9 @@ __global__ void __launch_bounds__(1024) k_group_fast(GroupArgs G, int nchunks) {
         if (G.job_slice && e >= G.first && e < G.first + G.count) {
             const int nj = (hist[e] + G.cmax - 1) / G.cmax;
             for (int j = 0; j < nj; j++) G.job_slice[jobbase[e] + j] = e - G.first;
-            for (int r = hist[e]; r < nj * G.cmax; r++) {  // empty columns of the expert's last job
+            // empty columns of the expert's last job (wide jobs, which only the grouped GEMM uses, are
+            // described by their first position and the expert's count: their tails are not filled)
+            for (int r = hist[e]; r < nj * G.cmax && G.cmax <= 8; r++) {
                 const int q = (jobbase[e] + nj - 1) * G.cmax + (r - (nj - 1) * G.cmax);
                 G.job_token[q] = -1;
                 G.job_pos[q] = -1;
