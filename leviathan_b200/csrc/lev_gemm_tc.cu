@@ -458,8 +458,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 //   D[row][position] is stored as out[out_row(position)][row]: a warp writes 32 consecutive rows.
 // ---------------------------------------------------------------------------
 // The kernel is bound by the weight decode (an expert's weights are decoded for a few dozen tokens
-// only), so two CTAs share an SM: 3 stages x (16 KB weights + 16 KB tokens) and 128 TMEM columns each.
-constexpr int GR_STAGES = 3;
+// only), so three CTAs share an SM: 2 stages x (16 KB weights + 16 KB tokens) and 128 TMEM columns each.
+constexpr int GR_STAGES = 2;
 constexpr int GR_DECODE_WARPS = 8;
 constexpr int GR_THREADS = (2 + GR_DECODE_WARPS) * 32;
 constexpr int GR_W_BYTES = 128 * KS * 2;               // 16384
@@ -484,7 +484,7 @@ struct GroupedArgs {
 };
 
 template <int TYPE>
-__global__ void __launch_bounds__(GR_THREADS, 2) k_gemm_tc_grouped(const __grid_constant__ CUtensorMap xmap, GroupedArgs A) {
+__global__ void __launch_bounds__(GR_THREADS, 3) k_gemm_tc_grouped(const __grid_constant__ CUtensorMap xmap, GroupedArgs A) {
     const int job = blockIdx.y;
     if (job >= *A.njobs) return;  // whole CTA leaves before touching barriers or tensor memory
     extern __shared__ unsigned char smem_dyn[];
