@@ -447,7 +447,12 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
     mw = ctx.moe_upload(router, torch.cat(gu), torch.cat(dn), MOE_EXPERTS, MOE_HIDDEN, MOE_INTER, first, count)
     del gu, dn
     moe = {}
-    for tokens in (1, 32, 512):
+    for batch in (1, 32, 512):
+        # expert-parallel ranks each bring tokens: the batch is split across ranks when it divides
+        # (same global batch as one GPU), a single token cannot be split and runs one per rank
+        split = world > 1 and batch % world == 0
+        tokens = batch // world if split else batch
+        global_tokens = batch if (split or world == 1) else batch * world
         xt = [torch.randn((tokens, MOE_HIDDEN), generator=g, device=dev) for _ in range(8)]
         yo = torch.empty((tokens, MOE_HIDDEN), device=dev)
         if world > 1:
@@ -472,9 +477,11 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         idx = ctx.moe_route(mw, xt[0], MOE_TOPK)[0]
         distinct = int(torch.unique(idx).numel())
         byts = MOE_ROUTER_BYTES + distinct * MOE_EXPERT_BYTES
-        moe[f"T{tokens}"] = {"ms_per_layer": ms, "tokens_per_s": tokens / (ms * 1e-3), "distinct_experts": distinct,
-                             "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
-                             "hbm_frac": byts / ms / 1e6 / peaks["hbm_gbs"]}
+        entry = {"ms_per_layer": ms, "global_tokens": global_tokens, "tokens_per_s": global_tokens / (ms * 1e-3)}
+        if world == 1:
+            entry.update({"distinct_experts": distinct, "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
+                          "hbm_frac": byts / ms / 1e6 / peaks["hbm_gbs"]})
+        moe[f"T{batch}"] = entry
     out["moe_layer"] = {"workload": "128 experts Q4_0 (GU 1408x2816, DN 2816x704), top-8, hidden 2816",
                         "parallelism": "single GPU" if world == 1 else f"expert-parallel over {world} GPUs", **moe}
     mw.free()

@@ -210,12 +210,19 @@ extern "C" int lev_moe_layer_ep(lev_ctx* ctx, const lev_moe_weights* w, const fl
     LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_D, yb + 256, &d));
     float* ypairs = (float*)d;
 
+    // every rank routes its own tokens (the router is replicated); tokens and routing are then
+    // gathered so that each rank can run the pairs of its resident experts
+    int32_t* idx_l = idx + (size_t)rank * tokens * top_k;
+    float* wts_l = wts + (size_t)rank * tokens * top_k;
+    LEV_TRY(lev_moe_route_dev(ctx, w, x, tokens, top_k, idx_l, wts_l, scores));
+    LEV_NCCL(ctx, g_nccl.GroupStart());
     LEV_NCCL(ctx, g_nccl.AllGather(x, xall, (size_t)tokens * w->hidden, NCCL_FLOAT32, ctx->dist->comm, ctx->stream));
-    LEV_TRY(lev_moe_route_dev(ctx, w, xall, tall, top_k, idx, wts, scores));
-    // pairs whose experts live elsewhere contribute zero to this rank's partial
-    LEV_CUDA(ctx, cudaMemsetAsync(ypairs, 0, (size_t)pairs * w->hidden * 4, ctx->stream));
+    LEV_NCCL(ctx, g_nccl.AllGather(idx_l, idx, (size_t)tokens * top_k, NCCL_INT32, ctx->dist->comm, ctx->stream));
+    LEV_NCCL(ctx, g_nccl.AllGather(wts_l, wts, (size_t)tokens * top_k, NCCL_FLOAT32, ctx->dist->comm, ctx->stream));
+    LEV_NCCL(ctx, g_nccl.GroupEnd());
     LEV_TRY(lev_moe_experts_dev(ctx, w, xall, tall, top_k, idx, ypairs, nullptr));
-    LEV_TRY(lev_moe_combine_dev(ctx, ypairs, wts, tall, top_k, w->hidden, partial));
+    // slots of experts that live elsewhere are skipped: no zero fill of the pair outputs is needed
+    LEV_TRY(lev_moe_combine_resident_dev(ctx, ypairs, wts, tall, top_k, w->hidden, partial, idx, w->local_first, w->local_count));
     LEV_NCCL(ctx, g_nccl.ReduceScatter(partial, out, (size_t)tokens * w->hidden, NCCL_FLOAT32, NCCL_SUM, ctx->dist->comm,
                                       ctx->stream));
     size_t own = (size_t)tokens * top_k * 4;

@@ -123,3 +123,5 @@ int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, in
 int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
                         const int32_t* idx, float* y_pairs, float* act_out);
 int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out);
+int lev_moe_combine_resident_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden,
+                                 float* out, const int32_t* idx, int first, int count);

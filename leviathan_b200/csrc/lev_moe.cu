@@ -443,7 +443,7 @@ __global__ void __launch_bounds__(1024) k_group_fast(GroupArgs G, int nchunks) {
 // out[t][h] = sum_k w[t][k] * y[t][k][h]: a separate multiply and add per
 // slot in rank order from zero (Sources/LeviathanCore/Gemma4.swift:4459-4466)
 __global__ void k_combine(const float* __restrict__ y, const float* __restrict__ w, int64_t tokens, int top_k,
-                          int hidden, float* __restrict__ out) {
+                          int hidden, float* __restrict__ out, const int32_t* __restrict__ idx, int first, int count) {
     pdl_launch_dependents();
     pdl_wait();
     int64_t total = tokens * hidden;
@@ -451,8 +451,14 @@ __global__ void k_combine(const float* __restrict__ y, const float* __restrict__
         int64_t t = i / hidden;
         int h = (int)(i - t * hidden);
         float acc = 0.f;
-        for (int k = 0; k < top_k; k++)
+        for (int k = 0; k < top_k; k++) {
+            // expert-parallel partial: slots whose expert lives on another GPU were never computed here
+            if (idx) {
+                const int e = idx[t * top_k + k];
+                if (e < first || e >= first + count) continue;
+            }
             acc = __fadd_rn(acc, __fmul_rn(w[t * top_k + k], y[(t * top_k + k) * hidden + h]));
+        }
         out[i] = acc;
     }
 }
@@ -753,8 +759,14 @@ static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, co
 }
 
 int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out) {
+    return lev_moe_combine_resident_dev(ctx, y, wts, tokens, top_k, hidden, out, nullptr, 0, 0);
+}
+
+// idx != NULL: only the slots routed to experts [first, first + count) enter the sum
+int lev_moe_combine_resident_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden,
+                                 float* out, const int32_t* idx, int first, int count) {
     LEV_CUDA(ctx, launch_pdl(k_combine, dim3(grid_for(ctx, tokens * hidden, 256, 8)), dim3(256), (size_t)0, ctx->stream, y, wts,
-                             tokens, top_k, hidden, out));
+                             tokens, top_k, hidden, out, idx, first, count));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_combine");
 }
