@@ -332,6 +332,7 @@ extern "C" int lev_matvec(lev_ctx* ctx, const lev_weights* w, int64_t row0, int6
 
     const float* dx = x;
     float* dy = y;
+    bool y_direct = false;
     size_t xb = (size_t)x_count * sizeof(float), yb = (size_t)n_cols * (size_t)rows * sizeof(float);
     if (flags & LEV_FLAG_HOST_IO) {
         if (flags & LEV_FLAG_CHECK_FINITE) {  // the reference checks on the host before any device work
@@ -340,10 +341,20 @@ extern "C" int lev_matvec(lev_ctx* ctx, const lev_weights* w, int64_t row0, int6
         }
         void *px, *py;
         LEV_TRY(lev_scratch(ctx, LEV_SCR_X, xb, &px));
-        LEV_TRY(lev_scratch(ctx, LEV_SCR_Y, yb, &py));
         LEV_CUDA(ctx, cudaMemcpyAsync(px, x, xb, cudaMemcpyHostToDevice, ctx->stream));
         dx = (const float*)px;
-        dy = (float*)py;
+        // page-locked, device-mapped output buffers are written by the kernel itself (posted writes
+        // over the host link): one copy and its launch less per call
+        cudaPointerAttributes pa;
+        if (cudaPointerGetAttributes(&pa, y) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer &&
+            !(flags & LEV_FLAG_CHECK_FINITE)) {
+            dy = (float*)pa.devicePointer;
+            y_direct = true;
+        } else {
+            (void)cudaGetLastError();  // an unregistered host pointer is not an error here
+            LEV_TRY(lev_scratch(ctx, LEV_SCR_Y, yb, &py));
+            dy = (float*)py;
+        }
     } else {
         // aliasing x and y is rejected like scratch aliasing in the reference
         // (Sources/LeviathanCore/Gemma4.swift:2096-2100)
@@ -364,7 +375,7 @@ extern "C" int lev_matvec(lev_ctx* ctx, const lev_weights* w, int64_t row0, int6
         LEV_TRY(lev_launch_matvec_plain(ctx, w, row0, rows, dx, n_cols, dy));
 
     if (flags & LEV_FLAG_CHECK_FINITE) LEV_TRY(lev_launch_finite_check(ctx, dy, (int64_t)n_cols * rows, LEV_DEV_NONFINITE_OUTPUT));
-    if (flags & LEV_FLAG_HOST_IO)
+    if ((flags & LEV_FLAG_HOST_IO) && !y_direct)
         LEV_CUDA(ctx, cudaMemcpyAsync(y, dy, yb, cudaMemcpyDeviceToHost, ctx->stream));
     if (flags & (LEV_FLAG_CHECK_FINITE | LEV_FLAG_HOST_IO)) {
         int bits = 0;

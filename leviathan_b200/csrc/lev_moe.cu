@@ -248,6 +248,7 @@ __global__ void __launch_bounds__(1024) k_group(GroupArgs G) {
     int* jobbase = offs + G.experts + 1;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     for (int e = tid; e < G.experts; e += blockDim.x) hist[e] = 0;
+    pdl_wait();  // see k_group_fast: waits for the router, never triggers its dependents early
     __syncthreads();
     bool bad = false;
     for (int i = tid; i < G.pairs; i += blockDim.x) {
@@ -344,6 +345,10 @@ __global__ void __launch_bounds__(1024) k_group_fast(GroupArgs G, int nchunks) {
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, nwarps = blockDim.x >> 5;
     for (int e = tid; e < G.experts; e += blockDim.x) hist[e] = 0;
     for (int i = tid; i < nchunks * G.experts; i += blockDim.x) ch[i] = 0;
+    // Launched with programmatic serialization so that the CTA is resident while the router still
+    // runs.  It never triggers its own dependents early: the kernels that follow read the job
+    // table before their own dependency wait and rely on this grid having completed.
+    pdl_wait();
     __syncthreads();
     bool bad = false;
     for (int c = warp; c < nchunks; c += nwarps) {
@@ -603,9 +608,9 @@ static int group_dev(lev_ctx* ctx, const int32_t* idx, int64_t tokens, int top_k
             LEV_CUDA(ctx, cudaFuncSetAttribute(k_group_fast, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
             configured[ctx->device & 15] = true;
         }
-        k_group_fast<<<1, 1024, fast, ctx->stream>>>(G, nchunks);
+        LEV_CUDA(ctx, launch_pdl(k_group_fast, dim3(1), dim3(1024), fast, ctx->stream, G, nchunks));
     } else {
-        k_group<<<1, 1024, smem, ctx->stream>>>(G);
+        LEV_CUDA(ctx, launch_pdl(k_group, dim3(1), dim3(1024), smem, ctx->stream, G));
     }
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_group");

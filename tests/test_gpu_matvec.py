@@ -231,3 +231,61 @@ def test_hardware_profile(ctx):
     p = ctx.hardware_profile()
     assert p["cc_major"] == 10 and p["sm_count"] > 100 and p["warp_width"] == 32
     assert p["free_memory"] > 0 and "B200" in p["device_name"]
+
+
+@pytest.mark.parametrize("name,rows,cols", [("q4_k", 2400, 4096), ("q6_k", 1040, 12288), ("q4_0", 4096, 4096)])
+def test_bench_sized_rows_and_row_windows(ctx, name, rows, cols):
+    """Shapes with the bench's K (every SM gets tiles, warps share tiles, the ring refills),
+    a row count that is not a multiple of the tile height, and a 16-aligned row window."""
+    t = H.TYPES[name]
+    w = H.quantized(t, 900, rows, cols)
+    x = Q.normal(901, (1, cols), 1.0)
+    wh = ctx.upload(w, t, rows, cols)
+    xd = torch.from_numpy(x).cuda()
+    ref = O.matvec_f64(t, w, rows, cols, x[0])
+    y = ctx.matvec(wh, xd, schedule=lev.SCHEDULE_STREAM).cpu().numpy()
+    assert O.max_rel_err(y[0], ref) < H.REPORT_TOL
+    # the same call again gives the same bits (fixed summation order)
+    y2 = ctx.matvec(wh, xd, schedule=lev.SCHEDULE_STREAM).cpu().numpy()
+    assert np.array_equal(y.view(np.uint32), y2.view(np.uint32))
+    n_win = min(1000, rows - 160 - 7)
+    win = ctx.matvec(wh, xd, row0=160, rows=n_win, schedule=lev.SCHEDULE_STREAM).cpu().numpy()
+    assert O.max_rel_err(win[0], ref[160:160 + n_win]) < H.REPORT_TOL
+    wh.free()
+
+
+def test_host_call_writes_page_locked_outputs_directly(ctx):
+    """LEV_FLAG_HOST_IO with a pinned (device-mapped) output buffer skips the device->host copy;
+    pageable buffers take the staged path.  Both give the same bits."""
+    t = H.TYPES["q4_k"]
+    rows, cols = 512, 1024
+    w = H.quantized(t, 910, rows, cols)
+    x = Q.normal(911, (1, cols), 1.0)
+    wh = ctx.upload(w, t, rows, cols)
+    pinned = torch.empty((1, rows), dtype=torch.float32).pin_memory()
+    ctx.matvec(wh, x, out=pinned.numpy())
+    pageable = np.empty((1, rows), np.float32)
+    ctx.matvec(wh, x, out=pageable)
+    assert np.array_equal(pinned.numpy().view(np.uint32), pageable.view(np.uint32))
+    assert O.max_rel_err(pageable[0], O.matvec_f64(t, w, rows, cols, x[0])) < H.REPORT_TOL
+    wh.free()
+
+
+def test_installed_op_serves_matching_tensors(ctx):
+    """lev_op_serves is the analogue of q4GeneratedServesTensor
+    (Sources/LeviathanCore/Gemma4.swift:989-1012): an installed op spec serves a resident
+    tensor whose quant, inDim and row count match."""
+    import json
+
+    doc = {"schema": 1, "op": "q4_k.matvec", "semantics": "dot(W_row, x)", "inDim": 1024, "outDim": 512,
+           "layout": "row-major-q4_k-blocks", "quant": "q4_k", "accumulate": "f32", "inputPrecision": "f32"}
+    op = ctx.op_install(json.dumps(doc))
+    w = H.quantized(H.TYPES["q4_k"], 920, 512, 1024)
+    good = ctx.upload(w, H.TYPES["q4_k"], 512, 1024)
+    other = ctx.upload(H.quantized(H.TYPES["q4_0"], 921, 512, 1024), H.TYPES["q4_0"], 512, 1024)
+    assert ctx.op_serves(op, good, 512)
+    assert not ctx.op_serves(op, good, 256)
+    assert not ctx.op_serves(op, other, 512)
+    ctx.op_uninstall(op)
+    good.free()
+    other.free()
