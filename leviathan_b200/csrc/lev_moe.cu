@@ -153,16 +153,38 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
 }
 
+// Grouping and job table, one CTA.  Experts outside [first, first+count) are
+// not resident on this GPU; their pairs are left out.
+struct GroupArgs {
+    const int32_t* idx;  // [pairs]
+    int pairs, top_k, experts, first, count, cmax;
+    int32_t* counts;     // [experts]
+    int32_t* offsets;    // [experts + 1]
+    int32_t* perm;       // [pairs] pair ids in grouped order
+    // job table (all optional)
+    int* njobs;          // [1]
+    int* job_slice;      // [max_jobs] local expert index
+    int* job_token;      // [max_jobs][cmax] token of each column, -1 = none
+    int* job_pos;        // [max_jobs][cmax] grouped position, -1 = none
+    int* job_pair;       // [max_jobs][cmax] pair id, -1 = none
+    int* status;
+};
+
 // one warp per token
+// fuse_group (single CTA, at most 32 token-slot pairs): warp 0 also builds the grouping and the
+// one-column-per-job table of k_group for these pairs, which saves a launch on the decode path
 __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ scores, int64_t tokens, int experts,
                                                      int top_k, const float* __restrict__ expert_scale,
-                                                     int32_t* __restrict__ idx, float* __restrict__ weights) {
+                                                     int32_t* __restrict__ idx, float* __restrict__ weights, GroupArgs G,
+                                                     int fuse_group) {
     extern __shared__ double sp[];  // [warps][experts] probabilities; selected ones are set to -1
-    pdl_launch_dependents();
+    // With the grouping fused in, the kernels that follow read the job table before their own
+    // dependency wait: they may only start when this grid has completed.
+    if (!fuse_group) pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int64_t tok = (int64_t)blockIdx.x * 4 + warp;
-    if (tok >= tokens) return;
+    if (tok < tokens) {
     double* p = sp + (size_t)warp * experts;
     const float* s = scores + tok * experts;
     float m = -INFINITY;
@@ -222,24 +244,46 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
         idx[tok * top_k + lane + 32] = isel2;
         weights[tok * top_k + lane + 32] = __fmul_rn((float)(psel2 / prob_sum), sc);
     }
+    }
+    if (!fuse_group) return;
+    __syncthreads();  // every token's indices are written (and visible inside the CTA)
+    if (warp != 0) return;
+    // pair `lane`: stable position among the resident pairs ordered by (expert, pair)
+    const int e = lane < G.pairs ? G.idx[lane] : -1;
+    const bool res = e >= G.first && e < G.first + G.count;
+    if (lane < G.pairs && (e < 0 || e >= G.experts)) atomicOr(G.status, LEV_DEV_NONFINITE_INPUT);
+    int pos = 0;
+    for (int j = 0; j < 32; j++) {
+        const int ej = __shfl_sync(0xffffffffu, e, j);
+        const bool rj = __shfl_sync(0xffffffffu, (int)res, j) != 0;
+        if (rj && (ej < e || (ej == e && j < lane))) pos++;
+    }
+    const int total = __popc(__ballot_sync(0xffffffffu, res));
+    for (int ex = lane; ex < G.experts; ex += 32) {
+        int cnt = 0, before = 0;
+        for (int j = 0; j < G.pairs; j++) {
+            const int ej = G.idx[j];
+            const bool rj = ej >= G.first && ej < G.first + G.count;
+            cnt += rj && ej == ex;
+            before += rj && ej < ex;
+        }
+        G.counts[ex] = cnt;
+        G.offsets[ex] = before;
+    }
+    if (lane == 0) {
+        G.offsets[G.experts] = total;
+        if (G.njobs) *G.njobs = total;
+    }
+    if (res) {
+        G.perm[pos] = lane;
+        if (G.job_slice) {
+            G.job_slice[pos] = e - G.first;
+            G.job_token[pos] = lane / G.top_k;
+            G.job_pos[pos] = pos;
+            G.job_pair[pos] = lane;
+        }
+    }
 }
-
-// Grouping and job table, one CTA.  Experts outside [first, first+count) are
-// not resident on this GPU; their pairs are left out.
-struct GroupArgs {
-    const int32_t* idx;  // [pairs]
-    int pairs, top_k, experts, first, count, cmax;
-    int32_t* counts;     // [experts]
-    int32_t* offsets;    // [experts + 1]
-    int32_t* perm;       // [pairs] pair ids in grouped order
-    // job table (all optional)
-    int* njobs;          // [1]
-    int* job_slice;      // [max_jobs] local expert index
-    int* job_token;      // [max_jobs][cmax] token of each column, -1 = none
-    int* job_pos;        // [max_jobs][cmax] grouped position, -1 = none
-    int* job_pair;       // [max_jobs][cmax] pair id, -1 = none
-    int* status;
-};
 
 __global__ void __launch_bounds__(1024) k_group(GroupArgs G) {
     extern __shared__ int sh[];  // hist[experts], offs[experts + 1], jobbase[experts + 1]
@@ -541,8 +585,16 @@ extern "C" int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w) {
 // ---------------------------------------------------------------------------
 // device-pointer stages
 // ---------------------------------------------------------------------------
+static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
+                          float* weights, float* scores, const GroupArgs* fuse);
+
 int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
                      float* weights, float* scores) {
+    return route_dev_impl(ctx, w, x, tokens, top_k, idx, weights, scores, nullptr);
+}
+
+static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
+                          float* weights, float* scores, const GroupArgs* fuse) {
     dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
     const size_t stage = (size_t)16 * w->hidden * sizeof(float);
     if (stage <= 200 * 1024 && w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0) {
@@ -559,8 +611,10 @@ int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, in
     ctx->launches++;
     LEV_CUDA(ctx, cudaGetLastError());
     size_t smem = (size_t)4 * w->experts * sizeof(double);
+    GroupArgs G = {};
+    if (fuse) G = *fuse;
     LEV_CUDA(ctx, launch_pdl(k_router_topk, dim3((unsigned)((tokens + 3) / 4)), dim3(128), smem, ctx->stream, (const float*)scores,
-                             tokens, (int)w->experts, top_k, (const float*)nullptr, idx, weights));
+                             tokens, (int)w->experts, top_k, (const float*)nullptr, idx, weights, G, fuse ? 1 : 0));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_router_topk");
 }
@@ -621,14 +675,55 @@ static int lev_moe_launch_act(lev_ctx* ctx, const float* gu, const int* perm, co
 
 // expert FFN for the pairs whose experts are resident; y_pairs is [pairs][hidden]
 // indexed by pair id (token*top_k + rank); act_out (optional) likewise [pairs][inter]
+static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                            const int32_t* idx, float* y_pairs, float* act_out, bool pre_grouped);
+
 int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
                        const int32_t* idx, float* y_pairs, float* act_out) {
+    return experts_dev_impl(ctx, w, x, tokens, top_k, idx, y_pairs, act_out, false);
+}
+
+// decode-sized calls run one job per (token, slot) pair on the one-launch kernel
+static bool moe_sliced(lev_ctx* ctx, const lev_moe_weights* w, int64_t pairs, const float* x) {
+    const int64_t gu_rows = 2 * (int64_t)w->inter;
+    return pairs <= 64 && lev_dense_jobs_supported(ctx, w->gate_up, gu_rows, (int)pairs, x, w->hidden) &&
+           lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)pairs, x, gu_rows);
+}
+
+// the grouping tables of a call inside the context's scratch (same layout for the same arguments)
+static int group_tables(lev_ctx* ctx, const lev_moe_weights* w, int64_t pairs, int cmax, int max_jobs, int32_t** counts,
+                        int32_t** offsets, int32_t** perm, JobTable* jt) {
+    size_t ints = (size_t)w->experts * 2 + 1 + pairs + 1 + max_jobs + (size_t)3 * max_jobs * cmax + 64;
+    void* gb;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_B, ints * sizeof(int), &gb));
+    int* p = (int*)gb;
+    *counts = p;
+    p += w->experts;
+    *offsets = p;
+    p += w->experts + 1;
+    *perm = p;
+    p += pairs;
+    jt->cmax = cmax;
+    jt->max_jobs = max_jobs;
+    jt->njobs = p;
+    p += 1;
+    jt->job_slice = p;
+    p += max_jobs;
+    jt->job_token = p;
+    p += (size_t)max_jobs * cmax;
+    jt->job_pos = p;
+    p += (size_t)max_jobs * cmax;
+    jt->job_pair = p;
+    return LEV_OK;
+}
+
+static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                            const int32_t* idx, float* y_pairs, float* act_out, bool pre_grouped) {
     const int64_t pairs = tokens * top_k;
     const int64_t gu_rows_ = 2 * (int64_t)w->inter;
     // decode-sized calls: one job per (token, slot) pair on the one-launch kernel, whose CTAs
     // build their activation tables themselves (no preparation launches, no table memory)
-    const bool sliced = pairs <= 64 && lev_dense_jobs_supported(ctx, w->gate_up, gu_rows_, (int)pairs, x, w->hidden) &&
-                        lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)pairs, x, gu_rows_);
+    const bool sliced = moe_sliced(ctx, w, pairs, x);
     // prefill-sized calls: grouped dequant-GEMM on the tensor cores (bf16 operands, f32 accumulate;
     // the 2e-2 bar of tensor-core prefill applies to this form)
     const char* mp = getenv("LEV_MOE_GEMM_MIN_PAIRS");
@@ -641,29 +736,11 @@ int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, 
     const int max_jobs = (int)mj;
 
     // grouping tables
-    size_t ints = (size_t)w->experts * 2 + 1 + pairs + 1 + max_jobs + (size_t)3 * max_jobs * cmax + 64;
-    void* gb;
-    LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_B, ints * sizeof(int), &gb));
-    int* p = (int*)gb;
-    int32_t* counts = p;
-    p += w->experts;
-    int32_t* offsets = p;
-    p += w->experts + 1;
-    int32_t* perm = p;
-    p += pairs;
+    int32_t *counts, *offsets, *perm;
     JobTable jt;
-    jt.cmax = cmax;
-    jt.max_jobs = max_jobs;
-    jt.njobs = p;
-    p += 1;
-    jt.job_slice = p;
-    p += max_jobs;
-    jt.job_token = p;
-    p += (size_t)max_jobs * cmax;
-    jt.job_pos = p;
-    p += (size_t)max_jobs * cmax;
-    jt.job_pair = p;
-    LEV_TRY(group_dev(ctx, idx, tokens, top_k, w->experts, w->local_first, w->local_count, counts, offsets, perm, &jt));
+    LEV_TRY(group_tables(ctx, w, pairs, cmax, max_jobs, &counts, &offsets, &perm, &jt));
+    if (!pre_grouped)
+        LEV_TRY(group_dev(ctx, idx, tokens, top_k, w->experts, w->local_first, w->local_count, counts, offsets, perm, &jt));
 
     // gate_up: columns = tokens of each job, outputs in grouped order [pos][2*inter]
     const int64_t gu_rows = 2 * (int64_t)w->inter;
@@ -957,8 +1034,34 @@ int lev_moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x,
     float* scores = (float*)((char*)a + 2 * ib);
     void* d;
     LEV_TRY(lev_scratch(ctx, LEV_SCR_MOE_D, (size_t)pairs * w->hidden * 4 + 256, &d));
-    LEV_TRY(lev_moe_route_dev(ctx, w, x, tokens, top_k, idx, wts, scores));
-    LEV_TRY(lev_moe_experts_dev(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr));
+    if (pairs <= 32 && tokens <= 4 && moe_sliced(ctx, w, pairs, x)) {
+        // decode: the top-k kernel also groups the pairs (one job per pair)
+        int32_t *counts, *offsets, *perm;
+        JobTable jt;
+        LEV_TRY(group_tables(ctx, w, pairs, 1, (int)pairs, &counts, &offsets, &perm, &jt));
+        GroupArgs G = {};
+        G.idx = idx;
+        G.pairs = (int)pairs;
+        G.top_k = top_k;
+        G.experts = w->experts;
+        G.first = w->local_first;
+        G.count = w->local_count;
+        G.cmax = 1;
+        G.counts = counts;
+        G.offsets = offsets;
+        G.perm = perm;
+        G.njobs = jt.njobs;
+        G.job_slice = jt.job_slice;
+        G.job_token = jt.job_token;
+        G.job_pos = jt.job_pos;
+        G.job_pair = jt.job_pair;
+        G.status = ctx->d_status;
+        LEV_TRY(route_dev_impl(ctx, w, x, tokens, top_k, idx, wts, scores, &G));
+        LEV_TRY(experts_dev_impl(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr, true));
+    } else {
+        LEV_TRY(lev_moe_route_dev(ctx, w, x, tokens, top_k, idx, wts, scores));
+        LEV_TRY(lev_moe_experts_dev(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr));
+    }
     return lev_moe_combine_dev(ctx, (const float*)d, wts, tokens, top_k, w->hidden, out);
 }
 
