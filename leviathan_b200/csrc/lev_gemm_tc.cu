@@ -6,14 +6,14 @@
 // as the block decoders form them, then one rounding to bf16; activations are bf16 already;
 // rust/crates/lev-forge/src/coopmat.rs:236-425, oracle rust/crates/lev-cli/src/main.rs:1201-1217).
 //
-// One CTA computes a tile of 256 tokens x 192 weight rows over the whole K:
+// One CTA computes a tile of 256 tokens x 176 weight rows over the whole K:
 //   * warp 0 (one thread): TMA loads of the activation tile, two boxes of 128 tokens x 64 k
 //     (128-byte rows, hardware 128B swizzle) per K-step into a 3-stage ring;
-//   * warps 2..13 (384 threads): decode the K-step's 192 x 64 weights from the GGUF blocks in
+//   * warps 2..12 (352 threads): decode the K-step's 176 x 64 weights from the GGUF blocks in
 //     global memory and store them as bf16 into the same K-major 128B-swizzled layout, then
 //     publish them to the async proxy (fence.proxy.async) and arrive on the stage's barrier;
-//   * warp 1 (one thread): for each K-step 4 x 2 tcgen05.mma (M = 128 tokens, N = 192 rows,
-//     K = 16) from shared-memory descriptors into two TMEM accumulators (384 of 512 columns),
+//   * warp 1 (one thread): for each K-step 4 x 2 tcgen05.mma (M = 128 tokens, N = 176 rows,
+//     K = 16) from shared-memory descriptors into two TMEM accumulators (352 of 512 columns),
 //     tcgen05.commit hands the stage back to the producers;
 //   * epilogue: warps 2..9 read the accumulators with tcgen05.ld (warp w owns TMEM lanes
 //     32*(w%4)...) and store Y rows with 16-byte stores.
@@ -28,10 +28,10 @@
 namespace {
 
 constexpr int TM = 256;      // tokens per CTA tile (two MMA tiles of 128)
-constexpr int RN = 192;      // weight rows per CTA tile (MMA N)
+constexpr int RN = 176;      // weight rows per CTA tile (MMA N): 12288 rows x 512 tokens -> 140 CTAs on 148 SMs
 constexpr int KS = 64;       // k per pipeline stage (one 128-byte swizzle row of bf16)
 constexpr int STAGES = 3;
-constexpr int kDequantWarps = 12;
+constexpr int kDequantWarps = 11;
 constexpr int kThreads = (2 + kDequantWarps) * 32;
 constexpr int kXHalfBytes = 128 * KS * 2;             // 16384: one TMA box
 constexpr int kXStageBytes = 2 * kXHalfBytes;         // 32768
@@ -342,7 +342,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             GTL_ADD(2, 1);
         }
     } else {
-        // ---- weight decode: thread = (2 rows 96 apart) x (byte group j); the raw bytes of the
+        // ---- weight decode: thread = (2 rows 88 apart) x (byte group j); the raw bytes of the
         // next K-step are requested before this one is decoded ----
         // lanes 0..7 of a warp take byte group 0 of eight consecutive rows, lanes 8..15 group 1, ...:
         // the eight 16-byte stores of one shared-memory wavefront then fall into eight different
@@ -421,7 +421,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                         const int tl = i * 4 + (lane >> 3);
                         const int tok = t0 + half * 128 + quarter * 32 + tl;
                         const uint4 o = *reinterpret_cast<const uint4*>(stg + tl * 36 + col4);
-                        if (tok < A.tokens) {
+                        if (tok < A.tokens && c + col4 < RN) {  // the last chunk of a tile may be narrower than 32
                             float* dst = A.y + (int64_t)tok * A.rows + r0 + c + col4;
                             if (r0 + c + col4 + 4 <= A.rows && A.y_vec) {
                                 *reinterpret_cast<uint4*>(dst) = o;

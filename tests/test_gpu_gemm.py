@@ -24,6 +24,8 @@ def ctx():
 
 @pytest.mark.parametrize("name,rows,cols,tokens", [
     ("q4_k", 256, 1024, 64), ("q4_k", 80, 512, 37), ("q6_k", 128, 768, 70), ("q4_0", 96, 704, 5), ("q4_0", 64, 2816, 128),
+    # several row tiles with a ragged last one, two token tiles (256 + 44)
+    ("q4_k", 400, 512, 300), ("q6_k", 360, 256, 130),
 ])
 def test_gemm_matches_rounded_operand_oracle(ctx, name, rows, cols, tokens):
     t = H.TYPES[name]
