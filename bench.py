@@ -452,11 +452,47 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         for wgu, wd in fused:
             wgu.free()
             wd.free()
-    # MoE layer
     if world > 1:
         from leviathan_b200 import dist as lev_dist
+        from leviathan_b200 import quant as Qd
 
         lev_dist.init_from_torch(ctx)
+        # dense row-split: every rank holds rows [r*R/G, (r+1)*R/G) of the same Q4_K tensor, activations
+        # are replicated, outputs are all-gathered (NCCL); collectives are timed eagerly with events
+        first, per = lev_dist.row_shard(FFN, rank, world)
+        gw = torch.Generator(device=dev).manual_seed(SEED ^ 0x500)
+        wq = Qd.quantize(Q4_K, torch.randn((FFN, HIDDEN), generator=gw, device=dev) * 0.02)
+        row_bytes = (HIDDEN // 256) * 144
+        w_loc = ctx.upload(wq[first * row_bytes:(first + per) * row_bytes].contiguous(), Q4_K, per, HIDDEN)
+        del wq
+        xb = torch.randn((512, HIDDEN), generator=gw, device=dev).to(torch.bfloat16)
+        xv = torch.randn((1, HIDDEN), generator=gw, device=dev)
+        yb, yv = torch.empty((512, FFN), device=dev), torch.empty((1, FFN), device=dev)
+
+        def eager_ms(fn, iters=20):
+            import torch.distributed as dist
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize()
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record()
+            for _ in range(iters):
+                fn()
+            a1.record()
+            a1.synchronize()
+            t = torch.tensor([a0.elapsed_time(a1) / iters], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item()
+
+        ms = eager_ms(lambda: ctx.gemm_prefill_rowsplit_allgather(w_loc, xb, world, out=yb))
+        flop = 2.0 * 512 * HIDDEN * FFN
+        out["prefill_gemm_rowsplit"] = {"workload": "X bf16 [512x4096] x Q4_K [12288x4096], rows split, all-gather of Y",
+                                        "ms": ms, "tflops": flop / ms / 1e9}
+        ms = eager_ms(lambda: ctx.matvec_rowsplit_allgather(w_loc, xv, world, out=yv))
+        out["matvec_rowsplit"] = {"workload": "Q4_K [12288x4096] matvec, rows split, all-gather of y", "ms": ms,
+                                  "gbs": (GATE_BYTES + 4 * (HIDDEN + FFN)) / ms / 1e6}
+        w_loc.free()
+    # MoE layer
     g = torch.Generator(device=dev).manual_seed(SEED ^ 0x400)
     first, count = (0, MOE_EXPERTS) if world == 1 else (rank * (MOE_EXPERTS // world), MOE_EXPERTS // world)
     gu, dn = [], []
