@@ -315,10 +315,6 @@ def run_gpu(args):
     barrier()
     e2e_ms = 1000.0 * (time.perf_counter() - t0) / args.steps
 
-    extras = None
-    if not args.no_extras:
-        extras = run_extras(ctx, inst[0][0], dev, s, world, rank)
-
     if world > 1:
         t = torch.tensor([ms_per_step, e2e_ms], device=dev, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -365,7 +361,7 @@ def run_gpu(args):
             "e2e": {"value": world * STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * (HIDDEN + HIDDEN + FFN), "d2h_bytes_per_step": 4 * (FFN + FFN + HIDDEN)},
             "gpu_launches": launches_per_step * args.steps * reps,
-            "clocks": clocks, "parity": parity, "extras": extras,
+            "clocks": clocks, "parity": parity,
         }
         if not args.no_cpu and world == 1:
             times, threads, build = cpu_step_timer(None, 11, 3)
@@ -373,7 +369,31 @@ def run_gpu(args):
             line["cpu_baseline"] = {"value": STEP_BYTES / cms / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                                     "sample": f"11 full steps (median) of the same three matvecs, oracle C port "
                                               f"({build} build), row chunks over all host threads"}
-        print(json.dumps(line))
+    # Side measurements come last and under a watchdog: if they fail or stall on any rank (they use
+    # collectives), the headline line is still printed and every rank leaves.
+    line_ref = line if rank == 0 else None
+
+    def emit(extras):
+        if rank == 0:
+            line_ref["extras"] = extras
+            print(json.dumps(line_ref), flush=True)
+
+    if args.no_extras:
+        emit(None)
+    else:
+        def bail():
+            emit({"error": "side measurements did not finish within 240 s"})
+            os._exit(0)
+
+        timer = threading.Timer(240.0, bail)
+        timer.daemon = True
+        timer.start()
+        try:
+            extras = run_extras(ctx, inst[0][0], dev, s, world, rank)
+        except Exception as exc:  # noqa: BLE001 -- reported in the JSON line
+            extras = {"error": repr(exc)[:300]}
+        timer.cancel()
+        emit(extras)
     if world > 1:
         dist.destroy_process_group()
 
