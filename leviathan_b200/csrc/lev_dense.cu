@@ -45,12 +45,12 @@ struct DenseArgs {
     int depth;         // ring stages per warp
     int sps;           // K-steps per stage
     int debug;         // bit 0: skip the arithmetic
-    // sliced form (JOBS): the call is a device-side list of jobs, each one activation column
+    // sliced form (JOBS): the call is a device-side list of jobs, each up to CMAX activation columns
     // against one slice (expert) of the tensor
     const int* njobs_dev;   // [1] jobs in the list
     const int* job_slice;   // [job] slice index, in units of tiles_per_job tiles
-    const int* job_src;     // [job] source row of the job's activations, -1 = none
-    const int* job_out;     // [job] output row, -1 = none
+    const int* job_src;     // [job][CMAX] source row of each column's activations, -1 = none
+    const int* job_out;     // [job][CMAX] output row of each column, -1 = none
     int tiles_per_job;
     int gelu_inter;         // > 0: activation e = gelu_tanh(src[e]) * src[gelu_inter + e]
     int table_stride;       // bytes between the tables of consecutive jobs in shared memory
@@ -60,7 +60,6 @@ constexpr int kMaxJobTables = 3;  // jobs whose tables one CTA of the sliced for
 
 template <int TYPE, int CMAX, int W, bool JOBS>
 __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) {
-    static_assert(!JOBS || CMAX == 1, "the sliced form takes one column per job");
     using D = StreamDims<CMAX>;
     constexpr int NT = D::kNT, GLT = D::kGlt, TERMS = D::kTerms;
     constexpr int kStepBytes = step_bytes(TYPE);
@@ -148,7 +147,7 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
             const int i2 = live ? idx : items - 1;
             const int jj = JOBS ? i2 / per_job : 0, ii = i2 - jj * per_job;
             const int chunk = ii / (CMAX * 4), rem = ii - chunk * (CMAX * 4), c = rem >> 2, tt = rem & 3;
-            const int src_row = JOBS ? A.job_src[job0 + jj] : c;
+            const int src_row = JOBS ? A.job_src[(job0 + jj) * CMAX + c] : c;
             const bool has = JOBS ? src_row >= 0 : c < A.n_cols;
             const float* xr = A.x + (int64_t)(has ? src_row : 0) * A.x_ld;
             if (JOBS) {
@@ -267,14 +266,18 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
     // tables, output row and tile-in-job of the tile being worked on
     const uint4* xs = reinterpret_cast<const uint4*>(tables0);
     const float* sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
-    int job = 0, tij = tile0 + tl, orow = 0;
+    int job = 0, tij = tile0 + tl;
+    int orow[CMAX];
+#pragma unroll
+    for (int c = 0; c < CMAX; c++) orow[c] = 0;
     auto enter_tile = [&]() {
         if (JOBS) {
             job = (tile0 + tl) / tpj;
             tij = tile0 + tl - job * tpj;
             xs = reinterpret_cast<const uint4*>(tables0 + (size_t)(job - job0) * A.table_stride);
             sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
-            orow = A.job_out[job];
+#pragma unroll
+            for (int c = 0; c < CMAX; c++) orow[c] = A.job_out[job * CMAX + c];
         } else {
             tij = tile0 + tl;
         }
@@ -319,8 +322,8 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
                     if (t == 0) {
                         if (whole) {
                             const int64_t row = (int64_t)tij * 16 + g;
-                            const int oc = JOBS ? orow : c;
-                            if (JOBS ? orow >= 0 : c < A.n_cols) {
+                            const int oc = JOBS ? orow[c] : c;
+                            if (JOBS ? orow[c] >= 0 : c < A.n_cols) {
                                 if (row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = va;
                                 if (row + 8 < A.rows) A.y[(int64_t)oc * A.out_ld + row + 8] = vb;
                             }
@@ -374,7 +377,7 @@ __global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) 
         }
         const int c = idx >> 4;
         if (JOBS) {
-            const int pjob = (tile0 + tile) / tpj, ptij = tile0 + tile - pjob * tpj, oc = A.job_out[pjob];
+            const int pjob = (tile0 + tile) / tpj, ptij = tile0 + tile - pjob * tpj, oc = A.job_out[pjob * CMAX + c];
             const int64_t row = (int64_t)ptij * 16 + (idx & 15);
             if (oc >= 0 && row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = acc;
         } else {
@@ -516,25 +519,37 @@ int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows
 // Sliced form: a device-side list of up to max_jobs jobs, job j = one activation column (row
 // job_src[j] of x, optionally through gelu_tanh(gate) * up) against slice job_slice[j] of the
 // tensor (slice = rows_per_job consecutive rows), result to row job_out[j] of y.
-bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, const float* x,
-                              int64_t x_ld) {
-    if (!w->packed || rows_per_job % 16 != 0 || max_jobs < 1 || env_int("LEV_DENSE", 1) == 0) return false;
-    if (((uintptr_t)x & 15) != 0 || x_ld % 4 != 0) return false;
-    if (max_jobs > ctx->prop.multiProcessorCount) return false;  // keeps a CTA within kMaxJobTables jobs
-    const size_t stride = (lev_stream_table_bytes(w, 1, 2, 1, nullptr) + 255) & ~(size_t)255;
-    return kMaxJobTables * stride + 8 * 2 * (size_t)step_bytes(w->type) <= 110 * 1024;
+// shared-memory budget of the sliced form: half an SM when the tables allow it (so that consecutive
+// launches co-reside), else the whole SM
+static size_t jobs_cap(size_t tables, size_t step) {
+    return tables + 8 * 2 * step <= 110 * 1024 ? 110 * 1024 : 200 * 1024;
 }
 
-int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, const int* njobs_dev,
+bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax,
+                              const float* x, int64_t x_ld) {
+    if (!w->packed || rows_per_job % 16 != 0 || max_jobs < 1 || env_int("LEV_DENSE", 1) == 0) return false;
+    if (cmax != 1 && cmax != 4) return false;
+    if (((uintptr_t)x & 15) != 0 || x_ld % 4 != 0) return false;
+    // a CTA's run of tiles may touch at most kMaxJobTables jobs
+    const int64_t tpj = rows_per_job / 16, sms = ctx->prop.multiProcessorCount;
+    const int64_t max_tiles = (int64_t)max_jobs * tpj, grid = max_tiles < sms ? max_tiles : sms;
+    const int64_t run = (max_tiles + grid - 1) / grid;
+    if ((run + tpj - 1) / tpj + 1 > kMaxJobTables) return false;
+    const size_t stride = (lev_stream_table_bytes(w, cmax, 2, 1, nullptr) + 255) & ~(size_t)255;
+    const size_t step = step_bytes(w->type);
+    return kMaxJobTables * stride + 8 * 2 * step <= jobs_cap(kMaxJobTables * stride, step);
+}
+
+int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax, const int* njobs_dev,
                        const int* job_slice, const int* job_src, const int* job_out, const float* x, int64_t x_ld,
                        int gelu_inter, float* y, int64_t out_ld) {
-    if (!lev_dense_jobs_supported(ctx, w, rows_per_job, max_jobs, x, x_ld))
+    if (!lev_dense_jobs_supported(ctx, w, rows_per_job, max_jobs, cmax, x, x_ld))
         return lev_fail(ctx, LEV_UNSUPPORTED, "sliced dense kernel: shape not served");
     constexpr int W = 8;
     const int64_t tpj = rows_per_job / 16, chunks = lev_stream_chunks(w), spt = chunks / 4;
     const size_t step = step_bytes(w->type);
-    const size_t stride = (lev_stream_table_bytes(w, 1, 2, 1, nullptr) + 255) & ~(size_t)255;
-    const size_t cap = 110 * 1024;
+    const size_t stride = (lev_stream_table_bytes(w, cmax, 2, 1, nullptr) + 255) & ~(size_t)255;
+    const size_t cap = jobs_cap(kMaxJobTables * stride, step);
     const int sms = ctx->prop.multiProcessorCount;
     const int64_t max_tiles = (int64_t)max_jobs * tpj;
     const int grid = (int)(max_tiles < sms ? max_tiles : sms);
@@ -550,7 +565,7 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     A.x_ld = x_ld;
     A.cols = (int)w->cols;
     A.chunks = (int)chunks;
-    A.n_cols = 1;
+    A.n_cols = cmax;
     A.y = y;
     A.rows = rows_per_job;
     A.out_ld = out_ld;
@@ -566,9 +581,15 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     A.gelu_inter = gelu_inter;
     A.table_stride = (int)stride;
     const size_t smem = (size_t)W * depth * step + kMaxJobTables * stride;
-    int st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 1, W, true>(ctx, grid, smem, A)
+    int st;
+    if (cmax == 1)
+        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 1, W, true>(ctx, grid, smem, A)
              : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 1, W, true>(ctx, grid, smem, A)
                                         : launch_dense<LEV_GGML_Q4_0, 1, W, true>(ctx, grid, smem, A);
+    else
+        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, W, true>(ctx, grid, smem, A)
+             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, W, true>(ctx, grid, smem, A)
+                                        : launch_dense<LEV_GGML_Q4_0, 4, W, true>(ctx, grid, smem, A);
     if (st) return st;
     ctx->launches++;
     ctx->ev.grid = grid;

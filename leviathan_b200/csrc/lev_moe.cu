@@ -686,8 +686,17 @@ int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, 
 // decode-sized calls run one job per (token, slot) pair on the one-launch kernel
 static bool moe_sliced(lev_ctx* ctx, const lev_moe_weights* w, int64_t pairs, const float* x) {
     const int64_t gu_rows = 2 * (int64_t)w->inter;
-    return pairs <= 64 && lev_dense_jobs_supported(ctx, w->gate_up, gu_rows, (int)pairs, x, w->hidden) &&
-           lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)pairs, x, gu_rows);
+    return pairs <= 64 && lev_dense_jobs_supported(ctx, w->gate_up, gu_rows, (int)pairs, 1, x, w->hidden) &&
+           lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)pairs, 1, x, gu_rows);
+}
+
+// mid-sized calls: one job per expert and up to four of its tokens, still on the one-launch kernel
+static bool moe_sliced4(lev_ctx* ctx, const lev_moe_weights* w, int64_t pairs, const float* x) {
+    const int64_t gu_rows = 2 * (int64_t)w->inter;
+    int64_t mj = (int64_t)w->local_count + pairs / 4;
+    if (mj > pairs) mj = pairs;
+    return lev_dense_jobs_supported(ctx, w->gate_up, gu_rows, (int)mj, 4, x, w->hidden) &&
+           lev_dense_jobs_supported(ctx, w->down, w->hidden, (int)mj, 4, x, gu_rows);
 }
 
 // the grouping tables of a call inside the context's scratch (same layout for the same arguments)
@@ -730,7 +739,8 @@ static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float*
     const int64_t min_pairs = mp && *mp ? atoll(mp) : 512;
     const bool tensor = !sliced && pairs >= min_pairs && w->hidden % 4 == 0 && lev_gemm_grouped_supported(w->gate_up, (int)gu_rows_) &&
                         lev_gemm_grouped_supported(w->down, w->hidden);
-    const int cmax = sliced ? 1 : tensor ? lev_gemm_grouped_job_tokens() : (pairs <= 2 * (int64_t)w->local_count ? 4 : 8), terms = 2;
+    const bool sliced4 = !sliced && !tensor && moe_sliced4(ctx, w, pairs, x);
+    const int cmax = sliced ? 1 : tensor ? lev_gemm_grouped_job_tokens() : sliced4 ? 4 : (pairs <= 2 * (int64_t)w->local_count ? 4 : 8), terms = 2;
     int64_t mj = (int64_t)w->local_count + pairs / cmax;
     if (mj > pairs) mj = pairs;
     const int max_jobs = (int)mj;
@@ -766,10 +776,10 @@ static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float*
         if (act_out) LEV_TRY(lev_moe_launch_act(ctx, gu, perm, offsets + w->experts, pairs, w->inter, act_out));
         return LEV_OK;
     }
-    if (sliced) {
-        LEV_TRY(lev_dense_jobs_run(ctx, w->gate_up, gu_rows, max_jobs, jt.njobs, jt.job_slice, jt.job_token, jt.job_pos, x,
+    if (sliced || sliced4) {
+        LEV_TRY(lev_dense_jobs_run(ctx, w->gate_up, gu_rows, max_jobs, cmax, jt.njobs, jt.job_slice, jt.job_token, jt.job_pos, x,
                                    w->hidden, 0, gu, gu_rows));
-        LEV_TRY(lev_dense_jobs_run(ctx, w->down, w->hidden, max_jobs, jt.njobs, jt.job_slice, jt.job_pos, jt.job_pair, gu,
+        LEV_TRY(lev_dense_jobs_run(ctx, w->down, w->hidden, max_jobs, cmax, jt.njobs, jt.job_slice, jt.job_pos, jt.job_pair, gu,
                                    gu_rows, w->inter, y_pairs, w->hidden));
         if (act_out) LEV_TRY(lev_moe_launch_act(ctx, gu, perm, offsets + w->experts, pairs, w->inter, act_out));
         return LEV_OK;

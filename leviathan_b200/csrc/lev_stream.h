@@ -43,9 +43,9 @@ int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& 
 bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols);
 int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y);
 
-// sliced form of the one-launch kernel: a device-side job list, one activation column per job
-bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, const float* x,
-                              int64_t x_ld);
-int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, const int* njobs_dev,
+// sliced form of the one-launch kernel: a device-side job list, cmax (1 or 4) activation columns per job
+bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax,
+                              const float* x, int64_t x_ld);
+int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax, const int* njobs_dev,
                        const int* job_slice, const int* job_src, const int* job_out, const float* x, int64_t x_ld,
                        int gelu_inter, float* y, int64_t out_ld);
