@@ -59,7 +59,7 @@ struct DenseArgs {
 constexpr int kMaxJobTables = 3;  // jobs whose tables one CTA of the sliced form can hold
 
 template <int TYPE, int CMAX, int W, bool JOBS>
-__global__ void __launch_bounds__(W * 32, W <= 16 ? 2 : 1) k_dense(DenseArgs A) {
+__global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     using D = StreamDims<CMAX>;
     constexpr int NT = D::kNT, GLT = D::kGlt, TERMS = D::kTerms;
     constexpr int kStepBytes = step_bytes(TYPE);
@@ -545,11 +545,12 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
                        int gelu_inter, float* y, int64_t out_ld) {
     if (!lev_dense_jobs_supported(ctx, w, rows_per_job, max_jobs, cmax, x, x_ld))
         return lev_fail(ctx, LEV_UNSUPPORTED, "sliced dense kernel: shape not served");
-    constexpr int W = 8;
     const int64_t tpj = rows_per_job / 16, chunks = lev_stream_chunks(w), spt = chunks / 4;
     const size_t step = step_bytes(w->type);
     const size_t stride = (lev_stream_table_bytes(w, cmax, 2, 1, nullptr) + 255) & ~(size_t)255;
     const size_t cap = jobs_cap(kMaxJobTables * stride, step);
+    // a CTA that takes the whole SM anyway runs twelve warps
+    const int W = cap > 110 * 1024 && cmax == 4 && env_int("LEV_JOBS_WIDE", 1) ? 12 : 8;
     const int sms = ctx->prop.multiProcessorCount;
     const int64_t max_tiles = (int64_t)max_jobs * tpj;
     const int grid = (int)(max_tiles < sms ? max_tiles : sms);
@@ -583,13 +584,17 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     const size_t smem = (size_t)W * depth * step + kMaxJobTables * stride;
     int st;
     if (cmax == 1)
-        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 1, W, true>(ctx, grid, smem, A)
-             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 1, W, true>(ctx, grid, smem, A)
-                                        : launch_dense<LEV_GGML_Q4_0, 1, W, true>(ctx, grid, smem, A);
+        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 1, 8, true>(ctx, grid, smem, A)
+             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 1, 8, true>(ctx, grid, smem, A)
+                                        : launch_dense<LEV_GGML_Q4_0, 1, 8, true>(ctx, grid, smem, A);
+    else if (W == 8)
+        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, 8, true>(ctx, grid, smem, A)
+             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, 8, true>(ctx, grid, smem, A)
+                                        : launch_dense<LEV_GGML_Q4_0, 4, 8, true>(ctx, grid, smem, A);
     else
-        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, W, true>(ctx, grid, smem, A)
-             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, W, true>(ctx, grid, smem, A)
-                                        : launch_dense<LEV_GGML_Q4_0, 4, W, true>(ctx, grid, smem, A);
+        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, 12, true>(ctx, grid, smem, A)
+             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, 12, true>(ctx, grid, smem, A)
+                                        : launch_dense<LEV_GGML_Q4_0, 4, 12, true>(ctx, grid, smem, A);
     if (st) return st;
     ctx->launches++;
     ctx->ev.grid = grid;
