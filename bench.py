@@ -469,6 +469,22 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         ms = _graph_time(torch, stream, fused_step, 16)
         out["ffn_gate_up_concatenated"] = {"launches_per_step": 2, "ms_per_step": ms, "gbs": STEP_BYTES / ms / 1e6,
                                            "hbm_frac": STEP_BYTES / ms / 1e6 / peaks["hbm_gbs"]}
+        # the same set at n = 2, 4, 8 activation columns (weights are streamed once per launch)
+        cols = {}
+        for n in (2, 4, 8):
+            xn = torch.randn((n, HIDDEN), generator=g, device=dev)
+            an = torch.randn((n, FFN), generator=g, device=dev)
+            ygun, ydnn = torch.empty((n, 2 * FFN), device=dev), torch.empty((n, HIDDEN), device=dev)
+
+            def col_step(i, xn=xn, an=an, ygun=ygun, ydnn=ydnn):
+                wgu, wd = fused[i % 4]
+                ctx.matvec(wgu, xn, out=ygun)
+                ctx.matvec(wd, an, out=ydnn)
+
+            msn = _graph_time(torch, stream, col_step, 16)
+            byts = 2 * GATE_BYTES + DOWN_BYTES + n * VEC_BYTES
+            cols[f"n{n}"] = {"ms_per_step": msn, "gbs": byts / msn / 1e6, "hbm_frac": byts / msn / 1e6 / peaks["hbm_gbs"]}
+        out["ffn_columns"] = {"workload": "gate/up concatenated + down, n activation columns", **cols}
         for wgu, wd in fused:
             wgu.free()
             wd.free()
