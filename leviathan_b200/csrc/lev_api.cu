@@ -67,14 +67,6 @@ int lev_scratch(lev_ctx* ctx, int slot, size_t bytes, void** out) {
     return LEV_OK;
 }
 
-int lev_scratch_zeroed(lev_ctx* ctx, int slot, size_t bytes, void** out) {
-    size_t before = ctx->scratch_bytes[slot];
-    LEV_TRY(lev_scratch(ctx, slot, bytes, out));
-    if (ctx->scratch_bytes[slot] != before)
-        LEV_CUDA(ctx, cudaMemsetAsync(*out, 0, ctx->scratch_bytes[slot], ctx->stream));
-    return LEV_OK;
-}
-
 int lev_read_status(lev_ctx* ctx, int* bits) {
     LEV_CUDA(ctx, cudaMemcpyAsync(ctx->h_status, ctx->d_status, sizeof(int), cudaMemcpyDeviceToHost, ctx->stream));
     LEV_CUDA(ctx, cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream));

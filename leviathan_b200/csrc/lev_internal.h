@@ -49,8 +49,6 @@ enum {
     LEV_SCR_MOE_D = 5,   // expert outputs per (token, rank)
     LEV_SCR_XPREP = 6,   // split activations for the stream schedule
     LEV_SCR_DIST = 7,
-    LEV_SCR_COUNTERS = 8,  // tile counters of the stream schedule, zero between launches
-    LEV_SCR_PARTIALS = 9,  // per-warp partial sums of the stream schedule
     LEV_SCR_SLOTS = 12
 };
 
@@ -87,7 +85,6 @@ int lev_fail(lev_ctx* ctx, int status, const char* fmt, ...);
 int lev_cuda_check(lev_ctx* ctx, cudaError_t e, const char* what);
 int lev_scratch(lev_ctx* ctx, int slot, size_t bytes, void** out);
 // like lev_scratch, and the buffer is zero-filled whenever it is (re)allocated
-int lev_scratch_zeroed(lev_ctx* ctx, int slot, size_t bytes, void** out);
 // reads the device status word (synchronizes the stream) and clears it
 int lev_read_status(lev_ctx* ctx, int* bits);
 

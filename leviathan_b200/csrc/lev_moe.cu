@@ -72,7 +72,7 @@ __global__ void __launch_bounds__(256) k_router_logits_plain(const float* __rest
 // Staged form: a CTA of 8 warps takes 8 experts x 8 tokens; every warp brings its expert's row
 // and one token's activations into shared memory with one bulk copy each (all 16 rows are in
 // flight at once: the plain form is bound by the latency of 88 dependent rounds of loads), then
-// warp w computes expert w against the 8 tokens.  Needs 16-byte aligned rows.
+// the warps share the 8 x 8 products in register tiles of 2 x 4.  Needs 16-byte aligned rows.
 __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__ rw, const float* __restrict__ x,
                                                        int64_t tokens, int experts, int hidden,
                                                        float* __restrict__ scores, int* status) {
@@ -130,26 +130,40 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
         if (threadIdx.x == 0) atomicOr(status, LEV_DEV_TIMEOUT);
         return;
     }
-    if (e >= experts) return;
-    double acc[8];
+    // warp w computes experts {2a, 2a+1} x tokens {4b .. 4b+3} of the tile (a = w & 3, b = w >> 2):
+    // six conversions to double and six shared-memory loads feed eight FMAs
+    const int ea = 2 * (warp & 3), tb = 4 * (warp >> 2);
+    const int e0 = blockIdx.x * 8 + ea;
+    if (e0 >= experts || tb >= ntok) return;
+    double acc[2][4];
 #pragma unroll
-    for (int j = 0; j < 8; j++) acc[j] = 0.0;
-    const float* wr = ws + (size_t)warp * hidden;
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) acc[a][b] = 0.0;
+    const float* w0 = ws + (size_t)ea * hidden;
+    const float* x0 = xs + (size_t)tb * hidden;
     for (int i = lane; i < hidden; i += 32) {
-        const double wv = (double)wr[i];
+        const double wv0 = (double)w0[i], wv1 = (double)w0[hidden + i];
 #pragma unroll
-        for (int j = 0; j < 8; j++)
-            if (j < ntok) acc[j] = fma(wv, (double)xs[(size_t)j * hidden + i], acc[j]);
+        for (int b = 0; b < 4; b++) {
+            if (tb + b < ntok) {
+                const double xv = (double)x0[(size_t)b * hidden + i];
+                acc[0][b] = fma(wv0, xv, acc[0][b]);
+                acc[1][b] = fma(wv1, xv, acc[1][b]);
+            }
+        }
     }
     bool bad = false;
 #pragma unroll
-    for (int j = 0; j < 8; j++) {
-        if (j < ntok) {
-            float sv = (float)warp_butterfly(acc[j]);
-            bad |= !isfinite(sv);
-            if (lane == 0) scores[(t0 + j) * experts + e] = sv;
+    for (int a = 0; a < 2; a++)
+#pragma unroll
+        for (int b = 0; b < 4; b++) {
+            if (tb + b < ntok && e0 + a < experts) {
+                float sv = (float)warp_butterfly(acc[a][b]);
+                bad |= !isfinite(sv);
+                if (lane == 0) scores[(t0 + tb + b) * experts + e0 + a] = sv;
+            }
         }
-    }
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
 }
 
@@ -798,7 +812,7 @@ static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float*
     J.njobs_dev = jt.njobs;
     J.job_slice = jt.job_slice;
     J.outmap = jt.job_pos;
-    LEV_TRY(lev_stream_run(ctx, w->gate_up, J, tables, cmax, terms, gu, nullptr));
+    LEV_TRY(lev_stream_run(ctx, w->gate_up, J, tables, cmax, terms, gu));
 
     // down: columns = gelu_tanh(gate) * up of each grouped position, outputs by pair id
     lev_stream_source src2 = {};
@@ -815,7 +829,7 @@ static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float*
     J2.njobs_dev = jt.njobs;
     J2.job_slice = jt.job_slice;
     J2.outmap = jt.job_pair;
-    LEV_TRY(lev_stream_run(ctx, w->down, J2, tables, cmax, terms, y_pairs, nullptr));
+    LEV_TRY(lev_stream_run(ctx, w->down, J2, tables, cmax, terms, y_pairs));
     if (act_out) {
         // activations by pair id, recomputed from the gate_up outputs (diagnostic output)
         LEV_TRY(lev_moe_launch_act(ctx, gu, perm, offsets + w->experts, pairs, w->inter, act_out));

@@ -6,16 +6,17 @@
 // a process whose allocator owns the whole device and hands out nothing after
 // start-up, or on a thread that may not take the driver's allocation lock.  The
 // ordinary lev_matvec grows context-owned work buffers on demand; this entry
-// point never does.  Its work buffers (split activation tables, per-warp
-// partial sums, per-tile counters) live in one file-scope device array of fixed
-// size that every GPU loading the library carries until the process exits.
+// point never does.  Shapes the one-launch kernel serves need no work buffer at
+// all (it builds its activation tables in shared memory); for the others the
+// split activation tables live in one file-scope device array of fixed size
+// that every GPU loading the library carries until the process exits.
 //
 // Rules that follow from that design:
 //   - requests whose work buffers would not fit LEV_STATIC_SCRATCH_BYTES are
 //     refused with LEV_EXCEEDS_WORKLOAD and a message naming both sizes;
 //   - the array is shared by every call and every context on the device and
-//     keeps whatever the previous call left in it; the counters are cleared at
-//     the start of each call, everything else is overwritten before it is read;
+//     keeps whatever the previous call left in it; every byte a call reads is
+//     written by that call first;
 //   - two calls that overlap on the GPU (different streams or contexts) race on
 //     the array: callers serialise them;
 //   - the first call on a device looks the array's device address up (the
@@ -75,24 +76,17 @@ extern "C" int lev_matvec_static_scratch(lev_ctx* ctx, const lev_weights* w, int
     J.rows = rows;
     J.out_ld = rows;
     J.max_jobs = 1;
-    size_t tb = align256(lev_stream_table_bytes(w, n_cols, terms, 1, nullptr)), pb, cb;
-    lev_stream_workspace_bytes(ctx, w, J, n_cols, &pb, &cb);
-    pb = align256(pb);
-    cb = align256(cb);
-    if (tb + pb + cb > LEV_STATIC_SCRATCH_BYTES)
+    const size_t tb = align256(lev_stream_table_bytes(w, n_cols, terms, 1, nullptr));
+    if (tb > LEV_STATIC_SCRATCH_BYTES)
         return lev_fail(ctx, LEV_EXCEEDS_WORKLOAD,
-                        "this call needs %zu bytes of work buffers, the static scratch holds %u; use lev_matvec",
-                        tb + pb + cb, (unsigned)LEV_STATIC_SCRATCH_BYTES);
+                        "this call needs %zu bytes of work buffers, the static scratch holds %u; use lev_matvec", tb,
+                        (unsigned)LEV_STATIC_SCRATCH_BYTES);
     unsigned char* base = nullptr;
     LEV_TRY(scratch_address(ctx, &base));
     void* tables = base;
-    void* partials = base + tb;
-    void* counters = base + tb + pb;
-    // the counters must read zero when the kernel starts, whatever the last call left behind
-    LEV_CUDA(ctx, cudaMemsetAsync(counters, 0, cb, ctx->stream));
     lev_stream_source src = {};
     src.x = x;
     src.ld = w->cols;
     LEV_TRY(lev_stream_prepare(ctx, w, src, n_cols, terms, 1, tables));
-    return lev_stream_run_ws(ctx, w, J, tables, n_cols, terms, y, nullptr, partials, counters);
+    return lev_stream_run(ctx, w, J, tables, n_cols, terms, y);
 }

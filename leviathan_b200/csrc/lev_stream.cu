@@ -21,19 +21,20 @@
 // accumulators per sub-block; the Q4_0 "-8" offset enters as the accumulator
 // initial value and the Q4_K min term is accumulated on CUDA cores.
 //
-// Data movement.  The whole tensor (or, grouped, the list of expert slices)
-// is one linear stream of K-steps cut into equal contiguous ranges, one per
-// warp of a grid that is resident all at once.  Every warp owns a private
-// ring of kDepth shared-memory stages filled by bulk asynchronous copies
-// (cp.async.bulk global->shared completing on an mbarrier) that it issues
-// itself: about kDepth*2304 bytes per warp are in flight, no registers hold
-// them and warps never wait for each other.
+// Data movement.  Tiles are handed to CTAs in groups whose K-steps the CTA's warps split
+// evenly (a dense call sizes the groups so that the whole tensor is one resident wave; a
+// grouped call, whose tile count only the device knows, lets the CTAs stride over groups).
+// Every warp owns a private ring of shared-memory stages filled by bulk asynchronous copies
+// (cp.async.bulk global->shared completing on an mbarrier) that it issues itself; no registers
+// hold data in flight and warps never wait for each other.
 //
-// Reduction.  Tiles that lie wholly in one warp's range are written straight
-// to y; for the others each warp leaves one f32 per (row, column) in a
-// partials record and bumps the tile's counter; the warp that arrives last
-// adds the records in warp order, so the same call always gives the same
-// bits regardless of arrival order.
+// Reduction.  Tiles that lie wholly in one warp's range are written straight to y; for the
+// others each warp leaves one f32 per (row, column) in a shared-memory record and the CTA adds
+// the records in warp order after a barrier, so the same call always gives the same bits.
+//
+// This file serves the grouped expert FFN, dense calls with 5..8 columns and dense calls whose
+// activation tables do not fit shared memory; lev_dense.cu holds the one-launch kernel for the
+// rest.
 #include "lev_stream.h"
 #include "lev_stream_math.cuh"
 
@@ -685,41 +686,14 @@ static PrepArgs make_prep(lev_ctx* ctx, const lev_weights* w, const lev_stream_s
     return P;
 }
 
-// sizes of the two work buffers a call needs: per-warp partial sums and per-tile counters
-void lev_stream_workspace_bytes(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, int cmax,
-                                size_t* partial_bytes, size_t* counter_bytes) {
-    const int64_t steps = lev_stream_chunks(w) / 4, tiles_per_job = (J.rows + 15) / 16;
-    const int64_t max_steps = (int64_t)J.max_jobs * tiles_per_job * steps;
-    int ctas_per_sm = env_int("LEV_STREAM_CTAS_PER_SM", 3);
-    ctas_per_sm = ctas_per_sm < 1 ? 1 : (ctas_per_sm > 3 ? 3 : ctas_per_sm);
-    int grid = ctx->prop.multiProcessorCount * ctas_per_sm;
-    int64_t need_warps = (max_steps + 1) / 2;
-    if ((int64_t)grid * kWarpsPerCta > need_warps) grid = (int)((need_warps + kWarpsPerCta - 1) / kWarpsPerCta);
-    if (grid < 1) grid = 1;
-    *partial_bytes = (size_t)grid * kWarpsPerCta * 2 * cmax * 16 * sizeof(float);
-    *counter_bytes = (size_t)(J.max_jobs * tiles_per_job + 2) * sizeof(int);
-}
-
 int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, const void* tables, int cmax, int terms,
-                   float* y, const lev_stream_source* fused_src) {
-    size_t pb, cb;
-    lev_stream_workspace_bytes(ctx, w, J, cmax, &pb, &cb);
-    void *pbuf, *counters;
-    LEV_TRY(lev_scratch(ctx, LEV_SCR_PARTIALS, pb, &pbuf));
-    LEV_TRY(lev_scratch_zeroed(ctx, LEV_SCR_COUNTERS, cb, &counters));
-    return lev_stream_run_ws(ctx, w, J, tables, cmax, terms, y, fused_src, pbuf, counters);
-}
-
-// the launch itself, on caller-provided work buffers (counters zero on entry; left zero on exit)
-int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, const void* tables, int cmax, int terms,
-                      float* y, const lev_stream_source* fused_src, void* pbuf, void* counters) {
+                   float* y) {
     const int glt = cmax * terms;
     const int64_t chunks = lev_stream_chunks(w), steps = chunks / 4;
     const bool grouped = J.njobs_dev != nullptr;
     const int64_t tiles_per_job = (J.rows + 15) / 16;
     const int64_t max_steps = (int64_t)J.max_jobs * tiles_per_job * steps;
     if (max_steps > 0x7fffffff / 4) return lev_fail(ctx, LEV_EXCEEDS_WORKLOAD, "stream schedule: too many K-steps");
-    if (fused_src) return lev_fail(ctx, LEV_UNSUPPORTED, "in-kernel activation preparation is not built");
     if (terms != lev_stream_terms(cmax)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "stream schedule: %d terms with %d columns", terms, cmax);
 
     const size_t kStepBytes = step_bytes(w->type);
@@ -776,8 +750,6 @@ int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& 
     A.cmax = cmax;
     A.terms = terms;
     A.glt = glt;
-    (void)pbuf;      // reductions stay inside a CTA: the global work buffers are no longer touched
-    (void)counters;
     A.status = ctx->d_status;
     A.y = y;
     A.debug = env_int("LEV_STREAM_DEBUG", 0);
@@ -811,5 +783,5 @@ int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, i
     const int dbg = env_int("LEV_STREAM_DEBUG", 0);  // timing aids: bit 1 no main launch, bit 2 no preparation launch
     if (!(dbg & 4)) LEV_TRY(lev_stream_prepare(ctx, w, src, n_cols, terms, 1, tables));
     if (dbg & 2) return LEV_OK;
-    return lev_stream_run(ctx, w, J, tables, n_cols, terms, y, nullptr);
+    return lev_stream_run(ctx, w, J, tables, n_cols, terms, y);
 }

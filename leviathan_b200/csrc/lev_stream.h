@@ -30,14 +30,9 @@ int64_t lev_stream_chunks(const lev_weights* w);
 size_t lev_stream_table_bytes(const lev_weights* w, int cmax, int terms, int jobs, size_t* frag_bytes);
 int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_source& src, int cmax, int terms, int jobs,
                        void* tables);
-// fused_src != NULL (dense calls whose tables fit shared memory): every CTA builds the
-// tables itself and `tables` is unused
+// tables: what lev_stream_prepare wrote for the same (weights, cmax, terms, jobs)
 int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
-                   int terms, float* y, const lev_stream_source* fused_src);
-void lev_stream_workspace_bytes(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, int cmax,
-                                size_t* partial_bytes, size_t* counter_bytes);
-int lev_stream_run_ws(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
-                      int terms, float* y, const lev_stream_source* fused_src, void* partials, void* counters);
+                   int terms, float* y);
 
 // one-launch dense matvec (lev_dense.cu): n_cols <= 4 and tables that fit shared memory
 bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols);
