@@ -207,9 +207,20 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
     for (int i = lane; i < experts; i += 32) p[i] = exp((double)(s[i] - m));
     __syncwarp();
+    // ascending sequential sum like the reference's reduce(0, +); the loads are issued eight at a
+    // time so that only the additions are serial
     double sum = 0.0;
-    if (lane == 0)
-        for (int i = 0; i < experts; i++) sum += p[i];
+    if (lane == 0) {
+        int i = 0;
+        for (; i + 8 <= experts; i += 8) {
+            double v[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) v[u] = p[i + u];
+#pragma unroll
+            for (int u = 0; u < 8; u++) sum += v[u];
+        }
+        for (; i < experts; i++) sum += p[i];
+    }
     sum = __shfl_sync(0xffffffffu, sum, 0);
     for (int i = lane; i < experts; i += 32) p[i] = p[i] / sum;
     __syncwarp();
