@@ -17,7 +17,9 @@ import json
 import os
 import sys
 
-ref = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) != 2:
+    sys.exit(__doc__)
+ref = sys.argv[1]
 q4 = os.path.join(ref, "tools", "q4_lower")
 sys.path.insert(0, q4)
 from q4_op_model import Q4MatvecOp, check_op  # noqa: E402
