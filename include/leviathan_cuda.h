@@ -198,6 +198,16 @@ int lev_matvec_static_scratch(lev_ctx* ctx, const lev_weights* w, int64_t row0, 
                               int64_t y_capacity);
 size_t lev_static_scratch_bytes(void);
 
+/* No single counterpart in the reference: n_ops (1...4) resident tensors against the same
+ * activations in one call -- gate and up of an FFN, q/k/v of attention (the reference issues one
+ * matvec dispatch per tensor, Sources/LeviathanCore/Gemma4.swift:3747-3750; its expert tensors
+ * are stored gate/up-fused for the same reason, MoESIMDLowering.swift:106-107).  Whole tensors
+ * (no row window); y[i] is [n_cols][rows of tensor i] with y_capacity[i] elements.  Tensors of
+ * one format and inDim run as ONE launch; any other mix runs one matvec per tensor. */
+int lev_matvec_multi(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x,
+                     int64_t x_count, int n_cols, float* const* y, const int64_t* y_capacity,
+                     unsigned flags);
+
 /* ---- prefill dequant-GEMM ----------------------------------------------
  * Y[t][r] = sum_k bf16(W[r][k]) * X[t][k], f32 accumulate; X is bf16
  * [tokens][cols], Y is f32 [tokens][rows].  Replaces the act_f16 +

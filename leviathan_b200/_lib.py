@@ -65,6 +65,7 @@ SIGNATURES = {
     "lev_q4_0_matvec_host": (_I, [_P, _P, _Z, _L, _L, _P, _L, _P, C.POINTER(Evidence)]),
     "lev_q4_k_matvec_host": (_I, [_P, _P, _Z, _L, _L, _P, _L, _P, C.POINTER(Evidence)]),
     "lev_q6_k_matvec_host": (_I, [_P, _P, _Z, _L, _L, _P, _L, _P, C.POINTER(Evidence)]),
+    "lev_matvec_multi": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(_P), C.POINTER(_L), _U]),
     "lev_matvec_static_scratch": (_I, [_P, _P, _L, _L, _P, _L, _I, _P, _L]),
     "lev_static_scratch_bytes": (_Z, []),
     "lev_gemm_prefill": (_I, [_P, _P, _P, _L, _P, _U]),

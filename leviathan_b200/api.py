@@ -186,6 +186,23 @@ class Context:
                                         schedule, self._flags(host, check_finite)))
         return out[0] if one_d else out
 
+    def matvec_multi(self, ws, x, outs=None, check_finite: bool = False):
+        """Several resident tensors against the same activations (one launch when they share
+        format and inDim).  Returns one [n_cols][rows_i] array per tensor."""
+        host = not _is_torch(x)
+        x = np.ascontiguousarray(x, np.float32) if host else x.contiguous()
+        one_d = x.ndim == 1
+        n_cols = 1 if one_d else x.shape[0]
+        n = len(ws)
+        if outs is None:
+            outs = [self._empty_like_io(x, (n_cols, w.rows), np.float32, "float32") for w in ws]
+        wp = (C.c_void_p * n)(*[w.handle for w in ws])
+        yp = (C.c_void_p * n)(*[_ptr(o) for o in outs])
+        cap = (C.c_int64 * n)(*[int(o.size if host else o.numel()) for o in outs])
+        count = int(x.size if host else x.numel())
+        self._check(self.lib.lev_matvec_multi(self.handle, n, wp, _ptr(x), count, n_cols, yp, cap, self._flags(host, check_finite)))
+        return outs
+
     def matvec_static_scratch(self, w: Weights, x, row0: int = 0, rows: int | None = None, out=None):
         """lev_matvec_static_scratch: the stream-schedule matvec that allocates
         nothing (torch CUDA tensors only); see include/leviathan_cuda.h."""

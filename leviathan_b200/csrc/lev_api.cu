@@ -9,6 +9,7 @@
 #include <new>
 
 #include "lev_internal.h"
+#include "lev_stream.h"
 
 extern "C" int lev_cuda_abi_version(void) { return LEV_CUDA_ABI_VERSION; }
 
@@ -369,6 +370,75 @@ extern "C" int lev_matvec(lev_ctx* ctx, const lev_weights* w, int64_t row0, int6
     if (flags & LEV_FLAG_CHECK_FINITE) LEV_TRY(lev_launch_finite_check(ctx, dy, (int64_t)n_cols * rows, LEV_DEV_NONFINITE_OUTPUT));
     if ((flags & LEV_FLAG_HOST_IO) && !y_direct)
         LEV_CUDA(ctx, cudaMemcpyAsync(y, dy, yb, cudaMemcpyDeviceToHost, ctx->stream));
+    if (flags & (LEV_FLAG_CHECK_FINITE | LEV_FLAG_HOST_IO)) {
+        int bits = 0;
+        if (flags & LEV_FLAG_CHECK_FINITE) {
+            LEV_TRY(lev_read_status(ctx, &bits));
+        } else {
+            LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+        }
+        if (bits & LEV_DEV_NONFINITE_INPUT) return lev_fail(ctx, LEV_NONFINITE_INPUT, "activation vector");
+        if (bits & LEV_DEV_NONFINITE_OUTPUT) return lev_fail(ctx, LEV_NONFINITE_OUTPUT, "output vector");
+    }
+    return LEV_OK;
+}
+
+// Several resident tensors against the same activations.  One launch when the tensors share
+// format and inDim and the one-launch kernel serves them; otherwise one matvec per tensor.
+extern "C" int lev_matvec_multi(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int64_t x_count,
+                                int n_cols, float* const* y, const int64_t* y_capacity, unsigned flags) {
+    if (!ctx || !w || !x || !y || !y_capacity) return LEV_BAD_ARGUMENT;
+    if (n_ops < 1 || n_ops > 4) return lev_fail(ctx, LEV_BAD_ARGUMENT, "%d tensors (1...4)", n_ops);
+    if (n_cols < 1 || n_cols > LEV_MAX_COLUMNS)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d outside 1...%d", n_cols, LEV_MAX_COLUMNS);
+    for (int i = 0; i < n_ops; i++) {
+        if (!w[i] || !y[i]) return LEV_BAD_ARGUMENT;
+        if (x_count != (int64_t)n_cols * w[i]->cols)
+            return lev_fail(ctx, LEV_WRONG_INPUT_COUNT, "input count %lld, tensor %d expects %lld", (long long)x_count, i,
+                            (long long)((int64_t)n_cols * w[i]->cols));
+        if (y_capacity[i] < (int64_t)n_cols * w[i]->rows)
+            return lev_fail(ctx, LEV_BAD_DIMENSIONS, "output %d capacity %lld below %lld", i, (long long)y_capacity[i],
+                            (long long)((int64_t)n_cols * w[i]->rows));
+    }
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const bool host = flags & LEV_FLAG_HOST_IO;
+    const float* dx = x;
+    float* dy[4] = {nullptr, nullptr, nullptr, nullptr};
+    const size_t xb = (size_t)x_count * sizeof(float);
+    if (host) {
+        if (flags & LEV_FLAG_CHECK_FINITE)
+            for (int64_t i = 0; i < x_count; i++)
+                if (!isfinite(x[i])) return lev_fail(ctx, LEV_NONFINITE_INPUT, "activation vector");
+        void* px;
+        LEV_TRY(lev_scratch(ctx, LEV_SCR_X, xb, &px));
+        LEV_CUDA(ctx, cudaMemcpyAsync(px, x, xb, cudaMemcpyHostToDevice, ctx->stream));
+        dx = (const float*)px;
+        size_t total = 0;
+        for (int i = 0; i < n_ops; i++) total += ((size_t)n_cols * w[i]->rows * sizeof(float) + 255) & ~(size_t)255;
+        void* py;
+        LEV_TRY(lev_scratch(ctx, LEV_SCR_Y, total, &py));
+        size_t off = 0;
+        for (int i = 0; i < n_ops; i++) {
+            dy[i] = (float*)((char*)py + off);
+            off += ((size_t)n_cols * w[i]->rows * sizeof(float) + 255) & ~(size_t)255;
+        }
+    } else {
+        for (int i = 0; i < n_ops; i++) dy[i] = y[i];
+        if (flags & LEV_FLAG_CHECK_FINITE) LEV_TRY(lev_launch_finite_check(ctx, dx, x_count, LEV_DEV_NONFINITE_INPUT));
+    }
+    if (n_ops >= 2 && lev_dense_multi_supported(ctx, n_ops, w, dx, n_cols)) {
+        note_evidence(ctx, "lev_matvec_stream_multi", w[0], w[0]->rows, n_cols, 0, 0);
+        LEV_TRY(lev_dense_multi_run(ctx, n_ops, w, dx, n_cols, dy));
+    } else {
+        for (int i = 0; i < n_ops; i++)
+            LEV_TRY(lev_matvec(ctx, w[i], 0, w[i]->rows, dx, x_count, n_cols, dy[i], (int64_t)n_cols * w[i]->rows, LEV_SCHEDULE_AUTO, 0));
+    }
+    if (flags & LEV_FLAG_CHECK_FINITE)
+        for (int i = 0; i < n_ops; i++)
+            LEV_TRY(lev_launch_finite_check(ctx, dy[i], (int64_t)n_cols * w[i]->rows, LEV_DEV_NONFINITE_OUTPUT));
+    if (host)
+        for (int i = 0; i < n_ops; i++)
+            LEV_CUDA(ctx, cudaMemcpyAsync(y[i], dy[i], (size_t)n_cols * w[i]->rows * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     if (flags & (LEV_FLAG_CHECK_FINITE | LEV_FLAG_HOST_IO)) {
         int bits = 0;
         if (flags & LEV_FLAG_CHECK_FINITE) {

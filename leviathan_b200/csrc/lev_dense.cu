@@ -54,12 +54,20 @@ struct DenseArgs {
     int tiles_per_job;
     int gelu_inter;         // > 0: activation e = gelu_tanh(src[e]) * src[gelu_inter + e]
     int table_stride;       // bytes between the tables of consecutive jobs in shared memory
+    // multi form (MULTI): up to four tensors of one format and K against the same activations;
+    // the call's tiles are the tensors' tiles in order
+    int n_ops;
+    const uint4* wp_op[4];  // first tile of each tensor's row window
+    int tiles_cum[5];       // tiles before each tensor
+    float* y_op[4];         // [n_cols][rows_op]
+    int64_t rows_op[4];
 };
 
 constexpr int kMaxJobTables = 3;  // jobs whose tables one CTA of the sliced form can hold
 
-template <int TYPE, int CMAX, int W, bool JOBS>
+template <int TYPE, int CMAX, int W, bool JOBS, bool MULTI = false>
 __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
+    static_assert(!(JOBS && MULTI), "a call is either a job list or a list of tensors");
     using D = StreamDims<CMAX>;
     constexpr int NT = D::kNT, GLT = D::kGlt, TERMS = D::kTerms;
     constexpr int kStepBytes = step_bytes(TYPE);
@@ -110,17 +118,43 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         return reinterpret_cast<const unsigned char*>(A.wp) +
                (((int64_t)A.job_slice[job] * tpj + tij) * spt + k) * (int64_t)kStepBytes;
     };
+    // multi form: the tensor a global tile belongs to
+    auto op_of = [&](int gt) -> int {
+        int o = 0;
+        while (o + 1 < A.n_ops && gt >= A.tiles_cum[o + 1]) o++;
+        return o;
+    };
+    auto multi_src = [&](int q) -> const unsigned char* {
+        const int tq = q / spt, gt = tile0 + tq, kq = q - tq * spt, o = op_of(gt);
+        return reinterpret_cast<const unsigned char*>(A.wp_op[o]) + ((int64_t)(gt - A.tiles_cum[o]) * spt + kq) * (int64_t)kStepBytes;
+    };
+    // requests the next stage's K-steps into ring stage d (lane 0)
+    auto issue_stage = [&](int d) {
+        const int n = f_left < sps ? f_left : sps;
+        const unsigned dst = ring_s + d * stage_bytes, bar = bar_s + 8 * d;
+        if (MULTI) {
+            // consecutive steps are contiguous except where the next tile belongs to another tensor
+            mbar_expect(bar, n * kStepBytes);
+            int u = 0;
+            while (u < n) {
+                const unsigned char* a0 = multi_src(f_q + u);
+                int run = 1;
+                while (u + run < n && multi_src(f_q + u + run) == a0 + (size_t)run * kStepBytes) run++;
+                bulk_copy(dst + u * kStepBytes, a0, run * kStepBytes, bar);
+                u += run;
+            }
+        } else {
+            bulk_load(dst, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar);
+        }
+        f_ptr += n * kStepBytes;
+        f_q += n;
+        f_left -= n;
+    };
     if (lane == 0) {
         for (int d = 0; d < depth; d++) mbar_init(bar_s + 8 * d, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-        for (int d = 0; d < depth && f_left > 0; d++) {
-            const int n = f_left < sps ? f_left : sps;
-            bulk_load(ring_s + d * stage_bytes, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar_s + 8 * d);
-            f_ptr += n * kStepBytes;
-            f_q += n;
-            f_left -= n;
-        }
+        for (int d = 0; d < depth && f_left > 0; d++) issue_stage(d);
     }
     LaneOffsets<CMAX> O;
     O.init(lane);
@@ -267,6 +301,8 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     const uint4* xs = reinterpret_cast<const uint4*>(tables0);
     const float* sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
     int job = 0, tij = tile0 + tl;
+    float* cur_y = A.y;
+    int64_t cur_rows = A.rows, cur_ld = A.out_ld;
     int orow[CMAX];
 #pragma unroll
     for (int c = 0; c < CMAX; c++) orow[c] = 0;
@@ -278,6 +314,11 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
 #pragma unroll
             for (int c = 0; c < CMAX; c++) orow[c] = A.job_out[job * CMAX + c];
+        } else if (MULTI) {
+            const int o = op_of(tile0 + tl);
+            tij = tile0 + tl - A.tiles_cum[o];
+            cur_y = A.y_op[o];
+            cur_rows = cur_ld = A.rows_op[o];
         } else {
             tij = tile0 + tl;
         }
@@ -324,8 +365,8 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
                             const int64_t row = (int64_t)tij * 16 + g;
                             const int oc = JOBS ? orow[c] : c;
                             if (JOBS ? orow[c] >= 0 : c < A.n_cols) {
-                                if (row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = va;
-                                if (row + 8 < A.rows) A.y[(int64_t)oc * A.out_ld + row + 8] = vb;
+                                if (row < cur_rows) cur_y[(int64_t)oc * cur_ld + row] = va;
+                                if (row + 8 < cur_rows) cur_y[(int64_t)oc * cur_ld + row + 8] = vb;
                             }
                         } else {
                             rec[warp][r][c][g] = va;
@@ -347,13 +388,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         }
         // every lane has consumed its shared-memory reads of this stage: refill it
         __syncwarp();
-        if (lane == 0 && f_left > 0) {
-            const int n = f_left < sps ? f_left : sps;
-            bulk_load(ring_s + slot * stage_bytes, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar_s + 8 * slot);
-            f_ptr += n * kStepBytes;
-            f_q += n;
-            f_left -= n;
-        }
+        if (lane == 0 && f_left > 0) issue_stage(slot);
         if (++slot == depth) {
             slot = 0;
             phase ^= 1u;
@@ -380,6 +415,10 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             const int pjob = (tile0 + tile) / tpj, ptij = tile0 + tile - pjob * tpj, oc = A.job_out[pjob * CMAX + c];
             const int64_t row = (int64_t)ptij * 16 + (idx & 15);
             if (oc >= 0 && row < A.rows) A.y[(int64_t)oc * A.out_ld + row] = acc;
+        } else if (MULTI) {
+            const int o = op_of(tile0 + tile);
+            const int64_t row = (int64_t)(tile0 + tile - A.tiles_cum[o]) * 16 + (idx & 15);
+            if (c < A.n_cols && row < A.rows_op[o]) A.y_op[o][(int64_t)c * A.rows_op[o] + row] = acc;
         } else {
             const int64_t row = (int64_t)(tile0 + tile) * 16 + (idx & 15);
             if (c < A.n_cols && row < A.rows) A.y[(int64_t)c * A.out_ld + row] = acc;
@@ -396,18 +435,18 @@ extern "C" int lev_debug_timeline(long long* out) {
 namespace {
 #endif
 
-template <int TYPE, int CMAX, int W, bool JOBS = false>
+template <int TYPE, int CMAX, int W, bool JOBS = false, bool MULTI = false>
 int launch_dense(lev_ctx* ctx, int grid, size_t smem, const DenseArgs& A) {
     static size_t configured[16] = {};  // per device: largest dynamic shared memory opted in so far
     if (configured[ctx->device & 15] < smem) {
-        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W, JOBS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W, JOBS, MULTI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         // every instance asks for the same (largest) shared-memory carve-out: an SM whose split
         // would have to change between two launches cannot hold CTAs of both at once
-        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W, JOBS>, cudaFuncAttributePreferredSharedMemoryCarveout,
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_dense<TYPE, CMAX, W, JOBS, MULTI>, cudaFuncAttributePreferredSharedMemoryCarveout,
                                            (int)cudaSharedmemCarveoutMaxShared));
         configured[ctx->device & 15] = smem;
     }
-    LEV_CUDA(ctx, launch_pdl(k_dense<TYPE, CMAX, W, JOBS>, dim3(grid), dim3(W * 32), smem, ctx->stream, A));
+    LEV_CUDA(ctx, launch_pdl(k_dense<TYPE, CMAX, W, JOBS, MULTI>, dim3(grid), dim3(W * 32), smem, ctx->stream, A));
     return LEV_OK;
 }
 
@@ -436,11 +475,11 @@ struct DensePlan {
 };
 
 // Shape of a launch, or false when the tables do not fit beside a useful ring.
-bool dense_plan(lev_ctx* ctx, const lev_weights* w, int64_t rows, int n_cols, DensePlan* P) {
+bool dense_plan_tiles(lev_ctx* ctx, const lev_weights* w, int64_t tiles, int n_cols, DensePlan* P) {
     if (n_cols < 1 || n_cols > 4 || env_int("LEV_DENSE", 1) == 0) return false;
     const size_t step = step_bytes(w->type);
     const size_t tb = lev_stream_table_bytes(w, n_cols, 2, 1, nullptr);
-    const int64_t tiles = (rows + 15) / 16, spt = lev_stream_chunks(w) / 4;
+    const int64_t spt = lev_stream_chunks(w) / 4;
     if (tiles < 1 || tiles * spt > 0x7fffffff / 64) return false;
     int warps = env_int("LEV_DENSE_WARPS", 8);
     if (warps != 8 && warps != 12 && warps != 16 && warps != 24) warps = 8;
@@ -474,7 +513,78 @@ bool dense_plan(lev_ctx* ctx, const lev_weights* w, int64_t rows, int n_cols, De
     return true;
 }
 
+bool dense_plan(lev_ctx* ctx, const lev_weights* w, int64_t rows, int n_cols, DensePlan* P) {
+    return dense_plan_tiles(ctx, w, (rows + 15) / 16, n_cols, P);
+}
+
+template <int TYPE>
+int launch_multi_c(lev_ctx* ctx, int cmax, int grid, size_t smem, const DenseArgs& A) {
+    switch (cmax) {
+        case 1: return launch_dense<TYPE, 1, 8, false, true>(ctx, grid, smem, A);
+        case 2: return launch_dense<TYPE, 2, 8, false, true>(ctx, grid, smem, A);
+        case 3: return launch_dense<TYPE, 3, 8, false, true>(ctx, grid, smem, A);
+        case 4: return launch_dense<TYPE, 4, 8, false, true>(ctx, grid, smem, A);
+    }
+    return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d", cmax);
+}
+
 }  // namespace
+
+// Several whole tensors of one format and K against the same activations in one launch.
+bool lev_dense_multi_supported(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols) {
+    if (n_ops < 2 || n_ops > 4 || ((uintptr_t)x & 15) != 0 || env_int("LEV_DENSE_WARPS", 8) != 8) return false;
+    int64_t tiles = 0;
+    for (int i = 0; i < n_ops; i++) {
+        if (!w[i] || !w[i]->packed || w[i]->type != w[0]->type || w[i]->cols != w[0]->cols) return false;
+        tiles += (w[i]->rows + 15) / 16;
+    }
+    DensePlan P;
+    return dense_plan_tiles(ctx, w[0], tiles, n_cols, &P);
+}
+
+int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y) {
+    if (!lev_dense_multi_supported(ctx, n_ops, w, x, n_cols))
+        return lev_fail(ctx, LEV_UNSUPPORTED, "multi-tensor dense kernel: shapes not served");
+    const int64_t chunks = lev_stream_chunks(w[0]), spt = chunks / 4;
+    DenseArgs A = {};
+    int64_t tiles = 0;
+    A.n_ops = n_ops;
+    for (int i = 0; i < n_ops; i++) {
+        A.wp_op[i] = (const uint4*)w[i]->packed;
+        A.tiles_cum[i] = (int)tiles;
+        A.y_op[i] = y[i];
+        A.rows_op[i] = w[i]->rows;
+        tiles += (w[i]->rows + 15) / 16;
+    }
+    for (int i = n_ops; i <= 4; i++) A.tiles_cum[i] = (int)tiles;
+    DensePlan P;
+    dense_plan_tiles(ctx, w[0], tiles, n_cols, &P);
+    A.wp = A.wp_op[0];
+    A.spt = (int)spt;
+    A.tiles_base = (int)(tiles / P.grid);
+    A.tiles_rem = (int)(tiles % P.grid);
+    A.x = x;
+    A.x_ld = w[0]->cols;
+    A.cols = (int)w[0]->cols;
+    A.chunks = (int)chunks;
+    A.n_cols = n_cols;
+    A.y = y[0];
+    A.rows = w[0]->rows;
+    A.out_ld = w[0]->rows;
+    A.status = ctx->d_status;
+    A.depth = P.depth;
+    A.sps = P.sps;
+    A.debug = env_int("LEV_STREAM_DEBUG", 0);
+    const int t = w[0]->type;
+    int st = t == LEV_GGML_Q4_K   ? launch_multi_c<LEV_GGML_Q4_K>(ctx, n_cols, P.grid, P.smem, A)
+             : t == LEV_GGML_Q6_K ? launch_multi_c<LEV_GGML_Q6_K>(ctx, n_cols, P.grid, P.smem, A)
+                                  : launch_multi_c<LEV_GGML_Q4_0>(ctx, n_cols, P.grid, P.smem, A);
+    if (st) return st;
+    ctx->launches++;
+    ctx->ev.grid = P.grid;
+    ctx->ev.block = 8 * 32;
+    return lev_cuda_check(ctx, cudaGetLastError(), "k_dense (multi)");
+}
 
 bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols) {
     DensePlan P;

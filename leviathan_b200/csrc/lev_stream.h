@@ -44,3 +44,7 @@ bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_p
 int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax, const int* njobs_dev,
                        const int* job_slice, const int* job_src, const int* job_out, const float* x, int64_t x_ld,
                        int gelu_inter, float* y, int64_t out_ld);
+
+// multi form: several whole tensors of one format and K against the same activations, one launch
+bool lev_dense_multi_supported(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols);
+int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y);

@@ -117,6 +117,16 @@ __device__ __forceinline__ bool mbar_test(unsigned bar, unsigned parity) {
         : "memory");
     return ok != 0;
 }
+// the two halves of bulk_load, for stages filled by more than one copy
+__device__ __forceinline__ void mbar_expect(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void bulk_copy(unsigned dst, const void* src, unsigned bytes, unsigned bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(dst),
+        "l"(src), "r"(bytes), "r"(bar)
+        : "memory");
+}
 // bounded wait: false when the phase did not complete within kWaitCycles SM clocks (about a second)
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity) {
     long long t_start = 0;

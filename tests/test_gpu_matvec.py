@@ -289,3 +289,40 @@ def test_installed_op_serves_matching_tensors(ctx):
     ctx.op_uninstall(op)
     good.free()
     other.free()
+
+
+@pytest.mark.parametrize("name,rows_list,cols", [("q4_k", (1040, 512, 96), 1024), ("q6_k", (64, 80), 768),
+                                                 ("q4_0", (300, 300), 2816)])
+@pytest.mark.parametrize("n_cols", [1, 3])
+def test_matvec_multi_matches_single_calls(ctx, name, rows_list, cols, n_cols):
+    """lev_matvec_multi: several tensors against the same activations in one launch give each
+    tensor's own result (vs the f64 oracle, and close to the single-tensor call)."""
+    t = H.TYPES[name]
+    ws = [H.quantized(t, 700 + i, r, cols) for i, r in enumerate(rows_list)]
+    hs = [ctx.upload(w, t, r, cols) for w, r in zip(ws, rows_list)]
+    x = Q.normal(710, (n_cols, cols), 1.0)
+    xd = torch.from_numpy(x).cuda()
+    outs = ctx.matvec_multi(hs, xd, check_finite=True)
+    torch.cuda.synchronize()
+    for w, r, h, o in zip(ws, rows_list, hs, outs):
+        o = o.cpu().numpy()
+        single = ctx.matvec(h, xd, schedule=lev.SCHEDULE_STREAM).cpu().numpy()
+        for c in range(n_cols):
+            assert O.max_rel_err(o[c], O.matvec_f64(t, w, r, cols, x[c])) < H.REPORT_TOL
+            assert O.max_rel_err(o[c], single[c].astype(np.float64)) < 1e-5
+    # host buffers
+    houts = ctx.matvec_multi(hs, x)
+    for o, ho in zip(outs, houts):
+        assert np.array_equal(o.cpu().numpy().view(np.uint32), ho.view(np.uint32))
+    # tensors that do not share a format fall back to one launch per tensor
+    if name == "q4_k":
+        other = ctx.upload(H.quantized(H.TYPES["q4_0"], 720, 64, cols), H.TYPES["q4_0"], 64, cols)
+        mixed = ctx.matvec_multi([hs[0], other], xd)
+        assert np.array_equal(mixed[0].cpu().numpy().view(np.uint32), outs[0].cpu().numpy().view(np.uint32)) or \
+            O.max_rel_err(mixed[0].cpu().numpy()[0], outs[0].cpu().numpy()[0].astype(np.float64)) < 1e-5
+        other.free()
+    with pytest.raises(lev.LevError) as e:
+        ctx.matvec_multi(hs, xd[:, :-32].contiguous())
+    assert e.value.name == "wrongInputCount"
+    for h in hs:
+        h.free()
