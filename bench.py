@@ -515,6 +515,42 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         ms = _graph_time(torch, stream, fused_step, 16)
         out["ffn_gate_up_concatenated"] = {"launches_per_step": 2, "ms_per_step": ms, "gbs": STEP_BYTES / ms / 1e6,
                                            "hbm_frac": STEP_BYTES / ms / 1e6 / peaks["hbm_gbs"]}
+        # the set through lev_matvec_multi: gate and up stay separate resident tensors, one launch
+        sep = []
+        for i in range(4):
+            gq, uq, dq = make_instance(200 + i, dev)
+            sep.append((ctx.upload(gq, Q4_K, FFN, HIDDEN), ctx.upload(uq, Q4_K, FFN, HIDDEN), ctx.upload(dq, Q6_K, HIDDEN, FFN)))
+            del gq, uq, dq
+        yg2, yu2 = torch.empty((1, FFN), device=dev), torch.empty((1, FFN), device=dev)
+
+        def multi_step(i):
+            wg, wu, wd = sep[i % 4]
+            ctx.matvec_multi([wg, wu], xd, outs=[yg2, yu2])
+            ctx.matvec(wd, ad, out=ydn)
+
+        ms = _graph_time(torch, stream, multi_step, 16)
+        xp, ap_ = torch.from_numpy(x_h).pin_memory(), torch.from_numpy(a_h).pin_memory()
+        ygp, yup, ydp = (torch.empty(1, FFN).pin_memory(), torch.empty(1, FFN).pin_memory(), torch.empty(1, HIDDEN).pin_memory())
+
+        def multi_host_step(i):
+            wg, wu, wd = sep[i % 4]
+            ctx.matvec_multi([wg, wu], xp.numpy(), outs=[ygp.numpy(), yup.numpy()])
+            ctx.matvec(wd, ap_.numpy(), out=ydp.numpy())
+
+        for i in range(3):
+            multi_host_step(i)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for i in range(32):
+            multi_host_step(i)
+        torch.cuda.synchronize()
+        e2e_ms = 1000.0 * (time.perf_counter() - t0) / 32
+        out["ffn_matvec_multi"] = {"calls_per_step": 2, "ms_per_step": ms, "gbs": STEP_BYTES / ms / 1e6,
+                                   "hbm_frac": STEP_BYTES / ms / 1e6 / peaks["hbm_gbs"],
+                                   "e2e_ms_per_step": e2e_ms, "e2e_gbs": STEP_BYTES / e2e_ms / 1e6}
+        for ws_ in sep:
+            for w_ in ws_:
+                w_.free()
         # the same set at n = 2, 4, 8 activation columns (weights are streamed once per launch)
         cols = {}
         for n in (2, 4, 8):

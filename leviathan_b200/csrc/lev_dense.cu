@@ -124,9 +124,30 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         while (o + 1 < A.n_ops && gt >= A.tiles_cum[o + 1]) o++;
         return o;
     };
-    auto multi_src = [&](int q) -> const unsigned char* {
-        const int tq = q / spt, gt = tile0 + tq, kq = q - tq * spt, o = op_of(gt);
-        return reinterpret_cast<const unsigned char*>(A.wp_op[o]) + ((int64_t)(gt - A.tiles_cum[o]) * spt + kq) * (int64_t)kStepBytes;
+    // multi form, fetch cursor (lane 0): address of the next K-step; steps are contiguous inside a
+    // tensor, so the cursor only jumps where the next tile belongs to another tensor
+    const unsigned char* m_ptr = nullptr;
+    int m_k = 0, m_gt = 0, m_op = 0;
+    if (MULTI) {
+        const int tq = s / spt;
+        m_gt = tile0 + tq;
+        m_k = s - tq * spt;
+        m_op = op_of(m_gt);
+        m_ptr = reinterpret_cast<const unsigned char*>(A.wp_op[m_op]) +
+                ((int64_t)(m_gt - A.tiles_cum[m_op]) * spt + m_k) * (int64_t)kStepBytes;
+    }
+    auto multi_next = [&]() -> const unsigned char* {
+        const unsigned char* a = m_ptr;
+        m_ptr += kStepBytes;
+        if (++m_k == spt) {
+            m_k = 0;
+            m_gt++;
+            if (m_op + 1 < A.n_ops && m_gt == A.tiles_cum[m_op + 1]) {
+                m_op++;
+                m_ptr = reinterpret_cast<const unsigned char*>(A.wp_op[m_op]);
+            }
+        }
+        return a;
     };
     // requests the next stage's K-steps into ring stage d (lane 0)
     auto issue_stage = [&](int d) {
@@ -135,14 +156,20 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         if (MULTI) {
             // consecutive steps are contiguous except where the next tile belongs to another tensor
             mbar_expect(bar, n * kStepBytes);
-            int u = 0;
-            while (u < n) {
-                const unsigned char* a0 = multi_src(f_q + u);
-                int run = 1;
-                while (u + run < n && multi_src(f_q + u + run) == a0 + (size_t)run * kStepBytes) run++;
-                bulk_copy(dst + u * kStepBytes, a0, run * kStepBytes, bar);
-                u += run;
+            const unsigned char* a0 = multi_next();
+            int run = 1, done = 0;
+            for (int u = 1; u < n; u++) {
+                const unsigned char* a = multi_next();
+                if (a == a0 + (size_t)run * kStepBytes) {
+                    run++;
+                } else {
+                    bulk_copy(dst + done * kStepBytes, a0, run * kStepBytes, bar);
+                    done += run;
+                    a0 = a;
+                    run = 1;
+                }
             }
+            bulk_copy(dst + done * kStepBytes, a0, run * kStepBytes, bar);
         } else {
             bulk_load(dst, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar);
         }
