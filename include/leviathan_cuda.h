@@ -53,7 +53,17 @@ typedef enum lev_status {
     LEV_BAD_ARGUMENT = 12,
     LEV_OUT_OF_MEMORY = 13,
     LEV_BAD_OP_SPEC = 14,
-    LEV_UNSUPPORTED = 15
+    LEV_UNSUPPORTED = 15,
+    /* container errors, named after GGUFError (Sources/LeviathanCore/GGUF.swift:3-35);
+     * its integerOverflow case is LEV_INTEGER_OVERFLOW */
+    LEV_GGUF_BAD_MAGIC = 16,
+    LEV_GGUF_UNSUPPORTED_VERSION = 17,
+    LEV_GGUF_TRUNCATED = 18,
+    LEV_GGUF_UNKNOWN_VALUE_TYPE = 19,
+    LEV_GGUF_BAD_TENSOR = 20,
+    LEV_GGUF_DATA_BEYOND_EOF = 21,
+    LEV_GGUF_MISSING = 22, /* missingMetadata / missingTensor */
+    LEV_GGUF_UNSUPPORTED_TENSOR_TYPE = 23
 } lev_status;
 
 /* ggml tensor type ids of the block formats on the path
@@ -90,6 +100,7 @@ typedef struct lev_ctx lev_ctx;
 typedef struct lev_weights lev_weights;
 typedef struct lev_moe_weights lev_moe_weights;
 typedef struct lev_op lev_op;
+typedef struct lev_gguf lev_gguf;
 
 /* CUDA analogue of ForgeHardwareProfile (Sources/LeviathanCore/Forge.swift:17-30) */
 typedef struct lev_hw_profile {
@@ -277,6 +288,48 @@ int lev_op_describe(const lev_op* op, char* kind /*32*/, int64_t* in_dim, int64_
 /* does this installed op serve a weights handle of that geometry?
  * (q4GeneratedServesTensor, Sources/LeviathanCore/Gemma4.swift:989-1012) */
 int lev_op_serves(const lev_op* op, const lev_weights* w, int64_t rows);
+
+/* ---- GGUF container ------------------------------------------------------
+ * Replaces GGUFFile(path:) / GGUFFile.parse and its tensor directory
+ * (Sources/LeviathanCore/GGUF.swift:96-406; rust/crates/lev-gguf/src/lib.rs):
+ * versions 2 and 3, little-endian, the same caps on counts, string and array
+ * lengths and header size, `general.alignment` (default 32), and every tensor
+ * validated at open: known type, whole blocks, aligned offset, inside the
+ * file, no overlap, no duplicate name.  lev_gguf_open maps the file read-only;
+ * lev_gguf_parse reads caller-owned bytes that must outlive the handle.
+ * `err` (optional) receives the reason of a failure. */
+int lev_gguf_open(const char* path, lev_gguf** out, char* err, size_t err_len);
+int lev_gguf_parse(const void* bytes, size_t n_bytes, lev_gguf** out, char* err, size_t err_len);
+void lev_gguf_close(lev_gguf* g);
+int lev_gguf_summary(const lev_gguf* g, uint32_t* version, int64_t* n_tensors,
+                     int64_t* n_metadata, uint64_t* alignment, uint64_t* data_offset);
+/* index of a tensor by name, -1 when absent (GGUF.swift:384-389) */
+int64_t lev_gguf_find_tensor(const lev_gguf* g, const char* name);
+/* dims4 are innermost-first as stored; file_offset is absolute */
+int lev_gguf_tensor_info(const lev_gguf* g, int64_t index, const char** name, int* ggml_type,
+                         int* n_dims, int64_t* dims4, uint64_t* file_offset, uint64_t* n_bytes);
+const void* lev_gguf_tensor_data(const lev_gguf* g, int64_t index);
+/* metadata getters (metadataUInt / metadataFloat / metadataString, GGUF.swift:366-382) */
+int lev_gguf_meta_u64(const lev_gguf* g, const char* key, uint64_t* out);
+int lev_gguf_meta_f64(const lev_gguf* g, const char* key, double* out);
+int lev_gguf_meta_string(const lev_gguf* g, const char* key, const char** out, size_t* len);
+/* array metadata (GGUFValue.array, GGUF.swift:37-56): element value type and count, then one
+ * element at a time as its payload in the file (little-endian scalar, or a string's characters) */
+int lev_gguf_meta_array(const lev_gguf* g, const char* key, int* elem_type, uint64_t* count);
+int lev_gguf_meta_array_item(const lev_gguf* g, const char* key, uint64_t index,
+                             const void** payload, size_t* n_bytes);
+/* upload a Q4_0 / Q4_K / Q6_K tensor from the file: dims[0] = cols, dims[1] = rows;
+ * a third dimension (expert tensors [in, out, experts]) stacks the experts' rows */
+int lev_gguf_upload(lev_ctx* ctx, const lev_gguf* g, const char* name, lev_weights** out);
+/* one layer's routed-expert weights from a model file, with the checks of
+ * MoEModelBinding.bind (Sources/LeviathanCore/MoEModelBinding.swift:93-166): shape metadata
+ * under `<general.architecture>.` (block_count, expert_count, expert_used_count,
+ * embedding_length, expert_feed_forward_length), blk.<layer>.ffn_gate_up_exps.weight Q4_0
+ * [hidden, 2*inter, experts], blk.<layer>.ffn_down_exps.weight Q4_0 [inter, hidden, experts],
+ * blk.<layer>.ffn_gate_inp.weight f32 [hidden, experts].  local_count <= 0 keeps every expert
+ * resident; top_k (optional) receives expert_used_count. */
+int lev_gguf_moe_upload(lev_ctx* ctx, const lev_gguf* g, int layer, int local_first,
+                        int local_count, lev_moe_weights** out, int* top_k);
 
 /* ---- multi-GPU (one process per GPU, NCCL over NVLink) ------------------ */
 #define LEV_NCCL_ID_BYTES 128

@@ -118,9 +118,78 @@ struct Q6Backend {
     }
 };
 
+// GGUFFile (Sources/LeviathanCore/GGUF.swift:96-178): a validated container; `path` is mapped read-only.
+struct GGUFTensorInfo {
+    std::string name;
+    std::vector<int64_t> dims;  // innermost first
+    int ggmlType = 0;
+    uint64_t fileOffset = 0, byteCount = 0;
+};
+
+class GGUFFile {
+  public:
+    explicit GGUFFile(const std::string& path) {
+        char err[256] = {0};
+        int st = lev_gguf_open(path.c_str(), &g_, err, sizeof err);
+        if (st != LEV_OK) throw Error(st, err);
+        lev_gguf_summary(g_, &version, &tensorCount, &metadataCount, &alignment, &dataOffset);
+    }
+    ~GGUFFile() { lev_gguf_close(g_); }
+    GGUFFile(const GGUFFile&) = delete;
+    GGUFFile& operator=(const GGUFFile&) = delete;
+    lev_gguf* raw() const { return g_; }
+    GGUFTensorInfo tensor(const std::string& name) const {
+        int64_t i = lev_gguf_find_tensor(g_, name.c_str());
+        if (i < 0) throw Error(LEV_GGUF_MISSING, "tensor " + name);
+        return tensor(i);
+    }
+    GGUFTensorInfo tensor(int64_t index) const {
+        const char* name = nullptr;
+        int type = 0, nd = 0;
+        int64_t dims[4];
+        GGUFTensorInfo t;
+        int st = lev_gguf_tensor_info(g_, index, &name, &type, &nd, dims, &t.fileOffset, &t.byteCount);
+        if (st != LEV_OK) throw Error(st, "tensor index " + std::to_string(index));
+        t.name = name;
+        t.ggmlType = type;
+        t.dims.assign(dims, dims + nd);
+        return t;
+    }
+    uint64_t metadataUInt(const std::string& key) const {
+        uint64_t v = 0;
+        int st = lev_gguf_meta_u64(g_, key.c_str(), &v);
+        if (st != LEV_OK) throw Error(st, "metadata " + key);
+        return v;
+    }
+    double metadataFloat(const std::string& key) const {
+        double v = 0;
+        int st = lev_gguf_meta_f64(g_, key.c_str(), &v);
+        if (st != LEV_OK) throw Error(st, "metadata " + key);
+        return v;
+    }
+    std::string metadataString(const std::string& key) const {
+        const char* p = nullptr;
+        size_t n = 0;
+        int st = lev_gguf_meta_string(g_, key.c_str(), &p, &n);
+        if (st != LEV_OK) throw Error(st, "metadata " + key);
+        return std::string(p, n);
+    }
+    uint32_t version = 0;
+    int64_t tensorCount = 0, metadataCount = 0;
+    uint64_t alignment = 0, dataOffset = 0;
+
+  private:
+    lev_gguf* g_ = nullptr;
+};
+
 // A resident quantized tensor, addressed by (handle, row offset) like the runner's weights buffer.
 class Weights {
   public:
+    // a Q4_0 / Q4_K / Q6_K tensor of a container, uploaded from the mapping
+    Weights(const Context& c, const GGUFFile& file, const std::string& name) : c_(&c) {
+        c.check(lev_gguf_upload(c.raw(), file.raw(), name.c_str(), &w_));
+        lev_weights_info(w_, nullptr, &rows_, &cols_, nullptr);
+    }
     Weights(const Context& c, const std::vector<uint8_t>& ggufBytes, int ggmlType, int64_t rows, int64_t cols) : c_(&c) {
         c.check(lev_weights_upload(c.raw(), ggufBytes.data(), ggufBytes.size(), ggmlType, rows, cols, 0, &w_));
         rows_ = rows;

@@ -17,7 +17,9 @@ STATUS = {
     0: "ok", 1: "badDimensions", 2: "wrongInputCount", 3: "nonFiniteInput", 4: "nonFiniteScale",
     5: "nonFiniteOutput", 6: "exceedsModelWorkload", 7: "integerOverflow", 8: "deviceUnavailable",
     9: "kernelFailed", 10: "timeout", 11: "ncclError", 12: "badArgument", 13: "outOfMemory",
-    14: "badOpSpec", 15: "unsupported",
+    14: "badOpSpec", 15: "unsupported", 16: "badMagic", 17: "unsupportedVersion", 18: "truncated",
+    19: "unknownValueType", 20: "badTensor", 21: "dataBeyondEndOfFile", 22: "missing",
+    23: "unsupportedTensorType",
 }
 GGML_F32, GGML_Q4_0, GGML_Q4_K, GGML_Q6_K = 0, 2, 12, 14
 BLOCK = {GGML_Q4_0: (32, 18), GGML_Q4_K: (256, 144), GGML_Q6_K: (256, 210)}
@@ -82,6 +84,22 @@ SIGNATURES = {
     "lev_op_describe": (_I, [_P, C.c_char_p, C.POINTER(_L), C.POINTER(_L), C.POINTER(_I), C.POINTER(_I),
                              C.c_char_p, C.c_char_p]),
     "lev_op_serves": (_I, [_P, _P, _L]),
+    "lev_gguf_open": (_I, [C.c_char_p, C.POINTER(_P), C.c_char_p, _Z]),
+    "lev_gguf_parse": (_I, [_P, _Z, C.POINTER(_P), C.c_char_p, _Z]),
+    "lev_gguf_close": (None, [_P]),
+    "lev_gguf_summary": (_I, [_P, C.POINTER(C.c_uint32), C.POINTER(_L), C.POINTER(_L), C.POINTER(C.c_uint64),
+                              C.POINTER(C.c_uint64)]),
+    "lev_gguf_find_tensor": (_L, [_P, C.c_char_p]),
+    "lev_gguf_tensor_info": (_I, [_P, _L, C.POINTER(C.c_char_p), C.POINTER(_I), C.POINTER(_I), C.POINTER(_L * 4),
+                                  C.POINTER(C.c_uint64), C.POINTER(C.c_uint64)]),
+    "lev_gguf_tensor_data": (_P, [_P, _L]),
+    "lev_gguf_meta_u64": (_I, [_P, C.c_char_p, C.POINTER(C.c_uint64)]),
+    "lev_gguf_meta_f64": (_I, [_P, C.c_char_p, C.POINTER(C.c_double)]),
+    "lev_gguf_meta_string": (_I, [_P, C.c_char_p, C.POINTER(C.c_char_p), C.POINTER(_Z)]),
+    "lev_gguf_meta_array": (_I, [_P, C.c_char_p, C.POINTER(_I), C.POINTER(C.c_uint64)]),
+    "lev_gguf_meta_array_item": (_I, [_P, C.c_char_p, C.c_uint64, C.POINTER(_P), C.POINTER(_Z)]),
+    "lev_gguf_upload": (_I, [_P, _P, C.c_char_p, C.POINTER(_P)]),
+    "lev_gguf_moe_upload": (_I, [_P, _P, _I, _I, _I, C.POINTER(_P), C.POINTER(_I)]),
     "lev_dist_unique_id": (_I, [_P]),
     "lev_dist_init": (_I, [_P, _I, _I, _P]),
     "lev_dist_destroy": (_I, [_P]),

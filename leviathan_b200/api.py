@@ -397,3 +397,121 @@ class Context:
         self._check(self.lib.lev_gemm_prefill_rowsplit_allgather(self.handle, w_local.handle, _ptr(x_bf16), tokens,
                                                                  _ptr(out), 0))
         return out
+
+
+class GGUFFile:
+    """lev_gguf_*: a parsed GGUF v2/v3 container (GGUFFile in the reference,
+    Sources/LeviathanCore/GGUF.swift:96-406).  `source` is a path (mapped
+    read-only) or a bytes-like object (kept alive by this object).  Needs no
+    device; `upload` needs a Context."""
+
+    def __init__(self, source):
+        self.lib = L.load()
+        h = C.c_void_p()
+        err = C.create_string_buffer(256)
+        if isinstance(source, str):
+            st = self.lib.lev_gguf_open(source.encode(), C.byref(h), err, len(err))
+            self._keep = None
+        else:
+            self._keep = np.frombuffer(bytes(source), np.uint8)
+            st = self.lib.lev_gguf_parse(self._keep.ctypes.data, self._keep.size, C.byref(h), err, len(err))
+        if st != L.OK:
+            raise LevError(st, err.value.decode(errors="replace"))
+        self.handle = h
+        v, nt, nk, al, off = C.c_uint32(), C.c_int64(), C.c_int64(), C.c_uint64(), C.c_uint64()
+        self.lib.lev_gguf_summary(h, C.byref(v), C.byref(nt), C.byref(nk), C.byref(al), C.byref(off))
+        self.version, self.tensor_count, self.metadata_count = v.value, nt.value, nk.value
+        self.alignment, self.data_offset = al.value, off.value
+
+    def close(self):
+        if self.handle:
+            self.lib.lev_gguf_close(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def tensor(self, key) -> dict:
+        """Directory entry by index or name: name, ggml_type, dims (innermost first),
+        file_offset (absolute), n_bytes.  Raises LevError('missing') when absent."""
+        i = key if isinstance(key, int) else self.lib.lev_gguf_find_tensor(self.handle, key.encode())
+        name, ty, nd, dims = C.c_char_p(), C.c_int(), C.c_int(), (C.c_int64 * 4)()
+        off, nb = C.c_uint64(), C.c_uint64()
+        st = self.lib.lev_gguf_tensor_info(self.handle, i, C.byref(name), C.byref(ty), C.byref(nd), C.byref(dims),
+                                           C.byref(off), C.byref(nb))
+        if st != L.OK:
+            raise LevError(st, f"tensor {key!r}")
+        return {"index": i, "name": name.value.decode(), "ggml_type": ty.value, "dims": list(dims)[:nd.value],
+                "file_offset": off.value, "n_bytes": nb.value}
+
+    def tensors(self) -> list:
+        return [self.tensor(i) for i in range(self.tensor_count)]
+
+    def tensor_bytes(self, key) -> np.ndarray:
+        """The tensor's storage as a uint8 copy."""
+        t = self.tensor(key)
+        p = self.lib.lev_gguf_tensor_data(self.handle, t["index"])
+        return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(t["n_bytes"],)).copy()
+
+    def meta_uint(self, key: str) -> int:
+        v = C.c_uint64()
+        st = self.lib.lev_gguf_meta_u64(self.handle, key.encode(), C.byref(v))
+        if st != L.OK:
+            raise LevError(st, f"metadata {key}")
+        return v.value
+
+    def meta_float(self, key: str) -> float:
+        v = C.c_double()
+        st = self.lib.lev_gguf_meta_f64(self.handle, key.encode(), C.byref(v))
+        if st != L.OK:
+            raise LevError(st, f"metadata {key}")
+        return v.value
+
+    def meta_string(self, key: str) -> str:
+        p, n = C.c_char_p(), C.c_size_t()
+        st = self.lib.lev_gguf_meta_string(self.handle, key.encode(), C.byref(p), C.byref(n))
+        if st != L.OK:
+            raise LevError(st, f"metadata {key}")
+        return C.string_at(p, n.value).decode(errors="replace")
+
+    _SCALAR = {0: "<u1", 1: "<i1", 2: "<u2", 3: "<i2", 4: "<u4", 5: "<i4", 6: "<f4", 7: "<u1", 10: "<u8", 11: "<i8",
+               12: "<f8"}
+
+    def meta_array(self, key: str) -> list:
+        """An array value as a Python list (strings, ints, floats or bools)."""
+        et, n = C.c_int(), C.c_uint64()
+        st = self.lib.lev_gguf_meta_array(self.handle, key.encode(), C.byref(et), C.byref(n))
+        if st != L.OK:
+            raise LevError(st, f"metadata {key}")
+        out = []
+        p, nb = C.c_void_p(), C.c_size_t()
+        for i in range(n.value):
+            self.lib.lev_gguf_meta_array_item(self.handle, key.encode(), i, C.byref(p), C.byref(nb))
+            raw = C.string_at(p, nb.value)
+            if et.value == 8:
+                out.append(raw.decode(errors="replace"))
+            else:
+                v = np.frombuffer(raw, self._SCALAR[et.value])[0].item()
+                out.append(bool(v) if et.value == 7 else v)
+        return out
+
+    def upload(self, ctx: "Context", name: str) -> Weights:
+        """lev_gguf_upload: a quantized tensor straight from the mapping to the device."""
+        h = C.c_void_p()
+        ctx._check(self.lib.lev_gguf_upload(ctx.handle, self.handle, name.encode(), C.byref(h)))
+        ty, rows, cols, nb = C.c_int(), C.c_int64(), C.c_int64(), C.c_size_t()
+        self.lib.lev_weights_info(h, C.byref(ty), C.byref(rows), C.byref(cols), C.byref(nb))
+        return Weights(ctx, h, ty.value, rows.value, cols.value, nb.value)
+
+    def moe_upload(self, ctx: "Context", layer: int, local_first: int = 0, local_count: int = 0):
+        """lev_gguf_moe_upload: (MoEWeights of blk.<layer>, the file's expert_used_count)."""
+        h, k = C.c_void_p(), C.c_int()
+        ctx._check(self.lib.lev_gguf_moe_upload(ctx.handle, self.handle, layer, local_first, local_count, C.byref(h),
+                                                C.byref(k)))
+        arch = self.meta_string("general.architecture")
+        experts = self.meta_uint(f"{arch}.expert_count")
+        hidden, inter = self.meta_uint(f"{arch}.embedding_length"), self.meta_uint(f"{arch}.expert_feed_forward_length")
+        return MoEWeights(ctx, h, experts, hidden, inter, local_first, local_count or experts), k.value

@@ -31,6 +31,14 @@ extern "C" const char* lev_status_name(int s) {
         case LEV_OUT_OF_MEMORY: return "outOfMemory";
         case LEV_BAD_OP_SPEC: return "badOpSpec";
         case LEV_UNSUPPORTED: return "unsupported";
+        case LEV_GGUF_BAD_MAGIC: return "badMagic";
+        case LEV_GGUF_UNSUPPORTED_VERSION: return "unsupportedVersion";
+        case LEV_GGUF_TRUNCATED: return "truncated";
+        case LEV_GGUF_UNKNOWN_VALUE_TYPE: return "unknownValueType";
+        case LEV_GGUF_BAD_TENSOR: return "badTensor";
+        case LEV_GGUF_DATA_BEYOND_EOF: return "dataBeyondEndOfFile";
+        case LEV_GGUF_MISSING: return "missing";
+        case LEV_GGUF_UNSUPPORTED_TENSOR_TYPE: return "unsupportedTensorType";
     }
     return "unknown";
 }

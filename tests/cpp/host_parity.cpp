@@ -4,6 +4,8 @@
 //     rejected (Sources/leviathan-tests/main.swift:705-743)
 //   Q6_K single-row dot of -315 (Sources/leviathan-tests/main.swift:1091-1120)
 //   MoE region 16 / 2 / 32 / 512 (Sources/leviathan-tests/main.swift:8925-8946)
+//   GGUF container with one Q4_0 tensor [32, 4] (Sources/leviathan-tests/main.swift:508-531), written
+//     to argv[1] when given, opened, and uploaded from the mapping
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -31,7 +33,15 @@ static std::string errorName(F&& f) {
     return "none";
 }
 
-int main() {
+static void put(std::vector<uint8_t>& b, uint64_t v, int n) {
+    for (int i = 0; i < n; i++) b.push_back((uint8_t)(v >> (8 * i)));
+}
+static void putString(std::vector<uint8_t>& b, const char* s) {
+    put(b, std::strlen(s), 8);
+    for (const char* p = s; *p; p++) b.push_back((uint8_t)*p);
+}
+
+int main(int argc, char** argv) {
     lev::Context ctx(0);
     // ---- Q4_0: two rows of one block with zero nibbles, d = +1.0 (0x3C00) and d = -1.0 (0xBC00):
     // every value is (0 - 8) * d, so the rows give -8 * sum(x) and +8 * sum(x).
@@ -107,6 +117,45 @@ int main() {
         bool all512 = true;
         for (float f : o.out) all512 = all512 && f == 512.0f;
         CHECK(all512);
+    }
+    // ---- GGUF: v3, alignment 32, one uint64 key, tensor [inDim 32, outDim 4] of zero nibbles with d = 1
+    if (argc > 1) {
+        std::vector<uint8_t> b = {'G', 'G', 'U', 'F'};
+        put(b, 3, 4);
+        put(b, 1, 8);
+        put(b, 2, 8);
+        putString(b, "general.alignment");
+        put(b, 4, 4);
+        put(b, 32, 4);
+        putString(b, "gemma4.context_length");
+        put(b, 10, 4);
+        put(b, 262144, 8);
+        putString(b, "test_tensor");
+        put(b, 2, 4);
+        put(b, 32, 8);
+        put(b, 4, 8);
+        put(b, 2, 4);
+        put(b, 0, 8);
+        while (b.size() % 32) b.push_back(0);
+        for (int r = 0; r < 4; r++) {
+            b.push_back(0x00);
+            b.push_back(0x3C);
+            for (int i = 0; i < 16; i++) b.push_back(0);
+        }
+        FILE* f = std::fopen(argv[1], "wb");
+        CHECK(f && std::fwrite(b.data(), 1, b.size(), f) == b.size());
+        std::fclose(f);
+        lev::GGUFFile file(argv[1]);
+        CHECK(file.version == 3 && file.tensorCount == 1 && file.alignment == 32);
+        CHECK(file.metadataUInt("gemma4.context_length") == 262144);
+        auto info = file.tensor("test_tensor");
+        CHECK(info.dims.size() == 2 && info.dims[0] == 32 && info.dims[1] == 4 && info.ggmlType == LEV_GGML_Q4_0);
+        CHECK(info.fileOffset == b.size() - 72 && info.byteCount == 72);
+        CHECK(errorName([&] { file.tensor("absent"); }) == "missing");
+        lev::Weights w(ctx, file, "test_tensor");
+        CHECK(w.rows() == 4 && w.cols() == 32);
+        auto y = lev::Runner::matvec(ctx, w, 0, 4, x);
+        for (int r = 0; r < 4; r++) CHECK(std::fabs(y[r] - (float)(-8.0 * sum)) <= 1e-4f * std::fmax(1.0, std::fabs(8.0 * sum)));
     }
     std::printf("ok %d\n", checks);
     return 0;

@@ -34,6 +34,6 @@ def test_cpp_host_mirror_compiles_and_links(tmp_path):
 @pytest.mark.gpu
 @pytest.mark.skipif(shutil.which("g++") is None, reason="no C++ compiler")
 def test_cpp_host_parity_program(tmp_path):
-    out = subprocess.run([_build(tmp_path)], capture_output=True, text=True, timeout=120)
+    out = subprocess.run([_build(tmp_path), str(tmp_path / "known.gguf")], capture_output=True, text=True, timeout=120)
     assert out.returncode == 0, out.stdout + out.stderr
     assert out.stdout.strip().startswith("ok ")
