@@ -548,6 +548,35 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         out["ffn_matvec_multi"] = {"calls_per_step": 2, "ms_per_step": ms, "gbs": STEP_BYTES / ms / 1e6,
                                    "hbm_frac": STEP_BYTES / ms / 1e6 / peaks["hbm_gbs"],
                                    "e2e_ms_per_step": e2e_ms, "e2e_gbs": STEP_BYTES / e2e_ms / 1e6}
+        # the whole FFN block of a decode layer: norm -> gate, up -> gelu(gate) * up -> down -> residual
+        # (Sources/LeviathanCore/Gemma4.swift:3741-3753), as five launches and as two fused ones
+        nw = torch.ones(HIDDEN, device=dev) + 0.1 * torch.randn(HIDDEN, generator=g, device=dev)
+        hbuf, gubuf = torch.empty((1, HIDDEN), device=dev), torch.empty((1, 2 * FFN), device=dev)
+        actbuf, xo = torch.empty((1, FFN), device=dev), torch.empty((1, HIDDEN), device=dev)
+        halves = [gubuf[:, :FFN], gubuf[:, FFN:]]
+
+        def block_unfused(i):
+            wg, wu, wd = sep[i % 4]
+            ctx.rmsnorm(xd, nw, 1e-6, out=hbuf)
+            ctx.matvec_multi([wg, wu], hbuf, outs=halves)
+            ctx.gelu_up(gubuf, out=actbuf)
+            ctx.matvec(wd, actbuf, out=ydn)
+            ctx.axpy(1.0, ydn, xd, out=xo)
+
+        def block_fused(i):
+            wg, wu, wd = sep[i % 4]
+            ctx.matvec_multi_fused([wg, wu], xd, "rmsnorm", nw, 1e-6, outs=halves)
+            ctx.matvec_fused(wd, gubuf, "gelu_up", residual=xd, alpha=1.0, out=xo)
+
+        ms_u = _graph_time(torch, stream, block_unfused, 16)
+        ref_out = xo.clone()
+        ms_f = _graph_time(torch, stream, block_fused, 16)
+        agree = float((xo - ref_out).abs().max() / ref_out.abs().max().clamp_min(1.0))
+        out["ffn_block"] = {"workload": "rmsnorm -> Q4_K gate, up -> gelu_up -> Q6_K down -> residual, batch 1",
+                            "unfused": {"launches": 5, "ms_per_step": ms_u, "gbs": STEP_BYTES / ms_u / 1e6},
+                            "fused": {"launches": 2, "ms_per_step": ms_f, "gbs": STEP_BYTES / ms_f / 1e6,
+                                      "hbm_frac": STEP_BYTES / ms_f / 1e6 / peaks["hbm_gbs"]},
+                            "max_abs_diff_over_max": agree}
         for ws_ in sep:
             for w_ in ws_:
                 w_.free()

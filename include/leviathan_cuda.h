@@ -230,6 +230,44 @@ int lev_gemm_prefill(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int
  * (rust/crates/lev-forge/src/coopmat.rs:49-58). */
 int lev_act_bf16(lev_ctx* ctx, const float* x, int64_t n, void* out_bf16);
 
+/* ---- the steps either side of a decode matvec ----------------------------
+ * Device pointers; asynchronous on the context's stream.
+ * lev_rmsnorm: y[v] = x[v] * (1 / sqrt(mean(x[v]^2) + eps)) * weight (weight NULL: no scale), g4_rmsnorm
+ * (Sources/LeviathanCore/Gemma4.swift:4247-4268; tiled form :4323-4358).  x == y is allowed.
+ * inverse_out (optional) receives 1 / sqrt(...) per vector for lev_rmsnorm_cached, the cached apply
+ * of a statistics group (Sources/LeviathanCore/RMSStatisticsKernels.swift:42-130).
+ * lev_gelu_up: out[v][e] = gelu_tanh(gate_up[v][e]) * gate_up[v][inter + e], g4_gelu_up
+ * (Gemma4.swift:4364-4377).  lev_axpy: y = r + alpha * x, r may be y (g4_axpy, Gemma4.swift:4459). */
+int lev_rmsnorm(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, const float* weight,
+                float eps, float* y, float* inverse_out);
+int lev_rmsnorm_cached(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n,
+                       const float* weight, const float* inverse, float* y);
+int lev_gelu_up(lev_ctx* ctx, const float* gate_up, int64_t vectors, int64_t inter, float* out);
+int lev_axpy(lev_ctx* ctx, float alpha, const float* x, const float* r, int64_t n, float* y);
+
+/* The same steps folded into the matvec launch: the prologue is applied while the kernel builds
+ * its activation tables (the norm's statistic is reduced by every thread block for itself), the
+ * residual where output rows are stored.  y[c][r] = residual[c][r] + alpha * sum_k W[row0+r][k] *
+ * a[c][k] with a = x, rmsnorm(x) or gelu_up(x); with LEV_PROLOGUE_GELU_UP x is
+ * [n_cols][2 * cols] (gate then up).  Replaces the rmsnorm -> matvec, gelu_up -> matvec and
+ * matvec -> axpy dispatch pairs of the layer loop (Gemma4.swift:3740-3760, :3878).  Shapes the
+ * one-launch kernel does not serve run the same steps as separate launches. */
+enum { LEV_PROLOGUE_NONE = 0, LEV_PROLOGUE_RMSNORM = 1, LEV_PROLOGUE_GELU_UP = 2 };
+typedef struct lev_fusion {
+    int prologue;
+    const float* norm_weight; /* RMSNORM: device [cols], NULL = no scale */
+    float eps;                /* RMSNORM */
+    const float* residual;    /* device, y's layout, may be y itself; NULL: y = W a */
+    float alpha;              /* used with residual */
+} lev_fusion;
+int lev_matvec_fused(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x,
+                     int64_t x_count, int n_cols, const lev_fusion* fusion, float* y,
+                     int64_t y_capacity);
+/* several tensors of one inDim behind one prologue (no residual) */
+int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x,
+                           int64_t x_count, int n_cols, const lev_fusion* fusion, float* const* y,
+                           const int64_t* y_capacity);
+
 /* ---- routed MoE composite ----------------------------------------------
  * Expert weights are the fused gate_up tensor [experts][2*inter][hidden] and
  * the down tensor [experts][hidden][inter], both Q4_0

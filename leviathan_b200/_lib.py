@@ -46,6 +46,13 @@ class Evidence(C.Structure):
     ]
 
 
+class Fusion(C.Structure):
+    _fields_ = [("prologue", C.c_int), ("norm_weight", C.c_void_p), ("eps", C.c_float), ("residual", C.c_void_p),
+                ("alpha", C.c_float)]
+
+
+PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_GELU_UP = 0, 1, 2
+
 # name -> (restype, argtypes); every symbol the header declares
 _P, _I, _L, _Z, _U = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_uint
 SIGNATURES = {
@@ -70,6 +77,12 @@ SIGNATURES = {
     "lev_matvec_multi": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(_P), C.POINTER(_L), _U]),
     "lev_matvec_static_scratch": (_I, [_P, _P, _L, _L, _P, _L, _I, _P, _L]),
     "lev_static_scratch_bytes": (_Z, []),
+    "lev_rmsnorm": (_I, [_P, _P, _L, _L, _P, C.c_float, _P, _P]),
+    "lev_rmsnorm_cached": (_I, [_P, _P, _L, _L, _P, _P, _P]),
+    "lev_gelu_up": (_I, [_P, _P, _L, _L, _P]),
+    "lev_axpy": (_I, [_P, C.c_float, _P, _P, _L, _P]),
+    "lev_matvec_fused": (_I, [_P, _P, _L, _L, _P, _L, _I, C.POINTER(Fusion), _P, _L]),
+    "lev_matvec_multi_fused": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(Fusion), C.POINTER(_P), C.POINTER(_L)]),
     "lev_gemm_prefill": (_I, [_P, _P, _P, _L, _P, _U]),
     "lev_act_bf16": (_I, [_P, _P, _L, _P]),
     "lev_moe_weights_upload": (_I, [_P, _P, _P, _Z, _P, _Z, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),

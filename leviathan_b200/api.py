@@ -219,6 +219,88 @@ class Context:
                                                        _ptr(out), out.numel()))
         return out[0] if one_d else out
 
+    # -- the steps either side of a matvec (torch CUDA tensors only) --
+    def rmsnorm(self, x, weight=None, eps: float = 1e-6, out=None, want_inverse: bool = False):
+        """lev_rmsnorm over the rows of x [vectors][n]; out may be x."""
+        import torch
+
+        x2 = x.reshape(1, -1) if x.ndim == 1 else x
+        out = torch.empty_like(x2) if out is None else out
+        inv = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device) if want_inverse else None
+        self._flags(False, False)
+        self._check(self.lib.lev_rmsnorm(self.handle, _ptr(x2), x2.shape[0], x2.shape[1], _ptr(weight), eps, _ptr(out), _ptr(inv)))
+        out = out.reshape(x.shape)
+        return (out, inv) if want_inverse else out
+
+    def rmsnorm_cached(self, x, inverse, weight=None, out=None):
+        import torch
+
+        x2 = x.reshape(1, -1) if x.ndim == 1 else x
+        out = torch.empty_like(x2) if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_rmsnorm_cached(self.handle, _ptr(x2), x2.shape[0], x2.shape[1], _ptr(weight), _ptr(inverse), _ptr(out)))
+        return out.reshape(x.shape)
+
+    def gelu_up(self, gate_up, out=None):
+        """lev_gelu_up: rows are [gate | up]; returns [vectors][inter]."""
+        import torch
+
+        gu = gate_up.reshape(1, -1) if gate_up.ndim == 1 else gate_up
+        inter = gu.shape[1] // 2
+        out = torch.empty((gu.shape[0], inter), dtype=torch.float32, device=gu.device) if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_gelu_up(self.handle, _ptr(gu), gu.shape[0], inter, _ptr(out)))
+        return out[0] if gate_up.ndim == 1 else out
+
+    def axpy(self, alpha: float, x, r, out=None):
+        """lev_axpy: out = r + alpha * x (out may be r)."""
+        import torch
+
+        out = torch.empty_like(r) if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_axpy(self.handle, alpha, _ptr(x), _ptr(r), x.numel(), _ptr(out)))
+        return out
+
+    @staticmethod
+    def _fusion(prologue, norm_weight, eps, residual, alpha):
+        code = {None: L.PROLOGUE_NONE, "rmsnorm": L.PROLOGUE_RMSNORM, "gelu_up": L.PROLOGUE_GELU_UP}[prologue]
+        return L.Fusion(code, _ptr(norm_weight), eps, _ptr(residual), alpha)
+
+    def matvec_fused(self, w: Weights, x, prologue=None, norm_weight=None, eps: float = 1e-6, residual=None,
+                     alpha: float = 1.0, row0: int = 0, rows: int | None = None, out=None):
+        """lev_matvec_fused: out = residual + alpha * W prologue(x); prologue None, "rmsnorm" or
+        "gelu_up" (x rows are then [gate | up]).  out may be residual."""
+        import torch
+
+        rows = w.rows - row0 if rows is None else rows
+        x = x.contiguous()
+        one_d = x.ndim == 1
+        n_cols = 1 if one_d else x.shape[0]
+        if out is None:
+            out = torch.empty((n_cols, max(rows, 0)), dtype=torch.float32, device=x.device)
+        f = self._fusion(prologue, norm_weight, eps, residual, alpha)
+        self._flags(False, False)
+        self._check(self.lib.lev_matvec_fused(self.handle, w.handle, row0, rows, _ptr(x), x.numel(), n_cols, C.byref(f),
+                                              _ptr(out), out.numel()))
+        return out[0] if one_d and out.ndim == 2 else out
+
+    def matvec_multi_fused(self, ws, x, prologue=None, norm_weight=None, eps: float = 1e-6, outs=None):
+        """lev_matvec_multi_fused: several tensors behind one prologue."""
+        import torch
+
+        x = x.contiguous()
+        n_cols = 1 if x.ndim == 1 else x.shape[0]
+        n = len(ws)
+        if outs is None:
+            outs = [torch.empty((n_cols, w.rows), dtype=torch.float32, device=x.device) for w in ws]
+        wp = (C.c_void_p * n)(*[w.handle for w in ws])
+        yp = (C.c_void_p * n)(*[_ptr(o) for o in outs])
+        cap = (C.c_int64 * n)(*[int(o.numel()) for o in outs])
+        f = self._fusion(prologue, norm_weight, eps, None, 1.0)
+        self._flags(False, False)
+        self._check(self.lib.lev_matvec_multi_fused(self.handle, n, wp, _ptr(x), x.numel(), n_cols, C.byref(f), yp, cap))
+        return outs
+
     def _matvec_host(self, fn, blocks, out_dim, in_dim, x):
         blocks = np.ascontiguousarray(blocks, np.uint8)
         x = np.ascontiguousarray(x, np.float32)

@@ -61,7 +61,20 @@ struct DenseArgs {
     int tiles_cum[5];       // tiles before each tensor
     float* y_op[4];         // [n_cols][rows_op]
     int64_t rows_op[4];
+    // fused steps either side of the product (dense and multi forms)
+    int norm_on;            // activations are x * inv_rms(x) * norm_w, inv_rms computed by every CTA
+    const float* norm_w;    // [cols] or NULL (no scale)
+    float norm_eps;
+    const float* residual;  // dense form: y = residual + alpha * (W x), same layout as y; NULL: y = W x
+    float alpha;
 };
+
+// build switch for A/B timing of the fused prologue / epilogue code (-DLEV_NO_FUSION compiles it out)
+#ifdef LEV_NO_FUSION
+constexpr bool kFusion = false;
+#else
+constexpr bool kFusion = true;
+#endif
 
 constexpr int kMaxJobTables = 3;  // jobs whose tables one CTA of the sliced form can hold
 
@@ -192,6 +205,39 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     pdl_wait();  // weights are immutable and already on their way; x and y belong to the launches before
 
     TL(2);
+    // ---- RMSNorm statistic of each activation column (fused prologue): every CTA reduces the
+    // column itself, in a fixed order (thread-strided partials, warp tree, warps in order) ----
+    float inv_rms[CMAX];
+#pragma unroll
+    for (int c = 0; c < CMAX; c++) inv_rms[c] = 1.0f;
+    if (kFusion && !JOBS && A.norm_on) {
+        __shared__ float norm_part[W][CMAX];
+#pragma unroll
+        for (int c = 0; c < CMAX; c++) {
+            float ss = 0.f;
+            if (c < A.n_cols) {
+                const float* xr = A.x + (int64_t)c * A.x_ld;
+                for (int i = threadIdx.x * 4; i < A.cols; i += W * 128) {
+                    const float4 v = __ldg(reinterpret_cast<const float4*>(xr + i));
+                    ss = fmaf(v.x, v.x, ss);
+                    ss = fmaf(v.y, v.y, ss);
+                    ss = fmaf(v.z, v.z, ss);
+                    ss = fmaf(v.w, v.w, ss);
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+            if (lane == 0) norm_part[warp][c] = ss;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int c = 0; c < CMAX; c++) {
+            float tot = 0.f;
+#pragma unroll
+            for (int w2 = 0; w2 < W; w2++) tot += norm_part[w2][c];
+            inv_rms[c] = 1.0f / sqrtf(tot / (float)A.cols + A.norm_eps);
+        }
+    }
     // ---- activation tables, built by every CTA for itself ----
     // One item = (chunk, activation column, lane-of-quad tt): the 16 activations that feed lane
     // tt's B fragments of the chunk's four mma, both split terms.
@@ -221,7 +267,17 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             for (int m = 0; m < 4; m++) {
                 const int el = chunk * 64 + chunk_col<TYPE>(tt, m, 0, 0);
                 float4 v = __ldg(reinterpret_cast<const float4*>(xr + (el < A.cols ? el : 0)));
-                if (JOBS && A.gelu_inter > 0) {
+                if (kFusion && !JOBS && A.norm_on) {
+                    float inv = inv_rms[0];
+#pragma unroll
+                    for (int cc = 1; cc < CMAX; cc++) inv = c == cc ? inv_rms[cc] : inv;
+                    v = make_float4(v.x * inv, v.y * inv, v.z * inv, v.w * inv);
+                    if (A.norm_w) {
+                        const float4 nw = __ldg(reinterpret_cast<const float4*>(A.norm_w + (el < A.cols ? el : 0)));
+                        v = make_float4(v.x * nw.x, v.y * nw.y, v.z * nw.z, v.w * nw.w);
+                    }
+                }
+                if ((JOBS || kFusion) && A.gelu_inter > 0) {
                     const float4 u = __ldg(reinterpret_cast<const float4*>(xr + A.gelu_inter + (el < A.cols ? el : 0)));
                     v = make_float4(gelu_tanh_up(v.x, u.x), gelu_tanh_up(v.y, u.y), gelu_tanh_up(v.z, u.z), gelu_tanh_up(v.w, u.w));
                 }
@@ -392,8 +448,13 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
                             const int64_t row = (int64_t)tij * 16 + g;
                             const int oc = JOBS ? orow[c] : c;
                             if (JOBS ? orow[c] >= 0 : c < A.n_cols) {
-                                if (row < cur_rows) cur_y[(int64_t)oc * cur_ld + row] = va;
-                                if (row + 8 < cur_rows) cur_y[(int64_t)oc * cur_ld + row + 8] = vb;
+                                const int64_t at = (int64_t)oc * cur_ld + row;
+                                if (kFusion && !JOBS && !MULTI && A.residual) {
+                                    if (row < cur_rows) va = fmaf(A.alpha, va, A.residual[at]);
+                                    if (row + 8 < cur_rows) vb = fmaf(A.alpha, vb, A.residual[at + 8]);
+                                }
+                                if (row < cur_rows) cur_y[at] = va;
+                                if (row + 8 < cur_rows) cur_y[at + 8] = vb;
                             }
                         } else {
                             rec[warp][r][c][g] = va;
@@ -448,7 +509,10 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             if (c < A.n_cols && row < A.rows_op[o]) A.y_op[o][(int64_t)c * A.rows_op[o] + row] = acc;
         } else {
             const int64_t row = (int64_t)(tile0 + tile) * 16 + (idx & 15);
-            if (c < A.n_cols && row < A.rows) A.y[(int64_t)c * A.out_ld + row] = acc;
+            if (c < A.n_cols && row < A.rows) {
+                const int64_t at = (int64_t)c * A.out_ld + row;
+                A.y[at] = kFusion && A.residual ? fmaf(A.alpha, acc, A.residual[at]) : acc;
+            }
         }
     }
     TL(31);
@@ -569,8 +633,23 @@ bool lev_dense_multi_supported(lev_ctx* ctx, int n_ops, const lev_weights* const
     return dense_plan_tiles(ctx, w[0], tiles, n_cols, &P);
 }
 
-int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y) {
-    if (!lev_dense_multi_supported(ctx, n_ops, w, x, n_cols))
+// prologue fields shared by the dense and multi forms
+static void apply_fusion(DenseArgs& A, const lev_dense_fusion* f, int64_t cols) {
+    if (!f) return;
+    A.norm_on = f->norm_on;
+    A.norm_w = f->norm_w;
+    A.norm_eps = f->eps;
+    if (f->gelu_up) {
+        A.gelu_inter = (int)cols;
+        A.x_ld = 2 * cols;
+    }
+    A.residual = f->residual;
+    A.alpha = f->alpha;
+}
+
+int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y,
+                        const lev_dense_fusion* fusion) {
+    if (!lev_dense_multi_supported(ctx, n_ops, w, x, n_cols) || (fusion && fusion->residual))
         return lev_fail(ctx, LEV_UNSUPPORTED, "multi-tensor dense kernel: shapes not served");
     const int64_t chunks = lev_stream_chunks(w[0]), spt = chunks / 4;
     DenseArgs A = {};
@@ -602,6 +681,7 @@ int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, co
     A.depth = P.depth;
     A.sps = P.sps;
     A.debug = env_int("LEV_STREAM_DEBUG", 0);
+    apply_fusion(A, fusion, w[0]->cols);
     const int t = w[0]->type;
     int st = t == LEV_GGML_Q4_K   ? launch_multi_c<LEV_GGML_Q4_K>(ctx, n_cols, P.grid, P.smem, A)
              : t == LEV_GGML_Q6_K ? launch_multi_c<LEV_GGML_Q6_K>(ctx, n_cols, P.grid, P.smem, A)
@@ -620,7 +700,8 @@ bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64
 }
 
 // x: [n_cols][w->cols] device, y: [n_cols][rows] device.  No work buffers.
-int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y) {
+int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y,
+                  const lev_dense_fusion* fusion) {
     DensePlan P;
     if (!w->packed || row0 % 16 != 0 || ((uintptr_t)x & 15) != 0 || !dense_plan(ctx, w, rows, n_cols, &P))
         return lev_fail(ctx, LEV_UNSUPPORTED, "dense stream kernel: shape not served");
@@ -643,6 +724,7 @@ int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows
     A.depth = P.depth;
     A.sps = P.sps;
     A.debug = env_int("LEV_STREAM_DEBUG", 0);
+    apply_fusion(A, fusion, w->cols);
     int st = w->type == LEV_GGML_Q4_K   ? launch_dense_c<LEV_GGML_Q4_K>(ctx, n_cols, P.warps, P.grid, P.smem, A)
              : w->type == LEV_GGML_Q6_K ? launch_dense_c<LEV_GGML_Q6_K>(ctx, n_cols, P.warps, P.grid, P.smem, A)
                                         : launch_dense_c<LEV_GGML_Q4_0>(ctx, n_cols, P.warps, P.grid, P.smem, A);

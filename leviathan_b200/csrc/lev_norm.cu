@@ -1,0 +1,273 @@
+// The elementwise steps either side of a decode matvec — RMSNorm, gelu_tanh(gate) * up, axpy —
+// as stand-alone kernels, and the fused entry points that fold them into the one-launch matvec
+// (norm or activation while the activation tables are built, residual where the rows are stored).
+//
+// Semantics follow the reference's kernels: g4_rmsnorm y = x * (1 / sqrt(mean(x^2) + eps)) * w
+// (Sources/LeviathanCore/Gemma4.swift:4247-4268; the tiled form :4323-4358 reassociates the sum and
+// is gated against an f64 oracle, as this one is), g4_gelu_up (Gemma4.swift:4364-4377) and
+// g4_axpy (Gemma4.swift:4459).
+#include "lev_stream.h"
+#include "lev_stream_math.cuh"
+
+namespace {
+
+constexpr int kNormThreads = 256;
+
+// One CTA per vector.  The sum of squares is reduced in a fixed order (thread-strided f32 partials,
+// warp tree, warps in order), so repeated runs give the same bits.  x == y is allowed: every
+// thread finishes reading before the barrier and afterwards touches only its own elements.
+__global__ void __launch_bounds__(kNormThreads) k_rmsnorm(const float* x, int n, const float* __restrict__ w, float eps,
+                                                           float* y, float* inverse, const float* cached) {
+    __shared__ float part[kNormThreads / 32];
+    pdl_wait();
+    pdl_launch_dependents();
+    const float* xv = x + (int64_t)blockIdx.x * n;
+    float* yv = y + (int64_t)blockIdx.x * n;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float inv;
+    if (cached) {
+        inv = cached[blockIdx.x];
+    } else {
+        float ss = 0.f;
+        const int n4 = n & ~3;
+        for (int i = threadIdx.x * 4; i < n4; i += kNormThreads * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(xv + i);
+            ss = fmaf(v.x, v.x, ss);
+            ss = fmaf(v.y, v.y, ss);
+            ss = fmaf(v.z, v.z, ss);
+            ss = fmaf(v.w, v.w, ss);
+        }
+        if (threadIdx.x < n - n4) ss = fmaf(xv[n4 + threadIdx.x], xv[n4 + threadIdx.x], ss);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+        if (lane == 0) part[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < kNormThreads / 32; k++) tot += part[k];
+        inv = 1.0f / sqrtf(tot / (float)n + eps);
+        if (inverse && threadIdx.x == 0) inverse[blockIdx.x] = inv;
+    }
+    for (int i = threadIdx.x; i < n; i += kNormThreads) {
+        const float v = xv[i] * inv;
+        yv[i] = w ? v * w[i] : v;
+    }
+}
+
+// out[v][e] = gelu_tanh(src[v][e]) * src[v][inter + e]
+__global__ void k_gelu_up(const float* __restrict__ src, int64_t inter, int64_t total, float* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+        const int64_t v = i / inter, e = i - v * inter;
+        out[i] = gelu_tanh_up(src[v * 2 * inter + e], src[v * 2 * inter + inter + e]);
+    }
+}
+
+// y = r + alpha * x (r may be y)
+__global__ void k_axpy(float alpha, const float* __restrict__ x, const float* r, int64_t n, float* y) {
+    pdl_wait();
+    pdl_launch_dependents();
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+        y[i] = fmaf(alpha, x[i], r[i]);
+}
+
+int elementwise_grid(lev_ctx* ctx, int64_t n) {
+    const int64_t blocks = (n + 255) / 256, cap = (int64_t)ctx->prop.multiProcessorCount * 8;
+    return (int)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
+}
+
+int rmsnorm_dev(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, const float* w, float eps, float* y, float* inverse,
+                const float* cached) {
+    LEV_CUDA(ctx, launch_pdl(k_rmsnorm, dim3((unsigned)vectors), dim3(kNormThreads), 0, ctx->stream, x, (int)n, w, eps, y, inverse, cached));
+    ctx->launches++;
+    return LEV_OK;
+}
+
+int check_vectors(lev_ctx* ctx, int64_t vectors, int64_t n) {
+    if (vectors <= 0 || n <= 0 || n > LEV_MAX_DIM || vectors > (int64_t)1 << 24)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "%lld vectors of %lld elements", (long long)vectors, (long long)n);
+    return LEV_OK;
+}
+
+bool overlap(const void* a, size_t na, const void* b, size_t nb) {
+    const char *pa = (const char*)a, *pb = (const char*)b;
+    return pa < pb + nb && pb < pa + na;
+}
+
+}  // namespace
+
+extern "C" int lev_rmsnorm(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, const float* weight, float eps, float* y,
+                           float* inverse_out) {
+    if (!ctx || !x || !y) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_vectors(ctx, vectors, n));
+    if (!(eps >= 0.f) || !isfinite(eps)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "epsilon %g", (double)eps);
+    if (((uintptr_t)x & 15) != 0) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x is not 16-byte aligned");
+    if (vectors > 1 && n % 4 != 0) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "several vectors need n %% 4 == 0 (got %lld)", (long long)n);
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    return rmsnorm_dev(ctx, x, vectors, n, weight, eps, y, inverse_out, nullptr);
+}
+
+// the cached apply of the reference's statistics group (g4_rmsnorm_cached,
+// Sources/LeviathanCore/RMSStatisticsKernels.swift:104-130): y = x * inverse[v] * w, no new reduction
+extern "C" int lev_rmsnorm_cached(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, const float* weight,
+                                  const float* inverse, float* y) {
+    if (!ctx || !x || !y || !inverse) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_vectors(ctx, vectors, n));
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    return rmsnorm_dev(ctx, x, vectors, n, weight, 0.f, y, nullptr, inverse);
+}
+
+extern "C" int lev_gelu_up(lev_ctx* ctx, const float* gate_up, int64_t vectors, int64_t inter, float* out) {
+    if (!ctx || !gate_up || !out) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_vectors(ctx, vectors, inter));
+    if (overlap(gate_up, (size_t)vectors * 2 * inter * 4, out, (size_t)vectors * inter * 4))
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "input and output overlap");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    const int64_t total = vectors * inter;
+    LEV_CUDA(ctx, launch_pdl(k_gelu_up, dim3(elementwise_grid(ctx, total)), dim3(256), 0, ctx->stream, gate_up, inter, total, out));
+    ctx->launches++;
+    return LEV_OK;
+}
+
+extern "C" int lev_axpy(lev_ctx* ctx, float alpha, const float* x, const float* r, int64_t n, float* y) {
+    if (!ctx || !x || !r || !y) return LEV_BAD_ARGUMENT;
+    if (n <= 0) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "%lld elements", (long long)n);
+    if (overlap(x, (size_t)n * 4, y, (size_t)n * 4)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and y overlap");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    LEV_CUDA(ctx, launch_pdl(k_axpy, dim3(elementwise_grid(ctx, n)), dim3(256), 0, ctx->stream, alpha, x, r, n, y));
+    ctx->launches++;
+    return LEV_OK;
+}
+
+namespace {
+
+int check_fusion(lev_ctx* ctx, const lev_fusion* f) {
+    if (!f) return LEV_OK;
+    if (f->prologue != LEV_PROLOGUE_NONE && f->prologue != LEV_PROLOGUE_RMSNORM && f->prologue != LEV_PROLOGUE_GELU_UP)
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "unknown prologue %d", f->prologue);
+    if (f->prologue == LEV_PROLOGUE_RMSNORM && (!(f->eps >= 0.f) || !isfinite(f->eps)))
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "epsilon %g", (double)f->eps);
+    if (f->residual && !isfinite(f->alpha)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "alpha %g", (double)f->alpha);
+    return LEV_OK;
+}
+
+lev_dense_fusion to_dense(const lev_fusion* f) {
+    lev_dense_fusion d = {};
+    if (!f) return d;
+    d.norm_on = f->prologue == LEV_PROLOGUE_RMSNORM;
+    d.norm_w = f->norm_weight;
+    d.eps = f->eps;
+    d.gelu_up = f->prologue == LEV_PROLOGUE_GELU_UP;
+    d.residual = f->residual;
+    d.alpha = f->alpha;
+    return d;
+}
+
+// the prologue as a launch of its own, into the context's scratch
+int staged_prologue(lev_ctx* ctx, const lev_fusion* f, const float* x, int n_cols, int64_t cols, const float** dx) {
+    *dx = x;
+    if (!f || f->prologue == LEV_PROLOGUE_NONE) return LEV_OK;
+    void* p;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_X, (size_t)n_cols * cols * sizeof(float), &p));
+    if (f->prologue == LEV_PROLOGUE_RMSNORM) {
+        LEV_TRY(rmsnorm_dev(ctx, x, n_cols, cols, f->norm_weight, f->eps, (float*)p, nullptr, nullptr));
+    } else {
+        const int64_t total = (int64_t)n_cols * cols;
+        LEV_CUDA(ctx, launch_pdl(k_gelu_up, dim3(elementwise_grid(ctx, total)), dim3(256), 0, ctx->stream, x, cols, total, (float*)p));
+        ctx->launches++;
+    }
+    *dx = (const float*)p;
+    return LEV_OK;
+}
+
+}  // namespace
+
+// y[c][r] = residual[c][r] + alpha * sum_k W[row0 + r][k] * a[c][k], a = prologue(x).  Device pointers.
+extern "C" int lev_matvec_fused(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int64_t x_count,
+                                int n_cols, const lev_fusion* fusion, float* y, int64_t y_capacity) {
+    if (!ctx || !w || !x || !y) return LEV_BAD_ARGUMENT;
+    if (row0 < 0 || rows <= 0 || row0 > w->rows || rows > w->rows - row0)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "rows [%lld, +%lld) beyond the tensor's %lld rows", (long long)row0, (long long)rows,
+                        (long long)w->rows);
+    if (n_cols < 1 || n_cols > LEV_MAX_COLUMNS) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d outside 1...%d", n_cols, LEV_MAX_COLUMNS);
+    LEV_TRY(check_fusion(ctx, fusion));
+    const bool gelu = fusion && fusion->prologue == LEV_PROLOGUE_GELU_UP;
+    const int64_t per_col = gelu ? 2 * w->cols : w->cols;
+    if (x_count != (int64_t)n_cols * per_col)
+        return lev_fail(ctx, LEV_WRONG_INPUT_COUNT, "input count %lld, expected %lld", (long long)x_count, (long long)((int64_t)n_cols * per_col));
+    if (y_capacity < (int64_t)n_cols * rows)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "output capacity %lld below %lld", (long long)y_capacity, (long long)((int64_t)n_cols * rows));
+    const size_t yb = (size_t)n_cols * (size_t)rows * sizeof(float);
+    if (overlap(x, (size_t)x_count * 4, y, yb)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and y overlap");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) {
+        const lev_dense_fusion d = to_dense(fusion);
+        return lev_dense_run(ctx, w, row0, rows, x, n_cols, y, fusion ? &d : nullptr);
+    }
+    // shapes the one-launch kernel does not serve: the same steps as separate launches
+    const float* dx;
+    LEV_TRY(staged_prologue(ctx, fusion, x, n_cols, w->cols, &dx));
+    float* dy = y;
+    if (fusion && fusion->residual) {
+        void* p;
+        LEV_TRY(lev_scratch(ctx, LEV_SCR_Y, yb, &p));
+        dy = (float*)p;
+    }
+    if (lev_stream_supported(w, row0, rows, n_cols))
+        LEV_TRY(lev_launch_matvec_stream(ctx, w, row0, rows, dx, n_cols, dy));
+    else
+        LEV_TRY(lev_launch_matvec_plain(ctx, w, row0, rows, dx, n_cols, dy));
+    if (fusion && fusion->residual) {
+        const int64_t n = (int64_t)n_cols * rows;
+        LEV_CUDA(ctx, launch_pdl(k_axpy, dim3(elementwise_grid(ctx, n)), dim3(256), 0, ctx->stream, fusion->alpha, (const float*)dy,
+                                 fusion->residual, n, y));
+        ctx->launches++;
+    }
+    return LEV_OK;
+}
+
+// Several tensors of one inDim against prologue(x) (the gate and up projections behind one norm).
+// The residual epilogue is not offered here.
+extern "C" int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int64_t x_count, int n_cols,
+                                      const lev_fusion* fusion, float* const* y, const int64_t* y_capacity) {
+    if (!ctx || !w || !x || !y || !y_capacity) return LEV_BAD_ARGUMENT;
+    if (n_ops < 1 || n_ops > 4) return lev_fail(ctx, LEV_BAD_ARGUMENT, "%d tensors (1...4)", n_ops);
+    if (n_cols < 1 || n_cols > LEV_MAX_COLUMNS) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d outside 1...%d", n_cols, LEV_MAX_COLUMNS);
+    LEV_TRY(check_fusion(ctx, fusion));
+    if (fusion && fusion->residual) return lev_fail(ctx, LEV_BAD_ARGUMENT, "the multi-tensor call has no residual epilogue");
+    const bool gelu = fusion && fusion->prologue == LEV_PROLOGUE_GELU_UP;
+    for (int i = 0; i < n_ops; i++) {
+        if (!w[i] || !y[i]) return LEV_BAD_ARGUMENT;
+        const int64_t per_col = gelu ? 2 * w[i]->cols : w[i]->cols;
+        if (x_count != (int64_t)n_cols * per_col)
+            return lev_fail(ctx, LEV_WRONG_INPUT_COUNT, "input count %lld, tensor %d expects %lld", (long long)x_count, i,
+                            (long long)((int64_t)n_cols * per_col));
+        if (y_capacity[i] < (int64_t)n_cols * w[i]->rows)
+            return lev_fail(ctx, LEV_BAD_DIMENSIONS, "output %d capacity %lld below %lld", i, (long long)y_capacity[i],
+                            (long long)((int64_t)n_cols * w[i]->rows));
+        if (overlap(x, (size_t)x_count * 4, y[i], (size_t)n_cols * w[i]->rows * 4)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and y overlap");
+    }
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (lev_dense_multi_supported(ctx, n_ops, w, x, n_cols)) {
+        const lev_dense_fusion d = to_dense(fusion);
+        return lev_dense_multi_run(ctx, n_ops, w, x, n_cols, y, fusion ? &d : nullptr);
+    }
+    // one tensor at a time; the prologue runs once when it has to be staged
+    bool all_dense = true;
+    for (int i = 0; i < n_ops; i++) all_dense = all_dense && lev_dense_supported(ctx, w[i], 0, w[i]->rows, x, n_cols);
+    if (all_dense) {
+        const lev_dense_fusion d = to_dense(fusion);
+        for (int i = 0; i < n_ops; i++) LEV_TRY(lev_dense_run(ctx, w[i], 0, w[i]->rows, x, n_cols, y[i], fusion ? &d : nullptr));
+        return LEV_OK;
+    }
+    const float* dx;
+    LEV_TRY(staged_prologue(ctx, fusion, x, n_cols, w[0]->cols, &dx));
+    for (int i = 0; i < n_ops; i++) {
+        if (lev_stream_supported(w[i], 0, w[i]->rows, n_cols))
+            LEV_TRY(lev_launch_matvec_stream(ctx, w[i], 0, w[i]->rows, dx, n_cols, y[i]));
+        else
+            LEV_TRY(lev_launch_matvec_plain(ctx, w[i], 0, w[i]->rows, dx, n_cols, y[i]));
+    }
+    return LEV_OK;
+}

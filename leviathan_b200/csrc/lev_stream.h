@@ -34,9 +34,20 @@ int lev_stream_prepare(lev_ctx* ctx, const lev_weights* w, const lev_stream_sour
 int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& job, const void* tables, int cmax,
                    int terms, float* y);
 
+// steps fused into the one-launch kernel either side of the product
+struct lev_dense_fusion {
+    int norm_on;            // activations = x * inv_rms(x) * norm_w
+    const float* norm_w;    // [cols] or NULL
+    float eps;
+    int gelu_up;            // x rows are [gate(cols) | up(cols)]; activations = gelu_tanh(gate) * up
+    const float* residual;  // y = residual + alpha * (W x); same layout as y, may be y itself
+    float alpha;
+};
+
 // one-launch dense matvec (lev_dense.cu): n_cols <= 4 and tables that fit shared memory
 bool lev_dense_supported(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols);
-int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y);
+int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x, int n_cols, float* y,
+                  const lev_dense_fusion* fusion = nullptr);
 
 // sliced form of the one-launch kernel: a device-side job list, cmax (1 or 4) activation columns per job
 bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax,
@@ -47,4 +58,5 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
 
 // multi form: several whole tensors of one format and K against the same activations, one launch
 bool lev_dense_multi_supported(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols);
-int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y);
+int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y,
+                        const lev_dense_fusion* fusion = nullptr);

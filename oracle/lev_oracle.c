@@ -545,6 +545,34 @@ void lev_or_quantize_q8(const float* x, long n, int8_t* q, float* d, float* s) {
 }
 
 /* ------------------------------------------------------------------ */
+/* RMSNorm                                                             */
+/* ------------------------------------------------------------------ */
+
+/* g4_rmsnorm, Sources/LeviathanCore/Gemma4.swift:4247-4268: one serial f32 sum in index order,
+ * inv = 1 / sqrt(ms / n + eps), y = x * inv * w (w NULL: no scale) */
+void lev_or_rmsnorm_f32(const float* x, long n, long vectors, const float* w, float eps, float* y) {
+    for (long v = 0; v < vectors; v++) {
+        const float* xv = x + v * n;
+        float ms = 0.0f;
+        for (long i = 0; i < n; i++) ms += xv[i] * xv[i];
+        ms = ms / (float)n + eps;
+        float inv = 1.0f / sqrtf(ms);
+        for (long i = 0; i < n; i++) y[v * n + i] = xv[i] * inv * (w ? w[i] : 1.0f);
+    }
+}
+
+/* the f64 statistic of rust/crates/lev-model/src/lib.rs:110-114, kept in f64 to the end */
+void lev_or_rmsnorm_f64(const float* x, long n, long vectors, const float* w, float eps, double* y) {
+    for (long v = 0; v < vectors; v++) {
+        const float* xv = x + v * n;
+        double ms = 0.0;
+        for (long i = 0; i < n; i++) ms += (double)xv[i] * (double)xv[i];
+        double inv = 1.0 / sqrt(ms / (double)n + (double)eps);
+        for (long i = 0; i < n; i++) y[v * n + i] = (double)xv[i] * inv * (w ? (double)w[i] : 1.0);
+    }
+}
+
+/* ------------------------------------------------------------------ */
 /* MoE region                                                          */
 /* ------------------------------------------------------------------ */
 

@@ -104,6 +104,9 @@ double lev_or_max_rel_err(const float* got, long n_got, const double* ref, long 
 void lev_or_quantize_q8(const float* x, long n, int8_t* q, float* d, float* s);
 
 /* ---- MoE region (Sources/LeviathanCore/MoESIMDLowering.swift:981-1030) ---- */
+/* Gemma4.swift:4247-4268 (serial f32) and lev-model/src/lib.rs:110-114 (f64 statistic) */
+void lev_or_rmsnorm_f32(const float* x, long n, long vectors, const float* w, float eps, float* y);
+void lev_or_rmsnorm_f64(const float* x, long n, long vectors, const float* w, float eps, double* y);
 double lev_or_gelu_tanh_up(double gate, double up);
 float lev_or_gelu_tanh_up_f32(float gate, float up); /* Gemma4.swift:4364-4377 */
 /* gu: [top_k][2*inter rows][hidden/32 blocks], dn: [top_k][hidden rows][inter/32 blocks].

@@ -82,6 +82,8 @@ def _load(path: str | None = None) -> C.CDLL:
     sig("lev_or_q6_k_dequant_block_f64", None, u8p, f64p)
     sig("lev_or_max_rel_err", C.c_double, f32p, L, f64p, L)
     sig("lev_or_quantize_q8", None, f32p, L, i8p, f32p, f32p)
+    sig("lev_or_rmsnorm_f32", None, f32p, L, L, f32p, C.c_float, f32p)
+    sig("lev_or_rmsnorm_f64", None, f32p, L, L, f32p, C.c_float, f64p)
     sig("lev_or_gelu_tanh_up", C.c_double, C.c_double, C.c_double)
     sig("lev_or_gelu_tanh_up_f32", C.c_float, C.c_float, C.c_float)
     sig("lev_or_moe_region_f64", C.c_int, L, L, L, u8p, Z, u8p, Z, f32p, f64p, f64p, f64p, f64p)
@@ -316,6 +318,34 @@ def quantize_q8(x):
 
 
 # ---- MoE ----
+def rmsnorm_f32(x, w=None, eps: float = 1e-6) -> np.ndarray:
+    """[vectors][n] f32, the reference kernel's serial order (Gemma4.swift:4247-4268)."""
+    x = np.atleast_2d(_f32(x))
+    w = None if w is None else _f32(w)
+    y = np.empty_like(x)
+    lib().lev_or_rmsnorm_f32(_p(x), x.shape[1], x.shape[0], _p(w), eps, _p(y))
+    return y
+
+
+def rmsnorm_f64(x, w=None, eps: float = 1e-6) -> np.ndarray:
+    x = np.atleast_2d(_f32(x))
+    w = None if w is None else _f32(w)
+    y = np.empty(x.shape, np.float64)
+    lib().lev_or_rmsnorm_f64(_p(x), x.shape[1], x.shape[0], _p(w), eps, _p(y))
+    return y
+
+
+def gelu_up_rows(gate_up, inter: int, f64: bool = True) -> np.ndarray:
+    """[vectors][2*inter] -> [vectors][inter] through the scalar oracle functions."""
+    gu = np.atleast_2d(_f32(gate_up))
+    fn = gelu_tanh_up if f64 else gelu_tanh_up_f32
+    out = np.empty((gu.shape[0], inter), np.float64 if f64 else np.float32)
+    for v in range(gu.shape[0]):
+        for e in range(inter):
+            out[v, e] = fn(float(gu[v, e]), float(gu[v, inter + e]))
+    return out
+
+
 def gelu_tanh_up(g: float, u: float) -> float:
     return lib().lev_or_gelu_tanh_up(g, u)
 

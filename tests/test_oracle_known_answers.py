@@ -5,6 +5,7 @@ import math
 import numpy as np
 import pytest
 
+from leviathan_b200 import quant as Q
 from oracle import oracle as O
 
 
@@ -367,3 +368,22 @@ def test_combine_is_rank_ordered_f32_axpy():
     w = np.array([1.0, 1.0, 0.5], np.float32)
     out = O.combine(y, w)
     assert out.tolist() == [0.5, 2.5]
+
+
+def test_rmsnorm_known_answers():
+    # rust/crates/lev-model/src/lib.rs:432-435: a constant vector normalises to its weight
+    for fn in (O.rmsnorm_f32, O.rmsnorm_f64):
+        y = fn(np.full(8, 2.0, np.float32), np.full(8, 0.5, np.float32), 1e-6)
+        assert np.all(np.abs(y - 0.5) < 1e-5)
+    # the definition: x * (1 / sqrt(mean(x^2) + eps)) * w, and no scale without a weight
+    x = np.array([[3.0, -4.0, 0.0, 0.0], [1.0, 1.0, 1.0, 1.0]], np.float32)
+    w = np.array([1.0, 2.0, 3.0, 4.0], np.float32)
+    inv0 = 1.0 / np.sqrt(25.0 / 4.0 + 1e-6)
+    np.testing.assert_allclose(O.rmsnorm_f64(x, w, 1e-6)[0], np.array([3.0, -8.0, 0.0, 0.0]) * inv0, rtol=1e-12)
+    np.testing.assert_allclose(O.rmsnorm_f64(x, None, 1e-6)[1], np.full(4, 1.0 / np.sqrt(1.0 + 1e-6)), rtol=1e-7)
+    # the serial f32 form is itself measured against the f64 one, not assumed exact
+    big = Q.normal(9, (3, 2816), 1.0).astype(np.float32)
+    wb = (1.0 + Q.normal(10, (2816,), 0.1)).astype(np.float32)
+    assert O.max_rel_err(O.rmsnorm_f32(big, wb).reshape(-1), O.rmsnorm_f64(big, wb).reshape(-1)) < 1e-5
+    # epsilon keeps the zero vector finite
+    assert np.all(O.rmsnorm_f32(np.zeros(16, np.float32), None, 1e-6) == 0.0)
