@@ -596,6 +596,36 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
             byts = 2 * GATE_BYTES + DOWN_BYTES + n * VEC_BYTES
             cols[f"n{n}"] = {"ms_per_step": msn, "gbs": byts / msn / 1e6, "hbm_frac": byts / msn / 1e6 / peaks["hbm_gbs"]}
         out["ffn_columns"] = {"workload": "gate/up concatenated + down, n activation columns", **cols}
+        # decode attention over an fp16 paged KV cache: 16 query heads, 8 KV heads, head dimension 256,
+        # 4096 cached positions (33.5 MB of K and V per layer and sequence); six layers' caches are cycled
+        # so that each launch reads from HBM, blocks handed out in a shuffled order
+        import leviathan_b200 as lev_pkg
+        import random as _random
+
+        QH, KVH, HD, TOK, PAGE = 16, 8, 256, 4096, 16
+        caches = []
+        for li in range(6):
+            c = lev_pkg.PagedKV(TOK // PAGE + 1, PAGE, KVH, HD, slots=1, max_blocks=TOK // PAGE, dtype="f16", device=dev)
+            _random.Random(li).shuffle(c.free)
+            for p_ in range(0, TOK, PAGE):
+                c.ensure(0, p_)
+            c.k.copy_((torch.randn(c.k.shape, generator=g, device=dev) * 0.25).to(torch.float16))
+            c.v.copy_(torch.randn(c.v.shape, generator=g, device=dev).to(torch.float16))
+            caches.append(c)
+        qa = torch.randn((1, QH, HD), generator=g, device=dev)
+        oa = torch.empty_like(qa)
+        slot_a = torch.zeros(1, dtype=torch.int32, device=dev)
+        pos_a = torch.full((1,), TOK - 1, dtype=torch.int32, device=dev)
+
+        def attn_step(i):
+            ctx.attn_decode(caches[i % 6], slot_a, pos_a, qa, 0, 1.0, out=oa)
+
+        ms = _graph_time(torch, stream, attn_step, 24)
+        kv_bytes = 2 * TOK * KVH * HD * 2
+        out["attn_decode"] = {"workload": "16 q heads / 8 KV heads / head_dim 256 / 4096 positions, fp16 paged cache (page 16), batch 1",
+                              "launches_per_step": 2, "us_per_step": ms * 1e3, "kv_bytes": kv_bytes, "gbs": kv_bytes / ms / 1e6,
+                              "hbm_frac": kv_bytes / ms / 1e6 / peaks["hbm_gbs"]}
+        del caches
         for wgu, wd in fused:
             wgu.free()
             wd.free()

@@ -140,6 +140,8 @@ int lev_cuda_hardware_profile(lev_ctx* ctx, lev_hw_profile* out);
 /* cuda_stream is a cudaStream_t; NULL restores the context's own stream (pass
  * cudaStreamLegacy, not 0, to name the legacy default stream). */
 int lev_cuda_set_stream(lev_ctx* ctx, void* cuda_stream);
+/* waits for the stream; LEV_TIMEOUT if a kernel's bounded wait ran out, LEV_BAD_DIMENSIONS if a
+ * cache index lay outside its layout (kernels record these instead of faulting) */
 int lev_cuda_synchronize(lev_ctx* ctx);
 /* Launch counter: kernels launched by this context since creation. */
 int64_t lev_cuda_launch_count(const lev_ctx* ctx);
@@ -267,6 +269,37 @@ int lev_matvec_fused(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t r
 int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x,
                            int64_t x_count, int n_cols, const lev_fusion* fusion, float* const* y,
                            const int64_t* y_capacity);
+
+/* ---- decode attention over a paged KV cache ------------------------------
+ * Single-query attention of g4_attn (Sources/LeviathanCore/Gemma4.swift:4412-4457; f64 oracle
+ * Sources/LeviathanCore/AttentionLowering.swift:358-388): column c, at query position pos[c] of
+ * sequence slot[c], attends to positions [lo, pos[c]] (lo = pos + 1 - window when window > 0),
+ * weights softmax(scale * q.k), query head h reads KV head h / (q_heads / kv_heads).  The cache is
+ * the paged pool of attn_decode_paged (rust/crates/lev-forge/src/ops.rs:1038-1101;
+ * rust/crates/lev-model/src/kv.rs:36-85): pools [blocks][page][kv_heads][head_dim], block table
+ * [slots][max_blocks] (int32).  All pointers are device pointers; slot and pos are read on the
+ * device, so a decode step needs no host synchronisation.  A slot, position or table entry outside
+ * the layout is not followed: the column's output is NaN and the context's next status read
+ * reports it.  head_dim 128 or 256; q_heads / kv_heads 1, 2 or 4.
+ * lev_kv_append stores each column's new K and V rows (f32 [n_cols][kv_heads][head_dim]) at its
+ * position (attn_prep_paged's store, ops.rs:972-1036; the cache append of Gemma4.swift:3690-3698). */
+enum { LEV_KV_F32 = 0, LEV_KV_F16 = 1 };
+typedef struct lev_kv_layout {
+    int kv_type;    /* LEV_KV_F16 or LEV_KV_F32 */
+    int page;       /* positions per block (16 in the reference) */
+    int kv_heads;
+    int head_dim;
+    int64_t blocks; /* blocks in each pool */
+    int max_blocks; /* entries per row of the block table */
+    int slots;      /* rows of the block table */
+} lev_kv_layout;
+int lev_kv_append(lev_ctx* ctx, const lev_kv_layout* layout, void* k_pool, void* v_pool,
+                  const int32_t* block_table, const int32_t* slot, const int32_t* pos, int n_cols,
+                  const float* k, const float* v);
+int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* layout, const void* k_pool,
+                    const void* v_pool, const int32_t* block_table, const int32_t* slot,
+                    const int32_t* pos, int n_cols, int q_heads, const float* q, int window,
+                    float scale, float* out);
 
 /* ---- routed MoE composite ----------------------------------------------
  * Expert weights are the fused gate_up tensor [experts][2*inter][hidden] and

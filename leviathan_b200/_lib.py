@@ -53,6 +53,14 @@ class Fusion(C.Structure):
 
 PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_GELU_UP = 0, 1, 2
 
+
+class KVLayout(C.Structure):
+    _fields_ = [("kv_type", C.c_int), ("page", C.c_int), ("kv_heads", C.c_int), ("head_dim", C.c_int),
+                ("blocks", C.c_int64), ("max_blocks", C.c_int), ("slots", C.c_int)]
+
+
+KV_F32, KV_F16 = 0, 1
+
 # name -> (restype, argtypes); every symbol the header declares
 _P, _I, _L, _Z, _U = C.c_void_p, C.c_int, C.c_int64, C.c_size_t, C.c_uint
 SIGNATURES = {
@@ -83,6 +91,8 @@ SIGNATURES = {
     "lev_axpy": (_I, [_P, C.c_float, _P, _P, _L, _P]),
     "lev_matvec_fused": (_I, [_P, _P, _L, _L, _P, _L, _I, C.POINTER(Fusion), _P, _L]),
     "lev_matvec_multi_fused": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(Fusion), C.POINTER(_P), C.POINTER(_L)]),
+    "lev_kv_append": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _P, _P]),
+    "lev_attn_decode": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _I, _P, _I, C.c_float, _P]),
     "lev_gemm_prefill": (_I, [_P, _P, _P, _L, _P, _U]),
     "lev_act_bf16": (_I, [_P, _P, _L, _P]),
     "lev_moe_weights_upload": (_I, [_P, _P, _P, _Z, _P, _Z, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),

@@ -301,6 +301,24 @@ class Context:
         self._check(self.lib.lev_matvec_multi_fused(self.handle, n, wp, _ptr(x), x.numel(), n_cols, C.byref(f), yp, cap))
         return outs
 
+    # -- decode attention over a paged KV cache (torch CUDA tensors only) --
+    def kv_append(self, cache: "PagedKV", slot, pos, k, v):
+        """lev_kv_append: k, v f32 [n_cols][kv_heads][head_dim] to position pos[c] of sequence slot[c]."""
+        self._flags(False, False)
+        self._check(self.lib.lev_kv_append(self.handle, C.byref(cache.layout), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+                                           _ptr(slot), _ptr(pos), int(slot.numel()), _ptr(k.contiguous()), _ptr(v.contiguous())))
+
+    def attn_decode(self, cache: "PagedKV", slot, pos, q, window: int = 0, scale: float = 1.0, out=None):
+        """lev_attn_decode: q f32 [n_cols][q_heads][head_dim] -> out of the same shape."""
+        import torch
+
+        q = q.contiguous()
+        out = torch.empty_like(q) if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_attn_decode(self.handle, C.byref(cache.layout), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+                                             _ptr(slot), _ptr(pos), q.shape[0], q.shape[1], _ptr(q), window, scale, _ptr(out)))
+        return out
+
     def _matvec_host(self, fn, blocks, out_dim, in_dim, x):
         blocks = np.ascontiguousarray(blocks, np.uint8)
         x = np.ascontiguousarray(x, np.float32)
@@ -479,6 +497,53 @@ class Context:
         self._check(self.lib.lev_gemm_prefill_rowsplit_allgather(self.handle, w_local.handle, _ptr(x_bf16), tokens,
                                                                  _ptr(out), 0))
         return out
+
+
+class PagedKV:
+    """Device pools and block table of one layer's paged KV cache (pools [blocks][page][kv_heads][head_dim],
+    table [slots][max_blocks]; rust/crates/lev-model/src/kv.rs:36-85).  Block 0 is the scratch block every
+    unused table entry points to; `ensure` hands out the others, low ids first, like BlockManager.ensure."""
+
+    def __init__(self, blocks: int, page: int, kv_heads: int, head_dim: int, slots: int, max_blocks: int,
+                 dtype: str = "f16", device: str = "cuda"):
+        import torch
+
+        td = torch.float16 if dtype == "f16" else torch.float32
+        self.layout = L.KVLayout(L.KV_F16 if dtype == "f16" else L.KV_F32, page, kv_heads, head_dim, blocks, max_blocks, slots)
+        self.k = torch.zeros((blocks, page, kv_heads, head_dim), dtype=td, device=device)
+        self.v = torch.zeros_like(self.k)
+        self.table_host = np.zeros((slots, max_blocks), np.int32)
+        self.table = torch.zeros((slots, max_blocks), dtype=torch.int32, device=device)
+        self.free = list(range(blocks - 1, 0, -1))
+        self.owned = [[] for _ in range(slots)]
+        self.page, self.max_blocks = page, max_blocks
+
+    def ensure(self, slot: int, pos: int) -> int:
+        """Make sequence `slot` own the block of `pos`; returns the flat pool position."""
+        import torch
+
+        need = pos // self.page + 1
+        if need > self.max_blocks:
+            raise IndexError("beyond context")
+        grew = False
+        while len(self.owned[slot]) < need:
+            if not self.free:
+                raise MemoryError("out of blocks")
+            b = self.free.pop()
+            self.table_host[slot, len(self.owned[slot])] = b
+            self.owned[slot].append(b)
+            grew = True
+        if grew:
+            self.table.copy_(torch.from_numpy(self.table_host))
+        return self.owned[slot][pos // self.page] * self.page + pos % self.page
+
+    def release(self, slot: int):
+        import torch
+
+        while self.owned[slot]:
+            self.free.append(self.owned[slot].pop())
+        self.table_host[slot] = 0
+        self.table.copy_(torch.from_numpy(self.table_host))
 
 
 class GGUFFile:

@@ -164,7 +164,12 @@ extern "C" int lev_cuda_set_stream(lev_ctx* ctx, void* s) {
 
 extern "C" int lev_cuda_synchronize(lev_ctx* ctx) {
     if (!ctx) return LEV_BAD_ARGUMENT;
-    LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    // the wait also collects what kernels recorded instead of faulting: a bounded wait that ran out,
+    // a cache index outside its layout
+    int bits = 0;
+    LEV_TRY(lev_read_status(ctx, &bits));
+    if (bits & LEV_DEV_TIMEOUT) return lev_fail(ctx, LEV_TIMEOUT, "a kernel's bounded wait ran out");
+    if (bits & LEV_DEV_BAD_INDEX) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "a slot, position or block-table entry lay outside the cache layout");
     return LEV_OK;
 }
 

@@ -413,7 +413,7 @@ extern "C" int lev_gguf_moe_upload(lev_ctx* ctx, const lev_gguf* g, int layer, i
         *v = (int64_t)u;
         return LEV_OK;
     };
-    int64_t layers, experts, used, hidden, inter;
+    int64_t layers = 0, experts = 0, used = 0, hidden = 0, inter = 0;
     int st;
     if ((st = meta_int("block_count", 1 << 16, &layers))) return st;
     if ((st = meta_int("expert_count", LEV_MAX_EXPERTS, &experts))) return st;

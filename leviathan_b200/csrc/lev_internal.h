@@ -19,6 +19,7 @@
 #define LEV_DEV_NONFINITE_SCALE 2
 #define LEV_DEV_NONFINITE_OUTPUT 4
 #define LEV_DEV_TIMEOUT 8
+#define LEV_DEV_BAD_INDEX 16  // a slot, position or block-table entry outside the cache layout
 
 struct lev_dist_state;
 
@@ -49,6 +50,7 @@ enum {
     LEV_SCR_MOE_D = 5,   // expert outputs per (token, rank)
     LEV_SCR_XPREP = 6,   // split activations for the stream schedule
     LEV_SCR_DIST = 7,
+    LEV_SCR_ATTN = 8,    // attention partials per position range
     LEV_SCR_SLOTS = 12
 };
 

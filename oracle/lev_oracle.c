@@ -573,6 +573,47 @@ void lev_or_rmsnorm_f64(const float* x, long n, long vectors, const float* w, fl
 }
 
 /* ------------------------------------------------------------------ */
+/* Decode attention                                                    */
+/* ------------------------------------------------------------------ */
+
+/* fp64Attention, Sources/LeviathanCore/AttentionLowering.swift:358-388, with the score scale of
+ * attn_decode_paged (rust/crates/lev-forge/src/ops.rs:1072) as a parameter (1.0 in the Swift model).
+ * q [q_heads][hd]; k, v [tokens][kv_heads][hd]; the query sits at position tokens - 1. */
+int lev_or_attention_f64(const float* q, const float* k, const float* v, long q_heads, long kv_heads, long hd, long tokens,
+                         long window, double scale, double* out) {
+    if (q_heads <= 0 || kv_heads <= 0 || q_heads % kv_heads != 0 || hd <= 0 || tokens <= 0 || window < 0) return 1;
+    long qpos = tokens - 1;
+    long lo = (window != 0 && qpos + 1 > window) ? qpos + 1 - window : 0;
+    long group = q_heads / kv_heads;
+    double* s = (double*)malloc((size_t)tokens * sizeof(double));
+    if (!s) return 2;
+    for (long h = 0; h < q_heads; h++) {
+        long kvh = h / group;
+        double m = -INFINITY;
+        for (long t = lo; t <= qpos; t++) {
+            const float* kt = k + (t * kv_heads + kvh) * hd;
+            double d = 0.0;
+            for (long i = 0; i < hd; i++) d += (double)q[h * hd + i] * (double)kt[i];
+            s[t] = d * scale;
+            if (s[t] > m) m = s[t];
+        }
+        double l = 0.0;
+        for (long t = lo; t <= qpos; t++) {
+            s[t] = exp(s[t] - m);
+            l += s[t];
+        }
+        for (long i = 0; i < hd; i++) out[h * hd + i] = 0.0;
+        for (long t = lo; t <= qpos; t++) {
+            double w = s[t] / l;
+            const float* vt = v + (t * kv_heads + kvh) * hd;
+            for (long i = 0; i < hd; i++) out[h * hd + i] += w * (double)vt[i];
+        }
+    }
+    free(s);
+    return 0;
+}
+
+/* ------------------------------------------------------------------ */
 /* MoE region                                                          */
 /* ------------------------------------------------------------------ */
 

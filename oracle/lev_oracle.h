@@ -107,6 +107,9 @@ void lev_or_quantize_q8(const float* x, long n, int8_t* q, float* d, float* s);
 /* Gemma4.swift:4247-4268 (serial f32) and lev-model/src/lib.rs:110-114 (f64 statistic) */
 void lev_or_rmsnorm_f32(const float* x, long n, long vectors, const float* w, float eps, float* y);
 void lev_or_rmsnorm_f64(const float* x, long n, long vectors, const float* w, float eps, double* y);
+/* AttentionLowering.swift:358-388 */
+int lev_or_attention_f64(const float* q, const float* k, const float* v, long q_heads, long kv_heads, long hd, long tokens,
+                         long window, double scale, double* out);
 double lev_or_gelu_tanh_up(double gate, double up);
 float lev_or_gelu_tanh_up_f32(float gate, float up); /* Gemma4.swift:4364-4377 */
 /* gu: [top_k][2*inter rows][hidden/32 blocks], dn: [top_k][hidden rows][inter/32 blocks].

@@ -84,6 +84,7 @@ def _load(path: str | None = None) -> C.CDLL:
     sig("lev_or_quantize_q8", None, f32p, L, i8p, f32p, f32p)
     sig("lev_or_rmsnorm_f32", None, f32p, L, L, f32p, C.c_float, f32p)
     sig("lev_or_rmsnorm_f64", None, f32p, L, L, f32p, C.c_float, f64p)
+    sig("lev_or_attention_f64", C.c_int, f32p, f32p, f32p, L, L, L, L, L, C.c_double, f64p)
     sig("lev_or_gelu_tanh_up", C.c_double, C.c_double, C.c_double)
     sig("lev_or_gelu_tanh_up_f32", C.c_float, C.c_float, C.c_float)
     sig("lev_or_moe_region_f64", C.c_int, L, L, L, u8p, Z, u8p, Z, f32p, f64p, f64p, f64p, f64p)
@@ -333,6 +334,15 @@ def rmsnorm_f64(x, w=None, eps: float = 1e-6) -> np.ndarray:
     y = np.empty(x.shape, np.float64)
     lib().lev_or_rmsnorm_f64(_p(x), x.shape[1], x.shape[0], _p(w), eps, _p(y))
     return y
+
+
+def attention_f64(q, k, v, window: int = 0, scale: float = 1.0) -> np.ndarray:
+    """q [q_heads][hd], k / v [tokens][kv_heads][hd]; the query is at position tokens - 1
+    (AttentionLowering.swift:358-388)."""
+    q, k, v = _f32(q), _f32(k), _f32(v)
+    out = np.empty(q.shape, np.float64)
+    _check(lib().lev_or_attention_f64(_p(q), _p(k), _p(v), q.shape[0], k.shape[1], q.shape[1], k.shape[0], window, scale, _p(out)))
+    return out
 
 
 def gelu_up_rows(gate_up, inter: int, f64: bool = True) -> np.ndarray:

@@ -387,3 +387,33 @@ def test_rmsnorm_known_answers():
     assert O.max_rel_err(O.rmsnorm_f32(big, wb).reshape(-1), O.rmsnorm_f64(big, wb).reshape(-1)) < 1e-5
     # epsilon keeps the zero vector finite
     assert np.all(O.rmsnorm_f32(np.zeros(16, np.float32), None, 1e-6) == 0.0)
+
+
+def test_attention_oracle_analytic_cases():
+    """The reference holds no known-answer vector for attention (its f64 oracle,
+    AttentionLowering.swift:358-388, is only compared with its kernels), so the restatement is held to
+    cases with closed forms."""
+    rng = np.random.default_rng(3)
+    hd, kvh, qh, T = 8, 2, 4, 6
+    q = rng.standard_normal((qh, hd)).astype(np.float32)
+    v = rng.standard_normal((T, kvh, hd)).astype(np.float32)
+    # equal keys: plain mean of V of the head's KV head (query heads 0,1 -> KV head 0; 2,3 -> 1)
+    k = np.ones((T, kvh, hd), np.float32)
+    out = O.attention_f64(q, k, v)
+    for h in range(qh):
+        np.testing.assert_allclose(out[h], v[:, h // 2].astype(np.float64).mean(axis=0), rtol=1e-12)
+    # one position: its V row exactly
+    np.testing.assert_array_equal(O.attention_f64(q, k[:1], v[:1])[3], v[0, 1].astype(np.float64))
+    # a window of 2 sees the last two positions only
+    np.testing.assert_allclose(O.attention_f64(q, k, v, window=2)[0], v[-2:, 0].astype(np.float64).mean(axis=0), rtol=1e-12)
+    # a key aligned with the query and far larger takes all the weight; scale 0 removes the preference
+    k2 = np.zeros((T, kvh, hd), np.float32)
+    k2[4, 0] = 100.0 * q[0] / np.dot(q[0], q[0])
+    np.testing.assert_allclose(O.attention_f64(q, k2, v)[0], v[4, 0], rtol=1e-9, atol=1e-30)
+    np.testing.assert_allclose(O.attention_f64(q, k2, v, scale=0.0)[0], v[:, 0].astype(np.float64).mean(axis=0), rtol=1e-12)
+    # two positions, scores 0 and ln 3: weights 1/4 and 3/4
+    k3 = np.zeros((2, 1, hd), np.float32)
+    q3 = np.zeros((1, hd), np.float32)
+    q3[0, 0], k3[1, 0, 0] = 1.0, np.float32(np.log(3.0))
+    v3 = np.stack([np.full((1, hd), 4.0, np.float32), np.full((1, hd), 8.0, np.float32)])
+    np.testing.assert_allclose(O.attention_f64(q3, k3, v3)[0], np.full(hd, 7.0), rtol=1e-6)
