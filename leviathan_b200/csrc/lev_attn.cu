@@ -8,10 +8,10 @@
 // [slots][max_blocks], per activation column its sequence slot and query position.  Pool elements
 // are fp16 (half the bytes of the reference's f32 cache, the traffic that bounds this kernel) or f32.
 //
-// Work split: one thread block per (position range, KV head, column); each of its warps runs its own
-// online softmax over every fourth position, a lane holding headDim/32 consecutive elements of the
-// row (one 16-byte load per K or V row at headDim 256 in fp16); warps, then ranges, are merged
-// with the usual max / rescale rule in a fixed order.
+// Work split: one thread block per (position range, KV head, column), ranges sized so that the grid is
+// one wave of two blocks per SM; the rows of a range are staged in shared memory by asynchronous
+// copies issued all at once (see k_attn_split).  Warps, then ranges, are merged with the usual
+// max / rescale rule in a fixed order.
 #include <cuda_fp16.h>
 
 #include "lev_stream.h"
@@ -19,9 +19,11 @@
 
 namespace {
 
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 8;
 constexpr int kAttnUnroll = 4;
 constexpr int kMaxSplits = 128;
+constexpr int kMaxRoundPages = 128;      // block-table entries one round may span
+constexpr size_t kRoundBytes = 112 * 1024;  // K and V rows of a round in shared memory: two blocks per SM
 
 struct AttnArgs {
     const void* k_pool;
@@ -35,6 +37,7 @@ struct AttnArgs {
     float* part_acc;       // [cols][q_heads][splits][hd]
     int* status;
     int page, kv_heads, q_heads, max_blocks, slots, splits, window;
+    int round_cap;  // positions per round of the split kernel
     int64_t blocks;
     float scale;
 };
@@ -44,7 +47,7 @@ struct Row;
 template <>
 struct Row<__half, 8> {
     uint4 raw;
-    __device__ void load(const __half* p) { raw = __ldg(reinterpret_cast<const uint4*>(p)); }
+    __device__ void load_s(const __half* p) { raw = *reinterpret_cast<const uint4*>(p); }
     __device__ void get(float* f) const {
         const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
@@ -58,7 +61,7 @@ struct Row<__half, 8> {
 template <>
 struct Row<__half, 4> {
     uint2 raw;
-    __device__ void load(const __half* p) { raw = __ldg(reinterpret_cast<const uint2*>(p)); }
+    __device__ void load_s(const __half* p) { raw = *reinterpret_cast<const uint2*>(p); }
     __device__ void get(float* f) const {
         const __half2* h = reinterpret_cast<const __half2*>(&raw);
 #pragma unroll
@@ -72,9 +75,9 @@ struct Row<__half, 4> {
 template <>
 struct Row<float, 8> {
     float4 a, b;
-    __device__ void load(const float* p) {
-        a = __ldg(reinterpret_cast<const float4*>(p));
-        b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+    __device__ void load_s(const float* p) {
+        a = *reinterpret_cast<const float4*>(p);
+        b = *(reinterpret_cast<const float4*>(p) + 1);
     }
     __device__ void get(float* f) const {
         f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w, f[4] = b.x, f[5] = b.y, f[6] = b.z, f[7] = b.w;
@@ -83,7 +86,7 @@ struct Row<float, 8> {
 template <>
 struct Row<float, 4> {
     float4 a;
-    __device__ void load(const float* p) { a = __ldg(reinterpret_cast<const float4*>(p)); }
+    __device__ void load_s(const float* p) { a = *reinterpret_cast<const float4*>(p); }
     __device__ void get(float* f) const { f[0] = a.x, f[1] = a.y, f[2] = a.z, f[3] = a.w; }
 };
 
@@ -94,13 +97,38 @@ __device__ __forceinline__ bool column_ok(const AttnArgs& A, int col, int* slot,
     return *slot >= 0 && *slot < A.slots && *pos >= 0 && *pos < A.max_blocks * A.page;
 }
 
+// 16-byte asynchronous copy global -> shared, and its group fences
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+constexpr int kStages = 4;  // copy groups per round: compute on a quarter starts when it has landed
+
+// One thread block per (position range, KV head, column).  A range is walked in rounds of at most
+// `round_cap` positions.  A round: the block-table entries of its pages go to shared memory; every
+// thread then requests its share of the round's K and V rows with 16-byte asynchronous copies, all at
+// once, in four groups; as each group lands the warps take its positions (warp w: positions w, w + 8,
+// ...), four at a time: scores first, then one rescale of the running softmax state.  The rows of a
+// round are read from HBM exactly once and never pass through registers on their way in, so the
+// bytes in flight per SM are bounded by shared memory (two blocks of up to 112 KB), not registers.
 template <typename T, int VEC, int GROUP>
-__global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(AttnArgs A) {
+__global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     constexpr int HD = VEC * 32;
+    constexpr int kRowBytes = HD * (int)sizeof(T);
+    constexpr int kChunksPerRow = kRowBytes / 16;
+    extern __shared__ __align__(16) unsigned char attn_smem[];
     __shared__ float sm_m[kAttnWarps][GROUP], sm_l[kAttnWarps][GROUP];
-    __shared__ float sm_acc[kAttnWarps][GROUP][HD];
+    __shared__ int sm_tbl[kMaxRoundPages];
     const int split = blockIdx.x, kvh = blockIdx.y, col = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int round_cap = A.round_cap;
+    T* ks = reinterpret_cast<T*>(attn_smem);                                     // [round_cap][HD]
+    T* vs = reinterpret_cast<T*>(attn_smem + (size_t)round_cap * kRowBytes);     // [round_cap][HD]
     pdl_wait();
     pdl_launch_dependents();
     int slot, qpos;
@@ -112,8 +140,8 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(AttnArgs A) {
     const int n = qpos + 1 - lo;
     const int begin = lo + (int)((int64_t)n * split / A.splits), end = lo + (int)((int64_t)n * (split + 1) / A.splits);
     const int32_t* trow = A.table + (int64_t)slot * A.max_blocks;
-    const T* kp = static_cast<const T*>(A.k_pool);
-    const T* vp = static_cast<const T*>(A.v_pool);
+    const unsigned char* kp = static_cast<const unsigned char*>(A.k_pool);
+    const unsigned char* vp = static_cast<const unsigned char*>(A.v_pool);
 
     float qv[GROUP][VEC];
 #pragma unroll
@@ -131,50 +159,113 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(AttnArgs A) {
         for (int i = 0; i < VEC; i++) acc[g][i] = 0.f;
     }
     bool bad = false;
-    for (int base = begin + warp; base < end; base += kAttnWarps * kAttnUnroll) {
-        Row<T, VEC> kr[kAttnUnroll], vr[kAttnUnroll];
-        bool live[kAttnUnroll];
+    for (int r0 = begin; r0 < end; r0 += round_cap) {
+        const int rn = end - r0 < round_cap ? end - r0 : round_cap;  // positions of this round
+        const int page0 = r0 / A.page, pages = (r0 + rn - 1) / A.page - page0 + 1;
+        __syncthreads();  // the previous round's rows and table entries are no longer read
+        for (int j = threadIdx.x; j < pages; j += kAttnWarps * 32) {
+            int e = trow[page0 + j];
+            if (e < 0 || e >= A.blocks) {  // an entry outside the pool is recorded and not followed
+                bad = true;
+                e = -1;
+            }
+            sm_tbl[j] = e;
+        }
+        __syncthreads();
+        // ---- request every row of the round, a quarter of the positions per copy group ----
+        const int per_stage = (rn + kStages - 1) / kStages;
 #pragma unroll
-        for (int u = 0; u < kAttnUnroll; u++) {
-            const int p = base + u * kAttnWarps;
-            live[u] = p < end;
-            if (live[u]) {
-                const int64_t blk = trow[p / A.page];
-                if (blk < 0 || blk >= A.blocks) {  // a table entry outside the pool: record it, skip the row
-                    bad = true;
-                    live[u] = false;
-                } else {
-                    const int64_t at = ((blk * A.page + p % A.page) * A.kv_heads + kvh) * HD + lane * VEC;
-                    kr[u].load(kp + at);
-                    vr[u].load(vp + at);
+        for (int st = 0; st < kStages; st++) {
+            const int j0 = st * per_stage, j1 = j0 + per_stage < rn ? j0 + per_stage : rn;
+            const int chunks = (j1 - j0) * 2 * kChunksPerRow;
+            for (int id = threadIdx.x; id < chunks; id += kAttnWarps * 32) {
+                const int j = j0 + id / (2 * kChunksPerRow), rem = id % (2 * kChunksPerRow);
+                const int is_v = rem / kChunksPerRow, c = rem % kChunksPerRow;
+                const int p = r0 + j, pg = p / A.page, e = sm_tbl[pg - page0];
+                if (e < 0) continue;
+                const int64_t at = ((((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes) + c * 16;
+                unsigned char* dst = reinterpret_cast<unsigned char*>(is_v ? vs : ks) + (size_t)j * kRowBytes + c * 16;
+                cp_async16(smem_u32(dst), (is_v ? vp : kp) + at);
+            }
+            cp_async_commit();
+        }
+        // ---- take the groups as they land ----
+#pragma unroll
+        for (int st = 0; st < kStages; st++) {
+            if (st == 0) cp_async_wait<kStages - 1>();
+            if (st == 1) cp_async_wait<kStages - 2>();
+            if (st == 2) cp_async_wait<kStages - 3>();
+            if (st == 3) cp_async_wait<0>();
+            __syncthreads();  // every thread's copies of this group are visible
+            const int j0 = st * per_stage, j1 = j0 + per_stage < rn ? j0 + per_stage : rn;
+            for (int jb = j0 + warp; jb < j1; jb += kAttnWarps * kAttnUnroll) {
+                bool live[kAttnUnroll];
+                float sc[kAttnUnroll][GROUP];
+#pragma unroll
+                for (int u = 0; u < kAttnUnroll; u++) {
+                    const int j = jb + u * kAttnWarps;
+                    live[u] = j < j1;
+                    if (live[u]) live[u] = sm_tbl[(r0 + j) / A.page - page0] >= 0;
+                    float kf[VEC];
+                    if (live[u]) {
+                        Row<T, VEC> kr;
+                        kr.load_s(ks + (size_t)j * HD + lane * VEC);
+                        kr.get(kf);
+                    }
+#pragma unroll
+                    for (int g = 0; g < GROUP; g++) {
+                        float d = 0.f;
+                        if (live[u]) {
+#pragma unroll
+                            for (int i = 0; i < VEC; i++) d = fmaf(qv[g][i], kf[i], d);
+                        }
+                        sc[u][g] = d;
+                    }
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+                    for (int u = 0; u < kAttnUnroll; u++)
+#pragma unroll
+                        for (int g = 0; g < GROUP; g++) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
+#pragma unroll
+                for (int g = 0; g < GROUP; g++) {
+                    float m_new = m[g];
+#pragma unroll
+                    for (int u = 0; u < kAttnUnroll; u++) {
+                        sc[u][g] = live[u] ? sc[u][g] * A.scale : -INFINITY;
+                        m_new = fmaxf(m_new, sc[u][g]);
+                    }
+                    if (m_new == -INFINITY) continue;  // nothing live so far
+                    const float corr = expf(m[g] - m_new);  // 0 the first time (m = -inf)
+                    l[g] *= corr;
+#pragma unroll
+                    for (int i = 0; i < VEC; i++) acc[g][i] *= corr;
+#pragma unroll
+                    for (int u = 0; u < kAttnUnroll; u++) sc[u][g] = expf(sc[u][g] - m_new);  // dead rows: exp(-inf) = 0
+                    m[g] = m_new;
+                }
+#pragma unroll
+                for (int u = 0; u < kAttnUnroll; u++) {
+                    if (!live[u]) continue;  // warp-uniform
+                    float vf[VEC];
+                    Row<T, VEC> vr;
+                    vr.load_s(vs + (size_t)(jb + u * kAttnWarps) * HD + lane * VEC);
+                    vr.get(vf);
+#pragma unroll
+                    for (int g = 0; g < GROUP; g++) {
+                        l[g] += sc[u][g];
+#pragma unroll
+                        for (int i = 0; i < VEC; i++) acc[g][i] = fmaf(sc[u][g], vf[i], acc[g][i]);
+                    }
                 }
             }
         }
-#pragma unroll
-        for (int u = 0; u < kAttnUnroll; u++) {
-            if (!live[u]) continue;  // warp-uniform
-            float kf[VEC], vf[VEC];
-            kr[u].get(kf);
-            vr[u].get(vf);
-#pragma unroll
-            for (int g = 0; g < GROUP; g++) {
-                float s = 0.f;
-#pragma unroll
-                for (int i = 0; i < VEC; i++) s = fmaf(qv[g][i], kf[i], s);
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-                s *= A.scale;
-                const float m_new = fmaxf(m[g], s);
-                const float corr = expf(m[g] - m_new), pw = expf(s - m_new);
-                l[g] = fmaf(l[g], corr, pw);
-#pragma unroll
-                for (int i = 0; i < VEC; i++) acc[g][i] = fmaf(acc[g][i], corr, pw * vf[i]);
-                m[g] = m_new;
-            }
-        }
     }
-    if (bad && lane == 0) atomicOr(A.status, LEV_DEV_BAD_INDEX);
-    // ---- merge the warps (fixed order) ----
+    if (bad) atomicOr(A.status, LEV_DEV_BAD_INDEX);
+    // ---- merge the warps (fixed order); the row buffer is free now and holds their sums ----
+    __syncthreads();
+    float* sm_acc = reinterpret_cast<float*>(attn_smem);  // [kAttnWarps][GROUP][HD]
 #pragma unroll
     for (int g = 0; g < GROUP; g++) {
         if (lane == 0) {
@@ -182,7 +273,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(AttnArgs A) {
             sm_l[warp][g] = l[g];
         }
 #pragma unroll
-        for (int i = 0; i < VEC; i++) sm_acc[warp][g][lane * VEC + i] = acc[g][i];
+        for (int i = 0; i < VEC; i++) sm_acc[((size_t)warp * GROUP + g) * HD + lane * VEC + i] = acc[g][i];
     }
     __syncthreads();
     for (int item = threadIdx.x; item < GROUP * HD; item += kAttnWarps * 32) {
@@ -195,7 +286,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(AttnArgs A) {
         for (int w = 0; w < kAttnWarps; w++) {
             const float wgt = sm_m[w][g] == -INFINITY ? 0.f : expf(sm_m[w][g] - mm);
             ll = fmaf(sm_l[w][g], wgt, ll);
-            a = fmaf(sm_acc[w][g][i], wgt, a);
+            a = fmaf(sm_acc[((size_t)w * GROUP + g) * HD + i], wgt, a);
         }
         const int64_t ph = ((int64_t)col * A.q_heads + kvh * GROUP + g) * A.splits + split;
         A.part_acc[ph * HD + i] = a;
@@ -206,7 +297,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32) k_attn_split(AttnArgs A) {
     }
 }
 
-// out[col][head] = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M); one thread per element
+// out[col][head] = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M)
 __global__ void k_attn_merge(AttnArgs A, int hd) {
     __shared__ float wgt[kMaxSplits];
     __shared__ float inv_l;
@@ -220,23 +311,73 @@ __global__ void k_attn_merge(AttnArgs A, int hd) {
         return;
     }
     const int64_t ph = ((int64_t)col * A.q_heads + head) * A.splits;
+    // statistics: thread s holds range s (splits <= kMaxSplits <= blockDim.x); maxima and the sum go
+    // through warp shuffles and one shared array, always in the same order
+    __shared__ float red[kMaxSplits / 32];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float ms = -INFINITY, ls = 0.f;
+    if ((int)threadIdx.x < A.splits) {
+        const float2 v = *reinterpret_cast<const float2*>(A.part_ml + (ph + threadIdx.x) * 2);
+        ms = v.x;
+        ls = v.y;
+    }
+    float mm = ms;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+    if (lane == 0 && warp < kMaxSplits / 32) red[warp] = mm;
+    __syncthreads();
+    mm = red[0];
+#pragma unroll
+    for (int k = 1; k < kMaxSplits / 32; k++) mm = fmaxf(mm, red[k]);
+    const float w = ms == -INFINITY ? 0.f : expf(ms - mm);
+    if ((int)threadIdx.x < kMaxSplits) wgt[threadIdx.x] = w;
+    float ll = ls * w;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
+    __syncthreads();  // everyone has read red[] as maxima
+    if (lane == 0 && warp < kMaxSplits / 32) red[warp] = ll;
+    __syncthreads();
     if (threadIdx.x == 0) {
-        float mm = -INFINITY;
-        for (int s = 0; s < A.splits; s++) mm = fmaxf(mm, A.part_ml[(ph + s) * 2]);
-        float ll = 0.f;
-        for (int s = 0; s < A.splits; s++) {
-            const float ms = A.part_ml[(ph + s) * 2];
-            const float w = ms == -INFINITY ? 0.f : expf(ms - mm);
-            wgt[s] = w;
-            ll = fmaf(A.part_ml[(ph + s) * 2 + 1], w, ll);
-        }
-        inv_l = 1.0f / ll;
+        float tot = 0.f;
+#pragma unroll
+        for (int k = 0; k < kMaxSplits / 32; k++) tot += red[k];
+        inv_l = 1.0f / tot;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < hd; i += blockDim.x) {
+    // weighted sum of the ranges' rows: warp w takes ranges w, w + warps, ...; a lane holds four
+    // consecutive elements, so a row is read in 16-byte loads, eight rows in flight per lane
+    // (blockIdx.z selects which 128 elements of the head this block sums)
+    constexpr int kMergeWarps = 8;
+    __shared__ float4 sum[kMergeWarps][32];
+    const int warps = kMergeWarps;
+    {
+        const int qd = blockIdx.z * 32 + lane;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int sp = warp; sp < A.splits; sp += warps * 8) {
+            float4 t[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int s2 = sp + j * warps;
+                t[j] = s2 < A.splits ? *reinterpret_cast<const float4*>(A.part_acc + (ph + s2) * hd + qd * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int s2 = sp + j * warps;
+                const float wj = s2 < A.splits ? wgt[s2] : 0.f;
+                a.x = fmaf(t[j].x, wj, a.x);
+                a.y = fmaf(t[j].y, wj, a.y);
+                a.z = fmaf(t[j].z, wj, a.z);
+                a.w = fmaf(t[j].w, wj, a.w);
+            }
+        }
+        sum[warp][lane] = a;
+    }
+    __syncthreads();
+    if (threadIdx.x < 128) {
         float a = 0.f;
-        for (int s = 0; s < A.splits; s++) a = fmaf(A.part_acc[(ph + s) * hd + i], wgt[s], a);
-        o[i] = a * inv_l;
+#pragma unroll
+        for (int w2 = 0; w2 < kMergeWarps; w2++) a += reinterpret_cast<const float*>(&sum[w2][0])[threadIdx.x];
+        o[blockIdx.z * 128 + threadIdx.x] = a * inv_l;
     }
 }
 
@@ -294,13 +435,27 @@ AttnArgs base_args(lev_ctx* ctx, const lev_kv_layout* L, const int32_t* table, c
     return A;
 }
 
+template <typename T, int VEC, int GROUP>
+cudaError_t launch_split(dim3 grid, size_t smem, cudaStream_t stream, const AttnArgs& A) {
+    static bool configured[16] = {};  // per device: shared-memory opt-in of this instance
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(k_attn_split<T, VEC, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoundBytes);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(k_attn_split<T, VEC, GROUP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        configured[dev & 15] = true;
+    }
+    return launch_pdl(k_attn_split<T, VEC, GROUP>, grid, dim3(kAttnWarps * 32), smem, stream, A);
+}
+
 template <typename T, int VEC>
-cudaError_t launch_split_g(int group, dim3 grid, cudaStream_t stream, const AttnArgs& A) {
-    const dim3 block(kAttnWarps * 32);
+cudaError_t launch_split_g(int group, dim3 grid, size_t smem, cudaStream_t stream, const AttnArgs& A) {
     switch (group) {
-        case 1: return launch_pdl(k_attn_split<T, VEC, 1>, grid, block, 0, stream, A);
-        case 2: return launch_pdl(k_attn_split<T, VEC, 2>, grid, block, 0, stream, A);
-        case 4: return launch_pdl(k_attn_split<T, VEC, 4>, grid, block, 0, stream, A);
+        case 1: return launch_split<T, VEC, 1>(grid, smem, stream, A);
+        case 2: return launch_split<T, VEC, 2>(grid, smem, stream, A);
+        case 4: return launch_split<T, VEC, 4>(grid, smem, stream, A);
     }
     return cudaErrorInvalidValue;
 }
@@ -335,12 +490,21 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     if (window < 0 || !isfinite(scale)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "window %d, scale %g", window, (double)scale);
     if ((((uintptr_t)k_pool | (uintptr_t)v_pool) & 15) != 0) return lev_fail(ctx, LEV_BAD_ARGUMENT, "cache pools are not 16-byte aligned");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
-    // position ranges per (column, KV head): enough thread blocks for four per SM, at least 32 positions each
+    // position ranges per (column, KV head): one wave of two thread blocks per SM, at least 32
+    // positions per range; a range is walked in rounds of what fits the shared-memory budget
     const int64_t cap = (int64_t)L->max_blocks * L->page, span = window > 0 && window < cap ? window : cap;
-    int64_t splits = (4 * (int64_t)ctx->prop.multiProcessorCount + (int64_t)n_cols * L->kv_heads - 1) / ((int64_t)n_cols * L->kv_heads);
-    if (splits > span / 32) splits = span / 32;
+    const int64_t heads_kv = (int64_t)n_cols * L->kv_heads;
+    int64_t splits = 2 * (int64_t)ctx->prop.multiProcessorCount / heads_kv;
+    if (splits > (span + 31) / 32) splits = (span + 31) / 32;
     if (splits > kMaxSplits) splits = kMaxSplits;
     if (splits < 1) splits = 1;
+    const size_t row_bytes = (size_t)L->head_dim * (L->kv_type == LEV_KV_F16 ? 2 : 4);
+    int64_t round_cap = (int64_t)(kRoundBytes / (2 * row_bytes));
+    if (round_cap > (span + splits - 1) / splits + 1) round_cap = (span + splits - 1) / splits + 1;
+    if (round_cap > (int64_t)(kMaxRoundPages - 1) * L->page) round_cap = (int64_t)(kMaxRoundPages - 1) * L->page;
+    size_t smem = (size_t)round_cap * 2 * row_bytes;
+    const size_t merge_bytes = (size_t)kAttnWarps * group * L->head_dim * sizeof(float);
+    if (smem < merge_bytes) smem = merge_bytes;
     const int hd = L->head_dim;
     void* scr;
     const size_t heads = (size_t)n_cols * q_heads * splits;
@@ -354,16 +518,17 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     A.part_ml = (float*)scr + heads * hd;
     A.q_heads = q_heads;
     A.splits = (int)splits;
+    A.round_cap = (int)round_cap;
     A.window = window;
     A.scale = scale;
     const dim3 grid((unsigned)splits, L->kv_heads, n_cols);
     cudaError_t e;
     if (L->kv_type == LEV_KV_F16)
-        e = hd == 256 ? launch_split_g<__half, 8>(group, grid, ctx->stream, A) : launch_split_g<__half, 4>(group, grid, ctx->stream, A);
+        e = hd == 256 ? launch_split_g<__half, 8>(group, grid, smem, ctx->stream, A) : launch_split_g<__half, 4>(group, grid, smem, ctx->stream, A);
     else
-        e = hd == 256 ? launch_split_g<float, 8>(group, grid, ctx->stream, A) : launch_split_g<float, 4>(group, grid, ctx->stream, A);
+        e = hd == 256 ? launch_split_g<float, 8>(group, grid, smem, ctx->stream, A) : launch_split_g<float, 4>(group, grid, smem, ctx->stream, A);
     LEV_CUDA(ctx, e);
-    LEV_CUDA(ctx, launch_pdl(k_attn_merge, dim3(q_heads, n_cols), dim3(hd), 0, ctx->stream, A, hd));
+    LEV_CUDA(ctx, launch_pdl(k_attn_merge, dim3(q_heads, n_cols, hd / 128), dim3(256), 0, ctx->stream, A, hd));
     ctx->launches += 2;
     return LEV_OK;
 }
