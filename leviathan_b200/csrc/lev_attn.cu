@@ -23,7 +23,7 @@ constexpr int kAttnWarps = 8;
 constexpr int kAttnUnroll = 4;
 constexpr int kMaxSplits = 128;
 constexpr int kMaxRoundPages = 128;      // block-table entries one round may span
-constexpr size_t kRoundBytes = 112 * 1024;  // K and V rows of a round in shared memory: two blocks per SM
+constexpr size_t kRoundBytes = 111 * 1024;  // K and V rows of a round in shared memory: two blocks per SM
 
 struct AttnArgs {
     const void* k_pool;
@@ -107,6 +107,50 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
 }
 
+// Sums each of N (4, 8 or 16) per-lane values over the warp and leaves all N sums in every lane.
+// Halving exchanges: at each step a lane keeps half of its values and adds the partner's copy of
+// them, so N values cost N - 1 + log2(32 / N) shuffles instead of 5 N; the sums then go through N
+// floats of shared memory.  The order of additions is fixed.
+template <int N>
+__device__ __forceinline__ void reduce_scores(float* v, int lane, float* sm) {
+    static_assert(N == 4 || N == 8 || N == 16, "batch size");
+    int width = N;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        if (width > 1) {
+            const int half = width / 2;
+            const bool upper = (lane & o) != 0;  // this lane keeps the upper half of what it holds
+#pragma unroll
+            for (int i = 0; i < N / 2; i++) {
+                if (i < half) {
+                    const float send = upper ? v[i] : v[i + half];
+                    const float keep = upper ? v[i + half] : v[i];
+                    v[i] = keep + __shfl_xor_sync(0xffffffffu, send, o);
+                }
+            }
+            width = half;
+        } else {
+            v[0] += __shfl_xor_sync(0xffffffffu, v[0], o);
+        }
+    }
+    // lane holds value number idx: bit k of idx (from the top) is the lane's choice at step k
+    int idx = 0, w2 = N;
+#pragma unroll
+    for (int o = 16; o >= 1; o >>= 1) {
+        if (w2 > 1) {
+            w2 /= 2;
+            if (lane & o) idx += w2;
+        }
+    }
+    constexpr int kLow = 32 / N;  // lanes that hold the same value
+    __syncwarp();
+    if ((lane & (kLow - 1)) == 0) sm[idx] = v[0];
+    __syncwarp();
+#pragma unroll
+    for (int i = 0; i < N; i++) v[i] = sm[i];
+    __syncwarp();
+}
+
 constexpr int kStages = 4;  // copy groups per round: compute on a quarter starts when it has landed
 
 // One thread block per (position range, KV head, column).  A range is walked in rounds of at most
@@ -115,7 +159,7 @@ constexpr int kStages = 4;  // copy groups per round: compute on a quarter start
 // once, in four groups; as each group lands the warps take its positions (warp w: positions w, w + 8,
 // ...), four at a time: scores first, then one rescale of the running softmax state.  The rows of a
 // round are read from HBM exactly once and never pass through registers on their way in, so the
-// bytes in flight per SM are bounded by shared memory (two blocks of up to 112 KB), not registers.
+// bytes in flight per SM are bounded by shared memory (two blocks of up to 111 KB), not registers.
 template <typename T, int VEC, int GROUP>
 __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     constexpr int HD = VEC * 32;
@@ -124,6 +168,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     extern __shared__ __align__(16) unsigned char attn_smem[];
     __shared__ float sm_m[kAttnWarps][GROUP], sm_l[kAttnWarps][GROUP];
     __shared__ int sm_tbl[kMaxRoundPages];
+    __shared__ __align__(16) float sm_sc[kAttnWarps][16];
     const int split = blockIdx.x, kvh = blockIdx.y, col = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int round_cap = A.round_cap;
@@ -177,15 +222,18 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
 #pragma unroll
         for (int st = 0; st < kStages; st++) {
             const int j0 = st * per_stage, j1 = j0 + per_stage < rn ? j0 + per_stage : rn;
-            const int chunks = (j1 - j0) * 2 * kChunksPerRow;
-            for (int id = threadIdx.x; id < chunks; id += kAttnWarps * 32) {
-                const int j = j0 + id / (2 * kChunksPerRow), rem = id % (2 * kChunksPerRow);
-                const int is_v = rem / kChunksPerRow, c = rem % kChunksPerRow;
+            // a warp requests whole positions: the address is formed once, lanes take 16-byte pieces
+            for (int j = j0 + warp; j < j1; j += kAttnWarps) {
                 const int p = r0 + j, pg = p / A.page, e = sm_tbl[pg - page0];
                 if (e < 0) continue;
-                const int64_t at = ((((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes) + c * 16;
-                unsigned char* dst = reinterpret_cast<unsigned char*>(is_v ? vs : ks) + (size_t)j * kRowBytes + c * 16;
-                cp_async16(smem_u32(dst), (is_v ? vp : kp) + at);
+                const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
+                const unsigned kd = smem_u32(ks) + (unsigned)j * kRowBytes, vd = smem_u32(vs) + (unsigned)j * kRowBytes;
+#pragma unroll
+                for (int c = lane; c < 2 * kChunksPerRow; c += 32) {
+                    const bool is_v = c >= kChunksPerRow;
+                    const int cc = is_v ? c - kChunksPerRow : c;
+                    cp_async16((is_v ? vd : kd) + cc * 16, (is_v ? vp : kp) + at + cc * 16);
+                }
             }
             cp_async_commit();
         }
@@ -222,12 +270,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
                         sc[u][g] = d;
                     }
                 }
-#pragma unroll
-                for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-                    for (int u = 0; u < kAttnUnroll; u++)
-#pragma unroll
-                        for (int g = 0; g < GROUP; g++) sc[u][g] += __shfl_xor_sync(0xffffffffu, sc[u][g], o);
+                reduce_scores<kAttnUnroll * GROUP>(&sc[0][0], lane, &sm_sc[warp][0]);
 #pragma unroll
                 for (int g = 0; g < GROUP; g++) {
                     float m_new = m[g];
@@ -237,12 +280,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
                         m_new = fmaxf(m_new, sc[u][g]);
                     }
                     if (m_new == -INFINITY) continue;  // nothing live so far
-                    const float corr = expf(m[g] - m_new);  // 0 the first time (m = -inf)
+                    const float corr = __expf(m[g] - m_new);  // 0 the first time (m = -inf)
                     l[g] *= corr;
 #pragma unroll
                     for (int i = 0; i < VEC; i++) acc[g][i] *= corr;
 #pragma unroll
-                    for (int u = 0; u < kAttnUnroll; u++) sc[u][g] = expf(sc[u][g] - m_new);  // dead rows: exp(-inf) = 0
+                    for (int u = 0; u < kAttnUnroll; u++) sc[u][g] = __expf(sc[u][g] - m_new);  // dead rows: exp(-inf) = 0
                     m[g] = m_new;
                 }
 #pragma unroll
@@ -500,7 +543,7 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     if (splits < 1) splits = 1;
     const size_t row_bytes = (size_t)L->head_dim * (L->kv_type == LEV_KV_F16 ? 2 : 4);
     int64_t round_cap = (int64_t)(kRoundBytes / (2 * row_bytes));
-    if (round_cap > (span + splits - 1) / splits + 1) round_cap = (span + splits - 1) / splits + 1;
+    if (round_cap > (span + splits - 1) / splits) round_cap = (span + splits - 1) / splits;  // the longest range
     if (round_cap > (int64_t)(kMaxRoundPages - 1) * L->page) round_cap = (int64_t)(kMaxRoundPages - 1) * L->page;
     size_t smem = (size_t)round_cap * 2 * row_bytes;
     const size_t merge_bytes = (size_t)kAttnWarps * group * L->head_dim * sizeof(float);
