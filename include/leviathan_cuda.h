@@ -246,6 +246,11 @@ int lev_rmsnorm_cached(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n,
                        const float* weight, const float* inverse, float* y);
 int lev_gelu_up(lev_ctx* ctx, const float* gate_up, int64_t vectors, int64_t inter, float* out);
 int lev_axpy(lev_ctx* ctx, float alpha, const float* x, const float* r, int64_t n, float* y);
+/* Greedy token choice: out_index[v] = index of the maximum of x[v][0..n) (lowest index on ties, NaN
+ * never wins), out_margin[v] (optional) = best - second best; argmax of
+ * rust/crates/lev-forge/src/ops.rs:478-517.  Device pointers, no host synchronisation. */
+int lev_argmax(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, int32_t* out_index,
+               float* out_margin);
 
 /* The same steps folded into the matvec launch: the prologue is applied while the kernel builds
  * its activation tables (the norm's statistic is reduced by every thread block for itself), the

@@ -261,6 +261,17 @@ class Context:
         self._check(self.lib.lev_axpy(self.handle, alpha, _ptr(x), _ptr(r), x.numel(), _ptr(out)))
         return out
 
+    def argmax(self, x, want_margin: bool = False):
+        """lev_argmax over the rows of x [vectors][n]: int32 indices (and best - second best)."""
+        import torch
+
+        x2 = (x.reshape(1, -1) if x.ndim == 1 else x).contiguous()
+        idx = torch.empty(x2.shape[0], dtype=torch.int32, device=x.device)
+        mar = torch.empty(x2.shape[0], dtype=torch.float32, device=x.device) if want_margin else None
+        self._flags(False, False)
+        self._check(self.lib.lev_argmax(self.handle, _ptr(x2), x2.shape[0], x2.shape[1], _ptr(idx), _ptr(mar)))
+        return (idx, mar) if want_margin else idx
+
     @staticmethod
     def _fusion(prologue, norm_weight, eps, residual, alpha):
         code = {None: L.PROLOGUE_NONE, "rmsnorm": L.PROLOGUE_RMSNORM, "gelu_up": L.PROLOGUE_GELU_UP}[prologue]

@@ -204,15 +204,21 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
         for (int i = 0; i < VEC; i++) acc[g][i] = 0.f;
     }
     bool bad = false;
+    // positions -> pages without a division when the page size is a power of two (the usual case)
+    const int page_shift = (A.page & (A.page - 1)) == 0 ? __ffs(A.page) - 1 : -1;
+    auto page_of = [&](int p) { return page_shift >= 0 ? p >> page_shift : p / A.page; };
+    __shared__ int sm_any_bad;
+    if (threadIdx.x == 0) sm_any_bad = 0;
     for (int r0 = begin; r0 < end; r0 += round_cap) {
         const int rn = end - r0 < round_cap ? end - r0 : round_cap;  // positions of this round
-        const int page0 = r0 / A.page, pages = (r0 + rn - 1) / A.page - page0 + 1;
+        const int page0 = page_of(r0), pages = page_of(r0 + rn - 1) - page0 + 1;
         __syncthreads();  // the previous round's rows and table entries are no longer read
         for (int j = threadIdx.x; j < pages; j += kAttnWarps * 32) {
             int e = trow[page0 + j];
             if (e < 0 || e >= A.blocks) {  // an entry outside the pool is recorded and not followed
                 bad = true;
                 e = -1;
+                sm_any_bad = 1;
             }
             sm_tbl[j] = e;
         }
@@ -224,7 +230,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
             const int j0 = st * per_stage, j1 = j0 + per_stage < rn ? j0 + per_stage : rn;
             // a warp requests whole positions: the address is formed once, lanes take 16-byte pieces
             for (int j = j0 + warp; j < j1; j += kAttnWarps) {
-                const int p = r0 + j, pg = p / A.page, e = sm_tbl[pg - page0];
+                const int p = r0 + j, pg = page_of(p), e = sm_tbl[pg - page0];
                 if (e < 0) continue;
                 const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
                 const unsigned kd = smem_u32(ks) + (unsigned)j * kRowBytes, vd = smem_u32(vs) + (unsigned)j * kRowBytes;
@@ -238,6 +244,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
             cp_async_commit();
         }
         // ---- take the groups as they land ----
+        const bool any_bad = sm_any_bad != 0;  // written before the barrier that published the table
 #pragma unroll
         for (int st = 0; st < kStages; st++) {
             if (st == 0) cp_async_wait<kStages - 1>();
@@ -253,7 +260,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
                 for (int u = 0; u < kAttnUnroll; u++) {
                     const int j = jb + u * kAttnWarps;
                     live[u] = j < j1;
-                    if (live[u]) live[u] = sm_tbl[(r0 + j) / A.page - page0] >= 0;
+                    if (any_bad && live[u]) live[u] = sm_tbl[page_of(r0 + j) - page0] >= 0;
                     float kf[VEC];
                     if (live[u]) {
                         Row<T, VEC> kr;

@@ -441,9 +441,12 @@ extern "C" int lev_gguf_moe_upload(lev_ctx* ctx, const lev_gguf* g, int layer, i
         return LEV_OK;
     };
     const TensorInfo *gu, *dn, *rw;
-    if ((st = find(p + "ffn_gate_up_exps.weight", LEV_GGML_Q4_0, {hidden, 2 * inter, experts}, &gu))) return st;
-    if ((st = find(p + "ffn_down_exps.weight", LEV_GGML_Q4_0, {inter, hidden, experts}, &dn))) return st;
-    if ((st = find(p + "ffn_gate_inp.weight", LEV_GGML_F32, {hidden, experts}, &rw))) return st;
+    st = find(p + "ffn_gate_up_exps.weight", LEV_GGML_Q4_0, {hidden, 2 * inter, experts}, &gu);
+    if (st != LEV_OK) return st;
+    st = find(p + "ffn_down_exps.weight", LEV_GGML_Q4_0, {inter, hidden, experts}, &dn);
+    if (st != LEV_OK) return st;
+    st = find(p + "ffn_gate_inp.weight", LEV_GGML_F32, {hidden, experts}, &rw);
+    if (st != LEV_OK) return st;
     const uint64_t gu_stride = gu->bytes / (uint64_t)experts, dn_stride = dn->bytes / (uint64_t)experts;
     if (top_k) *top_k = (int)used;
     return lev_moe_weights_upload(ctx, reinterpret_cast<const float*>(g->data + rw->start),

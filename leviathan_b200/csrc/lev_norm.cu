@@ -271,3 +271,108 @@ extern "C" int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights
     }
     return LEV_OK;
 }
+
+// ---------------------------------------------------------------------------
+// Greedy token choice: index of the maximum of each row (lowest index on ties) and the gap to the
+// second best, after argmax of rust/crates/lev-forge/src/ops.rs:478-517.  A (best, index, second)
+// triple merges associatively and commutatively, so the row is cut into chunks over many thread
+// blocks and the triples merged in a second small launch; the result does not depend on the cut.
+// ---------------------------------------------------------------------------
+namespace {
+
+struct Top {
+    float best, second;
+    int idx;
+};
+
+__device__ __forceinline__ Top top_merge(const Top& a, const Top& b) {
+    const bool take = b.best > a.best || (b.best == a.best && b.idx < a.idx);
+    Top r;
+    r.best = take ? b.best : a.best;
+    r.idx = take ? b.idx : a.idx;
+    r.second = fmaxf(take ? fmaxf(a.best, b.second) : fmaxf(b.best, a.second), take ? a.second : b.second);
+    return r;
+}
+
+__device__ __forceinline__ Top top_block(Top t, Top* sm) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Top u;
+        u.best = __shfl_xor_sync(0xffffffffu, t.best, o);
+        u.second = __shfl_xor_sync(0xffffffffu, t.second, o);
+        u.idx = __shfl_xor_sync(0xffffffffu, t.idx, o);
+        t = top_merge(t, u);
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    if (lane == 0) sm[warp] = t;
+    __syncthreads();
+    t = sm[0];
+    for (int w = 1; w < warps; w++) t = top_merge(t, sm[w]);
+    return t;
+}
+
+constexpr float kLowest = -3.0e38f;  // the reference's starting value: anything below it never wins
+
+__global__ void __launch_bounds__(256) k_argmax_part(const float* __restrict__ x, int64_t n, int chunks, Top* part) {
+    __shared__ Top sm[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int chunk = blockIdx.x, row = blockIdx.y;
+    const int64_t per = ((n + chunks - 1) / chunks + 3) & ~(int64_t)3, i0 = chunk * per, i1 = i0 + per < n ? i0 + per : n;
+    const float* xr = x + row * n;
+    Top t = {kLowest, kLowest, 0};
+    auto see = [&](float v, int64_t i) {
+        if (v > t.best) {
+            t.second = t.best;
+            t.best = v;
+            t.idx = (int)i;
+        } else if (v > t.second) {
+            t.second = v;
+        }
+    };
+    const bool vec = (((uintptr_t)xr & 15) == 0) && (n % 4 == 0);
+    if (vec) {
+        for (int64_t i = i0 + threadIdx.x * 4; i + 3 < i1; i += 256 * 4) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(xr + i));
+            see(v.x, i), see(v.y, i + 1), see(v.z, i + 2), see(v.w, i + 3);
+        }
+        for (int64_t i = i0 + ((i1 - i0) & ~(int64_t)3) + threadIdx.x; i < i1; i += 256) see(xr[i], i);
+    } else {
+        for (int64_t i = i0 + threadIdx.x; i < i1; i += 256) see(xr[i], i);
+    }
+    t = top_block(t, sm);
+    if (threadIdx.x == 0) part[(int64_t)row * chunks + chunk] = t;
+}
+
+__global__ void __launch_bounds__(256) k_argmax_final(const Top* part, int chunks, int32_t* out, float* margin) {
+    __shared__ Top sm[8];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int row = blockIdx.x;
+    Top t = {kLowest, kLowest, 0};
+    for (int c = threadIdx.x; c < chunks; c += 256) t = top_merge(t, part[(int64_t)row * chunks + c]);
+    t = top_block(t, sm);
+    if (threadIdx.x == 0) {
+        out[row] = t.idx;
+        if (margin) margin[row] = t.best - t.second;
+    }
+}
+
+}  // namespace
+
+extern "C" int lev_argmax(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, int32_t* out_index, float* out_margin) {
+    if (!ctx || !x || !out_index) return LEV_BAD_ARGUMENT;
+    LEV_TRY(check_vectors(ctx, vectors, n));
+    if (vectors > 65535) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "%lld vectors", (long long)vectors);
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    // chunks of at least 4096 values, about four thread blocks per SM over all rows
+    int64_t chunks = (4 * (int64_t)ctx->prop.multiProcessorCount + vectors - 1) / vectors;
+    if (chunks > (n + 4095) / 4096) chunks = (n + 4095) / 4096;
+    if (chunks < 1) chunks = 1;
+    void* scr;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_ATTN, (size_t)vectors * chunks * sizeof(Top), &scr));
+    LEV_CUDA(ctx, launch_pdl(k_argmax_part, dim3((unsigned)chunks, (unsigned)vectors), dim3(256), 0, ctx->stream, x, n, (int)chunks, (Top*)scr));
+    LEV_CUDA(ctx, launch_pdl(k_argmax_final, dim3((unsigned)vectors), dim3(256), 0, ctx->stream, (const Top*)scr, (int)chunks, out_index, out_margin));
+    ctx->launches += 2;
+    return LEV_OK;
+}

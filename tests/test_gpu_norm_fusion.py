@@ -183,3 +183,24 @@ def test_fused_rejections(ctx):
         ctx.matvec_fused(wh, x, None, rows=65)
     assert e.value.name == "badDimensions"
     wh.free()
+
+
+@pytest.mark.parametrize("vectors,n", [(1, 262144), (1, 7), (3, 1000), (32, 4096), (2, 262145), (1, 1)])
+def test_argmax_index_and_margin(ctx, vectors, n):
+    x = Q.normal(vectors + n, (vectors, n), 1.0).astype(np.float32)
+    if n > 8:
+        x[0, 5] = x[0, n - 3] = 9.0      # a tie: the lower index wins, the margin is zero
+        x[-1, n // 2] = np.nan           # NaN never wins
+    idx, margin = ctx.argmax(dev(x), want_margin=True)
+    idx, margin = idx.cpu().numpy(), margin.cpu().numpy()
+    for v in range(vectors):
+        row = np.where(np.isnan(x[v]), -np.inf, x[v])
+        want = int(np.argmax(row))
+        assert idx[v] == want, (v, idx[v], want)
+        if n > 1:
+            second = np.partition(row, -2)[-2]
+            assert margin[v] == np.float32(row[want] - second)
+    if n > 8:
+        assert idx[0] == 5 and margin[0] == 0.0
+    again = ctx.argmax(dev(x))
+    assert np.array_equal(again.cpu().numpy(), idx)
