@@ -136,3 +136,25 @@ def test_indices_outside_the_layout_are_not_followed(ctx):
     with pytest.raises(lev.LevError) as e:
         ctx.attn_decode(bad, good[:1], pos[:1], torch.ones((1, 4, 64), device="cuda"), 0, 1.0)
     assert e.value.name == "unsupported"
+
+
+def test_full_size_context(ctx):
+    """The measured configuration: 16 query heads, 8 KV heads, head dimension 256, 4096 cached positions,
+    fp16 pages of 16 handed out in a shuffled order; full attention and the model's 1024 window."""
+    q_heads, kv_heads, hd, tokens = 16, 8, 256, 4096
+    cache = shuffled(lev.PagedKV(tokens // 16 + 1, 16, kv_heads, hd, slots=1, max_blocks=tokens // 16, dtype="f16"), 11)
+    k, v = fill(ctx, cache, 0, tokens, kv_heads, hd, 77, chunk=512)
+    q = Q.normal(78, (1, q_heads, hd), 1.0).astype(np.float32)
+    slot = torch.zeros(1, dtype=torch.int32, device="cuda")
+    pos = torch.tensor([tokens - 1], dtype=torch.int32, device="cuda")
+    for window in (0, 1024):
+        got = ctx.attn_decode(cache, slot, pos, torch.from_numpy(q).cuda(), window, 1.0).cpu().numpy()[0]
+        ref = O.attention_f64(q[0], k, v, window, 1.0)
+        assert np.all(np.isfinite(got))
+        assert O.max_rel_err(got.reshape(-1), ref.reshape(-1)) < TOL, window
+    # linearity in V: doubling every cached V row doubles the output exactly (powers of two are exact in fp16)
+    base = ctx.attn_decode(cache, slot, pos, torch.from_numpy(q).cuda(), 0, 1.0).cpu().numpy()
+    cache.v.mul_(2.0)
+    twice = ctx.attn_decode(cache, slot, pos, torch.from_numpy(q).cuda(), 0, 1.0).cpu().numpy()
+    assert np.array_equal(twice, 2.0 * base)
+    ctx.synchronize()
