@@ -104,14 +104,15 @@ extern "C" int lev_cuda_init(int device, lev_ctx** out_ctx) {
         return LEV_DEVICE_UNAVAILABLE;
     }
     if (cudaStreamCreateWithFlags(&ctx->own_stream, cudaStreamNonBlocking) != cudaSuccess ||
-        cudaMalloc((void**)&ctx->d_status, sizeof(int)) != cudaSuccess ||
+        // the status word, then the zero-initialised counters of kernels that elect a last thread block
+        cudaMalloc((void**)&ctx->d_status, (LEV_COUNTER_OFFSET + LEV_COUNTERS) * sizeof(int)) != cudaSuccess ||
         cudaMallocHost((void**)&ctx->h_status, sizeof(int)) != cudaSuccess ||
         cudaEventCreate(&ctx->ev0) != cudaSuccess || cudaEventCreate(&ctx->ev1) != cudaSuccess) {
         delete ctx;
         return LEV_DEVICE_UNAVAILABLE;
     }
     ctx->stream = ctx->own_stream;
-    cudaMemsetAsync(ctx->d_status, 0, sizeof(int), ctx->stream);
+    cudaMemsetAsync(ctx->d_status, 0, (LEV_COUNTER_OFFSET + LEV_COUNTERS) * sizeof(int), ctx->stream);
     cudaStreamSynchronize(ctx->stream);
     *out_ctx = ctx;
     return LEV_OK;

@@ -36,6 +36,7 @@ struct AttnArgs {
     float* part_ml;        // [cols][q_heads][splits][2]
     float* part_acc;       // [cols][q_heads][splits][hd]
     int* status;
+    int* counters;  // [cols][kv_heads] ranges finished so far (zero between calls); NULL: merge in a second launch
     int page, kv_heads, q_heads, max_blocks, slots, splits, window;
     int round_cap;  // positions per round of the split kernel
     int64_t blocks;
@@ -151,6 +152,78 @@ __device__ __forceinline__ void reduce_scores(float* v, int lane, float* sm) {
     __syncwarp();
 }
 
+// The last thread block of a (column, KV head) to finish its range merges all ranges of the GROUP
+// query heads: out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M), ranges always in index order, so
+// the result does not depend on which block came last.  Called by every thread of the block after it
+// has written its own partials (the first barrier inside also ends the caller's use of `scratch`);
+// blocks that are not last return at once.
+template <int GROUP>
+__device__ void finish_ranges(const AttnArgs& A, int col, int kvh, int hd, float* scratch) {
+    // scratch: (kMaxSplits + 1) * GROUP floats of shared memory the caller no longer reads
+    __shared__ int sm_last;
+    float(*sm_w)[kMaxSplits] = reinterpret_cast<float(*)[kMaxSplits]>(scratch);
+    float* sm_inv = scratch + GROUP * kMaxSplits;
+    __threadfence();  // this block's partials are visible device-wide before the count
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int prev = atomicAdd(A.counters + (int64_t)col * A.kv_heads + kvh, 1);
+        sm_last = prev == A.splits - 1;
+    }
+    __syncthreads();
+    if (!sm_last) return;
+    __threadfence();  // the other blocks' partials, published before their counts
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    // statistics, one warp per head (in turn): lanes stride the ranges
+    for (int gsel = warp; gsel < GROUP; gsel += (int)(blockDim.x >> 5)) {
+        const int64_t ph = ((int64_t)col * A.q_heads + kvh * GROUP + gsel) * A.splits;
+        float mm = -INFINITY;
+        for (int sp = lane; sp < A.splits; sp += 32) mm = fmaxf(mm, __ldcg(A.part_ml + (ph + sp) * 2));
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        float ll = 0.f;
+        for (int s0 = 0; s0 < A.splits; s0 += 32) {  // fixed order: blocks of 32 ranges, tree inside a block
+            const int sp = s0 + lane;
+            float w = 0.f, lv = 0.f;
+            if (sp < A.splits) {
+                const float ms = __ldcg(A.part_ml + (ph + sp) * 2);
+                w = ms == -INFINITY ? 0.f : __expf(ms - mm);
+                lv = __ldcg(A.part_ml + (ph + sp) * 2 + 1) * w;
+                sm_w[gsel][sp] = w;
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) lv += __shfl_xor_sync(0xffffffffu, lv, o);
+            ll += lv;
+        }
+        if (lane == 0) sm_inv[gsel] = 1.0f / ll;
+    }
+    __syncthreads();
+    // weighted sums: one thread per (head, four consecutive elements), eight rows in flight
+    const int quads = hd >> 2;
+    for (int item = threadIdx.x; item < GROUP * quads; item += blockDim.x) {
+        const int gsel = item / quads, qd = item - gsel * quads;
+        const int64_t ph = ((int64_t)col * A.q_heads + kvh * GROUP + gsel) * A.splits;
+        float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+        for (int s0 = 0; s0 < A.splits; s0 += 8) {
+            float4 tv[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                tv[j] = s0 + j < A.splits ? __ldcg(reinterpret_cast<const float4*>(A.part_acc + (ph + s0 + j) * hd) + qd) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const float wj = s0 + j < A.splits ? sm_w[gsel][s0 + j] : 0.f;
+                a.x = fmaf(tv[j].x, wj, a.x);
+                a.y = fmaf(tv[j].y, wj, a.y);
+                a.z = fmaf(tv[j].z, wj, a.z);
+                a.w = fmaf(tv[j].w, wj, a.w);
+            }
+        }
+        const float inv = sm_inv[gsel];
+        float4* o = reinterpret_cast<float4*>(A.out + ((int64_t)col * A.q_heads + kvh * GROUP + gsel) * hd) + qd;
+        *o = make_float4(a.x * inv, a.y * inv, a.z * inv, a.w * inv);
+    }
+    if (threadIdx.x == 0) A.counters[(int64_t)col * A.kv_heads + kvh] = 0;  // ready for the next call
+}
+
 constexpr int kStages = 4;  // copy groups per round: compute on a quarter starts when it has landed
 
 // One thread block per (position range, KV head, column).  A range is walked in rounds of at most
@@ -165,7 +238,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     constexpr int HD = VEC * 32;
     constexpr int kRowBytes = HD * (int)sizeof(T);
     constexpr int kChunksPerRow = kRowBytes / 16;
-    extern __shared__ __align__(16) unsigned char attn_smem[];
+    extern __shared__ __align__(128) unsigned char attn_smem[];
     __shared__ float sm_m[kAttnWarps][GROUP], sm_l[kAttnWarps][GROUP];
     __shared__ int sm_tbl[kMaxRoundPages];
     __shared__ __align__(16) float sm_sc[kAttnWarps][16];
@@ -179,7 +252,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     int slot, qpos;
     if (!column_ok(A, col, &slot, &qpos)) {
         if (threadIdx.x == 0 && split == 0 && kvh == 0) atomicOr(A.status, LEV_DEV_BAD_INDEX);
-        return;  // the merge kernel writes NaN for this column
+        if (A.counters && split == 0)  // no merge launch follows: this block writes the column's NaN
+            for (int i = threadIdx.x; i < GROUP * (int)HD; i += blockDim.x)
+                A.out[((int64_t)col * A.q_heads + kvh * GROUP) * HD + i] = __int_as_float(0x7FC00000);
+        return;  // (without counters the merge kernel writes NaN for this column)
     }
     const int lo = (A.window != 0 && qpos + 1 > A.window) ? qpos + 1 - A.window : 0;
     const int n = qpos + 1 - lo;
@@ -345,6 +421,265 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
             A.part_ml[ph * 2 + 1] = ll;
         }
     }
+    if (A.counters) finish_ranges<GROUP>(A, col, kvh, HD, reinterpret_cast<float*>(attn_smem));
+}
+
+// ---------------------------------------------------------------------------
+// Tensor-core form of the split kernel for fp16 caches.  Same staging as k_attn_split (rows of the
+// range to shared memory by asynchronous copies, all requested at once), but the rows are consumed
+// 16 positions at a time by mma.sync m16n8k16 from ldmatrix fragments:
+//   scores:  S[16 positions][8 columns] = K tile [16 x headDim] . Q^T, the columns being the GROUP
+//            query heads of this KV head, each as two fp16 terms (q = hi + lo * 2^-11, exact to 2^-22),
+//   output:  O^T[headDim][8 columns] += V^T tile [headDim x 16] . P, P the softmax weights of the
+//            batch in the same two-term form.
+// The 16-byte pieces of a row sit at piece ^ (row & 7), so the eight row addresses of an ldmatrix
+// fall into different banks.  Rows the copies do not fill (the tail of the last batch, rows whose
+// table entry was refused) are zeroed, because 0 * garbage is not 0 in a tensor core.
+// ---------------------------------------------------------------------------
+constexpr int kMmaWarps = 4;
+
+__device__ __forceinline__ void ldsm_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_trans(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+                 : "r"(addr));
+}
+// one of the two fp16 terms of x (x = hi + lo * 2^-11)
+__device__ __forceinline__ __half split_half(float x, int term) {
+    const __half hi = __float2half_rn(x);
+    return term ? __float2half_rn((x - __half2float(hi)) * 2048.0f) : hi;
+}
+__device__ __forceinline__ unsigned pack_half2(__half a, __half b) {
+    const __half2 h = __halves2half2(a, b);
+    return *reinterpret_cast<const unsigned*>(&h);
+}
+
+template <int HD, int GROUP>
+__global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A) {
+    constexpr int kRowBytes = HD * 2, kCpr = kRowBytes / 16, kSteps = HD / 16;
+    constexpr float kLo = 4.8828125e-4f;  // 2^-11
+    extern __shared__ __align__(128) unsigned char attn_smem[];
+    __shared__ float sm_m[kMmaWarps][GROUP], sm_l[kMmaWarps][GROUP];
+    __shared__ int sm_tbl[kMaxRoundPages];
+    __shared__ int sm_any_bad;
+    const int split = blockIdx.x, kvh = blockIdx.y, col = blockIdx.z;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    const int round_cap = A.round_cap;  // a multiple of 16
+    unsigned char* ks = attn_smem;
+    unsigned char* vs = attn_smem + (size_t)round_cap * kRowBytes;
+    const unsigned ks_s = smem_u32(ks), vs_s = smem_u32(vs);
+    pdl_wait();
+    pdl_launch_dependents();
+    int slot, qpos;
+    if (!column_ok(A, col, &slot, &qpos)) {
+        if (threadIdx.x == 0 && split == 0 && kvh == 0) atomicOr(A.status, LEV_DEV_BAD_INDEX);
+        if (A.counters && split == 0)  // no merge launch follows: this block writes the column's NaN
+            for (int i = threadIdx.x; i < GROUP * (int)HD; i += blockDim.x)
+                A.out[((int64_t)col * A.q_heads + kvh * GROUP) * HD + i] = __int_as_float(0x7FC00000);
+        return;  // (without counters the merge kernel writes NaN for this column)
+    }
+    const int lo = (A.window != 0 && qpos + 1 > A.window) ? qpos + 1 - A.window : 0;
+    const int n = qpos + 1 - lo;
+    const int begin = lo + (int)((int64_t)n * split / A.splits), end = lo + (int)((int64_t)n * (split + 1) / A.splits);
+    const int32_t* trow = A.table + (int64_t)slot * A.max_blocks;
+    const unsigned char* kp = static_cast<const unsigned char*>(A.k_pool);
+    const unsigned char* vp = static_cast<const unsigned char*>(A.v_pool);
+
+    // B fragments of Q^T: column g is (head g / 2, term g % 2); this lane holds dims 2t, 2t+1, 2t+8, 2t+9 of each step
+    unsigned qb[kSteps][2];
+    {
+        const int head = g >> 1, term = g & 1;
+        const bool used = head < GROUP;
+        const float* qh = A.q + ((int64_t)col * A.q_heads + kvh * GROUP + (used ? head : 0)) * HD;
+#pragma unroll
+        for (int s = 0; s < kSteps; s++) {
+            const float2 a = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t);
+            const float2 b = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t + 8);
+            qb[s][0] = used ? pack_half2(split_half(a.x, term), split_half(a.y, term)) : 0u;
+            qb[s][1] = used ? pack_half2(split_half(b.x, term), split_half(b.y, term)) : 0u;
+        }
+    }
+    // softmax state of head t (lanes t >= GROUP carry a dummy head over zero columns)
+    float m = -INFINITY, l = 0.f;
+    float acc[kSteps][4];  // O^T tile mt: dims mt*16 + g (and + 8), columns 2t (hi), 2t + 1 (lo)
+#pragma unroll
+    for (int mt = 0; mt < kSteps; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
+    bool bad = false;
+    const int page_shift = (A.page & (A.page - 1)) == 0 ? __ffs(A.page) - 1 : -1;
+    auto page_of = [&](int p) { return page_shift >= 0 ? p >> page_shift : p / A.page; };
+    if (threadIdx.x == 0) sm_any_bad = 0;
+    for (int r0 = begin; r0 < end; r0 += round_cap) {
+        const int rn = end - r0 < round_cap ? end - r0 : round_cap;  // positions of this round
+        const int rn16 = (rn + 15) & ~15;                            // rows the batches read
+        const int page0 = page_of(r0), pages = page_of(r0 + rn - 1) - page0 + 1;
+        __syncthreads();  // the previous round's rows and table entries are no longer read
+        for (int j = threadIdx.x; j < pages; j += kMmaWarps * 32) {
+            int e = trow[page0 + j];
+            if (e < 0 || e >= A.blocks) {  // an entry outside the pool is recorded and not followed
+                bad = true;
+                e = -1;
+                sm_any_bad = 1;
+            }
+            sm_tbl[j] = e;
+        }
+        __syncthreads();
+        // ---- request every row of the round in four copy groups of whole batches ----
+        const int per_stage = ((rn16 / 16 + kStages - 1) / kStages) * 16;
+#pragma unroll
+        for (int st = 0; st < kStages; st++) {
+            const int j0 = st * per_stage, j1 = j0 + per_stage < rn16 ? j0 + per_stage : rn16;
+            for (int j = j0 + warp; j < j1; j += kMmaWarps) {
+                const int p = r0 + j;
+                int e = -1;
+                int pg = 0;
+                if (j < rn) {
+                    pg = page_of(p);
+                    e = sm_tbl[pg - page0];
+                }
+                const unsigned kd = ks_s + (unsigned)j * kRowBytes, vd = vs_s + (unsigned)j * kRowBytes;
+                if (e >= 0) {
+                    const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
+#pragma unroll
+                    for (int c = lane; c < 2 * kCpr; c += 32) {
+                        const bool is_v = c >= kCpr;
+                        const int cc = is_v ? c - kCpr : c;
+                        cp_async16((is_v ? vd : kd) + ((cc ^ (j & 7)) << 4), (is_v ? vp : kp) + at + cc * 16);
+                    }
+                } else {  // a row no copy fills: zeros
+#pragma unroll
+                    for (int c = lane; c < 2 * kCpr; c += 32) {
+                        const bool is_v = c >= kCpr;
+                        const int cc = is_v ? c - kCpr : c;
+                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"((is_v ? vd : kd) + (cc << 4)), "r"(0u) : "memory");
+                    }
+                }
+            }
+            cp_async_commit();
+        }
+        // ---- take the groups as they land; batch b (16 positions) belongs to warp b % 4 ----
+        const bool any_bad = sm_any_bad != 0;
+#pragma unroll
+        for (int st = 0; st < kStages; st++) {
+            if (st == 0) cp_async_wait<kStages - 1>();
+            if (st == 1) cp_async_wait<kStages - 2>();
+            if (st == 2) cp_async_wait<kStages - 3>();
+            if (st == 3) cp_async_wait<0>();
+            __syncthreads();  // every thread's copies (and zero rows) of this group are visible
+            const int b0 = st * per_stage / 16, b1 = (st * per_stage + per_stage < rn16 ? st * per_stage + per_stage : rn16) / 16;
+            for (int b = b0; b < b1; b++) {
+                if ((b & (kMmaWarps - 1)) != warp) continue;
+                const int j0 = b * 16;
+                // ---- scores of the batch ----
+                float c[4] = {0.f, 0.f, 0.f, 0.f};
+                {
+                    float c2[4] = {0.f, 0.f, 0.f, 0.f};  // odd steps: two shorter dependent chains
+                    const int mi = lane >> 3, r = lane & 7;
+                    const int row = j0 + (mi & 1) * 8 + r;
+                    const unsigned base = ks_s + (unsigned)row * kRowBytes;
+#pragma unroll
+                    for (int s = 0; s < kSteps; s++) {
+                        unsigned a0, a1, a2, a3;
+                        ldsm_x4(base + (((2 * s + (mi >> 1)) ^ (row & 7)) << 4), a0, a1, a2, a3);
+                        mma16816((s & 1) ? c2 : c, a0, a1, a2, a3, qb[s][0], qb[s][1]);
+                    }
+#pragma unroll
+                    for (int i = 0; i < 4; i++) c[i] += c2[i];
+                }
+                // this lane: positions j0 + g and j0 + g + 8 of head t
+                bool live0 = j0 + g < rn, live1 = j0 + g + 8 < rn;
+                if (any_bad) {
+                    if (live0) live0 = sm_tbl[page_of(r0 + j0 + g) - page0] >= 0;
+                    if (live1) live1 = sm_tbl[page_of(r0 + j0 + g + 8) - page0] >= 0;
+                }
+                const float s0 = live0 ? fmaf(c[1], kLo, c[0]) * A.scale : -INFINITY;
+                const float s1 = live1 ? fmaf(c[3], kLo, c[2]) * A.scale : -INFINITY;
+                float bm = fmaxf(s0, s1);
+                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
+                const float m_new = fmaxf(m, bm);
+                float corr = 1.f, p0 = 0.f, p1 = 0.f;
+                if (m_new != -INFINITY) {
+                    corr = __expf(m - m_new);  // 0 the first time (m = -inf)
+                    p0 = __expf(s0 - m_new);   // dead rows: exp(-inf) = 0
+                    p1 = __expf(s1 - m_new);
+                }
+                m = m_new;
+                l = fmaf(l, corr, p0 + p1);  // this lane's share; summed over g at the end
+#pragma unroll
+                for (int mt = 0; mt < kSteps; mt++)
+#pragma unroll
+                    for (int i = 0; i < 4; i++) acc[mt][i] *= corr;
+                // ---- P as a B fragment: column g = (head g / 2, term g % 2), positions 2t, 2t+1, 2t+8, 2t+9 ----
+                unsigned pb0, pb1;
+                {
+                    const int head = g >> 1, term = g & 1;
+                    const int src_a = (2 * t) * 4 + (head & 3), src_b = (2 * t + 1) * 4 + (head & 3);
+                    float pa0 = __shfl_sync(0xffffffffu, p0, src_a), pb_0 = __shfl_sync(0xffffffffu, p0, src_b);
+                    float pa1 = __shfl_sync(0xffffffffu, p1, src_a), pb_1 = __shfl_sync(0xffffffffu, p1, src_b);
+                    if (head >= GROUP) pa0 = pb_0 = pa1 = pb_1 = 0.f;
+                    pb0 = pack_half2(split_half(pa0, term), split_half(pb_0, term));
+                    pb1 = pack_half2(split_half(pa1, term), split_half(pb_1, term));
+                }
+                // ---- O^T += V^T tile . P ----
+                {
+                    const int mi = lane >> 3, r = lane & 7;
+                    const int row = j0 + (mi >> 1) * 8 + r;
+                    const unsigned base = vs_s + (unsigned)row * kRowBytes;
+#pragma unroll
+                    for (int mt = 0; mt < kSteps; mt++) {
+                        unsigned a0, a1, a2, a3;
+                        ldsm_x4_trans(base + (((2 * mt + (mi & 1)) ^ (row & 7)) << 4), a0, a1, a2, a3);
+                        mma16816(acc[mt], a0, a1, a2, a3, pb0, pb1);
+                    }
+                }
+            }
+        }
+    }
+    if (bad) atomicOr(A.status, LEV_DEV_BAD_INDEX);
+    // ---- merge the warps (fixed order); the row buffer is free now and holds their sums ----
+    l += __shfl_xor_sync(0xffffffffu, l, 4);
+    l += __shfl_xor_sync(0xffffffffu, l, 8);
+    l += __shfl_xor_sync(0xffffffffu, l, 16);
+    __syncthreads();
+    float* sm_acc = reinterpret_cast<float*>(attn_smem);  // [kMmaWarps][GROUP][HD]
+    if (t < GROUP) {
+        if (g == 0) {
+            sm_m[warp][t] = m;
+            sm_l[warp][t] = l;
+        }
+#pragma unroll
+        for (int mt = 0; mt < kSteps; mt++) {
+            float* o = sm_acc + ((size_t)warp * GROUP + t) * HD + mt * 16 + g;
+            o[0] = fmaf(acc[mt][1], kLo, acc[mt][0]);
+            o[8] = fmaf(acc[mt][3], kLo, acc[mt][2]);
+        }
+    }
+    __syncthreads();
+    for (int item = threadIdx.x; item < GROUP * HD; item += kMmaWarps * 32) {
+        const int gg = item / HD, i = item - gg * HD;
+        float mm = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; w++) mm = fmaxf(mm, sm_m[w][gg]);
+        float ll = 0.f, a = 0.f;
+#pragma unroll
+        for (int w = 0; w < kMmaWarps; w++) {
+            const float wgt = sm_m[w][gg] == -INFINITY ? 0.f : __expf(sm_m[w][gg] - mm);
+            ll = fmaf(sm_l[w][gg], wgt, ll);
+            a = fmaf(sm_acc[((size_t)w * GROUP + gg) * HD + i], wgt, a);
+        }
+        const int64_t ph = ((int64_t)col * A.q_heads + kvh * GROUP + gg) * A.splits + split;
+        A.part_acc[ph * HD + i] = a;
+        if (i == 0) {
+            A.part_ml[ph * 2] = mm;
+            A.part_ml[ph * 2 + 1] = ll;
+        }
+    }
+    if (A.counters) finish_ranges<GROUP>(A, col, kvh, HD, reinterpret_cast<float*>(attn_smem));
 }
 
 // out[col][head] = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M)
@@ -500,6 +835,33 @@ cudaError_t launch_split(dim3 grid, size_t smem, cudaStream_t stream, const Attn
     return launch_pdl(k_attn_split<T, VEC, GROUP>, grid, dim3(kAttnWarps * 32), smem, stream, A);
 }
 
+constexpr size_t kRoundBytesMma = 112 * 1024;  // 112 rows of K and V at headDim 256: whole 16-row batches
+
+template <int HD, int GROUP>
+cudaError_t launch_split_mma(dim3 grid, size_t smem, cudaStream_t stream, const AttnArgs& A) {
+    static bool configured[16] = {};
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (!configured[dev & 15]) {
+        cudaError_t e = cudaFuncSetAttribute(k_attn_split_mma<HD, GROUP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kRoundBytesMma);
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(k_attn_split_mma<HD, GROUP>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+        if (e != cudaSuccess) return e;
+        configured[dev & 15] = true;
+    }
+    return launch_pdl(k_attn_split_mma<HD, GROUP>, grid, dim3(kMmaWarps * 32), smem, stream, A);
+}
+
+template <int HD>
+cudaError_t launch_split_mma_g(int group, dim3 grid, size_t smem, cudaStream_t stream, const AttnArgs& A) {
+    switch (group) {
+        case 1: return launch_split_mma<HD, 1>(grid, smem, stream, A);
+        case 2: return launch_split_mma<HD, 2>(grid, smem, stream, A);
+        case 4: return launch_split_mma<HD, 4>(grid, smem, stream, A);
+    }
+    return cudaErrorInvalidValue;
+}
+
 template <typename T, int VEC>
 cudaError_t launch_split_g(int group, dim3 grid, size_t smem, cudaStream_t stream, const AttnArgs& A) {
     switch (group) {
@@ -552,6 +914,16 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     int64_t round_cap = (int64_t)(kRoundBytes / (2 * row_bytes));
     if (round_cap > (span + splits - 1) / splits) round_cap = (span + splits - 1) / splits;  // the longest range
     if (round_cap > (int64_t)(kMaxRoundPages - 1) * L->page) round_cap = (int64_t)(kMaxRoundPages - 1) * L->page;
+    // fp16 caches go through the tensor-core kernel: rounds are whole batches of 16 positions
+    const bool use_mma = L->kv_type == LEV_KV_F16 && env_int("LEV_ATTN_MMA", 1) != 0;
+    if (use_mma) {
+        round_cap = (int64_t)(kRoundBytesMma / (2 * row_bytes)) & ~(int64_t)15;
+        const int64_t longest = ((span + splits - 1) / splits + 15) & ~(int64_t)15;
+        if (round_cap > longest) round_cap = longest;
+        const int64_t page_cap = ((int64_t)(kMaxRoundPages - 1) * L->page) & ~(int64_t)15;
+        if (round_cap > page_cap) round_cap = page_cap;
+        if (round_cap < 16) return lev_fail(ctx, LEV_UNSUPPORTED, "page size %d too small for the tensor-core attention kernel", L->page);
+    }
     size_t smem = (size_t)round_cap * 2 * row_bytes;
     const size_t merge_bytes = (size_t)kAttnWarps * group * L->head_dim * sizeof(float);
     if (smem < merge_bytes) smem = merge_bytes;
@@ -571,14 +943,21 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     A.round_cap = (int)round_cap;
     A.window = window;
     A.scale = scale;
+    // LEV_ATTN_ONE_LAUNCH=1: the last block of each (column, KV head) merges the ranges itself.  Off by
+    // default: at 4096 positions the serial tail of that block cost more than the second launch
+    // (19.7 us against 17.6 us per call).
+    const bool one_launch = heads_kv <= LEV_COUNTERS && env_int("LEV_ATTN_ONE_LAUNCH", 0) != 0;
+    A.counters = one_launch ? ctx->d_status + LEV_COUNTER_OFFSET : nullptr;
     const dim3 grid((unsigned)splits, L->kv_heads, n_cols);
     cudaError_t e;
-    if (L->kv_type == LEV_KV_F16)
+    if (use_mma)
+        e = hd == 256 ? launch_split_mma_g<256>(group, grid, smem, ctx->stream, A) : launch_split_mma_g<128>(group, grid, smem, ctx->stream, A);
+    else if (L->kv_type == LEV_KV_F16)
         e = hd == 256 ? launch_split_g<__half, 8>(group, grid, smem, ctx->stream, A) : launch_split_g<__half, 4>(group, grid, smem, ctx->stream, A);
     else
         e = hd == 256 ? launch_split_g<float, 8>(group, grid, smem, ctx->stream, A) : launch_split_g<float, 4>(group, grid, smem, ctx->stream, A);
     LEV_CUDA(ctx, e);
-    LEV_CUDA(ctx, launch_pdl(k_attn_merge, dim3(q_heads, n_cols, hd / 128), dim3(256), 0, ctx->stream, A, hd));
-    ctx->launches += 2;
+    if (!one_launch) LEV_CUDA(ctx, launch_pdl(k_attn_merge, dim3(q_heads, n_cols, hd / 128), dim3(256), 0, ctx->stream, A, hd));
+    ctx->launches += one_launch ? 1 : 2;
     return LEV_OK;
 }

@@ -21,6 +21,10 @@
 #define LEV_DEV_TIMEOUT 8
 #define LEV_DEV_BAD_INDEX 16  // a slot, position or block-table entry outside the cache layout
 
+// ints after the status word: counters that kernels leave at zero (ctx->d_status + LEV_COUNTER_OFFSET)
+#define LEV_COUNTER_OFFSET 64
+#define LEV_COUNTERS 65536
+
 struct lev_dist_state;
 
 struct lev_ctx {
