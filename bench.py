@@ -725,8 +725,47 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
             out["decode_layer"] = _decode_layer(ctx, mw, dev, stream, g, peaks)
         except Exception as e:  # a side measurement never takes the headline down
             out["decode_layer"] = {"error": repr(e)}
+        try:
+            out["head_argmax"] = _head_argmax(ctx, dev, stream, g, peaks)
+        except Exception as e:
+            out["head_argmax"] = {"error": repr(e)}
     mw.free()
     return out if rank == 0 else None
+
+
+def _head_argmax(ctx, dev, stream, g, peaks):
+    """The output head of the decode step: final norm folded into a Q6_K [262144 x 2816] matvec, then the
+    greedy token choice on the device (Sources/LeviathanCore/Gemma4.swift:3890-3905; argmax of
+    rust/crates/lev-forge/src/ops.rs:478-517).  One resident head (605 MB, beyond L2 by itself)."""
+    import torch
+
+    from leviathan_b200 import quant as Qd
+
+    V, H = 262144, MOE_HIDDEN
+    parts = []
+    for r0 in range(0, V, 32768):  # quantized in slabs to bound the f32 staging
+        parts.append(Qd.quantize(Q6_K, torch.randn((32768, H), generator=g, device=dev) * 0.02))
+    wh = ctx.upload(torch.cat(parts), Q6_K, V, H)
+    del parts
+    x = torch.randn((1, H), generator=g, device=dev)
+    ones = torch.ones(H, device=dev)
+    logits = torch.empty((1, V), device=dev)
+    tok = torch.empty(1, dtype=torch.int32, device=dev)
+
+    def step(i):
+        ctx.matvec_fused(wh, x, "rmsnorm", ones, 1e-6, out=logits)
+        ctx.lib.lev_argmax(ctx.handle, logits.data_ptr(), 1, V, tok.data_ptr(), None)
+
+    step(0)
+    torch.cuda.synchronize()
+    agree = int(tok.item()) == int(torch.argmax(logits[0]).item())
+    ms = _graph_time(torch, stream, step, 6)
+    ms_mv = _graph_time(torch, stream, lambda i: ctx.matvec_fused(wh, x, "rmsnorm", ones, 1e-6, out=logits), 6)
+    byts = V * (H // 256) * 210 + V * 4 + H * 4
+    wh.free()
+    return {"workload": "rmsnorm -> Q6_K [262144 x 2816] head matvec -> argmax on the device, batch 1", "launches_per_step": 3,
+            "us_per_step": ms * 1e3, "us_matvec": ms_mv * 1e3, "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
+            "hbm_frac": byts / ms / 1e6 / peaks["hbm_gbs"], "argmax_matches_torch": agree}
 
 
 def _decode_layer(ctx, mw, dev, stream, g, peaks):
