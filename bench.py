@@ -735,7 +735,7 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
 
 def _head_argmax(ctx, dev, stream, g, peaks):
     """The output head of the decode step: final norm folded into a Q6_K [262144 x 2816] matvec, then the
-    greedy token choice on the device (Sources/LeviathanCore/Gemma4.swift:3890-3905; argmax of
+    greedy token choice on the device (Sources/LeviathanCore/Gemma4.swift:3623-3643, whose softcap is monotonic and does not move the maximum; argmax of
     rust/crates/lev-forge/src/ops.rs:478-517).  One resident head (605 MB, beyond L2 by itself)."""
     import torch
 
@@ -772,8 +772,9 @@ def _decode_layer(ctx, mw, dev, stream, g, peaks):
     """One synthetic decoder layer at batch 1, every step a C-ABI call on one stream, no host round trip:
     norm -> q, k, v (one launch) -> cache append -> attention over 4096 cached positions -> output
     projection + residual -> shared FFN (norm -> gate, up; gelu-up -> down + residual) -> norm -> routed
-    MoE (128 experts, top-8) -> residual.  Rotary embedding and the per-head q/k norms of the model
-    (Sources/LeviathanCore/Gemma4.swift:3640-3700) are not part of this build and are left out."""
+    MoE (128 experts, top-8) -> residual.  The per-head q / k / v norms and the rotary embedding of a
+    local layer (Sources/LeviathanCore/Gemma4.swift:3662-3687) run as one launch between the projections
+    and the cache append."""
     import torch
 
     import leviathan_b200 as lev_pkg
@@ -794,7 +795,10 @@ def _decode_layer(ctx, mw, dev, stream, g, peaks):
                          wg=up(Qd.GGML_Q4_0, SH, H), wu=up(Qd.GGML_Q4_0, SH, H), wd=up(Qd.GGML_Q4_0, H, SH), cache=c))
     ones = torch.ones(H, device=dev)
     x = torch.randn((1, H), generator=g, device=dev)
-    qb, kb, vb = torch.empty((1, QH * HD), device=dev), torch.empty((1, KVH * HD), device=dev), torch.empty((1, KVH * HD), device=dev)
+    qkv = torch.empty((1, (QH + 2 * KVH) * HD), device=dev)
+    qb, kb, vb = qkv[:, :QH * HD], qkv[:, QH * HD:(QH + KVH) * HD], qkv[:, (QH + KVH) * HD:]
+    head_w = torch.ones(HD, device=dev)
+    inv_freq = (10000.0 ** (-torch.arange(HD // 2, device=dev, dtype=torch.float64) / (HD // 2))).float()
     ao, x1, gub = torch.empty((1, QH, HD), device=dev), torch.empty((1, H), device=dev), torch.empty((1, 2 * SH), device=dev)
     x2, hb, mo, x3 = (torch.empty((1, H), device=dev) for _ in range(4))
     slot = torch.zeros(1, dtype=torch.int32, device=dev)
@@ -804,8 +808,9 @@ def _decode_layer(ctx, mw, dev, stream, g, peaks):
     def layer(i):
         w = sets[i % 3]
         ctx.matvec_multi_fused([w["wq"], w["wk"], w["wv"]], x, "rmsnorm", ones, 1e-6, outs=[qb, kb, vb])
-        ctx.kv_append(w["cache"], slot, pos, kb.view(1, KVH, HD), vb.view(1, KVH, HD))
-        ctx.attn_decode(w["cache"], slot, pos, qb.view(1, QH, HD), 0, 1.0, out=ao)
+        ctx.qkv_norm_rope(qkv, QH, KVH, HD, head_w, head_w, 1e-6, inv_freq, pos)
+        ctx.kv_append(w["cache"], slot, pos, kb.reshape(1, KVH, HD), vb.reshape(1, KVH, HD))
+        ctx.attn_decode(w["cache"], slot, pos, qb.reshape(1, QH, HD), 0, 1.0, out=ao)
         ctx.matvec_fused(w["wo"], ao.view(1, QH * HD), None, residual=x, alpha=1.0, out=x1)
         ctx.matvec_multi_fused([w["wg"], w["wu"]], x1, "rmsnorm", ones, 1e-6, outs=[gub[:, :SH], gub[:, SH:]])
         ctx.matvec_fused(w["wd"], gub, "gelu_up", residual=x1, alpha=1.0, out=x2)
@@ -827,7 +832,7 @@ def _decode_layer(ctx, mw, dev, stream, g, peaks):
             if k_ != "cache":
                 v_.free()
     return {"workload": "hidden 2816: Q4_K q/k/v/o (16 q heads, 8 KV heads, head_dim 256), fp16 paged cache at 4096 positions, "
-                        "Q4_0 shared FFN 2112, 128-expert Q4_0 MoE top-8; batch 1; no rotary / per-head norms",
+                        "Q4_0 shared FFN 2112, 128-expert Q4_0 MoE top-8; batch 1",
             "launches_per_layer": int(launches), "us_per_layer": ms * 1e3, "algorithmic_bytes": total,
             "gbs": total / ms / 1e6, "hbm_frac": total / ms / 1e6 / peaks["hbm_gbs"], "outputs_finite": finite,
             "tokens_per_s_30_layers": 1.0 / (30 * ms * 1e-3)}

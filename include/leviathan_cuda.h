@@ -246,6 +246,15 @@ int lev_rmsnorm_cached(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n,
                        const float* weight, const float* inverse, float* y);
 int lev_gelu_up(lev_ctx* ctx, const float* gate_up, int64_t vectors, int64_t inter, float* out);
 int lev_axpy(lev_ctx* ctx, float alpha, const float* x, const float* r, int64_t n, float* y);
+/* The per-head steps between the q / k / v projections and the cache append of a local layer
+ * (Sources/LeviathanCore/Gemma4.swift:3662-3687) in one launch, in place on rows laid out as
+ * [q_heads | kv_heads (k) | kv_heads (v)] x head_dim: q heads RMSNorm(q_weight) then rotary, k heads
+ * RMSNorm(k_weight) then rotary, v heads the scale-free RMSNorm.  Rotary as g4_rope
+ * (Gemma4.swift:4390-4410): pairs (i, i + head_dim / 2) turned by inv_freq[i] * pos[column]; inv_freq
+ * NULL leaves rotary out.  Weights NULL: no scale.  kv_heads may be 0 (q only). */
+int lev_qkv_norm_rope(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int kv_heads, int head_dim,
+                      const float* q_weight, const float* k_weight, float eps,
+                      const float* inv_freq, const int32_t* pos);
 /* Greedy token choice: out_index[v] = index of the maximum of x[v][0..n) (lowest index on ties, NaN
  * never wins), out_margin[v] (optional) = best - second best; argmax of
  * rust/crates/lev-forge/src/ops.rs:478-517.  Device pointers, no host synchronisation. */

@@ -261,6 +261,14 @@ class Context:
         self._check(self.lib.lev_axpy(self.handle, alpha, _ptr(x), _ptr(r), x.numel(), _ptr(out)))
         return out
 
+    def qkv_norm_rope(self, qkv, q_heads: int, kv_heads: int, head_dim: int, q_weight=None, k_weight=None, eps: float = 1e-6,
+                      inv_freq=None, pos=None):
+        """lev_qkv_norm_rope, in place on qkv [n_cols][(q_heads + 2 * kv_heads) * head_dim]."""
+        self._flags(False, False)
+        self._check(self.lib.lev_qkv_norm_rope(self.handle, _ptr(qkv), qkv.shape[0], q_heads, kv_heads, head_dim, _ptr(q_weight),
+                                               _ptr(k_weight), eps, _ptr(inv_freq), _ptr(pos)))
+        return qkv
+
     def argmax(self, x, want_margin: bool = False):
         """lev_argmax over the rows of x [vectors][n]: int32 indices (and best - second best)."""
         import torch

@@ -376,3 +376,73 @@ extern "C" int lev_argmax(lev_ctx* ctx, const float* x, int64_t vectors, int64_t
     ctx->launches += 2;
     return LEV_OK;
 }
+
+// ---------------------------------------------------------------------------
+// The per-head steps between the q / k / v projections and the cache append of a local layer
+// (Sources/LeviathanCore/Gemma4.swift:3662-3687) in one launch over a [q heads | k heads | v heads]
+// row: q heads RMSNorm(q_weight) then rotary, k heads RMSNorm(k_weight) then rotary, v heads the
+// scale-free RMSNorm.  Rotary as g4_rope (Gemma4.swift:4390-4410): pairs (i, i + headDim/2) turned by
+// the angle inv_freq[i] * position, cos and sin in f32.  One thread block per (head, column), in place.
+// ---------------------------------------------------------------------------
+namespace {
+
+__global__ void __launch_bounds__(128) k_qkv_norm_rope(float* x, int q_heads, int kv_heads, int hd, const float* __restrict__ qw,
+                                                        const float* __restrict__ kw, float eps, const float* __restrict__ inv_freq,
+                                                        const int32_t* __restrict__ pos) {
+    __shared__ float row[512];
+    __shared__ float part[4];
+    pdl_wait();
+    pdl_launch_dependents();
+    const int head = blockIdx.x, col = blockIdx.y, heads = q_heads + 2 * kv_heads;
+    float* xv = x + ((int64_t)col * heads + head) * hd;
+    const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
+    const float* w = is_q ? qw : (is_k ? kw : nullptr);
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hd; i += 128) {
+        const float v = xv[i];
+        row[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf((part[0] + part[1] + part[2] + part[3]) / (float)hd + eps);
+    for (int i = threadIdx.x; i < hd; i += 128) {
+        const float v = row[i] * inv;
+        row[i] = w ? v * w[i] : v;
+    }
+    __syncthreads();
+    const bool turn = (is_q || is_k) && inv_freq != nullptr;
+    const int half = hd >> 1;
+    const float p = turn ? (float)pos[col] : 0.f;
+    for (int i = threadIdx.x; i < half; i += 128) {
+        const float a = row[i], b = row[i + half];
+        if (turn) {
+            float sn, cs;
+            sincosf(inv_freq[i] * p, &sn, &cs);
+            xv[i] = a * cs - b * sn;
+            xv[i + half] = a * sn + b * cs;
+        } else {
+            xv[i] = a;
+            xv[i + half] = b;
+        }
+    }
+}
+
+}  // namespace
+
+extern "C" int lev_qkv_norm_rope(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int kv_heads, int head_dim, const float* q_weight,
+                                 const float* k_weight, float eps, const float* inv_freq, const int32_t* pos) {
+    if (!ctx || !qkv) return LEV_BAD_ARGUMENT;
+    if (n_cols < 1 || n_cols > 65535 || q_heads < 0 || kv_heads < 0 || q_heads + 2 * kv_heads < 1 || q_heads + 2 * kv_heads > 65535)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "%d columns, %d query heads, %d KV heads", n_cols, q_heads, kv_heads);
+    if (head_dim < 2 || head_dim > 512 || head_dim % 2 != 0) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "head dimension %d (even, at most 512)", head_dim);
+    if (!(eps >= 0.f) || !isfinite(eps)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "epsilon %g", (double)eps);
+    if (inv_freq && !pos) return lev_fail(ctx, LEV_BAD_ARGUMENT, "rotary frequencies without positions");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * kv_heads, n_cols), dim3(128), 0, ctx->stream, qkv, q_heads, kv_heads, head_dim,
+                             q_weight, k_weight, eps, inv_freq, pos));
+    ctx->launches++;
+    return LEV_OK;
+}

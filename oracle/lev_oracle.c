@@ -572,6 +572,31 @@ void lev_or_rmsnorm_f64(const float* x, long n, long vectors, const float* w, fl
     }
 }
 
+/* per-head RMSNorm then rotary, in f64: g4_rmsnorm over each head (Gemma4.swift:4247-4268) followed by
+ * g4_rope (Gemma4.swift:4390-4410): pairs (i, i + hd/2) turned by inv_freq[i] * pos.  w NULL: no scale;
+ * inv_freq NULL: no rotary.  x, out [heads][hd]. */
+void lev_or_head_norm_rope_f64(const float* x, long heads, long hd, const float* w, float eps, const float* inv_freq, long pos,
+                               double* out) {
+    long half = hd / 2;
+    for (long h = 0; h < heads; h++) {
+        const float* xv = x + h * hd;
+        double ms = 0.0;
+        for (long i = 0; i < hd; i++) ms += (double)xv[i] * (double)xv[i];
+        double inv = 1.0 / sqrt(ms / (double)hd + (double)eps);
+        double* o = out + h * hd;
+        for (long i = 0; i < hd; i++) o[i] = (double)xv[i] * inv * (w ? (double)w[i] : 1.0);
+        if (!inv_freq) continue;
+        for (long i = 0; i < half; i++) {
+            /* the kernel forms the angle in f32 (inv[i] * float(pos)); so does the oracle, then f64 */
+            float f = inv_freq[i] * (float)pos;
+            double cs = cos((double)f), sn = sin((double)f);
+            double a = o[i], b = o[i + half];
+            o[i] = a * cs - b * sn;
+            o[i + half] = a * sn + b * cs;
+        }
+    }
+}
+
 /* ------------------------------------------------------------------ */
 /* Decode attention                                                    */
 /* ------------------------------------------------------------------ */

@@ -107,6 +107,9 @@ void lev_or_quantize_q8(const float* x, long n, int8_t* q, float* d, float* s);
 /* Gemma4.swift:4247-4268 (serial f32) and lev-model/src/lib.rs:110-114 (f64 statistic) */
 void lev_or_rmsnorm_f32(const float* x, long n, long vectors, const float* w, float eps, float* y);
 void lev_or_rmsnorm_f64(const float* x, long n, long vectors, const float* w, float eps, double* y);
+/* Gemma4.swift:4247-4268 per head, then Gemma4.swift:4390-4410 */
+void lev_or_head_norm_rope_f64(const float* x, long heads, long hd, const float* w, float eps, const float* inv_freq, long pos,
+                               double* out);
 /* AttentionLowering.swift:358-388 */
 int lev_or_attention_f64(const float* q, const float* k, const float* v, long q_heads, long kv_heads, long hd, long tokens,
                          long window, double scale, double* out);

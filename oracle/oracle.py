@@ -84,6 +84,7 @@ def _load(path: str | None = None) -> C.CDLL:
     sig("lev_or_quantize_q8", None, f32p, L, i8p, f32p, f32p)
     sig("lev_or_rmsnorm_f32", None, f32p, L, L, f32p, C.c_float, f32p)
     sig("lev_or_rmsnorm_f64", None, f32p, L, L, f32p, C.c_float, f64p)
+    sig("lev_or_head_norm_rope_f64", None, f32p, L, L, f32p, C.c_float, f32p, L, f64p)
     sig("lev_or_attention_f64", C.c_int, f32p, f32p, f32p, L, L, L, L, L, C.c_double, f64p)
     sig("lev_or_gelu_tanh_up", C.c_double, C.c_double, C.c_double)
     sig("lev_or_gelu_tanh_up_f32", C.c_float, C.c_float, C.c_float)
@@ -334,6 +335,16 @@ def rmsnorm_f64(x, w=None, eps: float = 1e-6) -> np.ndarray:
     y = np.empty(x.shape, np.float64)
     lib().lev_or_rmsnorm_f64(_p(x), x.shape[1], x.shape[0], _p(w), eps, _p(y))
     return y
+
+
+def head_norm_rope_f64(x, w=None, eps: float = 1e-6, inv_freq=None, pos: int = 0) -> np.ndarray:
+    """x [heads][hd]: RMSNorm per head (weight w or none), then rotary by inv_freq[i] * pos (or none)."""
+    x = _f32(x)
+    w = None if w is None else _f32(w)
+    inv_freq = None if inv_freq is None else _f32(inv_freq)
+    out = np.empty(x.shape, np.float64)
+    lib().lev_or_head_norm_rope_f64(_p(x), x.shape[0], x.shape[1], _p(w), eps, _p(inv_freq), pos, _p(out))
+    return out
 
 
 def attention_f64(q, k, v, window: int = 0, scale: float = 1.0) -> np.ndarray:

@@ -204,3 +204,32 @@ def test_argmax_index_and_margin(ctx, vectors, n):
         assert idx[0] == 5 and margin[0] == 0.0
     again = ctx.argmax(dev(x))
     assert np.array_equal(again.cpu().numpy(), idx)
+
+
+@pytest.mark.parametrize("q_heads,kv_heads,hd,cols", [(16, 8, 256, 1), (4, 2, 128, 3), (8, 0, 64, 2), (2, 2, 512, 1)])
+def test_qkv_norm_rope(ctx, q_heads, kv_heads, hd, cols):
+    heads = q_heads + 2 * kv_heads
+    x = Q.normal(31, (cols, heads * hd), 1.0).astype(np.float32)
+    qw = (1.0 + Q.normal(32, (hd,), 0.1)).astype(np.float32)
+    kw = (1.0 + Q.normal(33, (hd,), 0.1)).astype(np.float32)
+    inv = (10000.0 ** (-np.arange(hd // 2, dtype=np.float64) / (hd // 2))).astype(np.float32)
+    pos = np.array([4095, 17, 0][:cols], np.int32)
+    xd = dev(x)
+    ctx.qkv_norm_rope(xd, q_heads, kv_heads, hd, dev(qw), dev(kw), 1e-6, dev(inv), dev(pos))
+    got = xd.cpu().numpy().reshape(cols, heads, hd)
+    xr = x.reshape(cols, heads, hd)
+    for c in range(cols):
+        ref = np.concatenate([
+            O.head_norm_rope_f64(xr[c, :q_heads], qw, 1e-6, inv, int(pos[c])),
+            O.head_norm_rope_f64(xr[c, q_heads:q_heads + kv_heads], kw, 1e-6, inv, int(pos[c])) if kv_heads else np.empty((0, hd)),
+            O.head_norm_rope_f64(xr[c, q_heads + kv_heads:], None, 1e-6, None, 0) if kv_heads else np.empty((0, hd))])
+        assert O.max_rel_err(got[c].reshape(-1), ref.reshape(-1)) < 2e-5, (c,)
+    # without frequencies: the per-head norms alone, equal to lev_rmsnorm over heads as vectors
+    yd = dev(x)
+    ctx.qkv_norm_rope(yd, q_heads, kv_heads, hd, None, None, 1e-6, None, None)
+    plain = ctx.rmsnorm(dev(x.reshape(cols * heads, hd)), None, 1e-6).cpu().numpy()
+    assert O.max_rel_err(yd.cpu().numpy().reshape(-1), plain.astype(np.float64).reshape(-1)) < 1e-6
+    with pytest.raises(lev.LevError):
+        ctx.qkv_norm_rope(xd, q_heads, kv_heads, hd + 1, None, None, 1e-6, None, None)
+    with pytest.raises(lev.LevError):
+        ctx.qkv_norm_rope(xd, q_heads, kv_heads, hd, None, None, 1e-6, dev(inv), None)

@@ -417,3 +417,21 @@ def test_attention_oracle_analytic_cases():
     q3[0, 0], k3[1, 0, 0] = 1.0, np.float32(np.log(3.0))
     v3 = np.stack([np.full((1, hd), 4.0, np.float32), np.full((1, hd), 8.0, np.float32)])
     np.testing.assert_allclose(O.attention_f64(q3, k3, v3)[0], np.full(hd, 7.0), rtol=1e-6)
+
+
+def test_head_norm_rope_oracle_closed_forms():
+    hd = 8
+    x = np.zeros((2, hd), np.float32)
+    x[0, 0] = 2.0           # norm: 2 / sqrt(4/8) = 2 sqrt 2 at element 0
+    x[1, :] = 1.0
+    inv = np.array([np.pi / 2, 0.0, 0.0, 0.0], np.float32)  # pair (0, 4) turns by pos * 90 degrees
+    out = O.head_norm_rope_f64(x, None, 0.0, inv, 1)
+    np.testing.assert_allclose(out[0], [0, 0, 0, 0, 2 * np.sqrt(2), 0, 0, 0], atol=1e-6)   # (a, 0) -> (0, a)
+    np.testing.assert_allclose(out[1], [-1, 1, 1, 1, 1, 1, 1, 1], atol=1e-6)               # (1, 1) -> (-1, 1)
+    np.testing.assert_allclose(O.head_norm_rope_f64(x, None, 0.0, inv, 0)[1], np.ones(hd), atol=1e-12)  # position 0: no turn
+    np.testing.assert_allclose(O.head_norm_rope_f64(x, None, 0.0, None, 7), O.rmsnorm_f64(x, None, 0.0), rtol=1e-12)
+    # a turn keeps each pair's length
+    r = np.random.default_rng(1).standard_normal((3, hd)).astype(np.float32)
+    a = O.head_norm_rope_f64(r, None, 1e-6, np.array([0.3, 0.02, 1.7, 0.9], np.float32), 123)
+    b = O.rmsnorm_f64(r, None, 1e-6)
+    np.testing.assert_allclose(a[:, :4] ** 2 + a[:, 4:] ** 2, b[:, :4] ** 2 + b[:, 4:] ** 2, rtol=1e-9)
