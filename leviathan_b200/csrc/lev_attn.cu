@@ -39,6 +39,7 @@ struct AttnArgs {
     int* counters;  // [cols][kv_heads] ranges finished so far (zero between calls); NULL: merge in a second launch
     int page, kv_heads, q_heads, max_blocks, slots, splits, window;
     int round_cap;  // positions per round of the split kernel
+    int direct;     // one range per (column, KV head): the split kernel writes the output itself
     int64_t blocks;
     float scale;
 };
@@ -252,7 +253,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     int slot, qpos;
     if (!column_ok(A, col, &slot, &qpos)) {
         if (threadIdx.x == 0 && split == 0 && kvh == 0) atomicOr(A.status, LEV_DEV_BAD_INDEX);
-        if (A.counters && split == 0)  // no merge launch follows: this block writes the column's NaN
+        if ((A.counters || A.direct) && split == 0)  // no merge launch follows: this block writes the column's NaN
             for (int i = threadIdx.x; i < GROUP * (int)HD; i += blockDim.x)
                 A.out[((int64_t)col * A.q_heads + kvh * GROUP) * HD + i] = __int_as_float(0x7FC00000);
         return;  // (without counters the merge kernel writes NaN for this column)
@@ -414,6 +415,10 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
             ll = fmaf(sm_l[w][g], wgt, ll);
             a = fmaf(sm_acc[((size_t)w * GROUP + g) * HD + i], wgt, a);
         }
+        if (A.direct) {  // the only range of this head: no partials, no merge
+            A.out[((int64_t)col * A.q_heads + kvh * GROUP + g) * HD + i] = a / ll;
+            continue;
+        }
         const int64_t ph = ((int64_t)col * A.q_heads + kvh * GROUP + g) * A.splits + split;
         A.part_acc[ph * HD + i] = a;
         if (i == 0) {
@@ -475,7 +480,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
     int slot, qpos;
     if (!column_ok(A, col, &slot, &qpos)) {
         if (threadIdx.x == 0 && split == 0 && kvh == 0) atomicOr(A.status, LEV_DEV_BAD_INDEX);
-        if (A.counters && split == 0)  // no merge launch follows: this block writes the column's NaN
+        if ((A.counters || A.direct) && split == 0)  // no merge launch follows: this block writes the column's NaN
             for (int i = threadIdx.x; i < GROUP * (int)HD; i += blockDim.x)
                 A.out[((int64_t)col * A.q_heads + kvh * GROUP) * HD + i] = __int_as_float(0x7FC00000);
         return;  // (without counters the merge kernel writes NaN for this column)
@@ -671,6 +676,10 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
             const float wgt = sm_m[w][gg] == -INFINITY ? 0.f : __expf(sm_m[w][gg] - mm);
             ll = fmaf(sm_l[w][gg], wgt, ll);
             a = fmaf(sm_acc[((size_t)w * GROUP + gg) * HD + i], wgt, a);
+        }
+        if (A.direct) {  // the only range of this head: no partials, no merge
+            A.out[((int64_t)col * A.q_heads + kvh * GROUP + gg) * HD + i] = a / ll;
+            continue;
         }
         const int64_t ph = ((int64_t)col * A.q_heads + kvh * GROUP + gg) * A.splits + split;
         A.part_acc[ph * HD + i] = a;
@@ -946,8 +955,9 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     // LEV_ATTN_ONE_LAUNCH=1: the last block of each (column, KV head) merges the ranges itself.  Off by
     // default: at 4096 positions the serial tail of that block cost more than the second launch
     // (19.7 us against 17.6 us per call).
-    const bool one_launch = heads_kv <= LEV_COUNTERS && env_int("LEV_ATTN_ONE_LAUNCH", 0) != 0;
-    A.counters = one_launch ? ctx->d_status + LEV_COUNTER_OFFSET : nullptr;
+    A.direct = splits == 1;  // short windows, or enough columns to fill the GPU: no partials at all
+    const bool one_launch = A.direct || (heads_kv <= LEV_COUNTERS && env_int("LEV_ATTN_ONE_LAUNCH", 0) != 0);
+    A.counters = one_launch && !A.direct ? ctx->d_status + LEV_COUNTER_OFFSET : nullptr;
     const dim3 grid((unsigned)splits, L->kv_heads, n_cols);
     cudaError_t e;
     if (use_mma)

@@ -158,3 +158,23 @@ def test_full_size_context(ctx):
     twice = ctx.attn_decode(cache, slot, pos, torch.from_numpy(q).cuda(), 0, 1.0).cpu().numpy()
     assert np.array_equal(twice, 2.0 * base)
     ctx.synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_many_columns_take_one_range_each(ctx, dtype):
+    """Enough (column, KV head) pairs to fill the GPU: every pair is one range and writes its output
+    itself (no partials, no merge launch)."""
+    q_heads, kv_heads, hd, tokens, cols = 16, 8, 256, 300, 40
+    cache = shuffled(lev.PagedKV(32, 16, kv_heads, hd, slots=2, max_blocks=24, dtype=dtype), 13)
+    k, v = fill(ctx, cache, 1, tokens, kv_heads, hd, 90)
+    q = Q.normal(91, (cols, q_heads, hd), 1.0).astype(np.float32)
+    positions = [(7 * c + 3) % tokens for c in range(cols)]
+    slot = torch.ones(cols, dtype=torch.int32, device="cuda")
+    pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    l0 = ctx.launch_count()
+    got = ctx.attn_decode(cache, slot, pos, torch.from_numpy(q).cuda(), 0, 1.0).cpu().numpy()
+    assert ctx.launch_count() - l0 == 1
+    for c in (0, 1, 17, cols - 1):
+        ref = O.attention_f64(q[c], k[:positions[c] + 1], v[:positions[c] + 1], 0, 1.0)
+        assert O.max_rel_err(got[c].reshape(-1), ref.reshape(-1)) < TOL, c
+    ctx.synchronize()
