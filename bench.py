@@ -773,8 +773,8 @@ def _decode_layer(ctx, mw, dev, stream, g, peaks):
     norm -> q, k, v (one launch) -> cache append -> attention over 4096 cached positions -> output
     projection + residual -> shared FFN (norm -> gate, up; gelu-up -> down + residual) -> norm -> routed
     MoE (128 experts, top-8) -> residual.  The per-head q / k / v norms and the rotary embedding of a
-    local layer (Sources/LeviathanCore/Gemma4.swift:3662-3687) run as one launch between the projections
-    and the cache append."""
+    local layer and the cache append (Sources/LeviathanCore/Gemma4.swift:3662-3698) run as one launch after
+    the projections."""
     import torch
 
     import leviathan_b200 as lev_pkg
@@ -808,8 +808,7 @@ def _decode_layer(ctx, mw, dev, stream, g, peaks):
     def layer(i):
         w = sets[i % 3]
         ctx.matvec_multi_fused([w["wq"], w["wk"], w["wv"]], x, "rmsnorm", ones, 1e-6, outs=[qb, kb, vb])
-        ctx.qkv_norm_rope(qkv, QH, KVH, HD, head_w, head_w, 1e-6, inv_freq, pos)
-        ctx.kv_append(w["cache"], slot, pos, kb.reshape(1, KVH, HD), vb.reshape(1, KVH, HD))
+        ctx.qkv_norm_rope_append(qkv, QH, w["cache"], slot, pos, head_w, head_w, 1e-6, inv_freq)
         ctx.attn_decode(w["cache"], slot, pos, qb.reshape(1, QH, HD), 0, 1.0, out=ao)
         ctx.matvec_fused(w["wo"], ao.view(1, QH * HD), None, residual=x, alpha=1.0, out=x1)
         ctx.matvec_multi_fused([w["wg"], w["wu"]], x1, "rmsnorm", ones, 1e-6, outs=[gub[:, :SH], gub[:, SH:]])

@@ -314,6 +314,14 @@ int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* layout, const void* k_poo
                     const void* v_pool, const int32_t* block_table, const int32_t* slot,
                     const int32_t* pos, int n_cols, int q_heads, const float* q, int window,
                     float scale, float* out);
+/* lev_qkv_norm_rope whose launch also stores the finished k and v heads at pos[column] of sequence
+ * slot[column] of the cache (lev_kv_append without a launch of its own); kv_heads and head_dim come
+ * from the layout. */
+int lev_qkv_norm_rope_append(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int head_dim,
+                             const float* q_weight, const float* k_weight, float eps,
+                             const float* inv_freq, const int32_t* pos, const lev_kv_layout* layout,
+                             void* k_pool, void* v_pool, const int32_t* block_table,
+                             const int32_t* slot);
 
 /* ---- routed MoE composite ----------------------------------------------
  * Expert weights are the fused gate_up tensor [experts][2*inter][hidden] and

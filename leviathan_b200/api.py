@@ -269,6 +269,15 @@ class Context:
                                                _ptr(k_weight), eps, _ptr(inv_freq), _ptr(pos)))
         return qkv
 
+    def qkv_norm_rope_append(self, qkv, q_heads: int, cache: "PagedKV", slot, pos, q_weight=None, k_weight=None,
+                             eps: float = 1e-6, inv_freq=None):
+        """lev_qkv_norm_rope_append: as qkv_norm_rope, and k / v also go to the cache at (slot, pos)."""
+        self._flags(False, False)
+        self._check(self.lib.lev_qkv_norm_rope_append(self.handle, _ptr(qkv), qkv.shape[0], q_heads, cache.layout.head_dim, _ptr(q_weight),
+                                                      _ptr(k_weight), eps, _ptr(inv_freq), _ptr(pos), C.byref(cache.layout),
+                                                      _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), _ptr(slot)))
+        return qkv
+
     def argmax(self, x, want_margin: bool = False):
         """lev_argmax over the rows of x [vectors][n]: int32 indices (and best - second best)."""
         import torch
@@ -323,9 +332,10 @@ class Context:
     # -- decode attention over a paged KV cache (torch CUDA tensors only) --
     def kv_append(self, cache: "PagedKV", slot, pos, k, v):
         """lev_kv_append: k, v f32 [n_cols][kv_heads][head_dim] to position pos[c] of sequence slot[c]."""
+        k, v = k.contiguous(), v.contiguous()  # held until the launch is queued
         self._flags(False, False)
         self._check(self.lib.lev_kv_append(self.handle, C.byref(cache.layout), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
-                                           _ptr(slot), _ptr(pos), int(slot.numel()), _ptr(k.contiguous()), _ptr(v.contiguous())))
+                                           _ptr(slot), _ptr(pos), int(slot.numel()), _ptr(k), _ptr(v)))
 
     def attn_decode(self, cache: "PagedKV", slot, pos, q, window: int = 0, scale: float = 1.0, out=None):
         """lev_attn_decode: q f32 [n_cols][q_heads][head_dim] -> out of the same shape."""

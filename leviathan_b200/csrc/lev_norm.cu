@@ -6,6 +6,8 @@
 // (Sources/LeviathanCore/Gemma4.swift:4247-4268; the tiled form :4323-4358 reassociates the sum and
 // is gated against an f64 oracle, as this one is), g4_gelu_up (Gemma4.swift:4364-4377) and
 // g4_axpy (Gemma4.swift:4459).
+#include <cuda_fp16.h>
+
 #include "lev_stream.h"
 #include "lev_stream_math.cuh"
 
@@ -386,9 +388,20 @@ extern "C" int lev_argmax(lev_ctx* ctx, const float* x, int64_t vectors, int64_t
 // ---------------------------------------------------------------------------
 namespace {
 
+// where the k and v heads also go when the call appends to a paged cache (k_pool NULL: nowhere)
+struct KvTarget {
+    void* k_pool;
+    void* v_pool;
+    const int32_t* table;
+    const int32_t* slot;
+    int* status;
+    int64_t blocks;
+    int page, max_blocks, slots, f16;
+};
+
 __global__ void __launch_bounds__(128) k_qkv_norm_rope(float* x, int q_heads, int kv_heads, int hd, const float* __restrict__ qw,
                                                         const float* __restrict__ kw, float eps, const float* __restrict__ inv_freq,
-                                                        const int32_t* __restrict__ pos) {
+                                                        const int32_t* __restrict__ pos, KvTarget C) {
     __shared__ float row[512];
     __shared__ float part[4];
     pdl_wait();
@@ -416,16 +429,38 @@ __global__ void __launch_bounds__(128) k_qkv_norm_rope(float* x, int q_heads, in
     const bool turn = (is_q || is_k) && inv_freq != nullptr;
     const int half = hd >> 1;
     const float p = turn ? (float)pos[col] : 0.f;
+    // cache append of the finished k / v head (optional): the row of this column's position
+    int64_t at = -1;
+    if (C.k_pool && !is_q) {
+        const int sl = C.slot[col], ps = pos[col];
+        int64_t blk = -1;
+        if (sl >= 0 && sl < C.slots && ps >= 0 && ps < C.max_blocks * C.page) blk = C.table[(int64_t)sl * C.max_blocks + ps / C.page];
+        if (blk >= 0 && blk < C.blocks) {
+            at = ((blk * C.page + ps % C.page) * kv_heads + (is_k ? head - q_heads : head - q_heads - kv_heads)) * hd;
+        } else if (threadIdx.x == 0) {
+            atomicOr(C.status, LEV_DEV_BAD_INDEX);  // recorded, not followed
+        }
+    }
+    void* pool = is_k ? C.k_pool : C.v_pool;
     for (int i = threadIdx.x; i < half; i += 128) {
-        const float a = row[i], b = row[i + half];
+        float a = row[i], b = row[i + half];
         if (turn) {
             float sn, cs;
             sincosf(inv_freq[i] * p, &sn, &cs);
-            xv[i] = a * cs - b * sn;
-            xv[i + half] = a * sn + b * cs;
-        } else {
-            xv[i] = a;
-            xv[i + half] = b;
+            const float ra = a * cs - b * sn, rb = a * sn + b * cs;
+            a = ra;
+            b = rb;
+        }
+        xv[i] = a;
+        xv[i + half] = b;
+        if (at >= 0) {
+            if (C.f16) {
+                static_cast<__half*>(pool)[at + i] = __float2half_rn(a);
+                static_cast<__half*>(pool)[at + i + half] = __float2half_rn(b);
+            } else {
+                static_cast<float*>(pool)[at + i] = a;
+                static_cast<float*>(pool)[at + i + half] = b;
+            }
         }
     }
 }
@@ -441,8 +476,30 @@ extern "C" int lev_qkv_norm_rope(lev_ctx* ctx, float* qkv, int n_cols, int q_hea
     if (!(eps >= 0.f) || !isfinite(eps)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "epsilon %g", (double)eps);
     if (inv_freq && !pos) return lev_fail(ctx, LEV_BAD_ARGUMENT, "rotary frequencies without positions");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    KvTarget none = {};
     LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * kv_heads, n_cols), dim3(128), 0, ctx->stream, qkv, q_heads, kv_heads, head_dim,
-                             q_weight, k_weight, eps, inv_freq, pos));
+                             q_weight, k_weight, eps, inv_freq, pos, none));
+    ctx->launches++;
+    return LEV_OK;
+}
+
+// The same launch also stores the finished k and v heads at pos[column] of sequence slot[column] of a paged
+// cache (lev_kv_append's job; the append of Sources/LeviathanCore/Gemma4.swift:3688-3698 without a launch).
+extern "C" int lev_qkv_norm_rope_append(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int head_dim, const float* q_weight,
+                                        const float* k_weight, float eps, const float* inv_freq, const int32_t* pos,
+                                        const lev_kv_layout* L, void* k_pool, void* v_pool, const int32_t* block_table, const int32_t* slot) {
+    if (!ctx || !qkv || !pos || !L || !k_pool || !v_pool || !block_table || !slot) return LEV_BAD_ARGUMENT;
+    if (L->kv_type != LEV_KV_F16 && L->kv_type != LEV_KV_F32) return lev_fail(ctx, LEV_BAD_ARGUMENT, "cache element type %d", L->kv_type);
+    if (L->head_dim != head_dim || L->kv_heads < 1 || L->page <= 0 || L->blocks <= 0 || L->max_blocks <= 0 || L->slots <= 0)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "cache layout does not match the heads (head_dim %d / %d)", L->head_dim, head_dim);
+    if (n_cols < 1 || n_cols > 65535 || q_heads < 0 || q_heads + 2 * L->kv_heads > 65535)
+        return lev_fail(ctx, LEV_BAD_DIMENSIONS, "%d columns, %d query heads, %d KV heads", n_cols, q_heads, L->kv_heads);
+    if (head_dim < 2 || head_dim > 512 || head_dim % 2 != 0) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "head dimension %d (even, at most 512)", head_dim);
+    if (!(eps >= 0.f) || !isfinite(eps)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "epsilon %g", (double)eps);
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    KvTarget C = {k_pool, v_pool, block_table, slot, ctx->d_status, L->blocks, L->page, L->max_blocks, L->slots, L->kv_type == LEV_KV_F16};
+    LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * L->kv_heads, n_cols), dim3(128), 0, ctx->stream, qkv, q_heads, L->kv_heads,
+                             head_dim, q_weight, k_weight, eps, inv_freq, pos, C));
     ctx->launches++;
     return LEV_OK;
 }

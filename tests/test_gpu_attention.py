@@ -178,3 +178,34 @@ def test_many_columns_take_one_range_each(ctx, dtype):
         ref = O.attention_f64(q[c], k[:positions[c] + 1], v[:positions[c] + 1], 0, 1.0)
         assert O.max_rel_err(got[c].reshape(-1), ref.reshape(-1)) < TOL, c
     ctx.synchronize()
+
+
+@pytest.mark.parametrize("dtype", ["f16", "f32"])
+def test_norm_rope_append_in_one_launch_equals_the_two_calls(ctx, dtype):
+    q_heads, kv_heads, hd, cols = 16, 8, 256, 3
+    a = lev.PagedKV(16, 16, kv_heads, hd, slots=2, max_blocks=8, dtype=dtype)
+    b = lev.PagedKV(16, 16, kv_heads, hd, slots=2, max_blocks=8, dtype=dtype)
+    positions = [37, 5, 100]
+    for cache in (a, b):
+        for p in positions:
+            cache.ensure(1, p)
+    x = Q.normal(55, (cols, (q_heads + 2 * kv_heads) * hd), 1.0).astype(np.float32)
+    qw = torch.from_numpy((1.0 + Q.normal(56, (hd,), 0.1)).astype(np.float32)).cuda()
+    inv = torch.from_numpy((10000.0 ** (-np.arange(hd // 2, dtype=np.float64) / (hd // 2))).astype(np.float32)).cuda()
+    slot = torch.ones(cols, dtype=torch.int32, device="cuda")
+    pos = torch.tensor(positions, dtype=torch.int32, device="cuda")
+    xa, xb = torch.from_numpy(x).cuda(), torch.from_numpy(x).cuda()
+    ctx.qkv_norm_rope(xa, q_heads, kv_heads, hd, qw, qw, 1e-6, inv, pos)
+    kv = xa.view(cols, q_heads + 2 * kv_heads, hd)
+    ctx.kv_append(a, slot, pos, kv[:, q_heads:q_heads + kv_heads], kv[:, q_heads + kv_heads:])
+    l0 = ctx.launch_count()
+    ctx.qkv_norm_rope_append(xb, q_heads, b, slot, pos, qw, qw, 1e-6, inv)
+    assert ctx.launch_count() - l0 == 1
+    assert torch.equal(xa, xb) and torch.equal(a.k, b.k) and torch.equal(a.v, b.v)
+    assert float(b.k.float().abs().sum()) > 0
+    ctx.synchronize()
+    # a position outside the table is recorded, not followed
+    bad = torch.tensor([37, 5, 4096], dtype=torch.int32, device="cuda")
+    ctx.qkv_norm_rope_append(torch.from_numpy(x).cuda(), q_heads, b, slot, bad, qw, qw, 1e-6, inv)
+    with pytest.raises(lev.LevError):
+        ctx.synchronize()
