@@ -626,6 +626,27 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
                               "launches_per_step": 2, "us_per_step": ms * 1e3, "kv_bytes": kv_bytes, "gbs": kv_bytes / ms / 1e6,
                               "hbm_frac": kv_bytes / ms / 1e6 / peaks["hbm_gbs"]}
         del caches
+        # the same shape at 32 sequences in one call (1.07 GB of K and V): the per-call fixed part amortised
+        NB = 32
+        cb = lev_pkg.PagedKV(NB * (TOK // PAGE) + 1, PAGE, KVH, HD, slots=NB, max_blocks=TOK // PAGE, dtype="f16", device=dev)
+        _random.Random(99).shuffle(cb.free)
+        for s_ in range(NB):
+            cb.ensure(s_, TOK - 1)
+        cb.k.copy_((torch.randn(cb.k.shape, generator=g, device=dev) * 0.25).to(torch.float16))
+        cb.v.copy_(torch.randn(cb.v.shape, generator=g, device=dev).to(torch.float16))
+        qb32 = torch.randn((NB, QH, HD), generator=g, device=dev)
+        ob32 = torch.empty_like(qb32)
+        slot_b = torch.arange(NB, dtype=torch.int32, device=dev)
+        pos_b = torch.full((NB,), TOK - 1, dtype=torch.int32, device=dev)
+        l0 = ctx.launch_count()
+        ctx.attn_decode(cb, slot_b, pos_b, qb32, 0, 1.0, out=ob32)
+        n_launch = ctx.launch_count() - l0
+        ms = _graph_time(torch, stream, lambda i: ctx.attn_decode(cb, slot_b, pos_b, qb32, 0, 1.0, out=ob32), 8)
+        out["attn_decode_b32"] = {"workload": "the same heads and context, 32 sequences in one call (fp16 paged cache, 1.07 GB of K and V)",
+                                  "launches_per_step": int(n_launch), "us_per_step": ms * 1e3, "kv_bytes": NB * kv_bytes,
+                                  "gbs": NB * kv_bytes / ms / 1e6, "hbm_frac": NB * kv_bytes / ms / 1e6 / peaks["hbm_gbs"],
+                                  "tokens_per_s": NB / (ms * 1e-3)}
+        del cb
         for wgu, wd in fused:
             wgu.free()
             wd.free()
