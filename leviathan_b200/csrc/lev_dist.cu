@@ -139,6 +139,10 @@ extern "C" int lev_matvec_rowsplit_allgather(lev_ctx* ctx, const lev_weights* w,
     if (!ctx || !w || !x || !y_full) return LEV_BAD_ARGUMENT;
     if (!ctx->dist) return lev_fail(ctx, LEV_BAD_ARGUMENT, "lev_dist_init has not been called");
     if (flags & LEV_FLAG_HOST_IO) return lev_fail(ctx, LEV_UNSUPPORTED, "multi-GPU entry points take device pointers");
+    // a finite check that fails on one rank only would make that rank leave before the collective its
+    // peers have already queued; every rank must issue the same sequence
+    if (flags & LEV_FLAG_CHECK_FINITE)
+        return lev_fail(ctx, LEV_UNSUPPORTED, "multi-GPU entry points do not take LEV_FLAG_CHECK_FINITE: check the inputs before the call");
     const int world = ctx->dist->world;
     const int64_t rl = w->rows, rt = rl * world;
     if (n_cols < 1 || n_cols > LEV_MAX_COLUMNS) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d", n_cols);
@@ -162,6 +166,10 @@ extern "C" int lev_gemm_prefill_rowsplit_allgather(lev_ctx* ctx, const lev_weigh
     if (!ctx || !w || !x_bf16 || !y_full) return LEV_BAD_ARGUMENT;
     if (!ctx->dist) return lev_fail(ctx, LEV_BAD_ARGUMENT, "lev_dist_init has not been called");
     if (flags & LEV_FLAG_HOST_IO) return lev_fail(ctx, LEV_UNSUPPORTED, "multi-GPU entry points take device pointers");
+    // a finite check that fails on one rank only would make that rank leave before the collective its
+    // peers have already queued; every rank must issue the same sequence
+    if (flags & LEV_FLAG_CHECK_FINITE)
+        return lev_fail(ctx, LEV_UNSUPPORTED, "multi-GPU entry points do not take LEV_FLAG_CHECK_FINITE: check the inputs before the call");
     const int world = ctx->dist->world;
     const int64_t rl = w->rows;
     size_t part = (size_t)tokens * rl * sizeof(float);
@@ -184,6 +192,10 @@ extern "C" int lev_moe_layer_ep(lev_ctx* ctx, const lev_moe_weights* w, const fl
     if (!ctx || !w || !x || !out) return LEV_BAD_ARGUMENT;
     if (!ctx->dist) return lev_fail(ctx, LEV_BAD_ARGUMENT, "lev_dist_init has not been called");
     if (flags & LEV_FLAG_HOST_IO) return lev_fail(ctx, LEV_UNSUPPORTED, "multi-GPU entry points take device pointers");
+    // a finite check that fails on one rank only would make that rank leave before the collective its
+    // peers have already queued; every rank must issue the same sequence
+    if (flags & LEV_FLAG_CHECK_FINITE)
+        return lev_fail(ctx, LEV_UNSUPPORTED, "multi-GPU entry points do not take LEV_FLAG_CHECK_FINITE: check the inputs before the call");
     if (tokens <= 0 || tokens > (1 << 20)) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "tokens %lld", (long long)tokens);
     if (top_k <= 0 || top_k > LEV_MAX_TOP_K || top_k > w->experts)
         return lev_fail(ctx, LEV_BAD_DIMENSIONS, "topK %d with %d experts", top_k, w->experts);

@@ -246,6 +246,14 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
                 bi = oi;
             }
         }
+        // Non-finite scores make every probability NaN: no comparison above succeeds and bi keeps its
+        // sentinel.  Record it and select a valid index (the rank) with weight zero rather than
+        // follow the sentinel into shared memory.
+        if (bi >= experts) {
+            if (lane == 0) atomicOr(G.status, LEV_DEV_NONFINITE_OUTPUT);
+            bi = k < experts ? k : 0;
+            best = 0.0;
+        }
         prob_sum += best;  // rank order, like topIdx.reduce
         if (lane == (k & 31)) {
             if (k < 32) {
@@ -262,12 +270,12 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     if (lane < top_k) {
         float sc = expert_scale ? expert_scale[isel] : 1.0f;
         idx[tok * top_k + lane] = isel;
-        weights[tok * top_k + lane] = __fmul_rn((float)(psel / prob_sum), sc);
+        weights[tok * top_k + lane] = prob_sum > 0.0 ? __fmul_rn((float)(psel / prob_sum), sc) : 0.0f;
     }
     if (lane + 32 < top_k) {
         float sc = expert_scale ? expert_scale[isel2] : 1.0f;
         idx[tok * top_k + lane + 32] = isel2;
-        weights[tok * top_k + lane + 32] = __fmul_rn((float)(psel2 / prob_sum), sc);
+        weights[tok * top_k + lane + 32] = prob_sum > 0.0 ? __fmul_rn((float)(psel2 / prob_sum), sc) : 0.0f;
     }
     }
     if (!fuse_group) return;
@@ -638,6 +646,8 @@ static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x
     size_t smem = (size_t)4 * w->experts * sizeof(double);
     GroupArgs G = {};
     if (fuse) G = *fuse;
+    G.status = ctx->d_status;  // the selection loop reports non-finite scores there
+    static_assert((size_t)4 * LEV_MAX_EXPERTS * sizeof(double) <= 48 * 1024, "k_router_topk runs without a shared-memory opt-in");
     LEV_CUDA(ctx, launch_pdl(k_router_topk, dim3((unsigned)((tokens + 3) / 4)), dim3(128), smem, ctx->stream, (const float*)scores,
                              tokens, (int)w->experts, top_k, (const float*)nullptr, idx, weights, G, fuse ? 1 : 0));
     ctx->launches++;

@@ -22,7 +22,9 @@
 //   - the first call on a device looks the array's device address up (the
 //     array's name is only a host-side handle, not a pointer a kernel could
 //     use) and opts the kernel in to its shared-memory size; make that first
-//     call before starting any stream capture.
+//     call before starting any stream capture, and from one thread at a time
+//     (two first calls at once would both do the look-up; they store the same
+//     address, but the table is not synchronised).
 #include "lev_internal.h"
 #include "lev_stream.h"
 
@@ -64,9 +66,25 @@ extern "C" int lev_matvec_static_scratch(lev_ctx* ctx, const lev_weights* w, int
     if (y_capacity < (int64_t)n_cols * rows)
         return lev_fail(ctx, LEV_BAD_DIMENSIONS, "output capacity %lld below %lld", (long long)y_capacity,
                         (long long)((int64_t)n_cols * rows));
+    {   // aliasing x and y is rejected like in lev_matvec
+        const char *xa = (const char*)x, *ya = (const char*)y;
+        const size_t xb = (size_t)x_count * sizeof(float), yb = (size_t)n_cols * (size_t)rows * sizeof(float);
+        if (xa < ya + yb && ya < xa + xb) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and y overlap");
+    }
     if (!lev_stream_supported(w, row0, rows, n_cols))
         return lev_fail(ctx, LEV_UNSUPPORTED, "the stream schedule does not serve this tensor or row window");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    {   // evidence of this call (the kernels fill in grid and block)
+        lev_evidence* e = &ctx->ev;
+        snprintf(e->device_name, sizeof e->device_name, "%.127s", ctx->prop.name);
+        snprintf(e->kernel_name, sizeof e->kernel_name, "lev_matvec_static_scratch");
+        e->out_dim = rows;
+        e->in_dim = w->cols;
+        e->n_cols = n_cols;
+        e->weight_bytes = (size_t)rows * (size_t)w->blocks_per_row * (size_t)lev_block_bytes(w->type);
+        e->gpu_us = 0.f;
+        e->status = LEV_OK;
+    }
     // the one-launch kernel builds its tables in shared memory and needs no work buffers at all
     if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) return lev_dense_run(ctx, w, row0, rows, x, n_cols, y);
 

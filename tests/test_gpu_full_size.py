@@ -64,6 +64,17 @@ def test_full_size_matvec_properties(ctx, name, rows, cols):
     # n = 2 columns give each column's own result
     yy = ctx.matvec(wh, torch.cat([x1, x2]), schedule=lev.SCHEDULE_STREAM).cpu().numpy()
     assert _rel(yy[0], ys.astype(np.float64)) < 1e-5 and _rel(yy[1], y2.astype(np.float64)) < 1e-5
+    # n = 4 and n = 8 columns: sampled rows of every column against the f64 oracle, and the first two
+    # columns against their single-column results over every row
+    x8 = torch.cat([x1, x2, torch.randn((6, cols), generator=g, device="cuda")])
+    x8h = x8.cpu().numpy()
+    for n in (4, 8):
+        yn = ctx.matvec(wh, x8[:n].contiguous(), schedule=lev.SCHEDULE_STREAM).cpu().numpy()
+        assert _rel(yn[0], ys.astype(np.float64)) < 1e-5 and _rel(yn[1], y2.astype(np.float64)) < 1e-5
+        for r0 in (16, rows // 2 + 5, rows - 3):
+            for c in range(n):
+                ref = O.matvec_f64(t, wb[r0 * bpr:(r0 + 3) * bpr], 3, cols, x8h[c])
+                assert _rel(yn[c, r0:r0 + 3], ref) < H.REPORT_TOL, (name, n, c, r0)
     wh.free()
 
 
