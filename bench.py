@@ -7,6 +7,8 @@ batch 1 -- gate and up [12288 x 4096] in Q4_K and down [4096 x 12288] in Q6_K,
 weights N(0, 0.02) before quantization, activations N(0, 1), f32 -- one "step"
 being the three matvecs over ONE of several distinct resident weight
 instances, so that every step streams its weights from HBM rather than L2.
+The three products of a step are submitted as one list (lev_matvec_chain):
+one launch of the persistent kernel.
 
 Metric: algorithmic bytes (GGUF block bytes of the three tensors plus the f32
 vectors) per second.  `value` is timed with the activations already on the
@@ -40,10 +42,9 @@ DOWN_BYTES = HIDDEN * (FFN // 256) * 210      # 41,287,680
 VEC_BYTES = 4 * (HIDDEN + 2 * FFN + FFN + HIDDEN)  # x, gate out, up out, down in, down out
 STEP_BYTES = 2 * GATE_BYTES + DOWN_BYTES + VEC_BYTES  # 98,091,008
 SEED = 0x4C455649
-# dram__bytes_read + dram__bytes_write of one Q4_K 12288x4096 stream launch, from the ncu
-# capture summarised in profiles/k_dense_q4k_q6k_full_capture.txt
-Q4K_DRAM_TRAFFIC = 28_353_280
-Q6K_DRAM_TRAFFIC = 41_372_672
+# dram__bytes_read + dram__bytes_write of one launch of the persistent kernel over the three tensors of a
+# step, from the ncu capture summarised in profiles/k_chain_ffn_set_full_capture.txt (None: not captured)
+CHAIN_DRAM_TRAFFIC = None
 
 
 def _peaks():
@@ -113,17 +114,27 @@ def make_inputs():
     return x, a
 
 
+def tensor_seed(instance: int, j: int) -> int:
+    """Seed of tensor j (0 gate, 1 up, 2 down) of weight instance `instance`: 0x4C455649 ^ tensor index."""
+    return SEED ^ (16 * instance + j)
+
+
 def make_instance(i: int, device: str):
-    """Quantized gate/up/down of weight instance i (uint8 tensors on device)."""
+    """Quantized gate/up/down of weight instance i (uint8 tensors on `device`): N(0, 0.02) from
+    SplitMix64(tensor_seed) by Box-Muller, the same generator on both arms (numpy on the host,
+    the identical integer arithmetic in torch on the GPU)."""
     import torch
 
     from leviathan_b200 import quant as Q
 
-    g = torch.Generator(device=device).manual_seed(SEED + 16 * i)
     out = []
-    for t, rows, cols in ((Q4_K, FFN, HIDDEN), (Q4_K, FFN, HIDDEN), (Q6_K, HIDDEN, FFN)):
-        w = torch.randn((rows, cols), generator=g, device=device, dtype=torch.float32) * 0.02
+    for j, (t, rows, cols) in enumerate(((Q4_K, FFN, HIDDEN), (Q4_K, FFN, HIDDEN), (Q6_K, HIDDEN, FFN))):
+        if device == "cpu":
+            w = torch.from_numpy(Q.normal(tensor_seed(i, j), (rows, cols), 0.02))
+        else:
+            w = Q.normal_torch(tensor_seed(i, j), (rows, cols), 0.02, device=device)
         out.append(Q.quantize(t, w))
+        del w
     return out
 
 
@@ -131,7 +142,7 @@ def make_instance(i: int, device: str):
 # CPU arm: the oracle's threaded matvec (the reference's own CPU loops)
 # ---------------------------------------------------------------------------
 
-def cpu_step_timer(threads: int | None, steps: int, warmup: int):
+def cpu_step_timer(threads: int | None, steps: int, warmup: int, tensors=None):
     from oracle import oracle as O
 
     native = None
@@ -140,7 +151,7 @@ def cpu_step_timer(threads: int | None, steps: int, warmup: int):
     except Exception:
         native = None
     threads = threads or O.hardware_threads()
-    gate, up, down = [t.numpy() for t in make_instance(0, "cpu")]
+    gate, up, down = tensors if tensors is not None else [t.numpy() for t in make_instance(0, "cpu")]
     x, a = make_inputs()
 
     def step():
@@ -220,9 +231,7 @@ def run_gpu(args):
 
     def step(i):
         wg, wu, wd = inst[i % n_inst]
-        ctx.matvec(wg, x, out=yg.view(1, -1))
-        ctx.matvec(wu, x, out=yu.view(1, -1))
-        ctx.matvec(wd, a, out=yd.view(1, -1))
+        ctx.matvec_chain([dict(w=wg, x=x, out=yg), dict(w=wu, x=x, out=yu), dict(w=wd, x=a, out=yd)])
 
     def barrier():
         if world > 1:
@@ -236,6 +245,7 @@ def run_gpu(args):
     l0 = ctx.launch_count()
     step(0)
     launches_per_step = ctx.launch_count() - l0
+    chain_kernel = ctx.last_evidence()["kernel_name"]
 
     # K steps as one CUDA graph on a side stream; timed with events on that stream
     s = torch.cuda.Stream(device=dev)
@@ -301,11 +311,13 @@ def run_gpu(args):
     yup = torch.empty(1, FFN).pin_memory()
     ydp = torch.empty(1, HIDDEN).pin_memory()
 
+    xpn, apn, ygn, yun, ydn = xp.numpy(), ap.numpy(), ygp.numpy().reshape(-1), yup.numpy().reshape(-1), ydp.numpy().reshape(-1)
+
     def e2e_step(i):
+        # the same list through the host-buffer form of the C ABI: inputs copied in, one launch,
+        # outputs copied back, one synchronisation
         wg, wu, wd = inst[i % n_inst]
-        ctx.matvec(wg, xp.numpy(), out=ygp.numpy())
-        ctx.matvec(wu, xp.numpy(), out=yup.numpy())
-        ctx.matvec(wd, ap.numpy(), out=ydp.numpy())
+        ctx.matvec_chain([dict(w=wg, x=xpn, out=ygn), dict(w=wu, x=xpn, out=yun), dict(w=wd, x=apn, out=ydn)])
 
     for i in range(3):
         e2e_step(i)
@@ -327,6 +339,11 @@ def run_gpu(args):
         from oracle import oracle as O
 
         g_bytes = make_instance(0, dev)
+        # the host form of the generator gives the same bytes as the device form the GPU arm uses
+        from leviathan_b200 import quant as Q
+
+        head = Q.quantize(Q4_K, torch.from_numpy(Q.normal(tensor_seed(0, 0), (64, HIDDEN), 0.02)))
+        generator_match = bool(torch.equal(head, g_bytes[0][: head.numel()].cpu()))
         rows = 64
         sub = g_bytes[0][: rows * (HIDDEN // 256) * 144].cpu().numpy()
         ref = O.q4_k_matvec_f64(sub, rows, HIDDEN, x_h)
@@ -334,7 +351,8 @@ def run_gpu(args):
         torch.cuda.synchronize()
         subd = g_bytes[2][: rows * (FFN // 256) * 210].cpu().numpy()
         refd = O.q6_k_matvec_f64(subd, rows, FFN, a_h)
-        parity = {"q4_k_max_rel_err_64_rows": O.max_rel_err(yg[:rows].cpu().numpy(), ref),
+        parity = {"host_and_device_generators_give_the_same_bytes": generator_match,
+                  "q4_k_max_rel_err_64_rows": O.max_rel_err(yg[:rows].cpu().numpy(), ref),
                   "q6_k_max_rel_err_64_rows": O.max_rel_err(yd[:rows].cpu().numpy(), refd)}
 
     if rank == 0:
@@ -342,7 +360,7 @@ def run_gpu(args):
         value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
         q4k_bytes = GATE_BYTES + 4 * (HIDDEN + FFN)
         q6k_bytes = DOWN_BYTES + 4 * (HIDDEN + FFN)
-        ach = q4k_bytes / (k_q4k_ms * 1e-3) / 1e9
+        ach = STEP_BYTES / (ms_per_step * 1e-3) / 1e9
         line = {
             "metric": "Q4/Q6 matvec HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
@@ -352,21 +370,29 @@ def run_gpu(args):
                        "columns": 1, "bytes_per_step": STEP_BYTES, "weight_instances_per_gpu": n_inst,
                        "l2": f"inputs larger than L2: {n_inst} distinct instances = {n_inst * STEP_BYTES / 1e6:.0f} MB "
                              "cycled, one per step", "timing": f"median of {reps} replays of a {args.steps}-step CUDA graph",
+                       "generator": "SplitMix64 + Box-Muller, seed 0x4C455649 ^ (16 * instance + tensor); x seed ^ 0x100, "
+                                    "down input seed ^ 0x101",
                        "sharding": "independent FFN instances per rank, no collective"},
-            "roofline": {"bound": "hbm", "kernel": ctx.last_evidence()["kernel_name"] + ":q4_k",
+            # the dominant kernel is the one launch of a step: the persistent kernel over the three tensors
+            "roofline": {"bound": "hbm", "kernel": chain_kernel + ":k_chain(gate, up, down)",
                          "achieved": ach, "peak": peaks["hbm_gbs"], "peak_source": peak_kind, "unit": "GB/s",
-                         "frac": ach / peaks["hbm_gbs"], "traffic": Q4K_DRAM_TRAFFIC, "us_per_launch": k_q4k_ms * 1e3,
-                         "algorithmic_bytes_per_launch": q4k_bytes,
-                         "q6_k": {"achieved": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9, "us_per_launch": k_q6k_ms * 1e3,
-                                  "frac": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
-                                  "algorithmic_bytes_per_launch": q6k_bytes, "traffic": Q6K_DRAM_TRAFFIC}},
+                         "frac": ach / peaks["hbm_gbs"], "traffic": CHAIN_DRAM_TRAFFIC, "us_per_launch": ms_per_step * 1e3,
+                         "algorithmic_bytes_per_launch": STEP_BYTES,
+                         "single_tensor_launches": {
+                             "q4_k": {"achieved": q4k_bytes / (k_q4k_ms * 1e-3) / 1e9, "us_per_launch": k_q4k_ms * 1e3,
+                                      "frac": q4k_bytes / (k_q4k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                      "algorithmic_bytes_per_launch": q4k_bytes},
+                             "q6_k": {"achieved": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9, "us_per_launch": k_q6k_ms * 1e3,
+                                      "frac": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+                                      "algorithmic_bytes_per_launch": q6k_bytes}}},
             "e2e": {"value": world * STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * (HIDDEN + HIDDEN + FFN), "d2h_bytes_per_step": 4 * (FFN + FFN + HIDDEN)},
             "gpu_launches": launches_per_step * args.steps * reps,
             "clocks": clocks, "parity": parity,
         }
         if not args.no_cpu and world == 1:
-            times, threads, build = cpu_step_timer(None, 11, 3)
+            # instance 0 as the GPU arm generated it (the same bytes as the host generator gives)
+            times, threads, build = cpu_step_timer(None, 11, 3, [t.cpu().numpy() for t in make_instance(0, dev)])
             cms = statistics.median(times)
             line["cpu_baseline"] = {"value": STEP_BYTES / cms / 1e9, "unit": "GB/s", "cores": threads, "kind": "port",
                                     "sample": f"11 full steps (median) of the same three matvecs, oracle C port "
@@ -453,14 +479,17 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
                                "tensor_frac": flop / ms / 1e9 / peaks["bf16_tflops_sustained"]}
     if world == 1:
         # cfg1: one Q4_0 [4096 x 4096] matvec, 64 distinct instances (604 MB) cycled in one graph
-        gq = torch.Generator(device=dev).manual_seed(SEED ^ 0x200)
         c1 = []
         for i in range(64):
-            wf = torch.randn((4096, 4096), generator=gq, device=dev) * 0.02
+            wf = Q.normal_torch(SEED ^ (0x2000 + i), (4096, 4096), 0.02, device=dev)
             c1.append(ctx.upload(Q.quantize(2, wf), 2, 4096, 4096))
         del wf
-        x1 = torch.randn((1, 4096), generator=gq, device=dev)
+        x1 = torch.from_numpy(Q.normal(SEED ^ 0x200, (1, 4096), 1.0)).to(dev)
         y1 = torch.empty((1, 4096), device=dev)
+        y64 = torch.empty((64, 4096), device=dev)
+        # the same 64 products submitted as four lists of sixteen (one launch each)
+        ms16 = _graph_time(torch, stream, lambda i: ctx.matvec_chain(
+            [dict(w=c1[(16 * i + j) % 64], x=x1[0], out=y64[(16 * i + j) % 64]) for j in range(16)]), 4, reps=11) / 16
         g1 = torch.cuda.CUDAGraph()
         with torch.cuda.stream(stream):
             for i in range(3):
@@ -493,7 +522,9 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         med, mn = statistics.median(ts), min(ts)
         out["cfg1_q4_0_matvec"] = {"workload": "Q4_0 [4096x4096], batch 1, 64 instances cycled", "us_median": med * 1e3,
                                    "us_min": mn * 1e3, "gbs": b1 / med / 1e6, "hbm_frac": b1 / med / 1e6 / peaks["hbm_gbs"],
-                                   "single_launch_us": statistics.median(singles) * 1e3}
+                                   "single_launch_us": statistics.median(singles) * 1e3,
+                                   "us_in_lists_of_16": ms16 * 1e3, "gbs_in_lists_of_16": b1 / ms16 / 1e6,
+                                   "hbm_frac_in_lists_of_16": b1 / ms16 / 1e6 / peaks["hbm_gbs"]}
         for w1 in c1:
             w1.free()
         # the same FFN set with gate and up row-concatenated into one resident tensor: two launches

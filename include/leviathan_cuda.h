@@ -284,6 +284,30 @@ int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights* const* w,
                            int64_t x_count, int n_cols, const lev_fusion* fusion, float* const* y,
                            const int64_t* y_capacity);
 
+/* A recorded list of one-column products in one submission: the decode loop of the Rust runtime
+ * records its matvec steps and runs them together (Builder::matvec,
+ * rust/crates/lev-model/src/gpu.rs:334-370; Program::run, rust/crates/lev-vulkan/src/engine.rs:87-153),
+ * and the Swift layer loop issues matvec(gate), matvec(up), geluUp, matvec(down), axpy back to back
+ * (Sources/LeviathanCore/Gemma4.swift:3741-3753).  Ops take effect as if executed in order.  An op
+ * whose input (or residual) is written by an earlier op of the list, or whose output an earlier op
+ * reads, starts only after every earlier op has finished; the library detects this from the
+ * pointers, `depends` forces it.  Where the persistent kernel serves the list it is ONE launch and
+ * the weight stream does not pause between ops; otherwise each op runs as lev_matvec_fused.
+ * Device pointers; x has w->cols floats (2 * cols with LEV_PROLOGUE_GELU_UP), y has rows floats.
+ * With LEV_FLAG_HOST_IO every x and y is a host buffer (independent plain or gelu-up products only):
+ * distinct inputs are copied in once, outputs are copied back and the call synchronises;
+ * LEV_FLAG_CHECK_FINITE then checks inputs and outputs on the host like the one-shot entry points. */
+#define LEV_MAX_CHAIN_OPS 32
+typedef struct lev_chain_op {
+    const lev_weights* w;
+    int64_t row0, rows;
+    const float* x;
+    float* y;
+    int depends;
+    lev_fusion fusion; /* prologue LEV_PROLOGUE_NONE and residual NULL: a plain product */
+} lev_chain_op;
+int lev_matvec_chain(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned flags);
+
 /* ---- decode attention over a paged KV cache ------------------------------
  * Single-query attention of g4_attn (Sources/LeviathanCore/Gemma4.swift:4412-4457; f64 oracle
  * Sources/LeviathanCore/AttentionLowering.swift:358-388): column c, at query position pos[c] of

@@ -52,6 +52,13 @@ class Fusion(C.Structure):
 
 
 PROLOGUE_NONE, PROLOGUE_RMSNORM, PROLOGUE_GELU_UP = 0, 1, 2
+MAX_CHAIN_OPS = 32
+
+
+class ChainOp(C.Structure):
+    _fields_ = [("w", C.c_void_p), ("row0", C.c_int64), ("rows", C.c_int64), ("x", C.c_void_p), ("y", C.c_void_p),
+                ("depends", C.c_int), ("fusion", Fusion)]
+
 
 
 class KVLayout(C.Structure):
@@ -93,6 +100,7 @@ SIGNATURES = {
     "lev_qkv_norm_rope_append": (_I, [_P, _P, _I, _I, _I, _P, _P, C.c_float, _P, _P, C.POINTER(KVLayout), _P, _P, _P, _P]),
     "lev_argmax": (_I, [_P, _P, _L, _L, _P, _P]),
     "lev_matvec_fused": (_I, [_P, _P, _L, _L, _P, _L, _I, C.POINTER(Fusion), _P, _L]),
+    "lev_matvec_chain": (_I, [_P, _I, C.POINTER(ChainOp), _U]),
     "lev_matvec_multi_fused": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(Fusion), C.POINTER(_P), C.POINTER(_L)]),
     "lev_kv_append": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _P, _P]),
     "lev_attn_decode": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _I, _P, _I, C.c_float, _P]),

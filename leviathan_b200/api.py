@@ -329,6 +329,29 @@ class Context:
         self._check(self.lib.lev_matvec_multi_fused(self.handle, n, wp, _ptr(x), x.numel(), n_cols, C.byref(f), yp, cap))
         return outs
 
+    def matvec_chain(self, ops, check_finite: bool = False):
+        """lev_matvec_chain: a list of one-column products in one submission.  Each op is a dict with
+        keys w (Weights), x, out (all torch CUDA tensors, or all numpy arrays for the host-buffer form),
+        and optionally row0, rows, prologue, norm_weight, eps, residual, alpha, depends.  Returns the
+        list of outputs."""
+        n = len(ops)
+        arr = (L.ChainOp * n)()
+        host = n > 0 and not _is_torch(ops[0]["x"])
+        for i, o in enumerate(ops):
+            w = o["w"]
+            row0 = o.get("row0", 0)
+            rows = o.get("rows", w.rows - row0)
+            x, out = o["x"], o["out"]
+            if host:
+                assert x.dtype == np.float32 and x.flags["C_CONTIGUOUS"] and out.flags["C_CONTIGUOUS"]
+            else:
+                assert x.is_contiguous() and out.is_contiguous()
+            f = self._fusion(o.get("prologue"), o.get("norm_weight"), o.get("eps", 1e-6), o.get("residual"), o.get("alpha", 1.0))
+            arr[i] = L.ChainOp(w.handle, row0, rows, _ptr(x), _ptr(out), int(bool(o.get("depends", False))), f)
+        flags = self._flags(host, check_finite)
+        self._check(self.lib.lev_matvec_chain(self.handle, n, arr, flags))
+        return [o["out"] for o in ops]
+
     # -- decode attention over a paged KV cache (torch CUDA tensors only) --
     def kv_append(self, cache: "PagedKV", slot, pos, k, v):
         """lev_kv_append: k, v f32 [n_cols][kv_heads][head_dim] to position pos[c] of sequence slot[c]."""

@@ -11,6 +11,7 @@
 #include "lev_internal.h"
 #include "lev_stream.h"
 
+extern "C" int lev_cuda_destroy(lev_ctx* ctx);
 extern "C" int lev_cuda_abi_version(void) { return LEV_CUDA_ABI_VERSION; }
 
 extern "C" const char* lev_status_name(int s) {
@@ -112,7 +113,19 @@ extern "C" int lev_cuda_init(int device, lev_ctx** out_ctx) {
         return LEV_DEVICE_UNAVAILABLE;
     }
     ctx->stream = ctx->own_stream;
+    {   // tuning of the persistent matvec kernel, read once per context
+        const char* v = getenv("LEV_CHAIN");
+        ctx->chain_off = v && *v == '0';
+        v = getenv("LEV_CHAIN_WARPS");
+        ctx->chain_warps = v ? atoi(v) : 0;
+        v = getenv("LEV_CHAIN_DEPTH");
+        ctx->chain_depth = v ? atoi(v) : 0;
+    }
     cudaMemsetAsync(ctx->d_status, 0, (LEV_COUNTER_OFFSET + LEV_COUNTERS) * sizeof(int), ctx->stream);
+    if (lev_chain_init(ctx) != LEV_OK) {
+        lev_cuda_destroy(ctx);
+        return LEV_OUT_OF_MEMORY;
+    }
     cudaStreamSynchronize(ctx->stream);
     *out_ctx = ctx;
     return LEV_OK;
@@ -128,6 +141,7 @@ extern "C" int lev_cuda_destroy(lev_ctx* ctx) {
     for (int i = 0; i < LEV_SCR_SLOTS; i++)
         if (ctx->scratch[i]) cudaFree(ctx->scratch[i]);
     cudaFree(ctx->d_status);
+    if (ctx->chain_sync) cudaFree(ctx->chain_sync);
     cudaFreeHost(ctx->h_status);
     cudaEventDestroy(ctx->ev0);
     cudaEventDestroy(ctx->ev1);
@@ -169,7 +183,11 @@ extern "C" int lev_cuda_synchronize(lev_ctx* ctx) {
     // a cache index outside its layout
     int bits = 0;
     LEV_TRY(lev_read_status(ctx, &bits));
-    if (bits & LEV_DEV_TIMEOUT) return lev_fail(ctx, LEV_TIMEOUT, "a kernel's bounded wait ran out");
+    if (bits & LEV_DEV_TIMEOUT) {
+        // a kernel that gave up may have left arrival counters and flags of the persistent matvec kernel set
+        lev_chain_reset(ctx);
+        return lev_fail(ctx, LEV_TIMEOUT, "a kernel's bounded wait ran out");
+    }
     if (bits & LEV_DEV_BAD_INDEX) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "a slot, position or block-table entry lay outside the cache layout");
     return LEV_OK;
 }
@@ -440,7 +458,12 @@ extern "C" int lev_matvec_multi(lev_ctx* ctx, int n_ops, const lev_weights* cons
         for (int i = 0; i < n_ops; i++) dy[i] = y[i];
         if (flags & LEV_FLAG_CHECK_FINITE) LEV_TRY(lev_launch_finite_check(ctx, dx, x_count, LEV_DEV_NONFINITE_INPUT));
     }
-    if (n_ops >= 2 && lev_dense_multi_supported(ctx, n_ops, w, dx, n_cols)) {
+    lev_chain_item chain_items[4];
+    for (int i = 0; i < n_ops; i++) chain_items[i] = {w[i], 0, w[i]->rows, dx, dy[i], 0, nullptr};
+    if (n_cols == 1 && n_ops >= 2 && lev_chain_supported(ctx, n_ops, chain_items)) {
+        note_evidence(ctx, "lev_matvec_chain", w[0], w[0]->rows, n_cols, 0, 0);
+        LEV_TRY(lev_chain_run(ctx, n_ops, chain_items));
+    } else if (n_ops >= 2 && lev_dense_multi_supported(ctx, n_ops, w, dx, n_cols)) {
         note_evidence(ctx, "lev_matvec_stream_multi", w[0], w[0]->rows, n_cols, 0, 0);
         LEV_TRY(lev_dense_multi_run(ctx, n_ops, w, dx, n_cols, dy));
     } else {

@@ -42,6 +42,11 @@ struct lev_ctx {
     int* h_status;   // pinned mirror
     cudaEvent_t ev0, ev1;
     lev_dist_state* dist;
+    // persistent matvec kernel (lev_chain.cu): counters it leaves at zero and partial sums of tiles
+    // shared by thread blocks; tuning read once at lev_cuda_init
+    void* chain_sync;
+    void* chain_part;
+    int chain_off, chain_warps, chain_depth;
 };
 
 // Scratch slots (each one buffer; a call may use several at once).

@@ -203,6 +203,11 @@ extern "C" int lev_matvec_fused(lev_ctx* ctx, const lev_weights* w, int64_t row0
     const size_t yb = (size_t)n_cols * (size_t)rows * sizeof(float);
     if (overlap(x, (size_t)x_count * 4, y, yb)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and y overlap");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (n_cols == 1) {
+        const lev_dense_fusion d = to_dense(fusion);
+        const lev_chain_item it = {w, row0, rows, x, y, 0, &d};
+        if (lev_chain_supported(ctx, 1, &it)) return lev_chain_run(ctx, 1, &it);
+    }
     if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) {
         const lev_dense_fusion d = to_dense(fusion);
         return lev_dense_run(ctx, w, row0, rows, x, n_cols, y, fusion ? &d : nullptr);
@@ -251,6 +256,12 @@ extern "C" int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights
         if (overlap(x, (size_t)x_count * 4, y[i], (size_t)n_cols * w[i]->rows * 4)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and y overlap");
     }
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (n_cols == 1) {
+        const lev_dense_fusion d = to_dense(fusion);
+        lev_chain_item it[4];
+        for (int i = 0; i < n_ops; i++) it[i] = {w[i], 0, w[i]->rows, x, y[i], 0, &d};
+        if (lev_chain_supported(ctx, n_ops, it)) return lev_chain_run(ctx, n_ops, it);
+    }
     if (lev_dense_multi_supported(ctx, n_ops, w, x, n_cols)) {
         const lev_dense_fusion d = to_dense(fusion);
         return lev_dense_multi_run(ctx, n_ops, w, x, n_cols, y, fusion ? &d : nullptr);
@@ -271,6 +282,132 @@ extern "C" int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights
         else
             LEV_TRY(lev_launch_matvec_plain(ctx, w[i], 0, w[i]->rows, dx, n_cols, y[i]));
     }
+    return LEV_OK;
+}
+
+// A list of one-column products, each with its own prologue / epilogue, executed as if in order.
+// One launch when the persistent kernel serves the list; else one fused call per op.
+static_assert(LEV_MAX_CHAIN_OPS == kLevChainMaxOps, "the header's limit is the kernel's");
+static int chain_host(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned flags);
+
+extern "C" int lev_matvec_chain(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned flags) {
+    if (!ctx || !ops) return LEV_BAD_ARGUMENT;
+    if (n_ops < 1 || n_ops > LEV_MAX_CHAIN_OPS) return lev_fail(ctx, LEV_BAD_ARGUMENT, "%d ops (1...%d)", n_ops, LEV_MAX_CHAIN_OPS);
+    if (flags & LEV_FLAG_HOST_IO) return chain_host(ctx, n_ops, ops, flags);
+    if (flags & LEV_FLAG_CHECK_FINITE)
+        return lev_fail(ctx, LEV_UNSUPPORTED, "the finite checks of a list run with host buffers only (LEV_FLAG_HOST_IO)");
+    lev_chain_item items[LEV_MAX_CHAIN_OPS];
+    lev_dense_fusion fus[LEV_MAX_CHAIN_OPS];
+    for (int i = 0; i < n_ops; i++) {
+        const lev_chain_op& o = ops[i];
+        if (!o.w || !o.x || !o.y) return lev_fail(ctx, LEV_BAD_ARGUMENT, "op %d: null tensor, input or output", i);
+        if (o.row0 < 0 || o.rows <= 0 || o.row0 > o.w->rows || o.rows > o.w->rows - o.row0 || o.rows > LEV_MAX_DIM)
+            return lev_fail(ctx, LEV_BAD_DIMENSIONS, "op %d: rows [%lld, +%lld) beyond the tensor's %lld rows", i, (long long)o.row0,
+                            (long long)o.rows, (long long)o.w->rows);
+        LEV_TRY(check_fusion(ctx, &o.fusion));
+        const bool gelu = o.fusion.prologue == LEV_PROLOGUE_GELU_UP;
+        const size_t xb = (size_t)(gelu ? 2 : 1) * o.w->cols * sizeof(float), yb = (size_t)o.rows * sizeof(float);
+        if (overlap(o.x, xb, o.y, yb)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "op %d: x and y overlap", i);
+        fus[i] = to_dense(&o.fusion);
+        items[i].w = o.w;
+        items[i].row0 = o.row0;
+        items[i].rows = o.rows;
+        items[i].x = o.x;
+        items[i].y = o.y;
+        items[i].fusion = &fus[i];
+        // an op that reads what an earlier op writes, or writes what an earlier op reads or writes,
+        // starts only when every earlier op has finished on the whole GPU
+        int wait = o.depends != 0;
+        for (int j = 0; j < i && !wait; j++) {
+            const lev_chain_op& e = ops[j];
+            const bool egelu = e.fusion.prologue == LEV_PROLOGUE_GELU_UP;
+            const size_t exb = (size_t)(egelu ? 2 : 1) * e.w->cols * sizeof(float), eyb = (size_t)e.rows * sizeof(float);
+            wait = overlap(o.x, xb, e.y, eyb) || overlap(o.y, yb, e.x, exb) || overlap(o.y, yb, e.y, eyb) ||
+                   (o.fusion.residual && o.fusion.residual != o.y && overlap(o.fusion.residual, yb, e.y, eyb)) ||
+                   (e.fusion.residual && overlap(o.y, yb, e.fusion.residual, eyb));
+        }
+        items[i].wait = wait;
+    }
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    if (lev_chain_supported(ctx, n_ops, items)) {
+        lev_evidence* ev = &ctx->ev;
+        snprintf(ev->device_name, sizeof ev->device_name, "%.127s", ctx->prop.name);
+        snprintf(ev->kernel_name, sizeof ev->kernel_name, "lev_matvec_chain");
+        ev->out_dim = ops[0].rows;
+        ev->in_dim = ops[0].w->cols;
+        ev->n_cols = 1;
+        ev->weight_bytes = 0;
+        for (int i = 0; i < n_ops; i++)
+            ev->weight_bytes += (size_t)ops[i].rows * (size_t)ops[i].w->blocks_per_row * (size_t)lev_block_bytes(ops[i].w->type);
+        ev->gpu_us = 0.f;
+        ev->status = LEV_OK;
+        return lev_chain_run(ctx, n_ops, items);
+    }
+    for (int i = 0; i < n_ops; i++) {
+        const lev_chain_op& o = ops[i];
+        const bool gelu = o.fusion.prologue == LEV_PROLOGUE_GELU_UP;
+        LEV_TRY(lev_matvec_fused(ctx, o.w, o.row0, o.rows, o.x, (gelu ? 2 : 1) * o.w->cols, 1, &o.fusion, o.y, o.rows));
+    }
+    return LEV_OK;
+}
+
+// Host buffers: every op's x and y are host pointers (independent ops only).  Distinct inputs are
+// copied in once, the list runs as one launch, the outputs come back, one synchronisation.
+static int chain_host(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned flags) {
+    lev_chain_op dev[LEV_MAX_CHAIN_OPS];
+    const void* seen_x[LEV_MAX_CHAIN_OPS];
+    size_t seen_off[LEV_MAX_CHAIN_OPS];
+    int n_seen = 0;
+    size_t xb_total = 0, yb_total = 0;
+    for (int i = 0; i < n_ops; i++) {
+        const lev_chain_op& o = ops[i];
+        if (!o.w || !o.x || !o.y) return lev_fail(ctx, LEV_BAD_ARGUMENT, "op %d: null tensor, input or output", i);
+        if (o.row0 < 0 || o.rows <= 0 || o.row0 > o.w->rows || o.rows > o.w->rows - o.row0 || o.rows > LEV_MAX_DIM)
+            return lev_fail(ctx, LEV_BAD_DIMENSIONS, "op %d: rows [%lld, +%lld) beyond the tensor's %lld rows", i, (long long)o.row0,
+                            (long long)o.rows, (long long)o.w->rows);
+        LEV_TRY(check_fusion(ctx, &o.fusion));
+        if (o.depends || o.fusion.residual || (o.fusion.prologue == LEV_PROLOGUE_RMSNORM && o.fusion.norm_weight))
+            return lev_fail(ctx, LEV_UNSUPPORTED, "op %d: with host buffers the ops of a list are independent plain products", i);
+        const size_t xb = (size_t)(o.fusion.prologue == LEV_PROLOGUE_GELU_UP ? 2 : 1) * o.w->cols * sizeof(float);
+        if (flags & LEV_FLAG_CHECK_FINITE)
+            for (size_t k = 0; k < xb / sizeof(float); k++)
+                if (!isfinite(o.x[k])) return lev_fail(ctx, LEV_NONFINITE_INPUT, "activation vector of op %d", i);
+        int at = -1;
+        for (int j = 0; j < n_seen; j++)
+            if (seen_x[j] == o.x) at = j;
+        if (at < 0) {
+            at = n_seen++;
+            seen_x[at] = o.x;
+            seen_off[at] = xb_total;
+            xb_total += (xb + 255) & ~(size_t)255;
+        }
+        dev[i] = o;
+        dev[i].x = (const float*)seen_off[at];  // offsets for now
+        dev[i].y = (float*)yb_total;
+        yb_total += ((size_t)o.rows * sizeof(float) + 255) & ~(size_t)255;
+    }
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    void *px, *py;
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_X, xb_total, &px));
+    LEV_TRY(lev_scratch(ctx, LEV_SCR_Y, yb_total, &py));
+    for (int i = 0; i < n_ops; i++) {
+        dev[i].x = (const float*)((char*)px + (size_t)dev[i].x);
+        dev[i].y = (float*)((char*)py + (size_t)dev[i].y);
+    }
+    for (int j = 0; j < n_seen; j++) {
+        size_t xb = 0;
+        for (int i = 0; i < n_ops; i++)
+            if (ops[i].x == seen_x[j]) xb = (size_t)(ops[i].fusion.prologue == LEV_PROLOGUE_GELU_UP ? 2 : 1) * ops[i].w->cols * sizeof(float);
+        LEV_CUDA(ctx, cudaMemcpyAsync((char*)px + seen_off[j], seen_x[j], xb, cudaMemcpyHostToDevice, ctx->stream));
+    }
+    LEV_TRY(lev_matvec_chain(ctx, n_ops, dev, 0));
+    for (int i = 0; i < n_ops; i++)
+        LEV_CUDA(ctx, cudaMemcpyAsync(ops[i].y, dev[i].y, (size_t)ops[i].rows * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+    LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (flags & LEV_FLAG_CHECK_FINITE)
+        for (int i = 0; i < n_ops; i++)
+            for (int64_t k = 0; k < ops[i].rows; k++)
+                if (!isfinite(ops[i].y[k])) return lev_fail(ctx, LEV_NONFINITE_OUTPUT, "output vector of op %d", i);
     return LEV_OK;
 }
 

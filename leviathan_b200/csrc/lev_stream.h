@@ -60,3 +60,21 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
 bool lev_dense_multi_supported(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols);
 int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols, float* const* y,
                         const lev_dense_fusion* fusion = nullptr);
+
+// persistent form (lev_chain.cu): a list of one-column products in one launch, with the fused steps
+// of lev_dense_fusion per op; `wait`: the op reads what earlier ops of the list write
+struct lev_chain_item {
+    const lev_weights* w;
+    int64_t row0, rows;
+    const float* x;
+    float* y;
+    int wait;
+    const lev_dense_fusion* fusion;
+};
+constexpr int kLevChainMaxOps = 32;
+bool lev_chain_supported(lev_ctx* ctx, int n_ops, const lev_chain_item* items);
+int lev_chain_run(lev_ctx* ctx, int n_ops, const lev_chain_item* items);
+// buffers of the persistent kernel, allocated with the context
+int lev_chain_init(lev_ctx* ctx);
+// puts them back to zero (after a kernel gave up on a bounded wait)
+int lev_chain_reset(lev_ctx* ctx);

@@ -52,6 +52,45 @@ def normal(seed: int, shape, sigma: float = 1.0) -> np.ndarray:
     return (out[:n] * sigma).astype(np.float32).reshape(shape)
 
 
+def _wrap_i64(v: int) -> int:
+    v &= 0xFFFFFFFFFFFFFFFF
+    return v - (1 << 64) if v >= (1 << 63) else v
+
+
+def _lsr(z: torch.Tensor, s: int) -> torch.Tensor:
+    """logical shift right of a two's-complement int64 tensor"""
+    return (z >> s) & ((1 << (64 - s)) - 1)
+
+
+def normal_torch(seed: int, shape, sigma: float = 1.0, device="cuda") -> torch.Tensor:
+    """The same generator as `normal`, in torch on any device (int64 arithmetic wraps like uint64):
+    large synthetic tensors are built on the GPU in milliseconds.  SplitMix64 outputs are identical to
+    the bit; the Box-Muller transcendentals run in f64 on the device and are rounded to f32, so a value
+    can differ from the numpy form only where the two libraries' f64 results straddle an f32 rounding
+    boundary (about one element in 2^29)."""
+    n = 1
+    for d in shape:
+        n *= int(d)
+    pairs = (n + 1) // 2
+    k = torch.arange(1, 2 * pairs + 1, dtype=torch.int64, device=device)
+    z = k * _wrap_i64(0x9E3779B97F4A7C15) + _wrap_i64(seed)
+    z = (z ^ _lsr(z, 30)) * _wrap_i64(0xBF58476D1CE4E5B9)
+    z = (z ^ _lsr(z, 27)) * _wrap_i64(0x94D049BB133111EB)
+    z = z ^ _lsr(z, 31)
+    del k
+    u = _lsr(z, 11).to(torch.float64)
+    del z
+    u1 = (u[0::2] + 1.0) / 9007199254740992.0
+    u2 = u[1::2] / 9007199254740992.0
+    del u
+    r = torch.sqrt(-2.0 * torch.log(u1))
+    ang = 2.0 * np.pi * u2
+    out = torch.empty(2 * pairs, dtype=torch.float64, device=device)
+    out[0::2] = r * torch.cos(ang)
+    out[1::2] = r * torch.sin(ang)
+    return (out[:n] * sigma).to(torch.float32).reshape(*shape)
+
+
 def _f16_bytes(v: torch.Tensor) -> torch.Tensor:
     """f32 tensor [...] -> uint8 [..., 2] little-endian IEEE half bits."""
     return v.to(torch.float16).contiguous().view(torch.uint8).reshape(*v.shape, 2)
