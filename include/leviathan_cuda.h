@@ -159,6 +159,12 @@ int lev_weights_upload(lev_ctx* ctx, const void* bytes, size_t n_bytes, int ggml
 int lev_weights_free(lev_ctx* ctx, lev_weights* w);
 int lev_weights_info(const lev_weights* w, int* ggml_type, int64_t* rows, int64_t* cols,
                      size_t* gguf_bytes);
+/* A resident tensor is held twice: in GGUF order (read by lev_dequantize, the plain schedule and the
+ * prefill GEMM) and repacked in tile order for the stream schedule (the same bytes, permuted).  A
+ * decode-only host can release the GGUF-order copy, as the reference keeps one resident buffer per
+ * model (Sources/LeviathanCore/Gemma4.swift:2622-2631); the entry points that read it then return
+ * LEV_UNSUPPORTED for this tensor. */
+int lev_weights_release_gguf(lev_ctx* ctx, lev_weights* w);
 
 /* Block dequantization of rows [row0, row0+rows) to f32 [rows][cols],
  * bit-exact with Q4_0.decodeBlock (Q4.swift:54-69), Q6_K.decodeBlock

@@ -83,6 +83,7 @@ SIGNATURES = {
     "lev_cuda_last_evidence": (_I, [_P, C.POINTER(Evidence)]),
     "lev_weights_upload": (_I, [_P, _P, _Z, _I, _L, _L, _I, C.POINTER(_P)]),
     "lev_weights_free": (_I, [_P, _P]),
+    "lev_weights_release_gguf": (_I, [_P, _P]),
     "lev_weights_info": (_I, [_P, C.POINTER(_I), C.POINTER(_L), C.POINTER(_L), C.POINTER(_Z)]),
     "lev_dequantize": (_I, [_P, _P, _L, _L, _P, _U]),
     "lev_matvec": (_I, [_P, _P, _L, _L, _P, _L, _I, _P, _L, _I, _U]),

@@ -42,6 +42,11 @@ class Weights:
         self.ctx, self.handle = ctx, handle
         self.ggml_type, self.rows, self.cols, self.gguf_bytes = ggml_type, rows, cols, gguf_bytes
 
+    def release_gguf(self):
+        """lev_weights_release_gguf: drop the GGUF-order copy (decode-only use: the stream schedule keeps
+        the repacked bytes); dequantize, the plain schedule and prefill then refuse this tensor."""
+        self.ctx._check(self.ctx.lib.lev_weights_release_gguf(self.ctx.handle, self.handle))
+
     def free(self):
         if self.handle:
             self.ctx.lib.lev_weights_free(self.ctx.handle, self.handle)

@@ -282,6 +282,19 @@ extern "C" int lev_weights_free(lev_ctx* ctx, lev_weights* w) {
     return LEV_OK;
 }
 
+// Frees the GGUF-order copy of a tensor the stream schedule serves; the repacked copy (the same bytes in
+// tile order) stays.  A resident tensor then occupies its GGUF size once.
+extern "C" int lev_weights_release_gguf(lev_ctx* ctx, lev_weights* w) {
+    if (!ctx || !w) return LEV_BAD_ARGUMENT;
+    if (!w->packed) return lev_fail(ctx, LEV_UNSUPPORTED, "the tensor has no repacked copy: the GGUF-order bytes are the only ones");
+    if (!w->raw) return LEV_OK;
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
+    if (w->owns_raw) cudaFree(w->raw);
+    w->raw = nullptr;
+    return LEV_OK;
+}
+
 extern "C" int lev_weights_info(const lev_weights* w, int* type, int64_t* rows, int64_t* cols, size_t* bytes) {
     if (!w) return LEV_BAD_ARGUMENT;
     if (type) *type = w->type;

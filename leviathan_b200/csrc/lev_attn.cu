@@ -924,7 +924,7 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     if (round_cap > (span + splits - 1) / splits) round_cap = (span + splits - 1) / splits;  // the longest range
     if (round_cap > (int64_t)(kMaxRoundPages - 1) * L->page) round_cap = (int64_t)(kMaxRoundPages - 1) * L->page;
     // fp16 caches go through the tensor-core kernel: rounds are whole batches of 16 positions
-    const bool use_mma = L->kv_type == LEV_KV_F16 && env_int("LEV_ATTN_MMA", 1) != 0;
+    const bool use_mma = L->kv_type == LEV_KV_F16;
     if (use_mma) {
         round_cap = (int64_t)(kRoundBytesMma / (2 * row_bytes)) & ~(int64_t)15;
         const int64_t longest = ((span + splits - 1) / splits + 15) & ~(int64_t)15;
@@ -956,7 +956,7 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     // default: at 4096 positions the serial tail of that block cost more than the second launch
     // (19.7 us against 17.6 us per call).
     A.direct = splits == 1;  // short windows, or enough columns to fill the GPU: no partials at all
-    const bool one_launch = A.direct || (heads_kv <= LEV_COUNTERS && env_int("LEV_ATTN_ONE_LAUNCH", 0) != 0);
+    const bool one_launch = A.direct;
     A.counters = one_launch && !A.direct ? ctx->d_status + LEV_COUNTER_OFFSET : nullptr;
     const dim3 grid((unsigned)splits, L->kv_heads, n_cols);
     cudaError_t e;

@@ -21,13 +21,6 @@ namespace {
 
 constexpr int kMaxDepth = 8;
 
-#ifdef LEV_TIMELINE
-// development aid (not compiled into the product): per-warp clock stamps of the last launch
-__device__ long long lev_tl[160][24][32];
-#define TL(i) do { if (lane == 0 && (i) < 32) lev_tl[blockIdx.x][warp][(i)] = clock64(); } while (0)
-#else
-#define TL(i) do {} while (0)
-#endif
 
 struct DenseArgs {
     const uint4* wp;   // first tile of the call
@@ -44,7 +37,6 @@ struct DenseArgs {
     int* status;
     int depth;         // ring stages per warp
     int sps;           // K-steps per stage
-    int debug;         // bit 0: skip the arithmetic
     // sliced form (JOBS): the call is a device-side list of jobs, each up to CMAX activation columns
     // against one slice (expert) of the tensor
     const int* njobs_dev;   // [1] jobs in the list
@@ -69,12 +61,6 @@ struct DenseArgs {
     float alpha;
 };
 
-// build switch for A/B timing of the fused prologue / epilogue code (-DLEV_NO_FUSION compiles it out)
-#ifdef LEV_NO_FUSION
-constexpr bool kFusion = false;
-#else
-constexpr bool kFusion = true;
-#endif
 
 constexpr int kMaxJobTables = 3;  // jobs whose tables one CTA of the sliced form can hold
 
@@ -114,7 +100,6 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     const int nst = ntiles * spt;
     const int s = (int)((int64_t)nst * lw / W), e = (int)((int64_t)nst * (lw + 1) / W);
 
-    TL(0);
     const int sps = A.sps;  // K-steps per ring stage (one bulk copy, one barrier wait)
     const unsigned stage_bytes = (unsigned)sps * kStepBytes;
 
@@ -200,17 +185,15 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     O.init(lane);
     int tl = s / spt;    // CTA-local tile
     int k = s - tl * spt;
-    TL(1);
     pdl_launch_dependents();
     pdl_wait();  // weights are immutable and already on their way; x and y belong to the launches before
 
-    TL(2);
     // ---- RMSNorm statistic of each activation column (fused prologue): every CTA reduces the
     // column itself, in a fixed order (thread-strided partials, warp tree, warps in order) ----
     float inv_rms[CMAX];
 #pragma unroll
     for (int c = 0; c < CMAX; c++) inv_rms[c] = 1.0f;
-    if (kFusion && !JOBS && A.norm_on) {
+    if (!JOBS && A.norm_on) {
         __shared__ float norm_part[W][CMAX];
 #pragma unroll
         for (int c = 0; c < CMAX; c++) {
@@ -267,7 +250,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             for (int m = 0; m < 4; m++) {
                 const int el = chunk * 64 + chunk_col<TYPE>(tt, m, 0, 0);
                 float4 v = __ldg(reinterpret_cast<const float4*>(xr + (el < A.cols ? el : 0)));
-                if (kFusion && !JOBS && A.norm_on) {
+                if (!JOBS && A.norm_on) {
                     float inv = inv_rms[0];
 #pragma unroll
                     for (int cc = 1; cc < CMAX; cc++) inv = c == cc ? inv_rms[cc] : inv;
@@ -277,7 +260,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
                         v = make_float4(v.x * nw.x, v.y * nw.y, v.z * nw.z, v.w * nw.w);
                     }
                 }
-                if ((JOBS || kFusion) && A.gelu_inter > 0) {
+                if (A.gelu_inter > 0) {
                     const float4 u = __ldg(reinterpret_cast<const float4*>(xr + A.gelu_inter + (el < A.cols ? el : 0)));
                     v = make_float4(gelu_tanh_up(v.x, u.x), gelu_tanh_up(v.y, u.y), gelu_tanh_up(v.z, u.z), gelu_tanh_up(v.w, u.w));
                 }
@@ -363,9 +346,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         }
         if (bad) atomicOr(A.status, LEV_DEV_NONFINITE_INPUT);
     }
-    TL(3);
     __syncthreads();
-    TL(4);
 
     float yacc[NT][4];
     float mina[CMAX], minb[CMAX];
@@ -414,11 +395,8 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         }
         const int i1 = i0 + sps < e ? i0 + sps : e;
         for (int i = i0; i < i1; i++) {
-            TL(5 + 2 * (i - s));
             const uint4* st = reinterpret_cast<const uint4*>(ring + slot * stage_bytes + (i - i0) * kStepBytes);
-            if (!(A.debug & 1))
-                stream_step<TYPE, CMAX, true>(st, xs + k * (4 * GLT * 8), sa + k * (4 * kAuxPerChunk), lane, O, yacc, mina, minb);
-            TL(6 + 2 * (i - s));
+            stream_step<TYPE, CMAX, true>(st, xs + k * (4 * GLT * 8), sa + k * (4 * kAuxPerChunk), lane, O, yacc, mina, minb);
             k++;
             if (k == spt || i == e - 1) {
                 // ---- this warp's segment of the tile ends: fold to one f32 per (row, column) ----
@@ -449,7 +427,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
                             const int oc = JOBS ? orow[c] : c;
                             if (JOBS ? orow[c] >= 0 : c < A.n_cols) {
                                 const int64_t at = (int64_t)oc * cur_ld + row;
-                                if (kFusion && !JOBS && !MULTI && A.residual) {
+                                if (!JOBS && !MULTI && A.residual) {
                                     if (row < cur_rows) va = fmaf(A.alpha, va, A.residual[at]);
                                     if (row + 8 < cur_rows) vb = fmaf(A.alpha, vb, A.residual[at + 8]);
                                 }
@@ -482,9 +460,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             phase ^= 1u;
         }
     }
-    TL(29);
     __syncthreads();
-    TL(30);
     // ---- tiles shared between warps: add the warps' records in the order of their ranges ----
     // logical warp l owns steps [nst*l/W, nst*(l+1)/W); the one holding step q is ((q+1)*W - 1) / nst
     for (int item = threadIdx.x; item < ntiles * CMAX * 16; item += W * 32) {
@@ -511,20 +487,12 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             const int64_t row = (int64_t)(tile0 + tile) * 16 + (idx & 15);
             if (c < A.n_cols && row < A.rows) {
                 const int64_t at = (int64_t)c * A.out_ld + row;
-                A.y[at] = kFusion && A.residual ? fmaf(A.alpha, acc, A.residual[at]) : acc;
+                A.y[at] = A.residual ? fmaf(A.alpha, acc, A.residual[at]) : acc;
             }
         }
     }
-    TL(31);
 }
 
-#ifdef LEV_TIMELINE
-}  // namespace
-extern "C" int lev_debug_timeline(long long* out) {
-    return (int)cudaMemcpyFromSymbol(out, lev_tl, sizeof(lev_tl));
-}
-namespace {
-#endif
 
 template <int TYPE, int CMAX, int W, bool JOBS = false, bool MULTI = false>
 int launch_dense(lev_ctx* ctx, int grid, size_t smem, const DenseArgs& A) {
@@ -567,15 +535,14 @@ struct DensePlan {
 
 // Shape of a launch, or false when the tables do not fit beside a useful ring.
 bool dense_plan_tiles(lev_ctx* ctx, const lev_weights* w, int64_t tiles, int n_cols, DensePlan* P) {
-    if (n_cols < 1 || n_cols > 4 || env_int("LEV_DENSE", 1) == 0) return false;
+    if (n_cols < 1 || n_cols > 4) return false;
     const size_t step = step_bytes(w->type);
     const size_t tb = lev_stream_table_bytes(w, n_cols, 2, 1, nullptr);
     const int64_t spt = lev_stream_chunks(w) / 4;
     if (tiles < 1 || tiles * spt > 0x7fffffff / 64) return false;
-    int warps = env_int("LEV_DENSE_WARPS", 8);
-    if (warps != 8 && warps != 12 && warps != 16 && warps != 24) warps = 8;
+    const int warps = 8;
     // half of an SM's shared memory unless one CTA takes the SM
-    size_t cap = (size_t)env_int("LEV_DENSE_SMEM_KB", warps <= 16 ? 110 : 200) * 1024;
+    size_t cap = (size_t)110 * 1024;
     const int sms = ctx->prop.multiProcessorCount;
     const int grid = (int)(tiles < sms ? tiles : sms);
     const int64_t per_cta = ((tiles + grid - 1) / grid) * spt;
@@ -588,13 +555,10 @@ bool dense_plan_tiles(lev_ctx* ctx, const lev_weights* w, int64_t tiles, int n_c
     // K-steps one warp can hold in shared memory, cut into stages of sps steps
     int64_t room = (int64_t)((cap - tb) / ((size_t)warps * step));
     if (room > per_warp) room = per_warp;
-    int sps = env_int("LEV_DENSE_SPS", 2);
-    if (sps < 1) sps = 1;
+    int sps = 2;
     if (sps * 2 > room) sps = room >= 2 ? (int)(room / 2) : 1;  // at least two stages when there is room
     int64_t depth = room / sps;
     if (depth > kMaxDepth) depth = kMaxDepth;
-    const int forced = env_int("LEV_DENSE_DEPTH", 0);
-    if (forced > 0 && forced < depth) depth = forced;
     if (depth < 1) depth = 1;
     P->warps = warps;
     P->depth = (int)depth;
@@ -623,7 +587,7 @@ int launch_multi_c(lev_ctx* ctx, int cmax, int grid, size_t smem, const DenseArg
 
 // Several whole tensors of one format and K against the same activations in one launch.
 bool lev_dense_multi_supported(lev_ctx* ctx, int n_ops, const lev_weights* const* w, const float* x, int n_cols) {
-    if (n_ops < 2 || n_ops > 4 || ((uintptr_t)x & 15) != 0 || env_int("LEV_DENSE_WARPS", 8) != 8) return false;
+    if (n_ops < 2 || n_ops > 4 || ((uintptr_t)x & 15) != 0) return false;
     int64_t tiles = 0;
     for (int i = 0; i < n_ops; i++) {
         if (!w[i] || !w[i]->packed || w[i]->type != w[0]->type || w[i]->cols != w[0]->cols) return false;
@@ -680,7 +644,6 @@ int lev_dense_multi_run(lev_ctx* ctx, int n_ops, const lev_weights* const* w, co
     A.status = ctx->d_status;
     A.depth = P.depth;
     A.sps = P.sps;
-    A.debug = env_int("LEV_STREAM_DEBUG", 0);
     apply_fusion(A, fusion, w[0]->cols);
     const int t = w[0]->type;
     int st = t == LEV_GGML_Q4_K   ? launch_multi_c<LEV_GGML_Q4_K>(ctx, n_cols, P.grid, P.smem, A)
@@ -723,7 +686,6 @@ int lev_dense_run(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows
     A.status = ctx->d_status;
     A.depth = P.depth;
     A.sps = P.sps;
-    A.debug = env_int("LEV_STREAM_DEBUG", 0);
     apply_fusion(A, fusion, w->cols);
     int st = w->type == LEV_GGML_Q4_K   ? launch_dense_c<LEV_GGML_Q4_K>(ctx, n_cols, P.warps, P.grid, P.smem, A)
              : w->type == LEV_GGML_Q6_K ? launch_dense_c<LEV_GGML_Q6_K>(ctx, n_cols, P.warps, P.grid, P.smem, A)
@@ -746,7 +708,7 @@ static size_t jobs_cap(size_t tables, size_t step) {
 
 bool lev_dense_jobs_supported(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job, int max_jobs, int cmax,
                               const float* x, int64_t x_ld) {
-    if (!w->packed || rows_per_job % 16 != 0 || max_jobs < 1 || env_int("LEV_DENSE", 1) == 0) return false;
+    if (!w->packed || rows_per_job % 16 != 0 || max_jobs < 1) return false;
     if (cmax != 1 && cmax != 4) return false;
     if (((uintptr_t)x & 15) != 0 || x_ld % 4 != 0) return false;
     // a CTA's run of tiles may touch at most kMaxJobTables jobs
@@ -769,7 +731,7 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     const size_t stride = (lev_stream_table_bytes(w, cmax, 2, 1, nullptr) + 255) & ~(size_t)255;
     const size_t cap = jobs_cap(kMaxJobTables * stride, step);
     // a CTA that takes the whole SM anyway runs twelve warps
-    const int W = cap > 110 * 1024 && cmax == 4 && env_int("LEV_JOBS_WIDE", 1) ? 12 : 8;
+    const int W = cap > 110 * 1024 && cmax == 4 ? 12 : 8;
     const int sms = ctx->prop.multiProcessorCount;
     const int64_t max_tiles = (int64_t)max_jobs * tpj;
     const int grid = (int)(max_tiles < sms ? max_tiles : sms);
@@ -792,7 +754,6 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     A.status = ctx->d_status;
     A.depth = (int)depth;
     A.sps = 1;
-    A.debug = env_int("LEV_STREAM_DEBUG", 0);
     A.njobs_dev = njobs_dev;
     A.job_slice = job_slice;
     A.job_src = job_src;

@@ -175,6 +175,7 @@ extern "C" int lev_gemm_prefill(lev_ctx* ctx, const lev_weights* w, const void* 
     if (flags & LEV_FLAG_HOST_IO) return lev_fail(ctx, LEV_UNSUPPORTED, "lev_gemm_prefill takes device pointers");
     if (tokens <= 0 || tokens > (1 << 20)) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "tokens %lld", (long long)tokens);
     if (w->cols % 32) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "inDim %lld", (long long)w->cols);
+    if (!w->raw) return lev_fail(ctx, LEV_UNSUPPORTED, "the GGUF-order copy of this tensor was released: prefill reads it");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
     if (lev_gemm_tc_supported(w, x_bf16, tokens)) {
         snprintf(ctx->ev.kernel_name, sizeof ctx->ev.kernel_name, "lev_gemm_prefill_tcgen05");

@@ -40,15 +40,6 @@ constexpr int kStageBytes = kXStageBytes + kWStageBytes;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 2000000000LL;
 
-#ifdef LEV_TIMELINE
-__device__ long long lev_gemm_tl[16];  // development aid: cycle sums of CTA 0
-#define GTL_ADD(i, v) do { if (blockIdx.x == 0 && blockIdx.y == 0) lev_gemm_tl[i] += (v); } while (0)
-#define GTL_NOW() clock64()
-#else
-#define GTL_ADD(i, v) do { (void)(v); } while (0)
-#define GTL_NOW() 0ll
-#endif
-
 struct GemmTcArgs {
     const uint8_t* raw;   // GGUF blocks, row-major
     int type;
@@ -263,7 +254,6 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
 
 template <int TYPE>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, GemmTcArgs A) {
-    const long long k_start = GTL_NOW();
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) unsigned long long full_x[STAGES], full_w[STAGES], empty[STAGES], accum_full;
     __shared__ unsigned tmem_base_s;
@@ -297,9 +287,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
     const unsigned tmem_base = tmem_base_s;
     volatile int* abort_flag = &abort_s;
-    long long e0 = 0;  // development timing only
-    (void)e0;
-    if (threadIdx.x == 64) GTL_ADD(8, GTL_NOW() - k_start);
 
     if (warp == 0) {
         // ---- activation tiles by TMA ----
@@ -320,13 +307,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             for (int it = 0; it < kt && ok; it++) {
                 const int s = it % STAGES;
                 const unsigned ph = (it / STAGES) & 1;
-                const long long c0 = GTL_NOW();
                 ok = mbar_wait(s32(&full_x[s]), ph, abort_flag);
-                const long long c1 = GTL_NOW();
                 ok = ok && mbar_wait(s32(&full_w[s]), ph, abort_flag);
-                const long long c2 = GTL_NOW();
-                GTL_ADD(0, c1 - c0);
-                GTL_ADD(1, c2 - c1);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
                 const unsigned xs = s32(smem + (size_t)s * kStageBytes), ws = xs + kXStageBytes;
@@ -339,7 +321,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 umma_commit(s32(&empty[s]));  // the stage may be refilled when these MMAs have read it
             }
             umma_commit(s32(&accum_full));
-            GTL_ADD(2, 1);
         }
     } else {
         // ---- weight decode: thread = (2 rows 88 apart) x (byte group j); the raw bytes of the
@@ -370,10 +351,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                     load_raw<TYPE>(rowp[i], it + 1, j, valid[i], nxt[i]);
                 }
             }
-            const long long d0 = GTL_NOW();
             if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
-            const long long d1 = GTL_NOW();
-            if (threadIdx.x == 64) GTL_ADD(3, d1 - d0);
             if (!ok) break;
             unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
 #pragma unroll
@@ -381,14 +359,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
             __syncwarp();
             if (lane == 0) mbar_arrive(s32(&full_w[s]));
-            if (threadIdx.x == 64) GTL_ADD(4, GTL_NOW() - d1);
 #pragma unroll
             for (int i = 0; i < NR; i++) cur[i] = nxt[i];
         }
         // ---- epilogue: TMEM -> Y ----
-        e0 = GTL_NOW();
         if (ok && warp < 10 && mbar_wait(s32(&accum_full), 0, abort_flag)) {
-            if (threadIdx.x == 64) GTL_ADD(5, GTL_NOW() - e0);
             asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
             const int quarter = warp & 3, half = (warp - 2) >> 2;
             if (half < halves) {
@@ -437,8 +412,6 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             }
         }
     }
-    if (threadIdx.x == 64) GTL_ADD(6, GTL_NOW() - e0);
-    if (threadIdx.x == 64) GTL_ADD(7, GTL_NOW() - k_start);
     if (abort_s && threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
     asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
     __syncthreads();
@@ -677,17 +650,6 @@ __global__ void k_act_grouped_bf16(const float* __restrict__ gu, const int* __re
     }
 }
 
-#ifdef LEV_TIMELINE
-}  // namespace
-extern "C" int lev_debug_gemm_timeline(long long* out, int reset) {
-    if (reset) {
-        long long z[16] = {};
-        return (int)cudaMemcpyToSymbol(lev_gemm_tl, z, sizeof z);
-    }
-    return (int)cudaMemcpyFromSymbol(out, lev_gemm_tl, sizeof(long long) * 16);
-}
-namespace {
-#endif
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -721,7 +683,6 @@ int launch_tc(lev_ctx* ctx, const CUtensorMap& map, const GemmTcArgs& A, dim3 gr
 // shapes the tensor-memory kernel serves: rows whose K is a multiple of 64,
 // 16-byte aligned activations
 bool lev_gemm_tc_supported(const lev_weights* w, const void* x_bf16, int64_t tokens) {
-    if (getenv("LEV_GEMM_TC") && atoi(getenv("LEV_GEMM_TC")) == 0) return false;
     if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0 && w->type != LEV_GGML_Q6_K) return false;
     if (w->cols % KS != 0 || ((uintptr_t)x_bf16 & 15) != 0 || tokens < 1) return false;
     return encode_tiled() != nullptr;
@@ -763,9 +724,8 @@ int lev_gemm_tc_run(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int6
 // grouped form: host side
 // ---------------------------------------------------------------------------
 bool lev_gemm_grouped_supported(const lev_weights* w, int rows_per_expert) {
-    if (getenv("LEV_GEMM_TC") && atoi(getenv("LEV_GEMM_TC")) == 0) return false;
     if (w->type != LEV_GGML_Q4_K && w->type != LEV_GGML_Q4_0 && w->type != LEV_GGML_Q6_K) return false;
-    if (w->cols % KS != 0 || rows_per_expert < 1) return false;
+    if (w->cols % KS != 0 || rows_per_expert < 1 || !w->raw) return false;
     return encode_tiled() != nullptr;
 }
 

@@ -770,8 +770,7 @@ static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float*
     const bool sliced = moe_sliced(ctx, w, pairs, x);
     // prefill-sized calls: grouped dequant-GEMM on the tensor cores (bf16 operands, f32 accumulate;
     // the 2e-2 bar of tensor-core prefill applies to this form)
-    const char* mp = getenv("LEV_MOE_GEMM_MIN_PAIRS");
-    const int64_t min_pairs = mp && *mp ? atoll(mp) : 512;
+    const int64_t min_pairs = 512;
     const bool tensor = !sliced && pairs >= min_pairs && w->hidden % 4 == 0 && lev_gemm_grouped_supported(w->gate_up, (int)gu_rows_) &&
                         lev_gemm_grouped_supported(w->down, w->hidden);
     const bool sliced4 = !sliced && !tensor && moe_sliced4(ctx, w, pairs, x);

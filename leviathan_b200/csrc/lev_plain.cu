@@ -221,6 +221,7 @@ int launch_plain_nc(lev_ctx* ctx, const lev_weights* w, const uint8_t* base, int
 
 int lev_launch_matvec_plain(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, const float* x,
                             int n_cols, float* y) {
+    if (!w->raw) return lev_fail(ctx, LEV_UNSUPPORTED, "the GGUF-order copy of this tensor was released: only the stream schedule serves it");
     const uint8_t* base = w->raw + (size_t)row0 * (size_t)w->blocks_per_row * (size_t)lev_block_bytes(w->type);
     if (w->type == LEV_GGML_Q4_0) return launch_plain_nc<Q40Item>(ctx, w, base, rows, x, n_cols, y);
     if (w->type == LEV_GGML_Q4_K) return launch_plain_nc<Q4KItem>(ctx, w, base, rows, x, n_cols, y);
@@ -228,6 +229,7 @@ int lev_launch_matvec_plain(lev_ctx* ctx, const lev_weights* w, int64_t row0, in
 }
 
 int lev_launch_dequantize(lev_ctx* ctx, const lev_weights* w, int64_t row0, int64_t rows, float* out) {
+    if (!w->raw) return lev_fail(ctx, LEV_UNSUPPORTED, "the GGUF-order copy of this tensor was released");
     int bb = lev_block_bytes(w->type);
     const uint8_t* base = w->raw + (size_t)row0 * (size_t)w->blocks_per_row * (size_t)bb;
     const int block = 256;

@@ -330,7 +330,6 @@ struct StreamArgs {
     int cmax, terms, glt;
     int* status;            // device status word
     float* y;
-    int debug;              // bit 0: skip the arithmetic (data-movement timing only)
     int depth;              // ring stages per warp
 };
 
@@ -460,7 +459,7 @@ __global__ void __launch_bounds__(W * 32, OCC) k_stream(StreamArgs A) {
             const uint4* xchunk = jfrag + k * (4 * GLT * 8);
             const float* achunk = jaux + k * (4 * kAuxPerChunk);
 
-            if (!(A.debug & 1)) stream_step<TYPE, CMAX, XS>(st, xchunk, achunk, lane, O, yacc, mina, minb);
+            stream_step<TYPE, CMAX, XS>(st, xchunk, achunk, lane, O, yacc, mina, minb);
 
             // every lane has consumed its shared-memory reads of this stage: refill it
             __syncwarp();
@@ -706,7 +705,7 @@ int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, 
     // decode-sized tensors every byte is requested at kernel start.  Everything else runs two
     // CTAs of eight warps per SM with a four-stage ring.
     int variant = grouped ? 0 : 1, warps = kWarpsPerCta, occ = 2, depth = 4;
-    if (!grouped && cmax <= 4 && !env_int("LEV_STREAM_NARROW", 0) && (size_t)kWarpsWide * kStepBytes + tb <= smem_cap) {
+    if (!grouped && cmax <= 4 && (size_t)kWarpsWide * kStepBytes + tb <= smem_cap) {
         variant = 2;
         warps = kWarpsWide;
         occ = 1;
@@ -752,7 +751,6 @@ int lev_stream_run(lev_ctx* ctx, const lev_weights* w, const lev_stream_job& J, 
     A.glt = glt;
     A.status = ctx->d_status;
     A.y = y;
-    A.debug = env_int("LEV_STREAM_DEBUG", 0);
     A.out_cols = J.outmap ? 0x7fffffff : cmax;
     size_t smem = ring + (xs ? tb : 0);
     A.depth = depth;
@@ -784,8 +782,6 @@ int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, i
     J.max_jobs = 1;
     void* tables;
     LEV_TRY(lev_scratch(ctx, LEV_SCR_XPREP, lev_stream_table_bytes(w, n_cols, terms, 1, nullptr) + 256, &tables));
-    const int dbg = env_int("LEV_STREAM_DEBUG", 0);  // timing aids: bit 1 no main launch, bit 2 no preparation launch
-    if (!(dbg & 4)) LEV_TRY(lev_stream_prepare(ctx, w, src, n_cols, terms, 1, tables));
-    if (dbg & 2) return LEV_OK;
+    LEV_TRY(lev_stream_prepare(ctx, w, src, n_cols, terms, 1, tables));
     return lev_stream_run(ctx, w, J, tables, n_cols, terms, y);
 }

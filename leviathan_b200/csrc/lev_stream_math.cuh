@@ -192,50 +192,6 @@ __device__ __forceinline__ void stream_step(const uint4* st, const uint4* xchunk
     const int* boff0 = O.boff0;
     const int* boff1 = O.boff1;
     (void)g; (void)t; (void)boff0; (void)boff1; (void)mina; (void)minb;
-#ifdef LEV_SIM_LEAN
-if (TYPE == LEV_GGML_Q4_K) {
-    const uint4 h0 = st[g], h1 = st[8 + g];
-    const unsigned sa_lo = h0.y & 0x3F3F3F3Fu, sa_hi = (h0.w & 0x0F0F0F0Fu) | ((h0.y >> 2) & 0x30303030u);
-    const unsigned sb_lo = h1.y & 0x3F3F3F3Fu, sb_hi = (h1.w & 0x0F0F0F0Fu) | ((h1.y >> 2) & 0x30303030u);
-    const float dA = h2f_bits(h0.x & 0xffffu), dB = h2f_bits(h1.x & 0xffffu);
-#pragma unroll
-    for (int G = 0; G < 2; G++) {
-        float acc[4];
-#pragma unroll
-        for (int cc = 0; cc < 2; cc++) {
-            const int c = 2 * G + cc;
-            const uint4 q = st[16 + c * 32 + lane];
-            const unsigned w0 = q.x, w1 = q.y, w2 = q.z, w3 = q.w;
-            const unsigned w0s = w0 >> 8, w1s = w1 >> 8, w2s = w2 >> 8, w3s = w3 >> 8;
-            const uint4* xp = xchunk + c * (GLT * 8) + xoff[0];
-            const uint4 x0 = xp[0], x1 = xp[1];
-            if (cc == 0) mma16816_z(acc, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
-            else mma16816(acc, w0 & 0x000F000Fu, w2 & 0x000F000Fu, w0s & 0x000F000Fu, w2s & 0x000F000Fu, x0.x, x0.y);
-            mma16816(acc, w1 & 0x000F000Fu, w3 & 0x000F000Fu, w1s & 0x000F000Fu, w3s & 0x000F000Fu, x0.z, x0.w);
-            mma16816(acc, w0 & 0x00F000F0u, w2 & 0x00F000F0u, w0s & 0x00F000F0u, w2s & 0x00F000F0u, x1.x, x1.y);
-            mma16816(acc, w1 & 0x00F000F0u, w3 & 0x00F000F0u, w1s & 0x00F000F0u, w3s & 0x00F000F0u, x1.z, x1.w);
-        }
-        const float sA = dA * (__uint_as_float(__byte_perm(G ? sa_hi : sa_lo, 0x4B000000u, 0x7650u + t)) - 8388608.0f);
-        const float sB = dB * (__uint_as_float(__byte_perm(G ? sb_hi : sb_lo, 0x4B000000u, 0x7650u + t)) - 8388608.0f);
-        yacc[0][0] = fmaf(sA, acc[0], yacc[0][0]);
-        yacc[0][1] = fmaf(sA, acc[1], yacc[0][1]);
-        yacc[0][2] = fmaf(sB, acc[2], yacc[0][2]);
-        yacc[0][3] = fmaf(sB, acc[3], yacc[0][3]);
-    }
-    const unsigned ma = t < 2 ? (h0.z & 0x3F3F3F3Fu) : (((h0.w >> 4) & 0x0F0F0F0Fu) | ((h0.z >> 2) & 0x30303030u));
-    const unsigned mb = t < 2 ? (h1.z & 0x3F3F3F3Fu) : (((h1.w >> 4) & 0x0F0F0F0Fu) | ((h1.z >> 2) & 0x30303030u));
-    const unsigned mab = t & 1 ? (ma >> 16) : ma, mbb = t & 1 ? (mb >> 16) : mb;
-    const float dminA = h2f_bits(h0.x >> 16), dminB = h2f_bits(h1.x >> 16);
-    const float mA0 = dminA * byte_to_float(mab, 0), mA1 = dminA * byte_to_float(mab, 1);
-    const float mB0 = dminB * byte_to_float(mbb, 0), mB1 = dminB * byte_to_float(mbb, 1);
-    const float* sx0 = achunk + 2 * t * CMAX;
-#pragma unroll
-    for (int c = 0; c < CMAX; c++) {
-        mina[c] = fmaf(mA0, sx0[c], fmaf(mA1, sx0[CMAX + c], mina[c]));
-        minb[c] = fmaf(mB0, sx0[c], fmaf(mB1, sx0[CMAX + c], minb[c]));
-    }
-} else
-#endif
 if (TYPE == LEV_GGML_Q4_K) {
     const uint4 h0 = st[g], h1 = st[8 + g];
     // 6-bit scales of the 8 sub-blocks of rows g (h0) and g+8 (h1), four per word
@@ -364,12 +320,9 @@ if (TYPE == LEV_GGML_Q4_K) {
 }
 }
 
-int env_int(const char* name, int fallback);
-
 // launch with the programmatic-stream-serialization attribute (see pdl_wait)
 template <class Kernel, class... Args>
 cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaStream_t stream, const Args&... args) {
-    static const int enabled = env_int("LEV_PDL", 1);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -379,13 +332,8 @@ cudaError_t launch_pdl(Kernel kernel, dim3 grid, dim3 block, size_t smem, cudaSt
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = enabled ? 1 : 0;
+    cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kernel, args...);
-}
-
-inline int env_int(const char* name, int fallback) {
-    const char* v = getenv(name);
-    return v && *v ? atoi(v) : fallback;
 }
 
 }  // namespace

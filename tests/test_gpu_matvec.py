@@ -326,3 +326,26 @@ def test_matvec_multi_matches_single_calls(ctx, name, rows_list, cols, n_cols):
     assert e.value.name == "wrongInputCount"
     for h in hs:
         h.free()
+
+
+def test_release_of_the_gguf_order_copy(ctx):
+    """A decode-only host keeps a tensor once: after lev_weights_release_gguf the stream schedule gives
+    the same bits as before, and the entry points that read GGUF-order bytes refuse the tensor."""
+    t = H.TYPES["q4_k"]
+    rows, cols = 96, 1024
+    w = H.quantized(t, 77, rows, cols)
+    wh = ctx.upload(w, t, rows, cols)
+    x = torch.from_numpy(Q.normal(78, (2, cols), 1.0)).cuda()
+    before1 = ctx.matvec(wh, x[0], schedule=lev.SCHEDULE_STREAM).clone()
+    before2 = ctx.matvec(wh, x, schedule=lev.SCHEDULE_STREAM).clone()
+    wh.release_gguf()
+    wh.release_gguf()  # idempotent
+    assert torch.equal(ctx.matvec(wh, x[0], schedule=lev.SCHEDULE_STREAM).view(torch.int32), before1.view(torch.int32))
+    assert torch.equal(ctx.matvec(wh, x, schedule=lev.SCHEDULE_STREAM).view(torch.int32), before2.view(torch.int32))
+    with pytest.raises(lev.LevError) as e:
+        ctx.matvec(wh, x[0], schedule=lev.SCHEDULE_PLAIN)
+    assert e.value.name == "unsupported"
+    with pytest.raises(lev.LevError) as e:
+        ctx.dequantize(wh)
+    assert e.value.name == "unsupported"
+    wh.free()
