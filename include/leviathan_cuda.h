@@ -454,21 +454,38 @@ int lev_gguf_upload(lev_ctx* ctx, const lev_gguf* g, const char* name, lev_weigh
 int lev_gguf_moe_upload(lev_ctx* ctx, const lev_gguf* g, int layer, int local_first,
                         int local_count, lev_moe_weights** out, int* top_k);
 
-/* ---- multi-GPU (one process per GPU, NCCL over NVLink) ------------------ */
+/* ---- multi-GPU (one process per GPU on one NVSwitch box) -----------------
+ * The reference has no multi-GPU path (its expert loop runs slots one after another on one device,
+ * Sources/LeviathanCore/Gemma4.swift:3856-3880); these entry points shard that path where it splits.
+ * lev_dist_init creates an NCCL communicator and, where CUDA IPC allows, maps every rank's work heap
+ * into every other rank (LEV_DIST_HEAP_MB, default 96, read once at init): the data paths then run as
+ * plain peer stores with bounded flag waits, and NCCL is the fallback.  Every rank must make the same
+ * sequence of these calls.  Device pointers only; LEV_FLAG_CHECK_FINITE is refused (a check that fails
+ * on one rank would leave its peers waiting). */
 #define LEV_NCCL_ID_BYTES 128
 int lev_dist_unique_id(void* id128);
 int lev_dist_init(lev_ctx* ctx, int rank, int world, const void* id128);
 int lev_dist_destroy(lev_ctx* ctx);
+/* 1 when the ranks' peer-memory heaps are mapped (the fast forms run), 0 when the entry points fall back to NCCL */
+int lev_dist_peer_memory(const lev_ctx* ctx);
 /* rows of W are split across ranks; each rank computes its slice into
  * y_full[c][rank*rows_local ...] and the slices are all-gathered. */
 int lev_matvec_rowsplit_allgather(lev_ctx* ctx, const lev_weights* w_local, const float* x,
                                   int64_t x_count, int n_cols, float* y_full,
                                   int64_t y_capacity, unsigned flags);
+/* a list of row-split products (lev_matvec_chain over this rank's rows of every tensor): ops[i].w is the
+ * local slice (whole 16-row tiles), ops[i].y receives all rows_local * world outputs on every rank;
+ * independent ops, at most eight */
+int lev_matvec_chain_rowsplit(lev_ctx* ctx, int n_ops, const lev_chain_op* ops);
 int lev_gemm_prefill_rowsplit_allgather(lev_ctx* ctx, const lev_weights* w_local,
                                         const void* x_bf16, int64_t tokens, float* y_full,
                                         unsigned flags);
-/* expert-parallel layer: tokens are data-parallel (this rank's x rows),
- * experts are sharded as uploaded; all-to-all dispatch and combine. */
+/* expert-parallel layer: tokens are data-parallel (this rank's x rows, the same count on every rank),
+ * experts are sharded as uploaded.  Dispatch: every rank pushes its token rows, indices and weights to
+ * all ranks; each rank runs the pairs of its resident experts; combine: every pair's unweighted output
+ * row is stored to the token's rank, which adds its slots in rank order (the ordered axpy of
+ * Gemma4.swift:3878, :2171-2175), so the result equals the single-GPU layer bit for bit.  Without peer
+ * memory: NCCL all-gather + reduce-scatter, equal to f32 rounding. */
 int lev_moe_layer_ep(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens,
                      int top_k, float* out, int32_t* idx_out, float* w_out, unsigned flags);
 

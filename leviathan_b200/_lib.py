@@ -138,6 +138,8 @@ SIGNATURES = {
     "lev_dist_unique_id": (_I, [_P]),
     "lev_dist_init": (_I, [_P, _I, _I, _P]),
     "lev_dist_destroy": (_I, [_P]),
+    "lev_dist_peer_memory": (_I, [_P]),
+    "lev_matvec_chain_rowsplit": (_I, [_P, _I, C.POINTER(ChainOp)]),
     "lev_matvec_rowsplit_allgather": (_I, [_P, _P, _P, _L, _I, _P, _L, _U]),
     "lev_gemm_prefill_rowsplit_allgather": (_I, [_P, _P, _P, _L, _P, _U]),
     "lev_moe_layer_ep": (_I, [_P, _P, _P, _L, _I, _P, _P, _P, _U]),

@@ -543,6 +543,18 @@ class Context:
                                                            _ptr(out), out.numel(), 0))
         return out[0] if one_d else out
 
+    def matvec_chain_rowsplit(self, ops):
+        """lev_matvec_chain_rowsplit: ops like matvec_chain's (w = this rank's rows, out = the whole output)."""
+        n = len(ops)
+        arr = (L.ChainOp * n)()
+        for i, o in enumerate(ops):
+            w = o["w"]
+            f = self._fusion(o.get("prologue"), o.get("norm_weight"), o.get("eps", 1e-6), None, 1.0)
+            arr[i] = L.ChainOp(w.handle, 0, w.rows, _ptr(o["x"]), _ptr(o["out"]), 0, f)
+        self._flags(False, False)
+        self._check(self.lib.lev_matvec_chain_rowsplit(self.handle, n, arr))
+        return [o["out"] for o in ops]
+
     def gemm_prefill_rowsplit_allgather(self, w_local: Weights, x_bf16, world: int, out=None):
         import torch
 
