@@ -212,14 +212,28 @@ def run_gpu(args):
     dev = f"cuda:{local}"
     ctx = lev.Context(local)
 
-    # Each rank holds its own weight instances (no data-path collective: the
-    # FFN sets of different ranks are independent objects).
+    # One GPU: whole tensors.  Several GPUs: the output rows of every tensor are split over the ranks
+    # (each rank holds rows [rank * R / N, (rank + 1) * R / N) of the SAME instances), a step is the same
+    # three products, and every rank ends the step with the whole outputs: the slices travel as peer
+    # stores over NVLink (lev_matvec_chain_rowsplit).  Strong scaling: the work of a step is fixed.
+    from leviathan_b200 import dist as D
+
+    if world > 1:
+        D.init_from_torch(ctx)
     n_inst = args.instances
     inst = []
     for i in range(n_inst):
-        g, u, d = make_instance(rank * n_inst + i, dev)
-        inst.append((ctx.upload(g, Q4_K, FFN, HIDDEN), ctx.upload(u, Q4_K, FFN, HIDDEN),
-                     ctx.upload(d, Q6_K, HIDDEN, FFN)))
+        g, u, d = make_instance(i, dev)
+        if world > 1:
+            r0, nr = D.row_shard(FFN, rank, world)
+            d0, dn_ = D.row_shard(HIDDEN, rank, world)
+            g = D.slice_blocks(g, Q4_K, FFN, HIDDEN, r0, nr).clone()
+            u = D.slice_blocks(u, Q4_K, FFN, HIDDEN, r0, nr).clone()
+            d = D.slice_blocks(d, Q6_K, HIDDEN, FFN, d0, dn_).clone()
+            inst.append((ctx.upload(g, Q4_K, nr, HIDDEN), ctx.upload(u, Q4_K, nr, HIDDEN), ctx.upload(d, Q6_K, dn_, FFN)))
+        else:
+            inst.append((ctx.upload(g, Q4_K, FFN, HIDDEN), ctx.upload(u, Q4_K, FFN, HIDDEN),
+                         ctx.upload(d, Q6_K, HIDDEN, FFN)))
         del g, u, d
     torch.cuda.empty_cache()
     x_h, a_h = make_inputs()
@@ -231,7 +245,11 @@ def run_gpu(args):
 
     def step(i):
         wg, wu, wd = inst[i % n_inst]
-        ctx.matvec_chain([dict(w=wg, x=x, out=yg), dict(w=wu, x=x, out=yu), dict(w=wd, x=a, out=yd)])
+        ops = [dict(w=wg, x=x, out=yg), dict(w=wu, x=x, out=yu), dict(w=wd, x=a, out=yd)]
+        if world > 1:
+            ctx.matvec_chain_rowsplit(ops)
+        else:
+            ctx.matvec_chain(ops)
 
     def barrier():
         if world > 1:
@@ -246,6 +264,8 @@ def run_gpu(args):
     step(0)
     launches_per_step = ctx.launch_count() - l0
     chain_kernel = ctx.last_evidence()["kernel_name"]
+    torch.cuda.synchronize()
+    yg_step0, yd_step0 = yg[:64].cpu().numpy(), yd[:64].cpu().numpy()  # for the parity spot check below
 
     # K steps as one CUDA graph on a side stream; timed with events on that stream
     s = torch.cuda.Stream(device=dev)
@@ -314,10 +334,20 @@ def run_gpu(args):
     xpn, apn, ygn, yun, ydn = xp.numpy(), ap.numpy(), ygp.numpy().reshape(-1), yup.numpy().reshape(-1), ydp.numpy().reshape(-1)
 
     def e2e_step(i):
-        # the same list through the host-buffer form of the C ABI: inputs copied in, one launch,
-        # outputs copied back, one synchronisation
         wg, wu, wd = inst[i % n_inst]
-        ctx.matvec_chain([dict(w=wg, x=xpn, out=ygn), dict(w=wu, x=xpn, out=yun), dict(w=wd, x=apn, out=ydn)])
+        if world == 1:
+            # the same list through the host-buffer form of the C ABI: inputs copied in, one launch,
+            # outputs copied back, one synchronisation
+            ctx.matvec_chain([dict(w=wg, x=xpn, out=ygn), dict(w=wu, x=xpn, out=yun), dict(w=wd, x=apn, out=ydn)])
+        else:
+            # several GPUs: pinned host inputs to the device, the row-split list, whole outputs back
+            x.copy_(xp, non_blocking=True)
+            a.copy_(ap, non_blocking=True)
+            step(i)
+            ygp.view(-1).copy_(yg, non_blocking=True)
+            yup.view(-1).copy_(yu, non_blocking=True)
+            ydp.view(-1).copy_(yd, non_blocking=True)
+            torch.cuda.synchronize()
 
     for i in range(3):
         e2e_step(i)
@@ -347,17 +377,15 @@ def run_gpu(args):
         rows = 64
         sub = g_bytes[0][: rows * (HIDDEN // 256) * 144].cpu().numpy()
         ref = O.q4_k_matvec_f64(sub, rows, HIDDEN, x_h)
-        step(0)
-        torch.cuda.synchronize()
         subd = g_bytes[2][: rows * (FFN // 256) * 210].cpu().numpy()
         refd = O.q6_k_matvec_f64(subd, rows, FFN, a_h)
         parity = {"host_and_device_generators_give_the_same_bytes": generator_match,
-                  "q4_k_max_rel_err_64_rows": O.max_rel_err(yg[:rows].cpu().numpy(), ref),
-                  "q6_k_max_rel_err_64_rows": O.max_rel_err(yd[:rows].cpu().numpy(), refd)}
+                  "q4_k_max_rel_err_64_rows": O.max_rel_err(yg_step0, ref),
+                  "q6_k_max_rel_err_64_rows": O.max_rel_err(yd_step0, refd)}
 
     if rank == 0:
         peaks, peak_kind = _peaks()
-        value = world * STEP_BYTES / (ms_per_step * 1e-3) / 1e9
+        value = STEP_BYTES / (ms_per_step * 1e-3) / 1e9  # one step is the whole job at every N
         q4k_bytes = GATE_BYTES + 4 * (HIDDEN + FFN)
         q6k_bytes = DOWN_BYTES + 4 * (HIDDEN + FFN)
         ach = STEP_BYTES / (ms_per_step * 1e-3) / 1e9
@@ -365,14 +393,18 @@ def run_gpu(args):
             "metric": "Q4/Q6 matvec HBM GB/s", "value": value, "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step,
             "ms_per_step_min": ms_per_step_min,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "higher_is_better": True, "scaling": "strong" if world > 1 else "weak", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
             "config": {"workload": "ffn_matvec_set_b1", "gate_up": "Q4_K 12288x4096 x2", "down": "Q6_K 4096x12288",
                        "columns": 1, "bytes_per_step": STEP_BYTES, "weight_instances_per_gpu": n_inst,
                        "l2": f"inputs larger than L2: {n_inst} distinct instances = {n_inst * STEP_BYTES / 1e6:.0f} MB "
                              "cycled, one per step", "timing": f"median of {reps} replays of a {args.steps}-step CUDA graph",
                        "generator": "SplitMix64 + Box-Muller, seed 0x4C455649 ^ (16 * instance + tensor); x seed ^ 0x100, "
                                     "down input seed ^ 0x101",
-                       "sharding": "independent FFN instances per rank, no collective"},
+                       "sharding": "one GPU" if world == 1 else
+                                   f"output rows of every tensor split over {world} ranks; every rank ends a step with the whole "
+                                   f"outputs (slices pushed as peer stores over NVLink, bounded flag waits; "
+                                   f"peer memory mapped: {bool(ctx.lib.lev_dist_peer_memory(ctx.handle))})"},
             # the dominant kernel is the one launch of a step: the persistent kernel over the three tensors
             "roofline": {"bound": "hbm", "kernel": chain_kernel + ":k_chain(gate, up, down)",
                          "achieved": ach, "peak": peaks["hbm_gbs"], "peak_source": peak_kind, "unit": "GB/s",
@@ -385,7 +417,7 @@ def run_gpu(args):
                              "q6_k": {"achieved": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9, "us_per_launch": k_q6k_ms * 1e3,
                                       "frac": q6k_bytes / (k_q6k_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
                                       "algorithmic_bytes_per_launch": q6k_bytes}}},
-            "e2e": {"value": world * STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
+            "e2e": {"value": STEP_BYTES / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": 4 * (HIDDEN + HIDDEN + FFN), "d2h_bytes_per_step": 4 * (FFN + FFN + HIDDEN)},
             "gpu_launches": launches_per_step * args.steps * reps,
             "clocks": clocks, "parity": parity,
@@ -685,9 +717,11 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         from leviathan_b200 import dist as lev_dist
         from leviathan_b200 import quant as Qd
 
-        lev_dist.init_from_torch(ctx)
+        peer = bool(ctx.lib.lev_dist_peer_memory(ctx.handle))
+        out["peer_memory_mapped"] = peer
         # dense row-split: every rank holds rows [r*R/G, (r+1)*R/G) of the same Q4_K tensor, activations
-        # are replicated, outputs are all-gathered (NCCL); collectives are timed eagerly with events
+        # are replicated, every rank ends with the whole output (peer stores; NCCL all-gather as fallback).
+        # With peer memory the calls are our own kernels only and are timed inside a CUDA graph.
         first, per = lev_dist.row_shard(FFN, rank, world)
         gw = torch.Generator(device=dev).manual_seed(SEED ^ 0x500)
         wq = Qd.quantize(Q4_K, torch.randn((FFN, HIDDEN), generator=gw, device=dev) * 0.02)
@@ -698,18 +732,22 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         xv = torch.randn((1, HIDDEN), generator=gw, device=dev)
         yb, yv = torch.empty((512, FFN), device=dev), torch.empty((1, FFN), device=dev)
 
-        def eager_ms(fn, iters=20):
+        def eager_ms(fn, iters=16):
             import torch.distributed as dist
-            for _ in range(3):
-                fn()
-            torch.cuda.synchronize()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for _ in range(iters):
-                fn()
-            a1.record()
-            a1.synchronize()
-            t = torch.tensor([a0.elapsed_time(a1) / iters], device=dev, dtype=torch.float64)
+            if peer:
+                ms_ = _graph_time(torch, stream, lambda i: fn(), iters)
+            else:
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for _ in range(iters):
+                    fn()
+                a1.record()
+                a1.synchronize()
+                ms_ = a0.elapsed_time(a1) / iters
+            t = torch.tensor([ms_], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             return t.item()
 
@@ -744,19 +782,22 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         xt = [torch.randn((tokens, MOE_HIDDEN), generator=g, device=dev) for _ in range(8)]
         yo = torch.empty((tokens, MOE_HIDDEN), device=dev)
         if world > 1:
-            fn = lambda i: ctx.moe_layer(mw, xt[i % 8], MOE_TOPK, out=yo, expert_parallel=True)  # noqa: E731
-            # collectives are not captured: time eager calls with events
-            for i in range(3):
-                fn(i)
-            torch.cuda.synchronize()
-            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-            a0.record()
-            for i in range(16):
-                fn(i)
-            a1.record()
-            a1.synchronize()
-            ms = a0.elapsed_time(a1) / 16
             import torch.distributed as dist
+            fn = lambda i: ctx.moe_layer(mw, xt[i % 8], MOE_TOPK, out=yo, expert_parallel=True)  # noqa: E731
+            if bool(ctx.lib.lev_dist_peer_memory(ctx.handle)):
+                ms = _graph_time(torch, stream, fn, 8)
+            else:
+                # NCCL collectives are not captured: time eager calls with events
+                for i in range(3):
+                    fn(i)
+                torch.cuda.synchronize()
+                a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a0.record()
+                for i in range(16):
+                    fn(i)
+                a1.record()
+                a1.synchronize()
+                ms = a0.elapsed_time(a1) / 16
             t = torch.tensor([ms], device=dev, dtype=torch.float64)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
             ms = t.item()

@@ -124,14 +124,21 @@ struct PushArgs {
 __device__ void publish(char* const* peer, int world, int me, int phase) {
     HeapHeader* mine = reinterpret_cast<HeapHeader*>(peer[me]);
     __shared__ unsigned last;
-    __threadfence_system();
+    // one system-scope fence per block, by the thread that reports the block done: after the block-wide
+    // barrier it orders the stores of every thread of the block
     __syncthreads();
-    if (threadIdx.x == 0) last = atomicAdd(&mine->arrive, 1u) == gridDim.x - 1 ? 1u : 0u;
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        last = atomicAdd(&mine->arrive, 1u) == gridDim.x - 1 ? 1u : 0u;
+    }
     __syncthreads();
     if (!last) return;
-    if (threadIdx.x == 0) mine->arrive = 0u;
-    __threadfence_system();
     const unsigned epoch = *reinterpret_cast<volatile unsigned*>(&mine->epoch[phase]) + 1u;
+    if (threadIdx.x == 0) {
+        mine->arrive = 0u;
+        __threadfence_system();  // the other blocks' stores (observed through the counter) before the flags
+    }
+    __syncthreads();
     if (threadIdx.x < (unsigned)world) {
         HeapHeader* h = reinterpret_cast<HeapHeader*>(peer[threadIdx.x]);
         *reinterpret_cast<volatile unsigned*>(&h->flag[phase][me]) = epoch;
@@ -162,7 +169,7 @@ __device__ __forceinline__ bool wait_flag(const HeapHeader* h, int phase, int sr
             atomicOr(status, LEV_DEV_TIMEOUT);
             return false;
         }
-        __nanosleep(100);
+        __nanosleep(30);
     }
 }
 
@@ -170,8 +177,10 @@ __device__ __forceinline__ bool wait_flag(const HeapHeader* h, int phase, int sr
 // the round counts as done
 __global__ void k_wait_flags(HeapHeader* h, int world, int phase, int* status) {
     const unsigned done = *reinterpret_cast<volatile unsigned*>(&h->epoch[phase]);
-    if (threadIdx.x < (unsigned)world) wait_flag(h, phase, threadIdx.x, done, status);
-    __threadfence_system();
+    if (threadIdx.x < (unsigned)world) {
+        wait_flag(h, phase, threadIdx.x, done, status);
+        __threadfence_system();
+    }
     __syncthreads();
     if (threadIdx.x == 0) h->epoch[phase] = done + 1u;
 }
@@ -189,8 +198,10 @@ struct WaitCopyArgs {
 __global__ void __launch_bounds__(256) k_wait_copy(WaitCopyArgs A) {
     HeapHeader* h = reinterpret_cast<HeapHeader*>(A.heap);
     const unsigned done = *reinterpret_cast<volatile unsigned*>(&h->epoch[A.phase]);
-    if (threadIdx.x < (unsigned)A.world) wait_flag(h, A.phase, threadIdx.x, done, A.status);
-    __threadfence_system();
+    if (threadIdx.x < (unsigned)A.world) {
+        wait_flag(h, A.phase, threadIdx.x, done, A.status);
+        __threadfence_system();
+    }
     __syncthreads();
     const size_t par = (done & 1u) ? A.parity_bytes : 0;
     for (int part = 0; part < A.parts; part++) {
