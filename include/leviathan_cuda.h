@@ -266,6 +266,18 @@ int lev_qkv_norm_rope(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int kv_
  * rust/crates/lev-forge/src/ops.rs:478-517.  Device pointers, no host synchronisation. */
 int lev_argmax(lev_ctx* ctx, const float* x, int64_t vectors, int64_t n, int32_t* out_index,
                float* out_margin);
+/* The two ends of a decode step.  lev_embed_rows: y[t][0..cols) = value(w[tokens[t]][.]) * scale, the
+ * embedding-row decoder g4_q6_embed_row (Sources/LeviathanCore/Gemma4.swift:4210-4245; the caller at
+ * :3560-3578 passes scale = sqrt(hidden)); a Q6_K value is ((d * s) * level) * scale with every product
+ * rounded to f32, as there.  Q4_0 and Q4_K tensors are read the same way (decoded value * scale).
+ * tokens is DEVICE memory, so the id lev_argmax wrote feeds the next step without a host round trip; an
+ * id outside [0, rows) leaves a zero row and the next lev_cuda_synchronize returns LEV_BAD_DIMENSIONS.  Reads
+ * the tensor's GGUF-order copy: refused after lev_weights_release_gguf.
+ * lev_softcap: x = cap * tanh(x / cap) in place (g4_softcap, Gemma4.swift:4496-4503; tanh through
+ * exp(-2|x|), :4360-4367).  Asynchronous on the context's stream. */
+int lev_embed_rows(lev_ctx* ctx, const lev_weights* w, const int32_t* tokens, int64_t n_tokens,
+                   float scale, float* y);
+int lev_softcap(lev_ctx* ctx, float* x, int64_t n, float cap);
 
 /* The same steps folded into the matvec launch: the prologue is applied while the kernel builds
  * its activation tables (the norm's statistic is reduced by every thread block for itself), the
@@ -352,6 +364,13 @@ int lev_qkv_norm_rope_append(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, 
                              const float* inv_freq, const int32_t* pos, const lev_kv_layout* layout,
                              void* k_pool, void* v_pool, const int32_t* block_table,
                              const int32_t* slot);
+/* The same with q [n_cols][q_heads * head_dim], k and v [n_cols][kv_heads * head_dim] as three
+ * matrices, the form the projections of several sequences leave them in. */
+int lev_qkv_norm_rope_append_split(lev_ctx* ctx, float* q, float* k, float* v, int n_cols,
+                                   int q_heads, int head_dim, const float* q_weight,
+                                   const float* k_weight, float eps, const float* inv_freq,
+                                   const int32_t* pos, const lev_kv_layout* layout, void* k_pool,
+                                   void* v_pool, const int32_t* block_table, const int32_t* slot);
 
 /* ---- routed MoE composite ----------------------------------------------
  * Expert weights are the fused gate_up tensor [experts][2*inter][hidden] and

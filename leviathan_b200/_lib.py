@@ -99,7 +99,10 @@ SIGNATURES = {
     "lev_axpy": (_I, [_P, C.c_float, _P, _P, _L, _P]),
     "lev_qkv_norm_rope": (_I, [_P, _P, _I, _I, _I, _I, _P, _P, C.c_float, _P, _P]),
     "lev_qkv_norm_rope_append": (_I, [_P, _P, _I, _I, _I, _P, _P, C.c_float, _P, _P, C.POINTER(KVLayout), _P, _P, _P, _P]),
+    "lev_qkv_norm_rope_append_split": (_I, [_P, _P, _P, _P, _I, _I, _I, _P, _P, C.c_float, _P, _P, C.POINTER(KVLayout), _P, _P, _P, _P]),
     "lev_argmax": (_I, [_P, _P, _L, _L, _P, _P]),
+    "lev_embed_rows": (_I, [_P, _P, _P, _L, C.c_float, _P]),
+    "lev_softcap": (_I, [_P, _P, _L, C.c_float]),
     "lev_matvec_fused": (_I, [_P, _P, _L, _L, _P, _L, _I, C.POINTER(Fusion), _P, _L]),
     "lev_matvec_chain": (_I, [_P, _I, C.POINTER(ChainOp), _U]),
     "lev_matvec_multi_fused": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(Fusion), C.POINTER(_P), C.POINTER(_L)]),

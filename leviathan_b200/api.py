@@ -283,6 +283,15 @@ class Context:
                                                       _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), _ptr(slot)))
         return qkv
 
+    def qkv_norm_rope_append_split(self, q, k, v, q_heads: int, cache: "PagedKV", slot, pos, q_weight=None, k_weight=None,
+                                   eps: float = 1e-6, inv_freq=None):
+        """lev_qkv_norm_rope_append_split: q [n][q_heads * head_dim], k, v [n][kv_heads * head_dim] as three matrices."""
+        self._flags(False, False)
+        self._check(self.lib.lev_qkv_norm_rope_append_split(self.handle, _ptr(q), _ptr(k), _ptr(v), q.shape[0], q_heads, cache.layout.head_dim,
+                                                            _ptr(q_weight), _ptr(k_weight), eps, _ptr(inv_freq), _ptr(pos),
+                                                            C.byref(cache.layout), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table), _ptr(slot)))
+        return q, k, v
+
     def argmax(self, x, want_margin: bool = False):
         """lev_argmax over the rows of x [vectors][n]: int32 indices (and best - second best)."""
         import torch
@@ -293,6 +302,28 @@ class Context:
         self._flags(False, False)
         self._check(self.lib.lev_argmax(self.handle, _ptr(x2), x2.shape[0], x2.shape[1], _ptr(idx), _ptr(mar)))
         return (idx, mar) if want_margin else idx
+
+    def argmax_into(self, x, out_index):
+        """lev_argmax writing into an existing int32 tensor (the token ids of the next step)."""
+        self._flags(False, False)
+        self._check(self.lib.lev_argmax(self.handle, _ptr(x), x.shape[0], x.shape[1], _ptr(out_index), None))
+        return out_index
+
+    def embed_rows(self, w: Weights, tokens, scale: float = 1.0, out=None):
+        """lev_embed_rows: out[t] = row tokens[t] of w, decoded, times scale; tokens is an int32 device tensor."""
+        import torch
+
+        n = tokens.numel()
+        out = torch.empty((n, w.cols), dtype=torch.float32, device=tokens.device) if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_embed_rows(self.handle, w.handle, _ptr(tokens), n, scale, _ptr(out)))
+        return out
+
+    def softcap(self, x, cap: float):
+        """lev_softcap: x = cap * tanh(x / cap), in place."""
+        self._flags(False, False)
+        self._check(self.lib.lev_softcap(self.handle, _ptr(x), x.numel(), cap))
+        return x
 
     @staticmethod
     def _fusion(prologue, norm_weight, eps, residual, alpha):

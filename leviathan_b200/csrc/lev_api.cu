@@ -188,7 +188,7 @@ extern "C" int lev_cuda_synchronize(lev_ctx* ctx) {
         lev_chain_reset(ctx);
         return lev_fail(ctx, LEV_TIMEOUT, "a kernel's bounded wait ran out");
     }
-    if (bits & LEV_DEV_BAD_INDEX) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "a slot, position or block-table entry lay outside the cache layout");
+    if (bits & LEV_DEV_BAD_INDEX) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "a slot, position, block-table entry or token id lay outside its table");
     return LEV_OK;
 }
 

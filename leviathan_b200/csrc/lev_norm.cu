@@ -536,16 +536,25 @@ struct KvTarget {
     int page, max_blocks, slots, f16;
 };
 
-__global__ void __launch_bounds__(128) k_qkv_norm_rope(float* x, int q_heads, int kv_heads, int hd, const float* __restrict__ qw,
+// the rows the launch works on: column c's q heads at q + c * q_stride, its k heads at k + c * kv_stride, its
+// v heads at v + c * kv_stride (one [q | k | v] row per column, or three separate matrices)
+struct QkvRows {
+    float *q, *k, *v;
+    int64_t q_stride, kv_stride;
+};
+
+__global__ void __launch_bounds__(128) k_qkv_norm_rope(QkvRows X, int q_heads, int kv_heads, int hd, const float* __restrict__ qw,
                                                         const float* __restrict__ kw, float eps, const float* __restrict__ inv_freq,
                                                         const int32_t* __restrict__ pos, KvTarget C) {
     __shared__ float row[512];
     __shared__ float part[4];
     pdl_wait();
     pdl_launch_dependents();
-    const int head = blockIdx.x, col = blockIdx.y, heads = q_heads + 2 * kv_heads;
-    float* xv = x + ((int64_t)col * heads + head) * hd;
+    const int head = blockIdx.x, col = blockIdx.y;
     const bool is_q = head < q_heads, is_k = !is_q && head < q_heads + kv_heads;
+    float* xv = is_q ? X.q + col * X.q_stride + (int64_t)head * hd
+                     : (is_k ? X.k + col * X.kv_stride + (int64_t)(head - q_heads) * hd
+                             : X.v + col * X.kv_stride + (int64_t)(head - q_heads - kv_heads) * hd);
     const float* w = is_q ? qw : (is_k ? kw : nullptr);
     float ss = 0.f;
     for (int i = threadIdx.x; i < hd; i += 128) {
@@ -602,6 +611,11 @@ __global__ void __launch_bounds__(128) k_qkv_norm_rope(float* x, int q_heads, in
     }
 }
 
+QkvRows one_row(float* qkv, int q_heads, int kv_heads, int hd) {
+    const int64_t stride = (int64_t)(q_heads + 2 * kv_heads) * hd;
+    return {qkv, qkv + (int64_t)q_heads * hd, qkv + (int64_t)(q_heads + kv_heads) * hd, stride, stride};
+}
+
 }  // namespace
 
 extern "C" int lev_qkv_norm_rope(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int kv_heads, int head_dim, const float* q_weight,
@@ -614,18 +628,18 @@ extern "C" int lev_qkv_norm_rope(lev_ctx* ctx, float* qkv, int n_cols, int q_hea
     if (inv_freq && !pos) return lev_fail(ctx, LEV_BAD_ARGUMENT, "rotary frequencies without positions");
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
     KvTarget none = {};
-    LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * kv_heads, n_cols), dim3(128), 0, ctx->stream, qkv, q_heads, kv_heads, head_dim,
-                             q_weight, k_weight, eps, inv_freq, pos, none));
+    LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * kv_heads, n_cols), dim3(128), 0, ctx->stream,
+                             one_row(qkv, q_heads, kv_heads, head_dim), q_heads, kv_heads, head_dim, q_weight, k_weight, eps, inv_freq, pos, none));
     ctx->launches++;
     return LEV_OK;
 }
 
 // The same launch also stores the finished k and v heads at pos[column] of sequence slot[column] of a paged
 // cache (lev_kv_append's job; the append of Sources/LeviathanCore/Gemma4.swift:3688-3698 without a launch).
-extern "C" int lev_qkv_norm_rope_append(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int head_dim, const float* q_weight,
-                                        const float* k_weight, float eps, const float* inv_freq, const int32_t* pos,
-                                        const lev_kv_layout* L, void* k_pool, void* v_pool, const int32_t* block_table, const int32_t* slot) {
-    if (!ctx || !qkv || !pos || !L || !k_pool || !v_pool || !block_table || !slot) return LEV_BAD_ARGUMENT;
+namespace {
+int norm_rope_append(lev_ctx* ctx, QkvRows X, int n_cols, int q_heads, int head_dim, const float* q_weight, const float* k_weight, float eps,
+                     const float* inv_freq, const int32_t* pos, const lev_kv_layout* L, void* k_pool, void* v_pool,
+                     const int32_t* block_table, const int32_t* slot) {
     if (L->kv_type != LEV_KV_F16 && L->kv_type != LEV_KV_F32) return lev_fail(ctx, LEV_BAD_ARGUMENT, "cache element type %d", L->kv_type);
     if (L->head_dim != head_dim || L->kv_heads < 1 || L->page <= 0 || L->blocks <= 0 || L->max_blocks <= 0 || L->slots <= 0)
         return lev_fail(ctx, LEV_BAD_DIMENSIONS, "cache layout does not match the heads (head_dim %d / %d)", L->head_dim, head_dim);
@@ -635,8 +649,28 @@ extern "C" int lev_qkv_norm_rope_append(lev_ctx* ctx, float* qkv, int n_cols, in
     if (!(eps >= 0.f) || !isfinite(eps)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "epsilon %g", (double)eps);
     LEV_CUDA(ctx, cudaSetDevice(ctx->device));
     KvTarget C = {k_pool, v_pool, block_table, slot, ctx->d_status, L->blocks, L->page, L->max_blocks, L->slots, L->kv_type == LEV_KV_F16};
-    LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * L->kv_heads, n_cols), dim3(128), 0, ctx->stream, qkv, q_heads, L->kv_heads,
+    LEV_CUDA(ctx, launch_pdl(k_qkv_norm_rope, dim3(q_heads + 2 * L->kv_heads, n_cols), dim3(128), 0, ctx->stream, X, q_heads, L->kv_heads,
                              head_dim, q_weight, k_weight, eps, inv_freq, pos, C));
     ctx->launches++;
     return LEV_OK;
+}
+}  // namespace
+
+extern "C" int lev_qkv_norm_rope_append(lev_ctx* ctx, float* qkv, int n_cols, int q_heads, int head_dim, const float* q_weight,
+                                        const float* k_weight, float eps, const float* inv_freq, const int32_t* pos,
+                                        const lev_kv_layout* L, void* k_pool, void* v_pool, const int32_t* block_table, const int32_t* slot) {
+    if (!ctx || !qkv || !pos || !L || !k_pool || !v_pool || !block_table || !slot) return LEV_BAD_ARGUMENT;
+    return norm_rope_append(ctx, one_row(qkv, q_heads, L->kv_heads, head_dim), n_cols, q_heads, head_dim, q_weight, k_weight, eps, inv_freq, pos, L,
+                            k_pool, v_pool, block_table, slot);
+}
+
+// q [n_cols][q_heads * head_dim], k and v [n_cols][kv_heads * head_dim] as three matrices: the form the projections
+// of several sequences leave them in
+extern "C" int lev_qkv_norm_rope_append_split(lev_ctx* ctx, float* q, float* k, float* v, int n_cols, int q_heads, int head_dim,
+                                              const float* q_weight, const float* k_weight, float eps, const float* inv_freq,
+                                              const int32_t* pos, const lev_kv_layout* L, void* k_pool, void* v_pool,
+                                              const int32_t* block_table, const int32_t* slot) {
+    if (!ctx || !q || !k || !v || !pos || !L || !k_pool || !v_pool || !block_table || !slot) return LEV_BAD_ARGUMENT;
+    const QkvRows X = {q, k, v, (int64_t)q_heads * head_dim, (int64_t)L->kv_heads * head_dim};
+    return norm_rope_append(ctx, X, n_cols, q_heads, head_dim, q_weight, k_weight, eps, inv_freq, pos, L, k_pool, v_pool, block_table, slot);
 }

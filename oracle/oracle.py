@@ -455,3 +455,57 @@ def matvec_threaded(ggml_type, w, rows, cols, x, threads, lib_path=None):
 
 def hardware_threads() -> int:
     return lib().lev_or_hardware_threads()
+
+
+# ---- the ends of a decode step and the step itself ----
+def embed_row(ggml_type, w, rows, cols, token: int, scale: float) -> np.ndarray:
+    """Row `token` of a quantized tensor times scale: every value decoded as the reference decodes it,
+    then one f32 product (g4_q6_embed_row, Sources/LeviathanCore/Gemma4.swift:4210-4245:
+    y = d * s * level * scale, left to right in f32; d * s * level is exact in f32)."""
+    values, bts = BLOCK[ggml_type]
+    row_bytes = cols // values * bts
+    one = _u8(w)[token * row_bytes:(token + 1) * row_bytes]
+    return (dequantize_rows(ggml_type, one, 1, cols)[0] * np.float32(scale)).astype(np.float32)
+
+
+def softcap_f64(x, cap: float) -> np.ndarray:
+    """cap * tanh(x / cap) (g4_softcap, Gemma4.swift:4496-4503), in f64."""
+    return float(cap) * np.tanh(np.asarray(x, np.float64) / float(cap))
+
+
+def decode_step_f64(cfg, host, token: int, pos: int, k_cache, v_cache) -> dict:
+    """One token of one sequence through the synthetic decoder, every product in f64 (stage outputs are
+    rounded to f32 where the next oracle function takes f32).  The steps are the subset of
+    Gemma4Runner.forwardToken / forwardLayer (Gemma4.swift:3611-3905) the synthetic workload keeps:
+    embedding row * sqrt(hidden); per layer RMSNorm -> q, k, v; per-head RMSNorm(q_norm / k_norm / none)
+    and rotary on q and k; the new k, v rows (rounded to f16) stored at `pos`; attention over
+    [0, pos]; x += Wo a; RMSNorm -> softmax router, top-k, renormalized weights, experts, ordered
+    combine; x += that; final RMSNorm -> head -> softcap -> argmax.
+    `host[name]` holds GGUF block bytes / f32 arrays by tensor name; k_cache / v_cache are per-layer
+    f16 arrays [positions][kv_heads][head_dim] of this sequence, updated in place."""
+    H, QH, KVH, HD = cfg.hidden, cfg.q_heads, cfg.kv_heads, cfg.head_dim
+    inv_freq = (cfg.rope_base ** (-np.arange(HD // 2, dtype=np.float64) / (HD // 2))).astype(np.float32)
+    x = embed_row(cfg.head_type, host["token_embd"], cfg.vocab, H, token, np.float32(np.sqrt(np.float64(H)))).astype(np.float64)
+    routing = []
+    for l in range(cfg.layers):
+        p = f"blk.{l}."
+        h = rmsnorm_f64(x, host[p + "attn_norm"], cfg.eps)[0]
+        q = matvec_f64(cfg.weight_type, host[p + "attn_q"], QH * HD, H, h)
+        k = matvec_f64(cfg.weight_type, host[p + "attn_k"], KVH * HD, H, h)
+        v = matvec_f64(cfg.weight_type, host[p + "attn_v"], KVH * HD, H, h)
+        q = head_norm_rope_f64(q.reshape(QH, HD), host[p + "attn_q_norm"], cfg.eps, inv_freq, pos)
+        k = head_norm_rope_f64(k.reshape(KVH, HD), host[p + "attn_k_norm"], cfg.eps, inv_freq, pos)
+        v = head_norm_rope_f64(v.reshape(KVH, HD), None, cfg.eps, None, pos)
+        k_cache[l][pos] = k.astype(np.float16)
+        v_cache[l][pos] = v.astype(np.float16)
+        a = attention_f64(q, k_cache[l][:pos + 1].astype(np.float32), v_cache[l][:pos + 1].astype(np.float32), 0, cfg.attn_scale)
+        x1 = x + matvec_f64(cfg.weight_type, host[p + "attn_output"], H, QH * HD, a.reshape(-1))
+        h2 = rmsnorm_f64(x1, host[p + "ffn_norm"], cfg.eps)[0]
+        idx, wts, _, out64 = moe_token(H, cfg.expert_inter, cfg.experts, cfg.top_k, host[p + "ffn_gate_inp"],
+                                       host[p + "ffn_gate_up_exps"], host[p + "ffn_down_exps"], h2)
+        routing.append((idx, wts))
+        x = x1 + out64
+    hn = rmsnorm_f64(x, host["output_norm"], cfg.eps)[0]
+    raw = matvec_f64(cfg.head_type, host["token_embd"], cfg.vocab, H, hn)
+    logits = softcap_f64(raw, cfg.softcap)
+    return {"x": x, "logits": logits, "token": int(np.argmax(logits)), "routing": routing}

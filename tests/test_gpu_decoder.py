@@ -1,0 +1,125 @@
+"""The ends of a decode step (lev_embed_rows, lev_softcap) and the whole synthetic decoder step, eager and as
+one CUDA graph, against the f64 oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import leviathan_b200 as lev
+from leviathan_b200 import quant as Q
+from leviathan_b200.decoder import DecoderConfig, SyntheticDecoder
+from oracle import oracle as O
+
+from helpers import quantized, random_blocks
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ctx():
+    c = lev.Context(0)
+    yield c
+    c.close()
+
+
+@pytest.mark.parametrize("name,t,cols", [("q6_k", Q.GGML_Q6_K, 2816), ("q4_k", Q.GGML_Q4_K, 512), ("q4_0", Q.GGML_Q4_0, 96)])
+@pytest.mark.parametrize("encoded", [True, False])
+def test_embedding_rows_are_bit_exact(ctx, name, t, cols, encoded):
+    rows = 40
+    w = quantized(t, 11, rows, cols) if encoded else random_blocks(t, 12, rows, cols)
+    wd = ctx.upload(torch.from_numpy(w).cuda(), t, rows, cols)
+    toks = [0, 39, 17, 17, 3]
+    scale = math.sqrt(cols)
+    got = ctx.embed_rows(wd, torch.tensor(toks, dtype=torch.int32, device="cuda"), scale).cpu().numpy()
+    for i, tk in enumerate(toks):
+        want = O.embed_row(t, w, rows, cols, tk, scale)
+        assert np.array_equal(got[i].view(np.uint32), want.view(np.uint32)), (name, tk)
+    wd.free()
+
+
+def test_embedding_row_outside_the_tensor_is_reported_not_read(ctx):
+    w = quantized(Q.GGML_Q6_K, 5, 8, 256)
+    wd = ctx.upload(torch.from_numpy(w).cuda(), Q.GGML_Q6_K, 8, 256)
+    out = ctx.embed_rows(wd, torch.tensor([2, 8, -1], dtype=torch.int32, device="cuda"), 1.0)
+    with pytest.raises(lev.LevError):
+        ctx.synchronize()
+    o = out.cpu().numpy()
+    assert np.array_equal(o[0], O.embed_row(Q.GGML_Q6_K, w, 8, 256, 2, 1.0)) and not o[1].any() and not o[2].any()
+    ctx.synchronize()  # the report was consumed
+    wd.release_gguf()
+    with pytest.raises(lev.LevError):
+        ctx.embed_rows(wd, torch.tensor([1], dtype=torch.int32, device="cuda"), 1.0)
+    wd.free()
+
+
+def test_softcap(ctx):
+    x = np.concatenate([Q.normal(3, (100000,), 20.0), np.array([0.0, -0.0, 1e-30, 1e4, -1e4, 88.0, -3e38, 3e38], np.float32)])
+    got = ctx.softcap(torch.from_numpy(x.copy()).cuda(), 30.0).cpu().numpy()
+    want = O.softcap_f64(x, 30.0)
+    assert np.isfinite(got).all()
+    assert np.max(np.abs(got - want) / np.maximum(1.0, np.abs(want))) < 4e-6
+    assert np.array_equal(np.signbit(got), np.signbit(x))
+    assert got[-1] == 30.0 and got[-2] == -30.0
+    with pytest.raises(lev.LevError):
+        ctx.softcap(torch.zeros(4, device="cuda"), 0.0)
+
+
+SMALL = dict(hidden=256, layers=2, q_heads=4, kv_heads=2, head_dim=128, experts=8, top_k=2, expert_inter=64, vocab=512,
+             positions=48, page=16)
+
+
+def _reference_step(dec, cfg, batch, pos):
+    """per sequence: the oracle's step over host copies of this decoder's tensors and caches"""
+    out = []
+    for s in range(batch):
+        kc, vc = [], []
+        for L in dec.layers:
+            tab = L.cache.table_host[s]
+            k = L.cache.k.cpu().numpy().reshape(-1, cfg.page, cfg.kv_heads, cfg.head_dim)
+            v = L.cache.v.cpu().numpy().reshape(-1, cfg.page, cfg.kv_heads, cfg.head_dim)
+            kc.append(np.concatenate([k[b] for b in tab])[:cfg.positions].copy())
+            vc.append(np.concatenate([v[b] for b in tab])[:cfg.positions].copy())
+        out.append(O.decode_step_f64(cfg, dec.host, int(dec.tok[s].item()), pos, kc, vc))
+    return out
+
+
+@pytest.mark.parametrize("batch", [1, 3, 11])
+def test_decoder_step_against_the_f64_oracle_eager_and_as_one_graph(ctx, batch):
+    cfg = DecoderConfig(**SMALL)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        dec = SyntheticDecoder(ctx, cfg, batch=batch, keep_host_copies=True)
+        dec.tok.copy_(torch.tensor([(7 * s + 5) % cfg.vocab for s in range(batch)], dtype=torch.int32))
+        tok0 = dec.tok.clone()
+        stream.synchronize()
+        refs = _reference_step(dec, cfg, batch, cfg.positions - 1)
+        dec.step()
+        ctx.synchronize()
+        logits = dec.logits.cpu().numpy().copy()
+        toks = dec.tok.cpu().numpy().copy()
+        for s in range(batch):
+            want = refs[s]["logits"]
+            err = np.max(np.abs(logits[s] - want)) / max(1.0, float(np.max(np.abs(want))))
+            assert err < 2e-4, (s, err)
+            top2 = np.sort(want)[-2:]
+            if top2[1] - top2[0] > 1e-3:
+                assert toks[s] == refs[s]["token"]
+            assert toks[s] == int(np.argmax(logits[s]))
+        # the same step as one graph: same bits, and the token it leaves is the next step's input
+        dec.tok.copy_(tok0)
+        dec.capture()
+        l0 = ctx.launch_count()
+        dec.replay()
+        ctx.synchronize()
+        assert ctx.launch_count() == l0  # a replay makes no call into the library
+        assert np.array_equal(dec.logits.cpu().numpy().view(np.uint32), logits.view(np.uint32))
+        assert np.array_equal(dec.tok.cpu().numpy(), toks)
+        dec.replay()
+        ctx.synchronize()
+        second = dec.tok.cpu().numpy().copy()
+        dec.tok.copy_(torch.from_numpy(toks))
+        dec.step()
+        ctx.synchronize()
+        assert np.array_equal(dec.tok.cpu().numpy(), second)
+        dec.free()
