@@ -813,121 +813,73 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
         moe[f"T{batch}"] = entry
     out["moe_layer"] = {"workload": "128 experts Q4_0 (GU 1408x2816, DN 2816x704), top-8, hidden 2816",
                         "parallelism": "single GPU" if world == 1 else f"expert-parallel over {world} GPUs", **moe}
-    if world == 1:
-        try:
-            out["decode_layer"] = _decode_layer(ctx, mw, dev, stream, g, peaks)
-        except Exception as e:  # a side measurement never takes the headline down
-            out["decode_layer"] = {"error": repr(e)}
-        try:
-            out["head_argmax"] = _head_argmax(ctx, dev, stream, g, peaks)
-        except Exception as e:
-            out["head_argmax"] = {"error": repr(e)}
     mw.free()
+    if world == 1:
+        for b in (1, 32):
+            try:
+                out[f"decode_step_batch_{b}"] = _decode_step(ctx, dev, stream, peaks, b)
+            except Exception as e:  # a side measurement never takes the headline down
+                out[f"decode_step_batch_{b}"] = {"error": repr(e)}
     return out if rank == 0 else None
 
 
-def _head_argmax(ctx, dev, stream, g, peaks):
-    """The output head of the decode step: final norm folded into a Q6_K [262144 x 2816] matvec, then the
-    greedy token choice on the device (Sources/LeviathanCore/Gemma4.swift:3623-3643, whose softcap is monotonic and does not move the maximum; argmax of
-    rust/crates/lev-forge/src/ops.rs:478-517).  One resident head (605 MB, beyond L2 by itself)."""
+def _decode_step(ctx, dev, stream, peaks, batch):
+    """The synthetic 30-layer MoE decode step (leviathan_b200/decoder.py: the token loop of
+    Sources/LeviathanCore/Gemma4.swift:3611-3905 without its host round trips) as ONE CUDA graph: embedding row ->
+    30 x [norm, q/k/v, head norms + rotary + cache append, attention over 4096 cached positions, output
+    projection, norm, 128-expert top-8 MoE] -> norm -> Q6_K [262144 x 2816] head -> softcap -> argmax.  A replay
+    decodes one token per sequence and leaves the next token ids on the device."""
     import torch
 
-    from leviathan_b200 import quant as Qd
+    from leviathan_b200.decoder import DecoderConfig, SyntheticDecoder
 
-    V, H = 262144, MOE_HIDDEN
-    parts = []
-    for r0 in range(0, V, 32768):  # quantized in slabs to bound the f32 staging
-        parts.append(Qd.quantize(Q6_K, torch.randn((32768, H), generator=g, device=dev) * 0.02))
-    wh = ctx.upload(torch.cat(parts), Q6_K, V, H)
-    del parts
-    x = torch.randn((1, H), generator=g, device=dev)
-    ones = torch.ones(H, device=dev)
-    logits = torch.empty((1, V), device=dev)
-    tok = torch.empty(1, dtype=torch.int32, device=dev)
+    cfg = DecoderConfig()
+    with torch.cuda.stream(stream):
+        t0 = time.time()
+        dec = SyntheticDecoder(ctx, cfg, batch=batch, device=dev)
+        torch.cuda.synchronize()
+        build_s = time.time() - t0
+        l0 = ctx.launch_count()
+        dec.step()
+        ctx.synchronize()
+        launches = ctx.launch_count() - l0
+        finite = bool(torch.isfinite(dec.logits).all())
+        agree = bool((dec.tok.long() == torch.argmax(dec.logits, dim=1)).all())
+        dec.capture()
+        for _ in range(3):
+            dec.replay()
+        ts = []
+        for _ in range(9):
+            a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a0.record(stream)
+            dec.replay()
+            a1.record(stream)
+            a1.synchronize()
+            ts.append(a0.elapsed_time(a1))
+        ms = statistics.median(ts)
 
-    def step(i):
-        ctx.matvec_fused(wh, x, "rmsnorm", ones, 1e-6, out=logits)
-        ctx.lib.lev_argmax(ctx.handle, logits.data_ptr(), 1, V, tok.data_ptr(), None)
+        def head(i):
+            for a, b in dec._cols():
+                ctx.matvec_fused(dec.head, dec.x[a:b], "rmsnorm", dec.out_norm, cfg.eps, out=dec.logits[a:b])
+            ctx.softcap(dec.logits, cfg.softcap)
+            ctx.argmax_into(dec.logits, dec.tok)
 
-    step(0)
-    torch.cuda.synchronize()
-    agree = int(tok.item()) == int(torch.argmax(logits[0]).item())
-    ms = _graph_time(torch, stream, step, 6)
-    ms_mv = _graph_time(torch, stream, lambda i: ctx.matvec_fused(wh, x, "rmsnorm", ones, 1e-6, out=logits), 6)
-    byts = V * (H // 256) * 210 + V * 4 + H * 4
-    wh.free()
-    return {"workload": "rmsnorm -> Q6_K [262144 x 2816] head matvec -> argmax on the device, batch 1", "launches_per_step": 3,
-            "us_per_step": ms * 1e3, "us_matvec": ms_mv * 1e3, "algorithmic_bytes": byts, "gbs": byts / ms / 1e6,
-            "hbm_frac": byts / ms / 1e6 / peaks["hbm_gbs"], "argmax_matches_torch": agree}
-
-
-def _decode_layer(ctx, mw, dev, stream, g, peaks):
-    """One synthetic decoder layer at batch 1, every step a C-ABI call on one stream, no host round trip:
-    norm -> q, k, v (one launch) -> cache append -> attention over 4096 cached positions -> output
-    projection + residual -> shared FFN (norm -> gate, up; gelu-up -> down + residual) -> norm -> routed
-    MoE (128 experts, top-8) -> residual.  The per-head q / k / v norms and the rotary embedding of a
-    local layer and the cache append (Sources/LeviathanCore/Gemma4.swift:3662-3698) run as one launch after
-    the projections."""
-    import torch
-
-    import leviathan_b200 as lev_pkg
-    from leviathan_b200 import quant as Qd
-
-    H, QH, KVH, HD, SH, TOK, PAGE = MOE_HIDDEN, 16, 8, 256, 2112, 4096, 16
-    sets = []
-    for i in range(3):  # three layers' weights and caches are cycled (about 190 MB, beyond L2)
-        def up(t, rows, cols):
-            return ctx.upload(Qd.quantize(t, torch.randn((rows, cols), generator=g, device=dev) * 0.02), t, rows, cols)
-
-        c = lev_pkg.PagedKV(TOK // PAGE + 1, PAGE, KVH, HD, slots=1, max_blocks=TOK // PAGE, dtype="f16", device=dev)
-        for p_ in range(0, TOK, PAGE):
-            c.ensure(0, p_)
-        c.k.copy_((torch.randn(c.k.shape, generator=g, device=dev) * 0.1).to(torch.float16))
-        c.v.copy_(torch.randn(c.v.shape, generator=g, device=dev).to(torch.float16))
-        sets.append(dict(wq=up(Q4_K, QH * HD, H), wk=up(Q4_K, KVH * HD, H), wv=up(Q4_K, KVH * HD, H), wo=up(Q4_K, H, QH * HD),
-                         wg=up(Qd.GGML_Q4_0, SH, H), wu=up(Qd.GGML_Q4_0, SH, H), wd=up(Qd.GGML_Q4_0, H, SH), cache=c))
-    ones = torch.ones(H, device=dev)
-    x = torch.randn((1, H), generator=g, device=dev)
-    qkv = torch.empty((1, (QH + 2 * KVH) * HD), device=dev)
-    qb, kb, vb = qkv[:, :QH * HD], qkv[:, QH * HD:(QH + KVH) * HD], qkv[:, (QH + KVH) * HD:]
-    head_w = torch.ones(HD, device=dev)
-    inv_freq = (10000.0 ** (-torch.arange(HD // 2, device=dev, dtype=torch.float64) / (HD // 2))).float()
-    ao, x1, gub = torch.empty((1, QH, HD), device=dev), torch.empty((1, H), device=dev), torch.empty((1, 2 * SH), device=dev)
-    x2, hb, mo, x3 = (torch.empty((1, H), device=dev) for _ in range(4))
-    slot = torch.zeros(1, dtype=torch.int32, device=dev)
-    pos = torch.full((1,), TOK - 1, dtype=torch.int32, device=dev)
-    l0 = ctx.launch_count()
-
-    def layer(i):
-        w = sets[i % 3]
-        ctx.matvec_multi_fused([w["wq"], w["wk"], w["wv"]], x, "rmsnorm", ones, 1e-6, outs=[qb, kb, vb])
-        ctx.qkv_norm_rope_append(qkv, QH, w["cache"], slot, pos, head_w, head_w, 1e-6, inv_freq)
-        ctx.attn_decode(w["cache"], slot, pos, qb.reshape(1, QH, HD), 0, 1.0, out=ao)
-        ctx.matvec_fused(w["wo"], ao.view(1, QH * HD), None, residual=x, alpha=1.0, out=x1)
-        ctx.matvec_multi_fused([w["wg"], w["wu"]], x1, "rmsnorm", ones, 1e-6, outs=[gub[:, :SH], gub[:, SH:]])
-        ctx.matvec_fused(w["wd"], gub, "gelu_up", residual=x1, alpha=1.0, out=x2)
-        ctx.rmsnorm(x1, ones, 1e-6, out=hb)
-        ctx.moe_layer(mw, hb, MOE_TOPK, out=mo)
-        ctx.axpy(1.0, mo, x2, out=x3)
-
-    layer(0)
-    torch.cuda.synchronize()
-    launches = ctx.launch_count() - l0
-    finite = bool(torch.isfinite(x3).all())
-    ms = _graph_time(torch, stream, layer, 12)
-    dense_bytes = ((QH + 2 * KVH) * HD * H + H * QH * HD) * 144 // 256 + 3 * SH * H * 18 // 32
-    kv_bytes = 2 * TOK * KVH * HD * 2
-    moe_bytes = MOE_ROUTER_BYTES + MOE_TOPK * MOE_EXPERT_BYTES
-    total = dense_bytes + kv_bytes + moe_bytes
-    for w in sets:
-        for k_, v_ in w.items():
-            if k_ != "cache":
-                v_.free()
-    return {"workload": "hidden 2816: Q4_K q/k/v/o (16 q heads, 8 KV heads, head_dim 256), fp16 paged cache at 4096 positions, "
-                        "Q4_0 shared FFN 2112, 128-expert Q4_0 MoE top-8; batch 1",
-            "launches_per_layer": int(launches), "us_per_layer": ms * 1e3, "algorithmic_bytes": total,
-            "gbs": total / ms / 1e6, "hbm_frac": total / ms / 1e6 / peaks["hbm_gbs"], "outputs_finite": finite,
-            "tokens_per_s_30_layers": 1.0 / (30 * ms * 1e-3)}
+        ms_head = _graph_time(torch, stream, head, 4)
+    bt = cfg.bytes_per_token()
+    # weights are read once per step whatever the batch; every sequence reads its own cache; the experts a
+    # step touches: all top-8 at one sequence, the expected distinct count of a uniform routing otherwise
+    distinct = cfg.top_k if batch == 1 else cfg.experts * (1.0 - (1.0 - cfg.top_k / cfg.experts) ** batch)
+    step_bytes = cfg.layers * (bt["attention_weights"] + bt["router"] + distinct * bt["expert"] + batch * bt["kv_per_sequence"]) + bt["head"]
+    bound_ms = step_bytes / (peaks["hbm_gbs"] * 1e6)
+    dec.free()
+    del dec
+    torch.cuda.empty_cache()
+    return {"workload": f"30 layers, hidden 2816, Q4_0 q/k/v/o (16 q heads, 8 KV heads, head_dim 256), fp16 paged cache at 4096 "
+                        f"positions, 128-expert Q4_0 MoE top-8, tied Q6_K head 262144, softcap 30, argmax; batch {batch}",
+            "one_cuda_graph": True, "launches_per_step": int(launches), "ms_per_step": ms, "tokens_per_s": batch / ms * 1e3,
+            "algorithmic_bytes_per_step": int(step_bytes), "hbm_bound_ms": bound_ms, "hbm_frac": bound_ms / ms,
+            "us_head_softcap_argmax": ms_head * 1e3, "head_gbs": bt["head"] / ms_head / 1e6,
+            "outputs_finite": finite, "argmax_matches_torch": agree, "build_seconds": build_s}
 
 
 def main():

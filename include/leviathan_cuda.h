@@ -417,9 +417,14 @@ int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_
  * Accepts the op JSON of Q4OpIR (Sources/LeviathanCore/Q4Lowering.swift:50-145,
  * producer tools/q4_lower/q4_op_model.py:76-124) extended with
  * quant "q4_k" / "q6_k", `columns` and op "<quant>.gemm"; and the region JSON
- * of MoERegionIR (Sources/LeviathanCore/MoELowering.swift:176-283; scalar
- * fields and graphSha256, not the graph re-walk).  Unknown fields are
- * rejected.  Replaces installQ4GeneratedKernel / uninstall
+ * of MoERegionIR (Sources/LeviathanCore/MoELowering.swift:176-283): scalar
+ * fields, graphSha256 over the canonical node lines (:66-168), and the
+ * structural re-derivation of the region from its graph
+ * (MoERegionGraphWalk.walk, :300-571: three placeholders, per slot select ->
+ * linear -> split -> getitem 0/1 -> gelu(tanh) * up -> linear over the slot's
+ * down slice, one stack, static f32 shapes, no node shared between slots, the
+ * exact ATen census), whose dims the declared ones must equal.  Unknown fields
+ * are rejected.  Replaces installQ4GeneratedKernel / uninstall
  * (Sources/LeviathanCore/Gemma4.swift:1022-1110). */
 int lev_op_install_json(lev_ctx* ctx, const char* json, size_t json_len, lev_op** out);
 int lev_op_uninstall(lev_ctx* ctx, lev_op* op);

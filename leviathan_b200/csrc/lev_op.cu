@@ -11,8 +11,9 @@
 // Identity is the SHA-256 of the sorted-keys compact JSON (Q4Lowering.swift:
 // 176-181); for a region it is the graph digest over the canonical node lines
 // (MoELowering.swift:66-168), which must equal the document's graphSha256.
-// The region's full dataflow re-walk (MoELowering.swift:300-571) is not
-// repeated here; the scalar contract, the ATen census and the digest are.
+// The region's dataflow is re-derived from the graph itself (RegionWalk below,
+// the checks of MoERegionGraphWalk.walk, MoELowering.swift:300-571): the
+// document's declared dims must agree with what the graph says.
 #include <stdlib.h>
 
 #include <map>
@@ -239,6 +240,203 @@ bool canon_meta(const JVal& m, std::string& o) {
     return true;
 }
 
+
+// ---- structural re-derivation of the routed region from its graph ----
+// The supported graph is, for every slot s of topK:
+//   select(gu_weights, 0, s) -> linear(x, .) -> split(., inter, -1) -> getitem 0 / 1 -> gelu(tanh) * up
+//   -> linear(., select(down_weights, 0, s)), and one stack of the slots' outputs.
+// Every node is looked up by name from the consumer's operands, its operator, arity, constants and
+// static f32 shape are checked, and it is claimed for its slot; a node claimed twice, left unclaimed,
+// or of another operator fails the walk.  The dims the walk returns come from the placeholders' and the
+// splits' metadata only, never from the document's scalar fields.
+struct RegionDims { int64_t hidden = 0, inter = 0, top_k = 0, gate_up_out = 0; };
+
+class RegionWalk {
+  public:
+    std::string err;
+    bool run(const JVal& graph, RegionDims* out);
+
+  private:
+    static constexpr int64_t kDimCap = 4 * 8192;  // 4 * MoERegionIR.maxDim
+    std::map<std::string, const JVal*> by_name_;
+    std::map<std::string, int> claimed_;
+
+    bool fail(const std::string& m) { if (err.empty()) err = m; return false; }
+    static const std::string& str(const JVal& n, const char* k) {
+        static const std::string none;
+        const JP* v = n.get(k);
+        return v && (*v)->kind == JVal::Str ? (*v)->s : none;
+    }
+    static const std::vector<JP>& args(const JVal& n) { return (*n.get("args"))->arr; }
+    static const JVal& kwargs(const JVal& n) { return **n.get("kwargs"); }
+    // the node an operand {"__node__": name} names
+    const JVal* deref(const JVal& v) const {
+        if (v.kind != JVal::Obj || v.obj.size() != 1 || v.obj[0].first != "__node__" || v.obj[0].second->kind != JVal::Str) return nullptr;
+        auto it = by_name_.find(v.obj[0].second->s);
+        return it == by_name_.end() ? nullptr : it->second;
+    }
+    static bool is_int(const JVal& v, int64_t want) { return v.kind == JVal::Int && v.i == want; }
+    // operands of a call: exactly `n`, a trailing null (an absent bias) dropped first when allowed
+    static bool arity(const JVal& n, size_t want, bool drop_null = false) {
+        size_t have = args(n).size();
+        if (drop_null && have == want + 1 && args(n)[want]->kind == JVal::Null) have = want;
+        return have == want;
+    }
+    // node is a call of `target` without keyword operands
+    bool plain_call(const JVal& n, const char* target) const {
+        return str(n, "op") == "call_function" && str(n, "target") == target && kwargs(n).obj.empty();
+    }
+    // static f32 metadata of exactly this shape
+    static bool f32_shape(const JVal& meta, const std::vector<int64_t>& want) {
+        if (meta.kind != JVal::Obj) return false;
+        const JP* dt = meta.get("dtype"); const JP* sh = meta.get("shape");
+        if (!dt || (*dt)->kind != JVal::Str || (*dt)->s != "float32" || !sh || (*sh)->kind != JVal::Arr || (*sh)->arr.size() != want.size()) return false;
+        for (size_t i = 0; i < want.size(); i++) if (!is_int(*(*sh)->arr[i], want[i])) return false;
+        return true;
+    }
+    static bool has_f32_shape(const JVal& n, const std::vector<int64_t>& want) {
+        const JP* m = n.get("meta");
+        return m && f32_shape(**m, want);
+    }
+    // the bounded dims of a placeholder of this rank
+    bool placeholder_dims(const JVal& n, size_t rank, std::vector<int64_t>* dims) {
+        const JP* m = n.get("meta");
+        if (!m || (*m)->kind != JVal::Obj) return fail("input " + str(n, "name") + ": missing static meta");
+        const JP* dt = (*m)->get("dtype"); const JP* sh = (*m)->get("shape");
+        if (!dt || (*dt)->kind != JVal::Str || !sh || (*sh)->kind != JVal::Arr) return fail("input " + str(n, "name") + ": missing static meta");
+        if ((*dt)->s != "float32") return fail("input " + str(n, "name") + " dtype " + (*dt)->s + " != float32");
+        if ((*sh)->arr.size() != rank) return fail("input " + str(n, "name") + ": rank " + std::to_string((*sh)->arr.size()) + " != " + std::to_string(rank));
+        for (auto& d : (*sh)->arr) {
+            if (d->kind != JVal::Int || d->i < 0 || d->i > kDimCap) return fail("input " + str(n, "name") + ": dims out of bounds");
+            dims->push_back(d->i);
+        }
+        return true;
+    }
+    bool claim(const JVal& n, int slot, const char* what) {
+        if (!claimed_.emplace(str(n, "name"), slot).second)
+            return fail("slot " + std::to_string(slot) + " " + what + " (" + str(n, "name") + ") is reused or shared across slots");
+        return true;
+    }
+    bool slot(int s, const JVal& fin, const JVal& x, const JVal& gu, const JVal& dn, const RegionDims& D, int64_t dn_in, int64_t* inter);
+};
+
+bool RegionWalk::slot(int s, const JVal& fin, const JVal& x, const JVal& gu, const JVal& dn, const RegionDims& D, int64_t dn_in, int64_t* inter) {
+    const std::string S = "slot " + std::to_string(s) + ": ";
+    // down projection: linear(activation, select(down_weights, 0, s)), no bias
+    if (!plain_call(fin, "aten.linear.default") || !arity(fin, 2, true)) return fail(S + "final op must be aten.linear.default (input, weight) without bias");
+    const JVal* act = deref(*args(fin)[0]);
+    const JVal* dsel = deref(*args(fin)[1]);
+    if (!act || !dsel) return fail(S + "down linear operands must be node references");
+    if (!plain_call(*dsel, "aten.select.int") || !arity(*dsel, 3) || deref(*args(*dsel)[0]) != &dn || !is_int(*args(*dsel)[1], 0) || !is_int(*args(*dsel)[2], s))
+        return fail(S + "down weight select must be " + str(dn, "name") + "[0, " + std::to_string(s) + "]");
+    if (!has_f32_shape(fin, {1, D.hidden})) return fail(S + "down output meta malformed");
+    if (!has_f32_shape(*dsel, {D.hidden, dn_in})) return fail(S + "down slice meta malformed");
+    // activation: gelu(gate, tanh) * up, gate and up the two items of one split
+    if (!plain_call(*act, "aten.mul.Tensor") || !arity(*act, 2)) return fail(S + "activation must be aten.mul.Tensor");
+    const JVal* gelu = deref(*args(*act)[0]);
+    const JVal* up = deref(*args(*act)[1]);
+    if (!gelu || !up) return fail(S + "activation operands must be node references");
+    const JVal& gkw = kwargs(*gelu);
+    if (str(*gelu, "op") != "call_function" || str(*gelu, "target") != "aten.gelu.default" || !arity(*gelu, 1) || gkw.obj.size() != 1 ||
+        gkw.obj[0].first != "approximate" || gkw.obj[0].second->kind != JVal::Str || gkw.obj[0].second->s != "tanh")
+        return fail(S + "gelu must be approximate='tanh' only");
+    const JVal* gate = deref(*args(*gelu)[0]);
+    if (!gate) return fail(S + "gelu operand must be a node reference");
+    if (!plain_call(*gate, "operator.getitem") || !plain_call(*up, "operator.getitem") || !arity(*gate, 2) || !arity(*up, 2) ||
+        !is_int(*args(*gate)[1], 0) || !is_int(*args(*up)[1], 1) || !deref(*args(*gate)[0]) || deref(*args(*gate)[0]) != deref(*args(*up)[0]))
+        return fail(S + "gate/up must be getitems 0/1 of the SAME split");
+    const JVal& split = *deref(*args(*gate)[0]);
+    if (!plain_call(split, "aten.split.Tensor") || !arity(split, 3) || !is_int(*args(split)[2], -1)) return fail(S + "split must be (tensor, size, -1) with no kwargs");
+    const JVal& sz = *args(split)[1];
+    if (sz.kind != JVal::Int || sz.i <= 0 || sz.i > kDimCap) return fail(S + "split size must be a positive bounded int");
+    if (*inter && *inter != sz.i) return fail(S + "split size " + std::to_string(sz.i) + " != " + std::to_string(*inter));
+    *inter = sz.i;
+    const JP* sm = split.get("meta");
+    const JP* items = sm && (*sm)->kind == JVal::Obj ? (*sm)->get("items") : nullptr;
+    const JP* sdt = sm && (*sm)->kind == JVal::Obj ? (*sm)->get("dtype") : nullptr;
+    if (!items || !sdt || (*sdt)->kind != JVal::Str || (*sdt)->s != "seq" || (*items)->kind != JVal::Arr || (*items)->arr.size() != 2 ||
+        !f32_shape(*(*items)->arr[0], {1, sz.i}) || !f32_shape(*(*items)->arr[1], {1, sz.i}))
+        return fail(S + "split item metas must be 2x f32 [1, " + std::to_string(sz.i) + "]");
+    if (!has_f32_shape(*gate, {1, sz.i}) || !has_f32_shape(*up, {1, sz.i}) || !has_f32_shape(*act, {1, sz.i})) return fail(S + "gate / up / activation meta malformed");
+    // gate_up projection: linear(x, select(gu_weights, 0, s)), no bias, on the SHARED input
+    const JVal* lin = deref(*args(split)[0]);
+    if (!lin || !plain_call(*lin, "aten.linear.default") || !arity(*lin, 2, true) || deref(*args(*lin)[0]) != &x)
+        return fail(S + "GU linear must take the SHARED x placeholder, no bias");
+    const JVal* gsel = deref(*args(*lin)[1]);
+    if (!gsel || !plain_call(*gsel, "aten.select.int") || !arity(*gsel, 3) || deref(*args(*gsel)[0]) != &gu || !is_int(*args(*gsel)[1], 0) || !is_int(*args(*gsel)[2], s))
+        return fail(S + "GU weight select must be " + str(gu, "name") + "[0, " + std::to_string(s) + "]");
+    if (!has_f32_shape(*lin, {1, D.gate_up_out})) return fail(S + "GU output meta malformed");
+    if (!has_f32_shape(*gsel, {D.gate_up_out, D.hidden})) return fail(S + "GU slice meta malformed");
+    return claim(fin, s, "down linear") && claim(*dsel, s, "down select") && claim(*act, s, "activation") && claim(*gelu, s, "gelu") &&
+           claim(*gate, s, "gate") && claim(*up, s, "up") && claim(split, s, "split") && claim(*lin, s, "GU linear") && claim(*gsel, s, "GU select");
+}
+
+bool RegionWalk::run(const JVal& graph, RegionDims* out) {
+    const std::vector<JP>& nodes = (*graph.get("nodes"))->arr;
+    const std::vector<JP>& inputs = (*graph.get("inputs"))->arr;
+    const std::vector<JP>& outputs = (*graph.get("outputs"))->arr;
+    std::vector<const JVal*> placeholders, outs;
+    for (auto& np : nodes) {
+        const JVal& n = *np;
+        const std::string& kind = str(n, "op");
+        if (kind != "placeholder" && kind != "call_function" && kind != "output") return fail("unsupported node kind " + kind + " (" + str(n, "name") + ")");
+        if (kind != "call_function" && !kwargs(n).obj.empty()) return fail(kind + " node " + str(n, "name") + " must carry no kwargs");
+        if (!by_name_.emplace(str(n, "name"), &n).second) return fail("node name " + str(n, "name") + " appears twice");
+        if (kind == "placeholder") placeholders.push_back(&n);
+        if (kind == "output") outs.push_back(&n);
+    }
+    if (placeholders.size() != 3 || inputs.size() != 3) return fail("graph inputs must be the 3 placeholders");
+    for (int i = 0; i < 3; i++)
+        if (inputs[i]->kind != JVal::Str || inputs[i]->s != str(*placeholders[i], "name")) return fail("graph inputs must be the 3 placeholders");
+    const JVal &x = *placeholders[0], &gu = *placeholders[1], &dn = *placeholders[2];
+    std::vector<int64_t> xd, gd, dd;
+    if (!placeholder_dims(x, 2, &xd) || !placeholder_dims(gu, 3, &gd) || !placeholder_dims(dn, 3, &dd)) return false;
+    if (xd[0] != 1) return fail("x batch dim must be 1");
+    RegionDims D;
+    D.hidden = xd[1]; D.top_k = gd[0]; D.gate_up_out = gd[1];
+    const int64_t dn_in = dd[2];
+    if (gd[2] != D.hidden || dd[0] != D.top_k || dd[1] != D.hidden) return fail("input dims inconsistent with region");
+    // one output packing one value: the stack of the slots
+    if (outs.size() != 1 || outputs.empty() || outputs[0]->kind != JVal::Str || outputs[0]->s != str(*outs[0], "name") || args(*outs[0]).size() != 1 ||
+        args(*outs[0])[0]->kind != JVal::Arr || args(*outs[0])[0]->arr.size() != 1)
+        return fail("output must pack exactly one value");
+    const JVal* stack = deref(*args(*outs[0])[0]->arr[0]);
+    if (!stack || str(*stack, "op") != "call_function" || str(*stack, "target") != "aten.stack.default") return fail("output must be aten.stack.default");
+    // stack(list, dim = 0): dim left out, second operand, or keyword
+    const std::vector<JP>& sa = args(*stack);
+    const JVal& skw = kwargs(*stack);
+    const bool dim_ok = (sa.size() == 1 && skw.obj.empty()) || (sa.size() == 2 && skw.obj.empty() && is_int(*sa[1], 0)) ||
+                        (sa.size() == 1 && skw.obj.size() == 1 && skw.obj[0].first == "dim" && is_int(*skw.obj[0].second, 0));
+    if (!dim_ok || sa[0]->kind != JVal::Arr) return fail("stack must be (list of slots, dim 0)");
+    const std::vector<JP>& slots = sa[0]->arr;
+    if ((int64_t)slots.size() != D.top_k) return fail("stack has " + std::to_string(slots.size()) + " inputs != topK " + std::to_string(D.top_k));
+    if (!has_f32_shape(*stack, {D.top_k, 1, D.hidden})) return fail("stack output meta malformed");
+    claimed_.emplace(str(x, "name"), -1); claimed_.emplace(str(gu, "name"), -1); claimed_.emplace(str(dn, "name"), -1);
+    if (!claim(*stack, -1, "stack") || !claim(*outs[0], -1, "output")) return false;
+    int64_t inter = 0;
+    for (size_t s = 0; s < slots.size(); s++) {
+        const JVal* fin = deref(*slots[s]);
+        if (!fin) return fail("slot " + std::to_string(s) + " final: expected a node reference");
+        if (!slot((int)s, *fin, x, gu, dn, D, dn_in, &inter)) return false;
+    }
+    // exact census: every call is one the pattern claimed, in the pattern's counts
+    std::map<std::string, int64_t> census;
+    for (auto& np : nodes) {
+        if (str(*np, "op") != "call_function") continue;
+        census[str(*np, "target")]++;
+        if (!claimed_.count(str(*np, "name"))) return fail("unconsumed/extra graph node " + str(*np, "target") + " (" + str(*np, "name") + ")");
+    }
+    const int64_t K = D.top_k;
+    const std::map<std::string, int64_t> want = {{"aten.select.int", 2 * K}, {"aten.linear.default", 2 * K}, {"aten.split.Tensor", K},
+                                                 {"aten.gelu.default", K}, {"aten.mul.Tensor", K}, {"aten.stack.default", 1}, {"operator.getitem", 2 * K}};
+    if (census != want) return fail("ATen census does not match topK slots of select/linear/split/getitem/gelu/mul/linear");
+    if (inter == 0) return fail("no slots");
+    if (2 * inter != D.gate_up_out || dn_in != inter) return fail("inter " + std::to_string(inter) + " inconsistent with the expert tensors");
+    D.inter = inter;
+    *out = D;
+    return true;
+}
+
 }  // namespace
 
 struct lev_op {
@@ -346,7 +544,6 @@ static int parse_region(lev_ctx* ctx, const JVal& d, lev_op* op) {
         return bad(ctx, "graph needs nodes, inputs, outputs");
     if ((*nodes)->arr.size() > 512) return bad(ctx, "graph exceeds 512 nodes");
     std::string payload;
-    std::map<std::string, int> census;
     for (auto& n : (*nodes)->arr) {
         if (n->kind != JVal::Obj) return bad(ctx, "graph node is not an object");
         const JP* name = n->get("name"); const JP* nop = n->get("op"); const JP* tgt = n->get("target");
@@ -363,7 +560,6 @@ static int parse_region(lev_ctx* ctx, const JVal& d, lev_op* op) {
         line += ">|";
         if (meta && (*meta)->kind != JVal::Null) { if (!canon_meta(**meta, line)) return bad(ctx, "node meta"); } else line += "n";
         payload += line + "\n";
-        if ((*nop)->s == "call_function") census[(*tgt)->s]++;
     }
     auto strlist = [&](const JVal& a, std::string& o) { o += "l<"; for (size_t i = 0; i < a.arr.size(); i++) { if (i) o += ","; o += "s:" + a.arr[i]->s; } o += ">"; };
     payload += "inputs|"; strlist(**ins, payload);
@@ -372,10 +568,13 @@ static int parse_region(lev_ctx* ctx, const JVal& d, lev_op* op) {
     std::string digest = h.hex();
     if (digest != sha) return bad(ctx, "graphSha256 does not match the graph (" + digest + ")");
     const int K = (int)topk;
-    if (census["aten.select.int"] != 2 * K || census["aten.linear.default"] != 2 * K || census["aten.split.Tensor"] != K ||
-        census["aten.gelu.default"] != K || census["aten.mul.Tensor"] != K || census["aten.stack.default"] != 1 ||
-        census["operator.getitem"] != 2 * K || census.size() != 7)
-        return bad(ctx, "graph operator census does not match topK slots of linear/split/gelu/mul/linear");
+    // re-derive the region from the graph; the declared dims must agree with it
+    RegionWalk walk;
+    RegionDims D;
+    if (!walk.run(**g, &D)) return bad(ctx, "region graph: " + walk.err);
+    if (D.hidden != hidden || D.inter != inter || D.top_k != topk || D.gate_up_out != guo)
+        return bad(ctx, "declared dims disagree with the graph-derived hidden " + std::to_string(D.hidden) + " inter " + std::to_string(D.inter) +
+                            " topK " + std::to_string(D.top_k) + " gateUpOut " + std::to_string(D.gate_up_out));
     op->kind = "moe.routed-region"; op->identity = digest; op->in_dim = hidden; op->out_dim = hidden; op->type = LEV_GGML_Q4_0;
     op->columns = 1; op->hidden = (int)hidden; op->inter = (int)inter; op->top_k = K; op->tensor = gu; op->kernel = "lev_moe_experts";
     return LEV_OK;

@@ -2,6 +2,7 @@
 and region fixtures are accepted with the reference's identities; tampered
 ones are rejected.  Host-only: runs without a GPU (NULL context)."""
 import ctypes as C
+import hashlib
 import json
 import os
 
@@ -114,3 +115,173 @@ def test_region_tamper_is_rejected(lib):
     d["graph"]["nodes"][5]["args"], d["graph"]["nodes"][6]["args"] = d["graph"]["nodes"][6]["args"], d["graph"]["nodes"][5]["args"]
     st, _ = install(lib, json.dumps(d))
     assert st == 14
+
+
+# ---- the graph walk: tampers whose digest is recomputed, so that only the structural re-derivation can catch them ----
+def _canon_val(v):
+    if v is None:
+        return "n"
+    if isinstance(v, bool):
+        return "b:1" if v else "b:0"
+    if isinstance(v, int):
+        return f"i:{v}"
+    if isinstance(v, str):
+        return "s:" + v
+    if isinstance(v, dict):
+        assert list(v) == ["__node__"]
+        return "@" + v["__node__"]
+    return "l<" + ",".join(_canon_val(e) for e in v) + ">"
+
+
+def _canon_meta(m):
+    if m is None:
+        return "n"
+    out = "d<dtype:s:" + m["dtype"]
+    if isinstance(m.get("items"), list):
+        out += ",items:l<" + ",".join(_canon_meta(i) for i in m["items"]) + ">"
+    sh = m.get("shape")
+    out += ",shape:" + ("l<" + ",".join(f"i:{d}" for d in sh) + ">" if isinstance(sh, list) else "n") + ">"
+    return out
+
+
+def graph_digest(graph) -> str:
+    """The canonical node lines of MoELowering.swift:66-168, restated for the tests."""
+    lines = []
+    for n in graph["nodes"]:
+        kw = ",".join(f"{k}:{_canon_val(v)}" for k, v in sorted(n["kwargs"].items()))
+        lines.append(f'{n["name"]}|{n["op"]}|{n["target"]}|{_canon_val(n["args"])}|d<{kw}>|{_canon_meta(n.get("meta"))}\n')
+    payload = "".join(lines) + "inputs|" + _canon_val(graph["inputs"]) + "\noutputs|" + _canon_val(graph["outputs"])
+    return hashlib.sha256(payload.encode()).hexdigest()
+
+
+def _retamper(doc, edit):
+    d = json.loads(doc)
+    edit(d["graph"]["nodes"], d)
+    d["graphSha256"] = graph_digest(d["graph"])
+    return json.dumps(d)
+
+
+def _message(lib, doc):
+    """install with a context-free call and return (status, accepted handle)"""
+    st, h = install(lib, doc)
+    return st, h
+
+
+def test_the_test_digest_reproduces_the_reference_digests():
+    for reg in G["regions"]:
+        assert graph_digest(json.loads(reg["json"])["graph"]) == reg["graphSha256"]
+
+
+def _by_target(nodes, target):
+    return [n for n in nodes if n["target"] == target]
+
+
+def test_graph_walk_rejects_restructured_graphs_with_a_matching_digest(lib):
+    """Sources/leviathan-tests/main.swift:5778-5820 (swapped getitems, gelu approximate=none, an extra node) and the
+    other structural guards of MoERegionGraphWalk.walk, each with graphSha256 recomputed for the edited graph."""
+    doc = G["regions"][0]["json"]
+    ok, h = install(lib, _retamper(doc, lambda nodes, d: None))
+    assert ok == 0
+    lib.lev_op_uninstall(None, h)
+
+    def swap_getitems(nodes, d):
+        for n in _by_target(nodes, "operator.getitem"):
+            n["args"][1] = 1 - n["args"][1]
+
+    def gelu_none(nodes, d):
+        for n in _by_target(nodes, "aten.gelu.default"):
+            n["kwargs"] = {"approximate": "none"}
+
+    def extra_sin(nodes, d):
+        nodes.append({"name": "extra_sin", "op": "call_function", "target": "aten.sin.default", "args": [{"__node__": nodes[3]["name"]}],
+                      "kwargs": {}, "meta": None})
+
+    def slot_order(nodes, d):  # slot 0 selects expert row 1 and slot 1 row 0
+        sel = [n for n in _by_target(nodes, "aten.select.int") if n["args"][0]["__node__"] == "gu_weights"]
+        sel[0]["args"][2], sel[1]["args"][2] = sel[1]["args"][2], sel[0]["args"][2]
+
+    def shared_select(nodes, d):  # two slots read the same down slice node
+        lin = [n for n in _by_target(nodes, "aten.linear.default") if n["args"][0]["__node__"].startswith("mul")]
+        lin[1]["args"][1] = dict(lin[0]["args"][1])
+
+    def private_x(nodes, d):  # a slot's gate_up projection reads something other than the shared input
+        lin = [n for n in _by_target(nodes, "aten.linear.default") if n["args"][0]["__node__"] == "x"]
+        lin[1]["args"][0] = {"__node__": "gu_weights"}
+
+    def bias(nodes, d):
+        _by_target(nodes, "aten.linear.default")[0]["args"].append({"__node__": "x"})
+
+    def split_dim(nodes, d):
+        _by_target(nodes, "aten.split.Tensor")[0]["args"][2] = 1
+
+    def split_size(nodes, d):
+        _by_target(nodes, "aten.split.Tensor")[1]["args"][1] = 16
+
+    def meta_shape(nodes, d):
+        _by_target(nodes, "aten.mul.Tensor")[0]["meta"]["shape"] = [1, 64]
+
+    def meta_dtype(nodes, d):
+        nodes[0]["meta"]["dtype"] = "float16"
+
+    def stack_dim(nodes, d):
+        _by_target(nodes, "aten.stack.default")[0]["args"].append(1)
+
+    def stack_short(nodes, d):
+        _by_target(nodes, "aten.stack.default")[0]["args"][0].pop()
+
+    def batch_two(nodes, d):
+        nodes[0]["meta"]["shape"][0] = 2
+
+    def placeholder_kwargs(nodes, d):
+        nodes[0]["kwargs"] = {"a": 1}
+
+    def node_kind(nodes, d):
+        nodes[3]["op"] = "call_method"
+
+    def duplicate_name(nodes, d):
+        nodes[4]["name"] = nodes[3]["name"]
+
+    def inputs_order(nodes, d):
+        d["graph"]["inputs"] = ["gu_weights", "x", "down_weights"]
+
+    def mul_is_add(nodes, d):
+        _by_target(nodes, "aten.mul.Tensor")[0]["target"] = "aten.add.Tensor"
+
+    def huge_dim(nodes, d):
+        nodes[1]["meta"]["shape"][1] = 1 << 40
+
+    edits = [swap_getitems, gelu_none, extra_sin, slot_order, shared_select, private_x, bias, split_dim, split_size, meta_shape, meta_dtype,
+             stack_dim, stack_short, batch_two, placeholder_kwargs, node_kind, duplicate_name, inputs_order, mul_is_add, huge_dim]
+    for e in edits:
+        st, h = install(lib, _retamper(doc, e))
+        assert st == 14 and not h.value, e.__name__
+
+    # accepted spellings of the same graph: stack's dim as a second operand or as a keyword, a null bias operand
+    def dim_operand(nodes, d):
+        _by_target(nodes, "aten.stack.default")[0]["args"].append(0)
+
+    def dim_keyword(nodes, d):
+        _by_target(nodes, "aten.stack.default")[0]["kwargs"] = {"dim": 0}
+
+    def null_bias(nodes, d):
+        for n in _by_target(nodes, "aten.linear.default"):
+            n["args"].append(None)
+
+    for e in (dim_operand, dim_keyword, null_bias):
+        st, h = install(lib, _retamper(doc, e))
+        assert st == 0, e.__name__
+        lib.lev_op_uninstall(None, h)
+
+
+def test_declared_dims_must_agree_with_the_graph(lib):
+    """main.swift:5778-5781: the scalar fields lie, the graph (and its digest) are untouched."""
+    big = [r for r in G["regions"] if r["hidden"] != 96]
+    doc = (big[0] if big else G["regions"][0])["json"]
+    d = json.loads(doc)
+    for field, value in (("topK", d["topK"] - 1), ("hidden", d["hidden"] - 32), ("expertIntermediate", d["expertIntermediate"] + 32)):
+        e = dict(d)
+        e[field] = value
+        if field == "expertIntermediate":
+            e["gateUpOut"] = 2 * value
+        st, h = install(lib, json.dumps(e))
+        assert st == 14 and not h.value, field
