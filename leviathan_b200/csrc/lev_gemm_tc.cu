@@ -20,6 +20,8 @@
 // Every wait is bounded by about a second of SM clocks; on a timeout the CTA sets
 // LEV_DEV_TIMEOUT, skips the remaining work, frees its tensor memory and returns.
 #include <cuda.h>
+
+#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -39,6 +41,10 @@ constexpr int kWStageBytes = RN * KS * 2;             // 24576
 constexpr int kStageBytes = kXStageBytes + kWStageBytes;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 2000000000LL;
+#ifndef LEV_GEMM_AHEAD
+#define LEV_GEMM_AHEAD 3
+#endif
+constexpr int kAhead = LEV_GEMM_AHEAD;  // K-steps of raw weight bytes a decode thread has requested ahead of the one it decodes
 
 struct GemmTcArgs {
     const uint8_t* raw;   // GGUF blocks, row-major
@@ -63,25 +69,43 @@ __device__ __forceinline__ void mbar_arrive(unsigned bar) {
 __device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar), "r"(bytes) : "memory");
 }
+// A burst of try_waits as one tight loop (a few instructions a poll; a try_wait may itself block for a short,
+// hardware-defined time).  True when the phase has completed.
+__device__ __forceinline__ bool mbar_poll_burst(unsigned bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n"
+        " .reg .pred p, q;\n"
+        " .reg .u32 n;\n"
+        " mov.u32 n, 32;\n"
+        " mov.u32 %0, 0;\n"
+        "LEV_WAIT_LOOP:\n"
+        " mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        " @p bra LEV_WAIT_DONE;\n"
+        " sub.u32 n, n, 1;\n"
+        " setp.ne.u32 q, n, 0;\n"
+        " @q bra LEV_WAIT_LOOP;\n"
+        " bra LEV_WAIT_END;\n"
+        "LEV_WAIT_DONE:\n"
+        " mov.u32 %0, 1;\n"
+        "LEV_WAIT_END:\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
 // bounded wait; false on timeout or when another thread of the CTA has already given up
 __device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, volatile int* abort_flag) {
     long long t_start = 0;
-    for (unsigned i = 1;; i++) {
-        unsigned ok;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
-            : "=r"(ok)
-            : "r"(bar), "r"(parity)
-            : "memory");
-        if (ok) return true;
-        if ((i & 63u) == 0) {
-            if (*abort_flag) return false;
-            const long long now = clock64();
-            if (t_start == 0) t_start = now;
-            else if (now - t_start > kWaitCycles) {
-                *abort_flag = 1;
-                return false;
-            }
+    for (;;) {
+        if (mbar_poll_burst(bar, parity)) return true;
+        if (*abort_flag) return false;
+        const long long now = clock64();
+        if (t_start == 0) t_start = now;
+        else if (now - t_start > kWaitCycles) {
+            *abort_flag = 1;
+            return false;
         }
     }
 }
@@ -167,7 +191,7 @@ __device__ __forceinline__ void load_raw(const uint8_t* row, int it, int j, bool
     if (!valid) return;
     if (TYPE == LEV_GGML_Q4_K) {
         const uint8_t* blk = row + (int64_t)(it >> 2) * LEV_Q4_K_BYTES;
-        if ((it & 3) == 0) R.hdr = ldg16(blk);
+        R.hdr = ldg16(blk);
         R.q0 = ldg8(blk + 16 + 32 * (it & 3) + 8 * j);
     } else if (TYPE == LEV_GGML_Q4_0) {
         const uint8_t* blk = row + (int64_t)(2 * it + (j >> 1)) * LEV_Q4_0_BYTES;
@@ -332,35 +356,39 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
         constexpr int kRowStep = kDequantWarps * 8;   // rows covered by one pass of the decode threads
         constexpr int NR = RN / kRowStep;
         static_assert(RN % kRowStep == 0, "decode threads tile the weight rows evenly");
-        RowRaw<TYPE> cur[NR], nxt[NR];
+        RowRaw<TYPE> ahead[kAhead][NR];
         const uint8_t* rowp[NR];
         bool valid[NR];
 #pragma unroll
         for (int i = 0; i < NR; i++) {
             valid[i] = r0 + rb + kRowStep * i < A.rows;
             rowp[i] = A.raw + (r0 + (valid[i] ? rb + kRowStep * i : 0)) * A.row_bytes;
-            load_raw<TYPE>(rowp[i], 0, j, valid[i], cur[i]);
+#pragma unroll
+            for (int u = 0; u < kAhead; u++)
+                if (u < kt) load_raw<TYPE>(rowp[i], u, j, valid[i], ahead[u][i]);
         }
         bool ok = true;
-        for (int it = 0; it < kt && ok; it++) {
-            const int s = it % STAGES;
-            if (it + 1 < kt) {
+        for (int it0 = 0; it0 < kt && ok; it0 += kAhead) {
+#pragma unroll
+            for (int u = 0; u < kAhead; u++) {
+                const int it = it0 + u;
+                if (it >= kt || !ok) break;
+                const int s = it % STAGES;
+                RowRaw<TYPE> cur[NR];
 #pragma unroll
                 for (int i = 0; i < NR; i++) {
-                    nxt[i] = cur[i];  // keeps the block header that is reloaded only every fourth step
-                    load_raw<TYPE>(rowp[i], it + 1, j, valid[i], nxt[i]);
+                    cur[i] = ahead[u][i];
+                    if (it + kAhead < kt) load_raw<TYPE>(rowp[i], it + kAhead, j, valid[i], ahead[u][i]);
                 }
+                if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
+                if (!ok) break;
+                unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
+#pragma unroll
+                for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + kRowStep * i);
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s32(&full_w[s]));
             }
-            if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
-            if (!ok) break;
-            unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
-#pragma unroll
-            for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + kRowStep * i);
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s32(&full_w[s]));
-#pragma unroll
-            for (int i = 0; i < NR; i++) cur[i] = nxt[i];
         }
         // ---- epilogue: TMEM -> Y ----
         if (ok && warp < 10 && mbar_wait(s32(&accum_full), 0, abort_flag)) {
@@ -438,7 +466,7 @@ constexpr int GR_THREADS = (2 + GR_DECODE_WARPS) * 32;
 constexpr int GR_W_BYTES = 128 * KS * 2;               // 16384
 constexpr int GR_STAGE_BYTES = GR_W_BYTES + kXHalfBytes;   // 32768
 constexpr int GR_TMEM_COLS = 128;
-constexpr int GR_JOB_TOKENS = 128;
+constexpr int GR_JOB_TOKENS = 64;
 
 struct GroupedArgs {
     const uint8_t* raw;      // expert-stacked tensor, row-major GGUF blocks
@@ -535,7 +563,7 @@ __global__ void __launch_bounds__(GR_THREADS, 3) k_gemm_tc_grouped(const __grid_
         // ---- weight decode: thread = (2 rows 64 apart) x (byte group j) ----
         const int j = lane >> 3, rb = (warp - 2) * 8 + (lane & 7);
         constexpr int NR = 2;
-        RowRaw<TYPE> cur[NR], nxt[NR];
+        RowRaw<TYPE> ahead[kAhead][NR];
         const uint8_t* rowp[NR];
         bool valid[NR];
 #pragma unroll
@@ -543,28 +571,32 @@ __global__ void __launch_bounds__(GR_THREADS, 3) k_gemm_tc_grouped(const __grid_
             const int r = row0 + rb + 64 * i;
             valid[i] = r < A.rows_per_expert;
             rowp[i] = A.raw + ((int64_t)e * A.rows_per_expert + (valid[i] ? r : 0)) * A.row_bytes;
-            load_raw<TYPE>(rowp[i], 0, j, valid[i], cur[i]);
+#pragma unroll
+            for (int u = 0; u < kAhead; u++)
+                if (u < kt) load_raw<TYPE>(rowp[i], u, j, valid[i], ahead[u][i]);
         }
         bool ok = true;
-        for (int it = 0; it < kt && ok; it++) {
-            const int s = it % GR_STAGES;
-            if (it + 1 < kt) {
+        for (int it0 = 0; it0 < kt && ok; it0 += kAhead) {
+#pragma unroll
+            for (int u = 0; u < kAhead; u++) {
+                const int it = it0 + u;
+                if (it >= kt || !ok) break;
+                const int s = it % GR_STAGES;
+                RowRaw<TYPE> cur[NR];
 #pragma unroll
                 for (int i = 0; i < NR; i++) {
-                    nxt[i] = cur[i];
-                    load_raw<TYPE>(rowp[i], it + 1, j, valid[i], nxt[i]);
+                    cur[i] = ahead[u][i];
+                    if (it + kAhead < kt) load_raw<TYPE>(rowp[i], it + kAhead, j, valid[i], ahead[u][i]);
                 }
+                if (it >= GR_STAGES) ok = mbar_wait(s32(&empty[s]), ((it / GR_STAGES) & 1) ^ 1, abort_flag);
+                if (!ok) break;
+                unsigned char* wtile = smem + (size_t)s * GR_STAGE_BYTES;
+#pragma unroll
+                for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + 64 * i);
+                asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s32(&full_w[s]));
             }
-            if (it >= GR_STAGES) ok = mbar_wait(s32(&empty[s]), ((it / GR_STAGES) & 1) ^ 1, abort_flag);
-            if (!ok) break;
-            unsigned char* wtile = smem + (size_t)s * GR_STAGE_BYTES;
-#pragma unroll
-            for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + 64 * i);
-            asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive(s32(&full_w[s]));
-#pragma unroll
-            for (int i = 0; i < NR; i++) cur[i] = nxt[i];
         }
         // ---- epilogue: lane = weight row, TMEM columns = positions ----
         if (ok && mbar_wait(s32(&accum_full), 0, abort_flag)) {
@@ -618,6 +650,378 @@ __global__ void __launch_bounds__(GR_THREADS, 3) k_gemm_tc_grouped(const __grid_
     if (warp == 1) {
         asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(GR_TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Grouped form for Q4_0 with the raw blocks staged in shared memory.
+//
+// The kernel above spends most of its instructions on getting 18-byte blocks out of global memory with 2-byte
+// loads and on the bookkeeping around 32 values per thread and K-step.  Here the GGUF bytes of 128 rows x 256
+// columns (8 blocks = 144 bytes per row) are copied to shared memory asynchronously (cp.async, 16 bytes a copy
+// where the tensor's rows are 16-byte aligned, 4 bytes otherwise), one such group ahead of the one being
+// decoded; a decode thread owns ONE weight row, reads its two K-steps of the group with 16-byte shared loads
+// (rows 144 bytes apart: eight lanes cover the 32 banks) and turns a nibble into its value with two
+// instructions: a byte permute puts it into the mantissa of 128.0 (= 128 + q exactly) and one fused
+// multiply-add forms d * (128 + q) - 136 d = d * (q - 8), which is exact, so the value equals the reference
+// decoder's d * (q - 8) (Sources/LeviathanCore/Q4.swift:54-69) bit for bit; then one rounding to bf16.
+// The decoded K-step of a row (64 bf16 = 32 registers) goes straight into tensor memory with one tcgen05.st: the
+// MMA takes its A operand (the weights) from tensor memory, lane = weight row, and only the tokens from shared
+// memory, so decoded weights never pass through shared memory and need no swizzled stores or proxy fences.
+// Decode warps 2..5 take the even K-steps, warps 6..9 the odd ones; jobs hold up to 64 tokens, so two CTAs
+// share an SM: 5 x 8 KB tokens, 2 x 18 KB raw bytes, and 256 TMEM columns each (64 accumulator + 4 x 32 weights).
+// ---------------------------------------------------------------------------
+#ifndef LEV_SG_STAGES
+#define LEV_SG_STAGES 4
+#endif
+#ifndef LEV_SG_XSTAGES
+#define LEV_SG_XSTAGES 5
+#endif
+#ifndef LEV_SG_RAW
+#define LEV_SG_RAW 2
+#endif
+constexpr int SG_STAGES = LEV_SG_STAGES;      // decoded weight tiles in tensor memory (32 columns each)
+constexpr int SG_XSTAGES = LEV_SG_XSTAGES;    // token tiles (8 KB each): a TMA load takes several K-steps to arrive, so this ring is the deeper one
+constexpr int SG_RAW_SLOTS = LEV_SG_RAW;   // groups of raw bytes in shared memory: one being decoded, the others on their way
+constexpr int SG_X_BYTES = GR_JOB_TOKENS * KS * 2;          // 8192: one TMA box of 64 positions x 64 k
+constexpr int SG_GROUP_COLS = 256;
+constexpr int SG_ROW_BYTES = SG_GROUP_COLS / 32 * LEV_Q4_0_BYTES;   // 144
+constexpr int SG_RAW_BYTES = 128 * SG_ROW_BYTES;            // 18432
+constexpr int SG_SMEM = SG_XSTAGES * SG_X_BYTES + SG_RAW_SLOTS * SG_RAW_BYTES + 1024;
+constexpr int SG_ACC_COLS = 64;                       // accumulator: one column per token of the job
+constexpr int SG_A_COLS = KS / 2;                      // a K-step of one row: 64 bf16 = 32 columns
+constexpr int SG_TMEM_COLS = 256;
+static_assert(GR_JOB_TOKENS <= SG_ACC_COLS && SG_ACC_COLS + SG_STAGES * SG_A_COLS <= SG_TMEM_COLS && SG_ROW_BYTES % 16 == 0,
+              "staged grouped form geometry");
+
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(unsigned dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+
+// one Q4_0 block (f16 d, 16 nibble bytes in q[4]) -> its 32 values as 16 packed bf16 pairs in column order: low
+// nibbles are values 0..15, high nibbles 16..31
+__device__ __forceinline__ void q40_block_regs(unsigned dbits, const unsigned* q, unsigned* out) {
+    const float d = h2f(dbits);
+    const float c = __fmul_rn(d, -136.0f);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const unsigned l4 = q[k] & 0x0F0F0F0Fu, h4 = (q[k] >> 4) & 0x0F0F0F0Fu;
+        float lo[4], hi[4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) {
+            lo[i] = __fmaf_rn(d, __uint_as_float(__byte_perm(l4, 0x43000000u, 0x7054u + (i << 8))), c);
+            hi[i] = __fmaf_rn(d, __uint_as_float(__byte_perm(h4, 0x43000000u, 0x7054u + (i << 8))), c);
+        }
+        __nv_bfloat162 a = __floats2bfloat162_rn(lo[0], lo[1]), b = __floats2bfloat162_rn(lo[2], lo[3]);
+        __nv_bfloat162 e = __floats2bfloat162_rn(hi[0], hi[1]), f = __floats2bfloat162_rn(hi[2], hi[3]);
+        out[2 * k] = *reinterpret_cast<unsigned*>(&a);
+        out[2 * k + 1] = *reinterpret_cast<unsigned*>(&b);
+        out[8 + 2 * k] = *reinterpret_cast<unsigned*>(&e);
+        out[8 + 2 * k + 1] = *reinterpret_cast<unsigned*>(&f);
+    }
+}
+
+// K-step S (0..3) of a group: the 36 bytes at 36 * S of the row's 144, i.e. words S .. S + 8 of the twelve
+// words L loaded from the 16-byte chunk that holds byte 36 * S; out = the row's 64 values as 32 bf16 pairs
+template <int S>
+__device__ __forceinline__ void q40_kstep_regs(const unsigned* L, unsigned* out) {
+    const unsigned* w = L + S;
+    unsigned qa[4];
+#pragma unroll
+    for (int k = 0; k < 4; k++) qa[k] = __funnelshift_r(w[k], w[k + 1], 16);   // block 0: d in the low half of w[0], nibbles from byte 2
+    q40_block_regs(w[0] & 0xffffu, qa, out);
+    q40_block_regs(w[4] >> 16, w + 5, out + 16);                               // block 1: d in the high half of w[4], nibbles aligned
+}
+
+// 32 consecutive 32-bit columns of this thread's tensor-memory lane
+__device__ __forceinline__ void tmem_st32(unsigned taddr, const unsigned* v) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+        "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};\n" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]), "r"(v[10]), "r"(v[11]),
+        "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]),
+        "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+        : "memory");
+}
+
+// what a CTA needs to know of tile t = (job, row tile): the job's expert slice, first grouped position, token count
+struct SgTile {
+    int e, pos0, cnt, row0;
+};
+__device__ __forceinline__ SgTile sg_tile(const GroupedArgs& A, int t, int row_tiles) {
+    SgTile T;
+    const int job = t / row_tiles;
+    T.row0 = (t - job * row_tiles) * 128;
+    T.e = A.job_slice[job];
+    T.pos0 = A.job_pos[(int64_t)job * GR_JOB_TOKENS];
+    const int c = A.offsets[A.first_expert + T.e + 1] - T.pos0;
+    T.cnt = c > GR_JOB_TOKENS ? GR_JOB_TOKENS : c;
+    return T;
+}
+
+// The CTAs are persistent: CTA c works through tiles c, c + gridDim.x, ... of the job list, so tensor memory, the
+// barriers and the first trip to global memory are paid once per CTA, and the staging of a tile's first columns
+// runs while the previous tile is still being decoded.  Ring positions count K-steps over all of a CTA's tiles.
+template <int CW>
+__global__ void __launch_bounds__(GR_THREADS, 2) k_gemm_tc_grouped_q40(const __grid_constant__ CUtensorMap xmap, GroupedArgs A) {
+    extern __shared__ unsigned char smem_dyn[];
+    __shared__ __align__(8) unsigned long long full_x[SG_XSTAGES], empty_x[SG_XSTAGES], full_w[SG_STAGES], empty[SG_STAGES];
+    __shared__ __align__(8) unsigned long long accum_full, accum_empty;
+    __shared__ unsigned tmem_base_s;
+    __shared__ int abort_s;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
+    unsigned char* xbuf = smem;
+    unsigned char* rawbuf = xbuf + SG_XSTAGES * SG_X_BYTES;
+    const int row_tiles = (A.rows_per_expert + 127) >> 7;
+    const int total_tiles = *A.njobs * row_tiles;
+    const int my_tiles = (int)blockIdx.x < total_tiles ? (total_tiles - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+    const int kt = A.cols / KS;
+    const int ngroups = (kt + 3) >> 2;
+
+    if (threadIdx.x == 0) {
+        abort_s = 0;
+        for (int s = 0; s < SG_STAGES; s++) {
+            mbar_init(s32(&full_w[s]), GR_DECODE_WARPS / 2);
+            mbar_init(s32(&empty[s]), 1);
+        }
+        for (int s = 0; s < SG_XSTAGES; s++) {
+            mbar_init(s32(&full_x[s]), 1);
+            mbar_init(s32(&empty_x[s]), 1);
+        }
+        mbar_init(s32(&accum_full), 1);
+        mbar_init(s32(&accum_empty), GR_DECODE_WARPS);
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(s32(&tmem_base_s)), "r"(SG_TMEM_COLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+    const unsigned tmem_base = tmem_base_s;
+    volatile int* abort_flag = &abort_s;
+
+    if (warp == 0) {
+        // ---- token tiles by TMA ----
+        if (lane == 0) {
+            bool ok = true;
+            for (int k = 0; k < my_tiles && ok; k++) {
+                const SgTile T = sg_tile(A, (int)blockIdx.x + k * (int)gridDim.x, row_tiles);
+                for (int it = 0; it < kt; it++) {
+                    const int n = k * kt + it, s = n % SG_XSTAGES;
+                    if (n >= SG_XSTAGES && !mbar_wait(s32(&empty_x[s]), ((n / SG_XSTAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(s32(&full_x[s]), SG_X_BYTES);
+                    tma_load_2d(s32(xbuf + (size_t)s * SG_X_BYTES), &xmap, it * KS, T.pos0, s32(&full_x[s]));
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            bool ok = true;
+            for (int k = 0; k < my_tiles && ok; k++) {
+                const SgTile T = sg_tile(A, (int)blockIdx.x + k * (int)gridDim.x, row_tiles);
+                const int n_pad = (T.cnt + 15) & ~15;   // MMA N
+                const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(n_pad >> 3) << 17) | ((unsigned)(128 >> 4) << 24);
+                // the accumulator is free again when every decode warp has read tile k - 1 out of it
+                if (k > 0 && !mbar_wait(s32(&accum_empty), (k - 1) & 1, abort_flag)) break;
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                for (int it = 0; it < kt && ok; it++) {
+                    const int n = k * kt + it, s = n % SG_STAGES, sx = n % SG_XSTAGES;
+                    ok = mbar_wait(s32(&full_x[sx]), (n / SG_XSTAGES) & 1, abort_flag) && mbar_wait(s32(&full_w[s]), (n / SG_STAGES) & 1, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    const unsigned xs = s32(xbuf + (size_t)sx * SG_X_BYTES);
+                    const unsigned at = tmem_base + SG_ACC_COLS + (unsigned)s * SG_A_COLS;   // A: this stage's columns, lane = weight row
+#pragma unroll
+                    for (int kk = 0; kk < KS / 16; kk++) {
+                        const uint64_t bdesc = umma_desc(xs + kk * 32);
+                        const unsigned acc = (it | kk) ? 1u : 0u;
+                        asm volatile(
+                            "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n" ::"r"(
+                                tmem_base),
+                            "r"(at + kk * 8), "l"(bdesc), "r"(idesc), "r"(acc)
+                            : "memory");
+                    }
+                    umma_commit(s32(&empty[s]));      // both tiles may be refilled when these MMAs have read them
+                    umma_commit(s32(&empty_x[sx]));
+                }
+                if (ok) umma_commit(s32(&accum_full));
+            }
+        }
+    } else {
+        // ---- weight staging and decode: 256 threads; thread = weight row (tid & 127), K-step parity (tid >> 7) ----
+        // a warp reaches the 32 tensor-memory lanes 32 * (warp % 4) ..., so those are its weight rows
+        const int quarter = warp & 3, par = (warp - 2) >> 2;
+        const int row = quarter * 32 + lane;
+        const unsigned lane_addr = (unsigned)(quarter * 32) << 16;
+        // Copies of group g of the CTA's tile k into raw slot (k * ngroups + g) % SG_RAW_SLOTS.  Decode warp dw stages
+        // rows dw, dw + 8, ... (16 rows); nothing below divides by a run-time value.
+        //   16-byte pieces: lanes 0..26 take three rows at a time, nine pieces each;
+        //   4-byte pieces: a row is 36 words: all lanes take words 0..31 of a row, then the four words left over of
+        //   eight rows at once (lane = 4 * row + word).
+        const int dw = warp - 2;
+        const int l9 = lane / 9, p9 = lane - 9 * l9;          // 16-byte form: row of the triple, piece
+        const int l4 = lane >> 2, p4 = 32 + (lane & 3);        // 4-byte form, left-over words: row of the eight, word
+        auto stage_group = [&](const SgTile& T, int g, int slot) {
+            const int gbytes = min(SG_ROW_BYTES, (int)A.row_bytes - g * SG_ROW_BYTES);
+            const unsigned dst0 = s32(rawbuf + (size_t)slot * SG_RAW_BYTES);
+            const uint8_t* src0 = A.raw + ((int64_t)T.e * A.rows_per_expert + T.row0) * A.row_bytes + (int64_t)g * SG_ROW_BYTES;
+            if (CW == 16) {
+                if (lane < 27) {
+#pragma unroll
+                    for (int q = 0; q < 6; q++) {
+                        const int r = dw + 8 * (3 * q + l9);   // rows dw + 8 * (0..15)
+                        if (3 * q + l9 < 16 && T.row0 + r < A.rows_per_expert)
+                            cp_async16(dst0 + r * SG_ROW_BYTES + p9 * 16, src0 + (int64_t)r * A.row_bytes + p9 * 16);
+                    }
+                }
+            } else {
+#pragma unroll
+                for (int q = 0; q < 16; q++) {
+                    const int r = dw + 8 * q;
+                    if (4 * lane < gbytes && T.row0 + r < A.rows_per_expert)
+                        cp_async4(dst0 + r * SG_ROW_BYTES + 4 * lane, src0 + (int64_t)r * A.row_bytes + 4 * lane);
+                }
+#pragma unroll
+                for (int q = 0; q < 2; q++) {
+                    const int r = dw + 8 * (8 * q + l4);
+                    if (4 * p4 < gbytes && T.row0 + r < A.rows_per_expert)
+                        cp_async4(dst0 + r * SG_ROW_BYTES + 4 * p4, src0 + (int64_t)r * A.row_bytes + 4 * p4);
+                }
+            }
+        };
+        // Every thread commits one copy group per group of columns (an empty one past the end), so that "all but the
+        // newest SG_RAW_SLOTS - 2" always means: group G has landed.  (sk, sg, sslot) is the next group to stage: tile,
+        // group inside the tile, raw slot; the staging runs SG_RAW_SLOTS - 1 groups ahead of the decode and so crosses
+        // into the next tile before the decode does.
+        static_assert(SG_RAW_SLOTS == 2, "the staging below looks at most one tile ahead");
+        SgTile T = {0, 0, 0, 0};
+        if (my_tiles > 0) {
+            T = sg_tile(A, (int)blockIdx.x, row_tiles);
+            stage_group(T, 0, 0);
+        }
+        cp_async_commit();
+        int sk = 0, sg = 1, sslot = 1;   // the group after the one just staged
+        if (sg == ngroups) { sg = 0; sk = 1; }
+        bool ok = true;
+        for (int k = 0; k < my_tiles; k++) {
+            // the next tile's parameters are fetched a whole tile before the staging needs them
+            const SgTile Tnext = k + 1 < my_tiles ? sg_tile(A, (int)blockIdx.x + (k + 1) * (int)gridDim.x, row_tiles) : T;
+            for (int g = 0; g < ngroups; g++) {
+                const int G = k * ngroups + g;
+                cp_async_wait_but<0>();   // this thread's copies of group G have landed
+                decode_barrier();         // everyone's have, and everyone is done reading group G - 1's slot
+                if (sk < my_tiles && ok) stage_group(sk == k ? T : Tnext, sg, sslot);
+                cp_async_commit();
+                sslot ^= 1;
+                if (++sg == ngroups) { sg = 0; sk++; }
+                const unsigned char* rs = rawbuf + (size_t)(G % SG_RAW_SLOTS) * SG_RAW_BYTES + row * SG_ROW_BYTES;
+                // K-step sk of the group -> tensor memory; the four forms differ in compile-time word offsets only and
+                // each ends in its own tcgen05.st, so no register moves join them.  A row past the end of the expert
+                // decodes whatever its slot holds: its accumulator lane is never stored.
+                auto kstep = [&](auto sk_tag) {
+                    constexpr int SK = decltype(sk_tag)::value;
+                    const int it = 4 * g + SK;
+                    if (it >= kt || !ok) return;
+                    const int n = k * kt + it, s = n % SG_STAGES;
+                    unsigned L[12];
+                    const uint4* src = reinterpret_cast<const uint4*>(rs + ((36 * SK) & ~15));
+#pragma unroll
+                    for (int c = 0; c < 3; c++) {
+                        const uint4 v4 = src[c];
+                        L[4 * c] = v4.x; L[4 * c + 1] = v4.y; L[4 * c + 2] = v4.z; L[4 * c + 3] = v4.w;
+                    }
+                    if (n >= SG_STAGES) ok = mbar_wait(s32(&empty[s]), ((n / SG_STAGES) & 1) ^ 1, abort_flag);
+                    if (!ok) return;
+                    unsigned v[32];
+                    q40_kstep_regs<SK>(L, v);
+                    asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                    tmem_st32(tmem_base + lane_addr + SG_ACC_COLS + (unsigned)s * SG_A_COLS, v);
+                    asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory");
+                    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(s32(&full_w[s]));
+                };
+                if (par == 0) {
+                    kstep(std::integral_constant<int, 0>());
+                    kstep(std::integral_constant<int, 2>());
+                } else {
+                    kstep(std::integral_constant<int, 1>());
+                    kstep(std::integral_constant<int, 3>());
+                }
+            }
+            // ---- epilogue of tile k: lane = weight row, TMEM columns = positions ----
+            if (ok) ok = mbar_wait(s32(&accum_full), k & 1, abort_flag);
+            if (ok) {
+                asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+                const int n_pad = (T.cnt + 15) & ~15;
+                const int orow_w = T.row0 + row;
+                const int c = 32 * par;
+                unsigned v[32];
+                if (c < n_pad) {
+                    const unsigned taddr = tmem_base + lane_addr + (unsigned)c;
+                    if (c + 32 <= n_pad) {
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];\n"
+                            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                              "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                              "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                            : "r"(taddr)
+                            : "memory");
+                    } else {
+                        asm volatile(
+                            "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];\n"
+                            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                              "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
+                            : "r"(taddr)
+                            : "memory");
+#pragma unroll
+                        for (int q = 16; q < 32; q++) v[q] = 0u;
+                    }
+                    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+                }
+                // the values are in registers: the next tile's first MMA may overwrite the accumulator
+                asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+                __syncwarp();
+                if (lane == 0) mbar_arrive(s32(&accum_empty));
+                if (c < n_pad && orow_w < A.rows_per_expert) {
+#pragma unroll
+                    for (int q = 0; q < 32; q++) {
+                        if (c + q < T.cnt) {
+                            const int pos = T.pos0 + c + q;
+                            const int orow = A.out_row ? A.out_row[pos] : pos;
+                            A.out[(int64_t)orow * A.out_ld + orow_w] = __uint_as_float(v[q]);
+                        }
+                    }
+                }
+            }
+            T = Tnext;
+        }
+        cp_async_wait_but<0>();
+    }
+    if (abort_s && threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
+    asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(SG_TMEM_COLS) : "memory");
     }
 }
 
@@ -741,7 +1145,9 @@ int lev_gemm_grouped_run(lev_ctx* ctx, const lev_weights* w, int rows_per_expert
     CUtensorMap map;
     const cuuint64_t gdim[2] = {(cuuint64_t)w->cols, (cuuint64_t)capacity_rows};
     const cuuint64_t gstride[1] = {(cuuint64_t)w->cols * 2};
-    const cuuint32_t box[2] = {KS, 128};
+    // the staged Q4_0 kernel takes one box of GR_JOB_TOKENS positions per K-step, the general one a box of 128
+    const bool staged = w->type == LEV_GGML_Q4_0;
+    const cuuint32_t box[2] = {KS, staged ? (cuuint32_t)GR_JOB_TOKENS : 128u};
     const cuuint32_t estr[2] = {1, 1};
     CUresult cr = enc(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(xg_bf16), gdim, gstride, box, estr,
                       CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -762,6 +1168,23 @@ int lev_gemm_grouped_run(lev_ctx* ctx, const lev_weights* w, int rows_per_expert
     A.out_ld = out_ld;
     A.status = ctx->d_status;
     dim3 grid((unsigned)((rows_per_expert + 127) / 128), (unsigned)max_jobs);
+    if (staged) {
+        // 16-byte copies need every row of the tensor to start on a 16-byte boundary
+        const bool wide = A.row_bytes % 16 == 0 && w->cols % SG_GROUP_COLS == 0 && ((uintptr_t)A.raw & 15) == 0;
+        static bool configured_q40[2][16] = {};
+        if (!configured_q40[wide][ctx->device & 15]) {
+            if (wide) LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc_grouped_q40<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, SG_SMEM));
+            else LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc_grouped_q40<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, SG_SMEM));
+            configured_q40[wide][ctx->device & 15] = true;
+        }
+        // persistent CTAs, two per SM, each taking every gridDim.x-th tile of the device-side job list
+        int64_t ctas = 2 * (int64_t)ctx->prop.multiProcessorCount, most = (int64_t)grid.x * max_jobs;
+        const dim3 pgrid((unsigned)(ctas < most ? ctas : most));
+        if (wide) k_gemm_tc_grouped_q40<16><<<pgrid, GR_THREADS, SG_SMEM, ctx->stream>>>(map, A);
+        else k_gemm_tc_grouped_q40<4><<<pgrid, GR_THREADS, SG_SMEM, ctx->stream>>>(map, A);
+        ctx->launches++;
+        return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc_grouped_q40");
+    }
     const size_t smem = (size_t)GR_STAGES * GR_STAGE_BYTES + 1024;
     static bool configured[3][16] = {};
     const int ti = w->type == LEV_GGML_Q4_K ? 0 : (w->type == LEV_GGML_Q6_K ? 1 : 2);
