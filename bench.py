@@ -820,10 +820,14 @@ def run_extras(ctx, w_gate, dev, stream, world, rank):
                 out[f"decode_step_batch_{b}"] = _decode_step(ctx, dev, stream, peaks, b)
             except Exception as e:  # a side measurement never takes the headline down
                 out[f"decode_step_batch_{b}"] = {"error": repr(e)}
+    elif bool(ctx.lib.lev_dist_peer_memory(ctx.handle)):
+        # every rank decodes its own sequences, the experts are sharded: one sequence per rank, and 32 in all
+        for per_rank in sorted({1, max(1, 32 // world)}):
+            out[f"decode_step_batch_{per_rank * world}"] = _decode_step(ctx, dev, stream, peaks, per_rank, rank, world)
     return out if rank == 0 else None
 
 
-def _decode_step(ctx, dev, stream, peaks, batch):
+def _decode_step(ctx, dev, stream, peaks, batch, rank=0, world=1):
     """The synthetic 30-layer MoE decode step (leviathan_b200/decoder.py: the token loop of
     Sources/LeviathanCore/Gemma4.swift:3611-3905 without its host round trips) as ONE CUDA graph: embedding row ->
     30 x [norm, q/k/v, head norms + rotary + cache append, attention over 4096 cached positions, output
@@ -836,7 +840,7 @@ def _decode_step(ctx, dev, stream, peaks, batch):
     cfg = DecoderConfig()
     with torch.cuda.stream(stream):
         t0 = time.time()
-        dec = SyntheticDecoder(ctx, cfg, batch=batch, device=dev)
+        dec = SyntheticDecoder(ctx, cfg, batch=batch, device=dev, rank=rank, world=world)
         torch.cuda.synchronize()
         build_s = time.time() - t0
         l0 = ctx.launch_count()
@@ -857,27 +861,34 @@ def _decode_step(ctx, dev, stream, peaks, batch):
             a1.synchronize()
             ts.append(a0.elapsed_time(a1))
         ms = statistics.median(ts)
+        if world > 1:  # the slowest rank's median
+            import torch.distributed as dist
+
+            t = torch.tensor([ms], device=dev, dtype=torch.float64)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            ms = t.item()
 
         def head(i):
-            for a, b in dec._cols():
-                ctx.matvec_fused(dec.head, dec.x[a:b], "rmsnorm", dec.out_norm, cfg.eps, out=dec.logits[a:b])
-            ctx.softcap(dec.logits, cfg.softcap)
-            ctx.argmax_into(dec.logits, dec.tok)
+            dec.head_step()
 
         ms_head = _graph_time(torch, stream, head, 4)
     bt = cfg.bytes_per_token()
     # weights are read once per step whatever the batch; every sequence reads its own cache; the experts a
     # step touches: all top-8 at one sequence, the expected distinct count of a uniform routing otherwise
-    distinct = cfg.top_k if batch == 1 else cfg.experts * (1.0 - (1.0 - cfg.top_k / cfg.experts) ** batch)
-    step_bytes = cfg.layers * (bt["attention_weights"] + bt["router"] + distinct * bt["expert"] + batch * bt["kv_per_sequence"]) + bt["head"]
+    gbatch = batch * world
+    distinct = cfg.top_k if gbatch == 1 else cfg.experts * (1.0 - (1.0 - cfg.top_k / cfg.experts) ** gbatch)
+    # per GPU: its own sequences' caches, the replicated attention weights, router and head, its share of the experts
+    step_bytes = cfg.layers * (bt["attention_weights"] + bt["router"] + distinct / world * bt["expert"] + batch * bt["kv_per_sequence"]) + bt["head"]
     bound_ms = step_bytes / (peaks["hbm_gbs"] * 1e6)
     dec.free()
     del dec
     torch.cuda.empty_cache()
+    how = "" if world == 1 else f" over {world} GPUs ({batch} per GPU; attention and head local, experts sharded, expert-parallel MoE)"
     return {"workload": f"30 layers, hidden 2816, Q4_0 q/k/v/o (16 q heads, 8 KV heads, head_dim 256), fp16 paged cache at 4096 "
-                        f"positions, 128-expert Q4_0 MoE top-8, tied Q6_K head 262144, softcap 30, argmax; batch {batch}",
-            "one_cuda_graph": True, "launches_per_step": int(launches), "ms_per_step": ms, "tokens_per_s": batch / ms * 1e3,
-            "algorithmic_bytes_per_step": int(step_bytes), "hbm_bound_ms": bound_ms, "hbm_frac": bound_ms / ms,
+                        f"positions, 128-expert Q4_0 MoE top-8, tied Q6_K head 262144, softcap 30, argmax; batch {gbatch}{how}",
+            "projections": "prefill dequant-GEMM, bf16 activations" if batch >= 16 else "decode matvec, f32 activations",
+            "one_cuda_graph": True, "launches_per_step": int(launches), "ms_per_step": ms, "tokens_per_s": gbatch / ms * 1e3,
+            "algorithmic_bytes_per_step_per_gpu": int(step_bytes), "hbm_bound_ms": bound_ms, "hbm_frac": bound_ms / ms,
             "us_head_softcap_argmax": ms_head * 1e3, "head_gbs": bt["head"] / ms_head / 1e6,
             "outputs_finite": finite, "argmax_matches_torch": agree, "build_seconds": build_s}
 

@@ -430,10 +430,10 @@ class Context:
         return self._matvec_host(self.lib.lev_q4_k_matvec_host, blocks, out_dim, in_dim, x)
 
     # -- prefill --
-    def act_bf16(self, x):
+    def act_bf16(self, x, out=None):
         import torch
 
-        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device)
+        out = torch.empty(x.shape, dtype=torch.bfloat16, device=x.device) if out is None else out
         self._flags(False, False)
         self._check(self.lib.lev_act_bf16(self.handle, _ptr(x.contiguous()), x.numel(), _ptr(out)))
         return out

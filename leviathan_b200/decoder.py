@@ -77,13 +77,28 @@ class _Layer:
 class SyntheticDecoder:
     """`batch` sequences, each with `cfg.positions - 1` cached positions; `step()` decodes one token per
     sequence.  With `advance=False` (the timing form) the position stays at the last cache row, so a
-    step can repeat without running out of cache."""
+    step can repeat without running out of cache.
+
+    Projections: up to `gemm_from - 1` sequences go through the decode matvec (f32 activations, at most eight
+    columns a call); from `gemm_from` sequences on they go through the prefill dequant-GEMM on the tensor cores
+    (activations rounded to bf16, one pass over the weights whatever the batch), the numerics the reference's own
+    prefill path has (rust/crates/lev-forge/src/coopmat.rs:236-425).
+
+    Several GPUs (`world` > 1, the context already joined by dist.init_from_torch): every rank decodes its own
+    `batch` sequences (their caches differ by rank, the weights do not), attention and the head are local, and
+    the experts are sharded -- rank r keeps experts [r * E / world, (r + 1) * E / world) -- so the MoE of a step
+    is the expert-parallel layer: tokens go to the ranks that hold their experts and the expert rows come back
+    to be combined in slot order on the token's rank."""
 
     def __init__(self, ctx: Context, cfg: DecoderConfig, batch: int = 1, device="cuda", norm_sigma: float = 0.02,
-                 keep_host_copies: bool = False):
+                 keep_host_copies: bool = False, gemm_from: int = 16, rank: int = 0, world: int = 1):
         import torch
 
         self.ctx, self.cfg, self.batch, self.dev = ctx, cfg, batch, device
+        self.wide = batch >= gemm_from
+        self.rank, self.world = rank, world
+        if cfg.experts % world:
+            raise ValueError(f"{cfg.experts} experts do not split over {world} ranks")
         H, QH, KVH, HD = cfg.hidden, cfg.q_heads, cfg.kv_heads, cfg.head_dim
         self.host = {} if keep_host_copies else None
         self._seed = cfg.seed
@@ -99,7 +114,7 @@ class SyntheticDecoder:
             for s in range(batch):
                 cache.ensure(s, cfg.positions - 1)
             self._fill(cache.k, f"blk.{l}.cache_k")
-            self._fill(cache.v, f"blk.{l}.cache_v")
+            self._fill(cache.v, f"blk.{l}.cache_v")  # the two fills take their seeds in a per-rank range, see _fill
             self.layers.append(_Layer(wq, wk, wv, wo, moe, cache,
                                       self._norm(f"blk.{l}.attn_norm", H, norm_sigma), self._norm(f"blk.{l}.ffn_norm", H, norm_sigma),
                                       self._norm(f"blk.{l}.attn_q_norm", HD, norm_sigma), self._norm(f"blk.{l}.attn_k_norm", HD, norm_sigma)))
@@ -119,6 +134,9 @@ class SyntheticDecoder:
         self.v = torch.empty((B, KVH * HD), device=device)
         self.ao = torch.empty((B, QH, HD), device=device)
         self.logits = torch.empty((B, cfg.vocab), device=device)
+        if self.wide:
+            self.hb = torch.empty((B, H), dtype=torch.bfloat16, device=device)
+            self.aob = torch.empty((B, QH * HD), dtype=torch.bfloat16, device=device)
         self.graph = None
 
     # ---- synthetic tensors ----
@@ -144,19 +162,24 @@ class SyntheticDecoder:
 
         c = self.cfg
         E, H, I = c.experts, c.hidden, c.expert_inter
-        step = max(1, min(E, 16))
+        per = E // self.world
+        first = self.rank * per
+        step = max(1, min(per, 16))
         gu, dn = [], []
         for e0 in range(0, E, step):
             n = min(step, E - e0)
-            gu.append(Q.quantize(c.weight_type, Q.normal_torch(self._next_seed(), (n * 2 * I, H), c.sigma, self.dev)))
-            dn.append(Q.quantize(c.weight_type, Q.normal_torch(self._next_seed(), (n * H, I), c.sigma, self.dev)))
+            s_gu, s_dn = self._next_seed(), self._next_seed()   # every rank walks the same seeds
+            if e0 + n <= first or e0 >= first + per:
+                continue                                        # ... and builds only its own experts
+            gu.append(Q.quantize(c.weight_type, Q.normal_torch(s_gu, (n * 2 * I, H), c.sigma, self.dev)))
+            dn.append(Q.quantize(c.weight_type, Q.normal_torch(s_dn, (n * H, I), c.sigma, self.dev)))
         gu, dn = torch.cat(gu), torch.cat(dn)
         router = Q.normal_torch(self._next_seed(), (E, H), c.sigma, self.dev)
         if self.host is not None:
             self.host[f"blk.{l}.ffn_gate_up_exps"] = gu.cpu().numpy()
             self.host[f"blk.{l}.ffn_down_exps"] = dn.cpu().numpy()
             self.host[f"blk.{l}.ffn_gate_inp"] = router.cpu().numpy()
-        return self.ctx.moe_upload(router, gu, dn, E, H, I)
+        return self.ctx.moe_upload(router, gu, dn, E, H, I, first, per)
 
     def _norm(self, name, n, sigma):
         w = 1.0 + Q.normal_torch(self._next_seed(), (n,), sigma, self.dev)
@@ -171,7 +194,9 @@ class SyntheticDecoder:
         chunk = 1 << 26
         for o in range(0, flat.numel(), chunk):
             n = min(chunk, flat.numel() - o)
-            flat[o:o + n] = Q.normal_torch(self._next_seed(), (n,), 1.0, self.dev).to(torch.float16)
+            # weights share their seeds over the ranks, caches do not: every rank decodes its own sequences
+            seed = self._next_seed() ^ (self.rank << 40)
+            flat[o:o + n] = Q.normal_torch(seed, (n,), 1.0, self.dev).to(torch.float16)
 
     # ---- the step ----
     def _cols(self):
@@ -185,22 +210,44 @@ class SyntheticDecoder:
         ctx.embed_rows(self.head, self.tok, math.sqrt(c.hidden), out=self.x)
         x, x1 = self.x, self.x1
         for L in self.layers:
-            for a, b in self._cols():
-                ctx.matvec_multi_fused([L.wq, L.wk, L.wv], x[a:b], "rmsnorm", L.attn_norm, c.eps, outs=[self.q[a:b], self.k[a:b], self.v[a:b]])
+            if self.wide:
+                ctx.rmsnorm(x, L.attn_norm, c.eps, out=self.h)
+                ctx.act_bf16(self.h, out=self.hb)
+                ctx.gemm_prefill(L.wq, self.hb, out=self.q)
+                ctx.gemm_prefill(L.wk, self.hb, out=self.k)
+                ctx.gemm_prefill(L.wv, self.hb, out=self.v)
+            else:
+                for a, b in self._cols():
+                    ctx.matvec_multi_fused([L.wq, L.wk, L.wv], x[a:b], "rmsnorm", L.attn_norm, c.eps, outs=[self.q[a:b], self.k[a:b], self.v[a:b]])
             ctx.qkv_norm_rope_append_split(self.q, self.k, self.v, QH, L.cache, self.slot, self.pos, L.q_norm, L.k_norm, c.eps, self.inv_freq)
             ctx.attn_decode(L.cache, self.slot, self.pos, self.q.view(self.batch, QH, HD), 0, c.attn_scale, out=self.ao)
-            for a, b in self._cols():
-                ctx.matvec_fused(L.wo, self.ao[a:b].view(b - a, qw), None, residual=x[a:b], alpha=1.0, out=x1[a:b])
+            if self.wide:
+                ctx.act_bf16(self.ao.view(self.batch, qw), out=self.aob)
+                ctx.gemm_prefill(L.wo, self.aob, out=self.mo)
+                ctx.axpy(1.0, self.mo, x, out=x1)
+            else:
+                for a, b in self._cols():
+                    ctx.matvec_fused(L.wo, self.ao[a:b].view(b - a, qw), None, residual=x[a:b], alpha=1.0, out=x1[a:b])
             ctx.rmsnorm(x1, L.ffn_norm, c.eps, out=self.h)
-            ctx.moe_layer(L.moe, self.h, c.top_k, out=self.mo)
+            ctx.moe_layer(L.moe, self.h, c.top_k, out=self.mo, expert_parallel=self.world > 1)
             ctx.axpy(1.0, self.mo, x1, out=x)
-        for a, b in self._cols():
-            ctx.matvec_fused(self.head, x[a:b], "rmsnorm", self.out_norm, c.eps, out=self.logits[a:b])
-        ctx.softcap(self.logits, c.softcap)
-        ctx.argmax_into(self.logits, self.tok)
+        self.head_step()
         if advance:
             self.pos.add_(1)
         return self.tok
+
+    def head_step(self):
+        """final norm -> tied head -> softcap -> greedy argmax into the token ids (Gemma4.swift:3622-3643)"""
+        c, ctx, x = self.cfg, self.ctx, self.x
+        if self.wide:
+            ctx.rmsnorm(x, self.out_norm, c.eps, out=self.h)
+            ctx.act_bf16(self.h, out=self.hb)
+            ctx.gemm_prefill(self.head, self.hb, out=self.logits)
+        else:
+            for a, b in self._cols():
+                ctx.matvec_fused(self.head, x[a:b], "rmsnorm", self.out_norm, c.eps, out=self.logits[a:b])
+        ctx.softcap(self.logits, c.softcap)
+        ctx.argmax_into(self.logits, self.tok)
 
     def capture(self, advance: bool = False):
         """Records `step` as one CUDA graph on the context's stream; `replay()` then decodes a token."""
@@ -231,3 +278,43 @@ class SyntheticDecoder:
             L.moe.free()
         self.head.free()
         self.layers = []
+
+
+def _main():
+    """python -m leviathan_b200.decoder [--batch B] [--layers L] [--vocab V] [--steps N] [--graph]
+    builds the synthetic decoder on cuda:0, decodes N tokens per sequence and prints the rate."""
+    import argparse
+    import time
+
+    import torch
+
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--layers", type=int, default=30)
+    ap.add_argument("--vocab", type=int, default=262144)
+    ap.add_argument("--steps", type=int, default=16)
+    ap.add_argument("--graph", action="store_true", help="capture the step as one CUDA graph and replay it")
+    a = ap.parse_args()
+    ctx = Context(0)
+    cfg = DecoderConfig(layers=a.layers, vocab=a.vocab)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        dec = SyntheticDecoder(ctx, cfg, batch=a.batch)
+        if a.graph:
+            dec.capture()
+        run = dec.replay if a.graph else dec.step
+        run()
+        ctx.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(a.steps):
+            run()
+        ctx.synchronize()
+        dt = time.perf_counter() - t0
+    print(f"{a.steps} steps of {a.batch} sequences, {a.layers} layers, vocabulary {a.vocab}: {dt / a.steps * 1e3:.3f} ms per step, "
+          f"{a.batch * a.steps / dt:.1f} tokens/s, last tokens {dec.tok[:4].tolist()}")
+    dec.free()
+    ctx.close()
+
+
+if __name__ == "__main__":
+    _main()

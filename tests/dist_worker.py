@@ -138,6 +138,39 @@ def main():
     mw2.free()
     torch.cuda.synchronize()
     dist.barrier()
+
+    # the decode step on several GPUs: every rank decodes its own sequences, the experts are sharded; against the
+    # same step with every expert resident, on the same caches and tokens, eager and as one CUDA graph
+    from leviathan_b200.decoder import DecoderConfig, SyntheticDecoder
+
+    cfg = DecoderConfig(hidden=256, layers=2, q_heads=4, kv_heads=2, head_dim=128, experts=8 * world, top_k=2, expert_inter=64,
+                        vocab=512, positions=48, page=16)
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        dec = SyntheticDecoder(ctx, cfg, batch=2, rank=rank, world=world)
+        one = SyntheticDecoder(ctx, cfg, batch=2)
+        for a, b in zip(one.layers, dec.layers):
+            a.cache.k.copy_(b.cache.k)
+            a.cache.v.copy_(b.cache.v)
+        toks = torch.tensor([3 + 11 * rank, 40 + rank], dtype=torch.int32, device=dev)
+        dec.tok.copy_(toks)
+        one.tok.copy_(toks)
+        one.step()
+        dec.step()
+        torch.cuda.synchronize()
+        lo, le = one.logits.cpu().numpy(), dec.logits.cpu().numpy()
+        assert float(np.max(np.abs(lo - le))) / max(1.0, float(np.max(np.abs(lo)))) < 1e-4, "decoder: expert-parallel step"
+        assert np.array_equal(one.tok.cpu().numpy(), dec.tok.cpu().numpy()), "decoder: tokens"
+        if peer:  # the peer-memory exchange keeps its epochs on the device, so the step replays as a graph
+            dec.tok.copy_(toks)
+            dec.capture()
+            dist.barrier()
+            dec.replay()
+            torch.cuda.synchronize()
+            assert np.array_equal(dec.logits.cpu().numpy().view(np.uint32), le.view(np.uint32)), "decoder: graph replay"
+        dist.barrier()
+        dec.free()
+        one.free()
     mw.free()
     ctx.close()
     dist.destroy_process_group()

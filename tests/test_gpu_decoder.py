@@ -84,7 +84,7 @@ def _reference_step(dec, cfg, batch, pos):
     return out
 
 
-@pytest.mark.parametrize("batch", [1, 3, 11])
+@pytest.mark.parametrize("batch", [1, 3, 11, 20])
 def test_decoder_step_against_the_f64_oracle_eager_and_as_one_graph(ctx, batch):
     cfg = DecoderConfig(**SMALL)
     stream = torch.cuda.Stream()
@@ -101,9 +101,10 @@ def test_decoder_step_against_the_f64_oracle_eager_and_as_one_graph(ctx, batch):
         for s in range(batch):
             want = refs[s]["logits"]
             err = np.max(np.abs(logits[s] - want)) / max(1.0, float(np.max(np.abs(want))))
-            assert err < 2e-4, (s, err)
+            # from 16 sequences on the projections run on the tensor cores with bf16 activations (bar 2e-2)
+            assert err < (2e-2 if dec.wide else 2e-4), (s, err)
             top2 = np.sort(want)[-2:]
-            if top2[1] - top2[0] > 1e-3:
+            if top2[1] - top2[0] > (0.5 if dec.wide else 1e-3):
                 assert toks[s] == refs[s]["token"]
             assert toks[s] == int(np.argmax(logits[s]))
         # the same step as one graph: same bits, and the token it leaves is the next step's input
