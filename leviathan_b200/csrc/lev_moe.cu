@@ -167,6 +167,117 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
 }
 
+// Tiled form for sixteen tokens or more: a CTA of 8 warps takes 16 experts x 16 tokens and walks the hidden
+// dimension in chunks (two chunk buffers: the next chunk's bulk copies fly while this one is used); warp w keeps
+// a 4 x 8 tile of double accumulators (experts 4 * (w & 3) ..., tokens 8 * (w >> 2) ...), so twelve conversions to
+// double feed thirty-two FMAs where the 2 x 4 tile above needs six for eight: the kernel is bound by the
+// conversion unit.  A lane still adds its columns lane, lane + 32, ... in ascending order (chunk lengths are
+// multiples of 32), so the bits equal the other forms'.
+constexpr int kRouterChunk = 704;   // floats per row and chunk: 32 rows x 2816 B x 2 buffers = 176 KB
+
+__global__ void __launch_bounds__(256) k_router_logits_tile(const float* __restrict__ rw, const float* __restrict__ x,
+                                                            int64_t tokens, int experts, int hidden,
+                                                            float* __restrict__ scores, int* status) {
+    extern __shared__ __align__(128) unsigned char rsm[];
+    __shared__ __align__(8) unsigned long long bars[2];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int e_base = blockIdx.x * 16;
+    const int64_t t_base = (int64_t)blockIdx.y * 16;
+    const int ne = experts - e_base < 16 ? experts - e_base : 16;
+    const int nt = (int)(tokens - t_base < 16 ? tokens - t_base : 16);
+    const int nchunks = (hidden + kRouterChunk - 1) / kRouterChunk;
+    float* const base = reinterpret_cast<float*>(rsm);
+    if (threadIdx.x == 0) {
+        for (int b = 0; b < 2; b++)
+            asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"((unsigned)__cvta_generic_to_shared(&bars[b])), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    __syncthreads();
+    // buffer rows 0..15: the experts' chunk, rows 16..31: the tokens' chunk; lane r of warp 0 requests row r
+    auto request = [&](int c) {
+        const int len = hidden - c * kRouterChunk < kRouterChunk ? hidden - c * kRouterChunk : kRouterChunk;
+        const unsigned bar_s = (unsigned)__cvta_generic_to_shared(&bars[c & 1]);
+        if (lane == 0)
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_s), "r"((unsigned)((ne + nt) * len * 4)) : "memory");
+        __syncwarp();
+        const float* src = nullptr;
+        if (lane < 16) {
+            if (lane < ne) src = rw + (int64_t)(e_base + lane) * hidden + (int64_t)c * kRouterChunk;
+        } else if (lane - 16 < nt) {
+            src = x + (t_base + lane - 16) * hidden + (int64_t)c * kRouterChunk;
+        }
+        if (src)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                             (unsigned)__cvta_generic_to_shared(base + ((size_t)(c & 1) * 32 + lane) * kRouterChunk)),
+                         "l"(src), "r"((unsigned)len * 4u), "r"(bar_s)
+                         : "memory");
+    };
+    if (warp == 0) {
+        request(0);
+        if (nchunks > 1) request(1);
+    }
+    const int ea = 4 * (warp & 3), tb = 8 * (warp >> 2);
+    const bool works = ea < ne && tb < nt;
+    double acc[4][8];
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 8; b++) acc[a][b] = 0.0;
+    for (int c = 0; c < nchunks; c++) {
+        const unsigned bar_s = (unsigned)__cvta_generic_to_shared(&bars[c & 1]);
+        bool landed = false;
+        const long long t_start = clock64();
+        for (unsigned i = 1; !landed; i++) {
+            unsigned ok;
+            asm volatile(
+                "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                : "=r"(ok)
+                : "r"(bar_s), "r"((unsigned)((c >> 1) & 1))
+                : "memory");
+            landed = ok != 0;
+            if (!landed && (i & 63u) == 0 && clock64() - t_start > 2000000000LL) break;
+        }
+        if (!__syncthreads_and(landed ? 1 : 0)) {  // every thread leaves together
+            if (threadIdx.x == 0) atomicOr(status, LEV_DEV_TIMEOUT);
+            return;
+        }
+        if (works) {
+            const int len = hidden - c * kRouterChunk < kRouterChunk ? hidden - c * kRouterChunk : kRouterChunk;
+            const float* w0 = base + ((size_t)(c & 1) * 32 + ea) * kRouterChunk;
+            const float* x0 = base + ((size_t)(c & 1) * 32 + 16 + tb) * kRouterChunk;
+            for (int i = lane; i < len; i += 32) {
+                double wv[4], xv[8];
+#pragma unroll
+                for (int a = 0; a < 4; a++) wv[a] = (double)w0[(size_t)a * kRouterChunk + i];
+#pragma unroll
+                for (int b = 0; b < 8; b++) xv[b] = (double)x0[(size_t)b * kRouterChunk + i];
+#pragma unroll
+                for (int a = 0; a < 4; a++)
+#pragma unroll
+                    for (int b = 0; b < 8; b++) acc[a][b] = fma(wv[a], xv[b], acc[a][b]);
+            }
+        }
+        __syncthreads();  // the buffer is free again
+        if (warp == 0 && c + 2 < nchunks) request(c + 2);
+    }
+    if (!works) return;
+    bool bad = false;
+#pragma unroll
+    for (int a = 0; a < 4; a++)
+#pragma unroll
+        for (int b = 0; b < 8; b++) {
+            const float sv = (float)warp_butterfly(acc[a][b]);
+            if (ea + a < ne && tb + b < nt) {
+                bad |= !isfinite(sv);
+                if (lane == 0) scores[(t_base + tb + b) * experts + e_base + ea + a] = sv;
+            }
+        }
+    if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
+}
+
 // Grouping and job table, one CTA.  Experts outside [first, first+count) are
 // not resident on this GPU; their pairs are left out.
 struct GroupArgs {
@@ -630,7 +741,18 @@ static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x
                           float* weights, float* scores, const GroupArgs* fuse) {
     dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
     const size_t stage = (size_t)16 * w->hidden * sizeof(float);
-    if (stage <= 200 * 1024 && w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0) {
+    const bool aligned = w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0;
+    if (aligned && tokens >= 16) {
+        const size_t tile_smem = (size_t)2 * 32 * kRouterChunk * sizeof(float);
+        static bool configured_tile[16] = {};
+        if (!configured_tile[ctx->device & 15]) {
+            LEV_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem));
+            configured_tile[ctx->device & 15] = true;
+        }
+        dim3 tgrid((unsigned)((w->experts + 15) / 16), (unsigned)((tokens + 15) / 16));
+        LEV_CUDA(ctx, launch_pdl(k_router_logits_tile, tgrid, dim3(256), tile_smem, ctx->stream, (const float*)w->router_w, x, tokens,
+                                 (int)w->experts, (int)w->hidden, scores, ctx->d_status));
+    } else if (stage <= 200 * 1024 && aligned) {
         static bool configured[16] = {};
         if (!configured[ctx->device & 15]) {
             LEV_CUDA(ctx, cudaFuncSetAttribute(k_router_logits, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));

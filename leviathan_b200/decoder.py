@@ -109,6 +109,9 @@ class SyntheticDecoder:
             wk = self._tensor(f"blk.{l}.attn_k", cfg.weight_type, KVH * HD, H)
             wv = self._tensor(f"blk.{l}.attn_v", cfg.weight_type, KVH * HD, H)
             wo = self._tensor(f"blk.{l}.attn_output", cfg.weight_type, H, QH * HD)
+            if not self.wide:
+                for w in (wq, wk, wv, wo):
+                    w.release_gguf()   # only the decode kernels read these: one resident copy instead of two
             moe = self._experts(l)
             cache = PagedKV(batch * blocks_per_seq + 1, cfg.page, KVH, HD, slots=batch, max_blocks=blocks_per_seq, dtype="f16", device=device)
             for s in range(batch):
