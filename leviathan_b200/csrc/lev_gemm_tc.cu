@@ -52,9 +52,10 @@ struct GemmTcArgs {
     int64_t row_bytes;
     int64_t rows, cols;
     int tokens;
-    float* y;             // [tokens][rows]
+    float* y;             // [tokens][rows]; with a K split: [gridDim.z][tokens][rows] partial products
     int y_vec;            // rows of y start on 16-byte boundaries
     int* status;
+    int ksteps_per_split; // K-steps a CTA takes (blockIdx.z picks the range); the whole K without a split
 };
 
 __device__ __forceinline__ unsigned s32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -170,6 +171,18 @@ __device__ __forceinline__ float byte_f(unsigned w, unsigned k) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u + k)) - 8388608.0f;
 }
 
+// asynchronous copies into shared memory (raw weight bytes staged ahead of their decode)
+__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async4(unsigned dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
+
 // What one decode thread needs of one row for one K-step (64 columns): it is thread j = 0..3 of
 // the four that share the row and produces two 16-byte chunks (8 bf16 each) of the tile row.
 //   Q4_K: K-step = chunk c of block b; bytes qs[32c + 8j ..+8): low nibbles -> chunk j (sub-block
@@ -276,7 +289,85 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
     *reinterpret_cast<uint4*>(wtile + swz(r, ch_hi)) = pack8(hi);
 }
 
-template <int TYPE>
+// ---- staged decode of the dense kernel: two threads per weight row ----
+// The raw GGUF bytes of the tile's 176 rows x 256 columns (144 bytes per row for both 4-bit formats) are copied
+// to shared memory by cp.async one group ahead; a thread reads its row's bytes with 16-byte shared loads (rows
+// 144 bytes apart: eight lanes cover the 32 banks) and produces 32 of the K-step's 64 values, four 16-byte chunks
+// of the swizzled tile row.  Thread half h takes the low (0) or the high (1) nibbles, so both halves run the
+// same instructions with a shift of 4h.
+constexpr int DS_ROW_BYTES = 144;
+constexpr int DS_RAW_BYTES = RN * DS_ROW_BYTES;     // 25344 per group
+constexpr int kDecodeThreads = kDequantWarps * 32;   // 352 = 2 x RN
+static_assert(kDecodeThreads == 2 * RN && DS_RAW_BYTES % 16 == 0, "two decode threads per weight row");
+__device__ __forceinline__ void dense_decode_barrier() { asm volatile("bar.sync 1, %0;\n" ::"n"(kDecodeThreads) : "memory"); }
+
+// Q4_K: K-step c of the block whose 144 bytes start at blk; half h = sub-block 2c + h.  value = d1 * q - m1 with
+// d1 = d * sc, m1 = dmin * m as the reference forms them (rust/crates/lev-cpu/src/lib.rs:110-130); d1 * q is
+// exact in f32 (11 + 6 + 4 bits), so the fused multiply-add gives the bits of its multiply-then-subtract.
+__device__ __forceinline__ void q4k_half_store(const unsigned char* blk, int c, unsigned h, unsigned char* wtile, int r) {
+    const uint4 hdr = *reinterpret_cast<const uint4*>(blk);
+    const uint4 qa = *reinterpret_cast<const uint4*>(blk + 16 + 32 * c), qb = *reinterpret_cast<const uint4*>(blk + 32 + 32 * c);
+    const float d = h2f(hdr.x & 0xffffu), dmin = h2f(hdr.x >> 16);
+    const unsigned sc_w = c < 2 ? (hdr.y & 0x3F3F3F3Fu) : ((hdr.w & 0x0F0F0F0Fu) | ((hdr.y >> 2) & 0x30303030u));
+    const unsigned mn_w = c < 2 ? (hdr.z & 0x3F3F3F3Fu) : (((hdr.w >> 4) & 0x0F0F0F0Fu) | ((hdr.z >> 2) & 0x30303030u));
+    const unsigned sh = 8u * (2u * (unsigned)(c & 1) + h);
+    const float d1 = __fmul_rn(d, (float)((sc_w >> sh) & 0xffu)), nm1 = -__fmul_rn(dmin, (float)((mn_w >> sh) & 0xffu));
+    const unsigned w[8] = {qa.x, qa.y, qa.z, qa.w, qb.x, qb.y, qb.z, qb.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        float v[8];
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const unsigned n4 = (w[2 * j + k] >> (4u * h)) & 0x0F0F0F0Fu;
+#pragma unroll
+            for (int i = 0; i < 4; i++) v[4 * k + i] = __fmaf_rn(d1, __uint_as_float(__byte_perm(n4, 0x4B000000u, 0x7650u + i)) - 8388608.0f, nm1);
+        }
+        *reinterpret_cast<uint4*>(wtile + swz(r, 4 * (int)h + j)) = pack8(v);
+    }
+}
+
+// Q4_0: K-step S (0..3) of a 256-column group = the two blocks at byte 36 * S of the row's 144; half h takes the
+// low or high nibbles of both blocks: values 16h .. 16h + 15 of each, chunks 4b + 2h and 4b + 2h + 1.
+// d * (128 + q) - 136 d is exact and equals the reference's d * (q - 8) (Sources/LeviathanCore/Q4.swift:54-69).
+template <int S>
+__device__ __forceinline__ void q40_half_store(const unsigned char* rowraw, unsigned h, unsigned char* wtile, int r) {
+    const uint4* src = reinterpret_cast<const uint4*>(rowraw + ((36 * S) & ~15));
+    unsigned L[12];
+#pragma unroll
+    for (int c = 0; c < 3; c++) {
+        const uint4 v4 = src[c];
+        L[4 * c] = v4.x; L[4 * c + 1] = v4.y; L[4 * c + 2] = v4.z; L[4 * c + 3] = v4.w;
+    }
+    const unsigned* w = L + S;   // the 36 bytes start at word S of the window
+#pragma unroll
+    for (int b = 0; b < 2; b++) {
+        unsigned q[4];
+        unsigned dbits;
+        if (b == 0) {
+            dbits = w[0] & 0xffffu;
+#pragma unroll
+            for (int k = 0; k < 4; k++) q[k] = __funnelshift_r(w[k], w[k + 1], 16);
+        } else {
+            dbits = w[4] >> 16;
+#pragma unroll
+            for (int k = 0; k < 4; k++) q[k] = w[5 + k];
+        }
+        const float d = h2f(dbits), c136 = __fmul_rn(d, -136.0f);
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            float v[8];
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const unsigned n4 = (q[2 * j + k] >> (4u * h)) & 0x0F0F0F0Fu;
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[4 * k + i] = __fmaf_rn(d, __uint_as_float(__byte_perm(n4, 0x43000000u, 0x7054u + (i << 8))), c136);
+            }
+            *reinterpret_cast<uint4*>(wtile + swz(r, 4 * b + 2 * (int)h + j)) = pack8(v);
+        }
+    }
+}
+
+template <int TYPE, bool STAGED>
 __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__ CUtensorMap xmap, GemmTcArgs A) {
     extern __shared__ unsigned char smem_dyn[];
     __shared__ __align__(8) unsigned long long full_x[STAGES], full_w[STAGES], empty[STAGES], accum_full;
@@ -288,7 +379,11 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
     const int64_t r0 = (int64_t)blockIdx.x * RN;
     const int t0 = blockIdx.y * TM;
     const int halves = A.tokens - t0 > 128 ? 2 : 1;
-    const int kt = (int)(A.cols / KS);
+    // K split: this CTA's K-steps are [kbase, kbase + kt) of the tensor's, its output slab is blockIdx.z
+    const int kt_all = (int)(A.cols / KS);
+    const int kbase = (int)blockIdx.z * A.ksteps_per_split;
+    const int kt = kt_all - kbase < A.ksteps_per_split ? kt_all - kbase : A.ksteps_per_split;
+    float* const yout = A.y + (int64_t)blockIdx.z * A.tokens * A.rows;
 
     if (threadIdx.x == 0) {
         abort_s = 0;
@@ -320,8 +415,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                 if (it >= STAGES && !mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag)) break;
                 const unsigned dst = s32(smem + (size_t)s * kStageBytes);
                 mbar_expect_tx(s32(&full_x[s]), halves * kXHalfBytes);
-                tma_load_2d(dst, &xmap, it * KS, t0, s32(&full_x[s]));
-                if (halves == 2) tma_load_2d(dst + kXHalfBytes, &xmap, it * KS, t0 + 128, s32(&full_x[s]));
+                tma_load_2d(dst, &xmap, (kbase + it) * KS, t0, s32(&full_x[s]));
+                if (halves == 2) tma_load_2d(dst + kXHalfBytes, &xmap, (kbase + it) * KS, t0 + 128, s32(&full_x[s]));
             }
         }
     } else if (warp == 1) {
@@ -347,6 +442,59 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             umma_commit(s32(&accum_full));
         }
     } else {
+        bool ok = true;
+        if constexpr (STAGED) {
+            // ---- weight staging and decode: thread = (weight row, nibble half) ----
+            const int dt = threadIdx.x - 64;
+            const int row = dt % RN;
+            const unsigned half_h = (unsigned)(dt / RN);
+            unsigned char* rawbuf = smem + (size_t)STAGES * kStageBytes;
+            const int ngroups = kt >> 2;              // this form serves K in whole 256-column groups
+            // decode warp dw stages rows dw, dw + 11, ... (16 rows): lanes 0..26 take three rows at a time, nine
+            // 16-byte pieces each
+            const int dw = warp - 2;
+            const int l9 = lane / 9, p9 = lane - 9 * l9;
+            auto stage_group = [&](int g) {
+                const unsigned dst0 = s32(rawbuf + (size_t)(g & 1) * DS_RAW_BYTES);
+                const uint8_t* src0 = A.raw + r0 * A.row_bytes + (int64_t)((kbase >> 2) + g) * DS_ROW_BYTES;
+                if (lane < 27) {
+#pragma unroll
+                    for (int q = 0; q < 6; q++) {
+                        const int m = 3 * q + l9;
+                        const int r = dw + kDequantWarps * m;
+                        if (m < 16 && r0 + r < A.rows) cp_async16(dst0 + r * DS_ROW_BYTES + p9 * 16, src0 + (int64_t)r * A.row_bytes + p9 * 16);
+                    }
+                }
+            };
+            if (ngroups > 0) stage_group(0);
+            cp_async_commit();
+            for (int g = 0; g < ngroups; g++) {
+                cp_async_wait_but<0>();       // this thread's copies of group g have landed
+                dense_decode_barrier();       // everyone's have, and everyone is done reading the other slot
+                if (g + 1 < ngroups && ok) stage_group(g + 1);
+                cp_async_commit();
+                const unsigned char* rowraw = rawbuf + (size_t)(g & 1) * DS_RAW_BYTES + row * DS_ROW_BYTES;
+                auto kstep = [&](auto s_tag) {
+                    constexpr int SK = decltype(s_tag)::value;
+                    const int it = 4 * g + SK;
+                    if (!ok) return;
+                    const int s = it % STAGES;
+                    if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
+                    if (!ok) return;
+                    unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
+                    if (TYPE == LEV_GGML_Q4_K) q4k_half_store(rowraw, SK, half_h, wtile, row);
+                    else q40_half_store<SK>(rowraw, half_h, wtile, row);
+                    asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(s32(&full_w[s]));
+                };
+                kstep(std::integral_constant<int, 0>());
+                kstep(std::integral_constant<int, 1>());
+                kstep(std::integral_constant<int, 2>());
+                kstep(std::integral_constant<int, 3>());
+            }
+            cp_async_wait_but<0>();
+        } else {
         // ---- weight decode: thread = (2 rows 88 apart) x (byte group j); the raw bytes of the
         // next K-step are requested before this one is decoded ----
         // lanes 0..7 of a warp take byte group 0 of eight consecutive rows, lanes 8..15 group 1, ...:
@@ -365,9 +513,8 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
             rowp[i] = A.raw + (r0 + (valid[i] ? rb + kRowStep * i : 0)) * A.row_bytes;
 #pragma unroll
             for (int u = 0; u < kAhead; u++)
-                if (u < kt) load_raw<TYPE>(rowp[i], u, j, valid[i], ahead[u][i]);
+                if (u < kt) load_raw<TYPE>(rowp[i], kbase + u, j, valid[i], ahead[u][i]);
         }
-        bool ok = true;
         for (int it0 = 0; it0 < kt && ok; it0 += kAhead) {
 #pragma unroll
             for (int u = 0; u < kAhead; u++) {
@@ -378,17 +525,18 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
 #pragma unroll
                 for (int i = 0; i < NR; i++) {
                     cur[i] = ahead[u][i];
-                    if (it + kAhead < kt) load_raw<TYPE>(rowp[i], it + kAhead, j, valid[i], ahead[u][i]);
+                    if (it + kAhead < kt) load_raw<TYPE>(rowp[i], kbase + it + kAhead, j, valid[i], ahead[u][i]);
                 }
                 if (it >= STAGES) ok = mbar_wait(s32(&empty[s]), ((it / STAGES) & 1) ^ 1, abort_flag);
                 if (!ok) break;
                 unsigned char* wtile = smem + (size_t)s * kStageBytes + kXStageBytes;
 #pragma unroll
-                for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], it, j, valid[i], wtile, rb + kRowStep * i);
+                for (int i = 0; i < NR; i++) decode_store<TYPE>(cur[i], kbase + it, j, valid[i], wtile, rb + kRowStep * i);
                 asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");  // generic stores -> visible to the tensor core's reads
                 __syncwarp();
                 if (lane == 0) mbar_arrive(s32(&full_w[s]));
             }
+        }
         }
         // ---- epilogue: TMEM -> Y ----
         if (ok && warp < 10 && mbar_wait(s32(&accum_full), 0, abort_flag)) {
@@ -425,7 +573,7 @@ __global__ void __launch_bounds__(kThreads, 1) k_gemm_tc(const __grid_constant__
                         const int tok = t0 + half * 128 + quarter * 32 + tl;
                         const uint4 o = *reinterpret_cast<const uint4*>(stg + tl * 36 + col4);
                         if (tok < A.tokens && c + col4 < RN) {  // the last chunk of a tile may be narrower than 32
-                            float* dst = A.y + (int64_t)tok * A.rows + r0 + c + col4;
+                            float* dst = yout + (int64_t)tok * A.rows + r0 + c + col4;
                             if (r0 + c + col4 + 4 <= A.rows && A.y_vec) {
                                 *reinterpret_cast<uint4*>(dst) = o;
                             } else {
@@ -694,16 +842,6 @@ constexpr int SG_TMEM_COLS = 256;
 static_assert(GR_JOB_TOKENS <= SG_ACC_COLS && SG_ACC_COLS + SG_STAGES * SG_A_COLS <= SG_TMEM_COLS && SG_ROW_BYTES % 16 == 0,
               "staged grouped form geometry");
 
-__device__ __forceinline__ void cp_async16(unsigned dst, const void* src) {
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async4(unsigned dst, const void* src) {
-    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(dst), "l"(src) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait_but() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory"); }
-__device__ __forceinline__ void decode_barrier() { asm volatile("bar.sync 1, 256;\n" ::: "memory"); }
 
 // one Q4_0 block (f16 d, 16 nibble bytes in q[4]) -> its 32 values as 16 packed bf16 pairs in column order: low
 // nibbles are values 0..15, high nibbles 16..31
@@ -1071,14 +1209,26 @@ EncodeTiledFn encode_tiled() {
     return fn;
 }
 
-template <int TYPE>
+// y = sum over the K splits' partial products, in split order (the same bits on every run)
+__global__ void __launch_bounds__(256) k_gemm_split_sum(const float4* __restrict__ part, int splits, int64_t n4, float4* __restrict__ y) {
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (int64_t)gridDim.x * blockDim.x) {
+        float4 a = part[i];
+        for (int z = 1; z < splits; z++) {
+            const float4 b = part[(int64_t)z * n4 + i];
+            a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+        }
+        y[i] = a;
+    }
+}
+
+template <int TYPE, bool STAGED>
 int launch_tc(lev_ctx* ctx, const CUtensorMap& map, const GemmTcArgs& A, dim3 grid, size_t smem) {
     static bool configured[16] = {};
     if (!configured[ctx->device & 15]) {
-        LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<TYPE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        LEV_CUDA(ctx, cudaFuncSetAttribute(k_gemm_tc<TYPE, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
         configured[ctx->device & 15] = true;
     }
-    k_gemm_tc<TYPE><<<grid, kThreads, smem, ctx->stream>>>(map, A);
+    k_gemm_tc<TYPE, STAGED><<<grid, kThreads, smem, ctx->stream>>>(map, A);
     return LEV_OK;
 }
 
@@ -1114,14 +1264,53 @@ int lev_gemm_tc_run(lev_ctx* ctx, const lev_weights* w, const void* x_bf16, int6
     A.y = y;
     A.y_vec = ((uintptr_t)y & 15) == 0 && (w->rows & 3) == 0;
     A.status = ctx->d_status;
+    A.ksteps_per_split = (int)(w->cols / KS);
     dim3 grid((unsigned)((w->rows + RN - 1) / RN), (unsigned)((tokens + TM - 1) / TM));
     const size_t smem = (size_t)STAGES * kStageBytes + 1024;
-    int st = w->type == LEV_GGML_Q4_K   ? launch_tc<LEV_GGML_Q4_K>(ctx, map, A, grid, smem)
-             : w->type == LEV_GGML_Q6_K ? launch_tc<LEV_GGML_Q6_K>(ctx, map, A, grid, smem)
-                                        : launch_tc<LEV_GGML_Q4_0>(ctx, map, A, grid, smem);
+    // Up to 128 tokens (decode batches) the kernel is bound by the weight decode: the 4-bit formats then decode from
+    // raw bytes staged in shared memory (40 % fewer instructions), when K comes in whole 256-column groups and every
+    // row starts on a 16-byte boundary (16-byte asynchronous copies).  Above that the token tiles' trip from L2 is
+    // the bound (measured: decode warps wait on the MMA's stage release 45 % of the time) and the register-staged
+    // form, which leaves shared memory to the pipeline, is the faster one (73 against 80 us on 512 x 12288 x 4096).
+    const bool staged = tokens <= 128 && w->type != LEV_GGML_Q6_K && w->cols % 256 == 0 && A.row_bytes % 16 == 0 &&
+                        ((uintptr_t)A.raw & 15) == 0;
+    const size_t smem_staged = smem + 2 * (size_t)DS_RAW_BYTES;
+    // A decode batch against a tensor of a few thousand rows makes a few dozen tiles, each a serial walk over the
+    // whole K: split K over gridDim.z (whole 256-column groups) until the SMs are covered, partial products to
+    // scratch, summed in split order by a second launch.
+    int splits = 1;
+    const int64_t groups = w->cols / 256, tiles = (int64_t)grid.x * grid.y;
+    const bool can_sum = ((uintptr_t)y & 15) == 0 && (tokens * w->rows) % 4 == 0;
+    if (staged && can_sum && tiles * 2 <= ctx->prop.multiProcessorCount && groups >= 2) {
+        int64_t want = ctx->prop.multiProcessorCount / tiles;
+        if (want > 8) want = 8;
+        if (want > groups) want = groups;
+        const int64_t per = (groups + want - 1) / want;          // groups per split
+        splits = (int)((groups + per - 1) / per);
+        A.ksteps_per_split = (int)(4 * per);
+    }
+    float* y_final = y;
+    if (splits > 1) {
+        void* scr;
+        LEV_TRY(lev_scratch(ctx, LEV_SCR_GEMM, (size_t)splits * tokens * w->rows * sizeof(float), &scr));
+        A.y = (float*)scr;
+        grid.z = (unsigned)splits;
+    }
+    int st = w->type == LEV_GGML_Q6_K ? launch_tc<LEV_GGML_Q6_K, false>(ctx, map, A, grid, smem)
+             : w->type == LEV_GGML_Q4_K
+                 ? (staged ? launch_tc<LEV_GGML_Q4_K, true>(ctx, map, A, grid, smem_staged) : launch_tc<LEV_GGML_Q4_K, false>(ctx, map, A, grid, smem))
+                 : (staged ? launch_tc<LEV_GGML_Q4_0, true>(ctx, map, A, grid, smem_staged) : launch_tc<LEV_GGML_Q4_0, false>(ctx, map, A, grid, smem));
     if (st) return st;
     ctx->launches++;
-    return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc");
+    LEV_TRY(lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_tc"));
+    if (splits > 1) {
+        const int64_t n4 = tokens * w->rows / 4;
+        int64_t blocks = (n4 + 255) / 256, cap = (int64_t)ctx->prop.multiProcessorCount * 4;
+        k_gemm_split_sum<<<(unsigned)(blocks < cap ? blocks : cap), 256, 0, ctx->stream>>>((const float4*)A.y, splits, n4, (float4*)y_final);
+        ctx->launches++;
+        return lev_cuda_check(ctx, cudaGetLastError(), "k_gemm_split_sum");
+    }
+    return LEV_OK;
 }
 
 // ---------------------------------------------------------------------------

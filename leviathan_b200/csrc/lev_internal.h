@@ -60,6 +60,7 @@ enum {
     LEV_SCR_XPREP = 6,   // split activations for the stream schedule
     LEV_SCR_DIST = 7,
     LEV_SCR_ATTN = 8,    // attention partials per position range
+    LEV_SCR_GEMM = 9,    // partial products of a K-split prefill GEMM
     LEV_SCR_SLOTS = 12
 };
 

@@ -26,6 +26,9 @@ def ctx():
     ("q4_k", 256, 1024, 64), ("q4_k", 80, 512, 37), ("q6_k", 128, 768, 70), ("q4_0", 96, 704, 5), ("q4_0", 64, 2816, 128),
     # several row tiles with a ragged last one, two token tiles (256 + 44)
     ("q4_k", 400, 512, 300), ("q6_k", 360, 256, 130),
+    # decode batches against tensors of a few row tiles: raw bytes staged in shared memory, K split over the grid
+    # (11 groups of 256 columns over 8 splits; 8 groups over 8; a ragged last row tile; one token)
+    ("q4_0", 528, 2816, 32), ("q4_k", 352, 2048, 32), ("q4_k", 200, 1024, 128), ("q4_0", 176, 512, 1),
 ])
 def test_gemm_matches_rounded_operand_oracle(ctx, name, rows, cols, tokens):
     t = H.TYPES[name]
