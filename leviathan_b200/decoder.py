@@ -167,7 +167,9 @@ class SyntheticDecoder:
         E, H, I = c.experts, c.hidden, c.expert_inter
         per = E // self.world
         first = self.rank * per
-        step = max(1, min(per, 16))
+        step = max(1, min(16, E // 8))   # experts per seed pair: the same walk whatever the number of ranks (up to 8)
+        if per % step:
+            raise ValueError(f"{per} experts per rank do not split into groups of {step}")
         gu, dn = [], []
         for e0 in range(0, E, step):
             n = min(step, E - e0)
