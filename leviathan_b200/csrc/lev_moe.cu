@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
 }
 
-// Tiled form for sixteen tokens or more: a CTA of 8 warps takes 16 experts x 16 tokens and walks the hidden
+// Tiled form for 128 tokens or more: a CTA of 8 warps takes 16 experts x 16 tokens and walks the hidden
 // dimension in chunks (two chunk buffers: the next chunk's bulk copies fly while this one is used); warp w keeps
 // a 4 x 8 tile of double accumulators (experts 4 * (w & 3) ..., tokens 8 * (w >> 2) ...), so twelve conversions to
 // double feed thirty-two FMAs where the 2 x 4 tile above needs six for eight: the kernel is bound by the
@@ -742,7 +742,7 @@ static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x
     dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
     const size_t stage = (size_t)16 * w->hidden * sizeof(float);
     const bool aligned = w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0;
-    if (aligned && tokens >= 16) {
+    if (aligned && tokens >= 128) {   // below that the tiles are too few to cover the SMs and the 8 x 8 form is the faster one
         const size_t tile_smem = (size_t)2 * 32 * kRouterChunk * sizeof(float);
         static bool configured_tile[16] = {};
         if (!configured_tile[ctx->device & 15]) {

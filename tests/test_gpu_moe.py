@@ -47,7 +47,7 @@ def models(ctx):
         m["mw"].free()
 
 
-@pytest.mark.parametrize("name,tokens", [("tail", 1), ("tail", 7), ("lanes", 5), ("gemma", 1), ("gemma", 32), ("gemma", 300)])
+@pytest.mark.parametrize("name,tokens", [("tail", 1), ("tail", 7), ("lanes", 5), ("gemma", 1), ("gemma", 32), ("gemma", 300), ("gemma", 130)])
 def test_router_is_bit_exact(ctx, models, name, tokens):
     m = models[name]
     e, h, i, k = m["dims"]
