@@ -370,6 +370,18 @@ class Context:
         keys w (Weights), x, out (all torch CUDA tensors, or all numpy arrays for the host-buffer form),
         and optionally row0, rows, prologue, norm_weight, eps, residual, alpha, depends.  Returns the
         list of outputs."""
+        self.chain_submit(self.chain_prepare(ops, check_finite))
+        return [o["out"] for o in ops]
+
+    def chain_submit(self, prepared):
+        """Submits a list built by chain_prepare: the bare C call, for loops that reuse the same buffers."""
+        n, arr, flags, host, _keep = prepared
+        if not host:
+            self._flags(False, False)
+        self._check(self.lib.lev_matvec_chain(self.handle, n, arr, flags))
+
+    def chain_prepare(self, ops, check_finite: bool = False):
+        """The lev_chain_op array of a list (see matvec_chain), built once; the buffers it names must stay alive."""
         n = len(ops)
         arr = (L.ChainOp * n)()
         host = n > 0 and not _is_torch(ops[0]["x"])
@@ -385,8 +397,7 @@ class Context:
             f = self._fusion(o.get("prologue"), o.get("norm_weight"), o.get("eps", 1e-6), o.get("residual"), o.get("alpha", 1.0))
             arr[i] = L.ChainOp(w.handle, row0, rows, _ptr(x), _ptr(out), int(bool(o.get("depends", False))), f)
         flags = self._flags(host, check_finite)
-        self._check(self.lib.lev_matvec_chain(self.handle, n, arr, flags))
-        return [o["out"] for o in ops]
+        return n, arr, flags, host, [(o["x"], o["out"], o.get("residual"), o.get("norm_weight")) for o in ops]
 
     # -- decode attention over a paged KV cache (torch CUDA tensors only) --
     def kv_append(self, cache: "PagedKV", slot, pos, k, v):

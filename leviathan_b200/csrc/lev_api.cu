@@ -473,7 +473,7 @@ extern "C" int lev_matvec_multi(lev_ctx* ctx, int n_ops, const lev_weights* cons
     }
     lev_chain_item chain_items[4];
     for (int i = 0; i < n_ops; i++) chain_items[i] = {w[i], 0, w[i]->rows, dx, dy[i], 0, nullptr};
-    if (n_cols == 1 && n_ops >= 2 && lev_chain_supported(ctx, n_ops, chain_items)) {
+    if (n_cols == 1 && n_ops >= 2 && lev_chain_preferred(ctx, n_ops, chain_items)) {
         note_evidence(ctx, "lev_matvec_chain", w[0], w[0]->rows, n_cols, 0, 0);
         LEV_TRY(lev_chain_run(ctx, n_ops, chain_items));
     } else if (n_ops >= 2 && lev_dense_multi_supported(ctx, n_ops, w, dx, n_cols)) {

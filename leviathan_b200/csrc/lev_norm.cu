@@ -206,7 +206,7 @@ extern "C" int lev_matvec_fused(lev_ctx* ctx, const lev_weights* w, int64_t row0
     if (n_cols == 1) {
         const lev_dense_fusion d = to_dense(fusion);
         const lev_chain_item it = {w, row0, rows, x, y, 0, &d};
-        if (lev_chain_supported(ctx, 1, &it)) return lev_chain_run(ctx, 1, &it);
+        if (lev_chain_preferred(ctx, 1, &it)) return lev_chain_run(ctx, 1, &it);
     }
     if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) {
         const lev_dense_fusion d = to_dense(fusion);
@@ -260,7 +260,7 @@ extern "C" int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights
         const lev_dense_fusion d = to_dense(fusion);
         lev_chain_item it[4];
         for (int i = 0; i < n_ops; i++) it[i] = {w[i], 0, w[i]->rows, x, y[i], 0, &d};
-        if (lev_chain_supported(ctx, n_ops, it)) return lev_chain_run(ctx, n_ops, it);
+        if (lev_chain_preferred(ctx, n_ops, it)) return lev_chain_run(ctx, n_ops, it);
     }
     if (lev_dense_multi_supported(ctx, n_ops, w, x, n_cols)) {
         const lev_dense_fusion d = to_dense(fusion);

@@ -768,7 +768,7 @@ int lev_launch_matvec_stream(lev_ctx* ctx, const lev_weights* w, int64_t row0, i
                              float* y) {
     if (n_cols == 1) {
         const lev_chain_item it = {w, row0, rows, x, y, 0, nullptr};
-        if (lev_chain_supported(ctx, 1, &it)) return lev_chain_run(ctx, 1, &it);
+        if (lev_chain_preferred(ctx, 1, &it)) return lev_chain_run(ctx, 1, &it);
     }
     if (lev_dense_supported(ctx, w, row0, rows, x, n_cols)) return lev_dense_run(ctx, w, row0, rows, x, n_cols, y);
     const int terms = lev_stream_terms(n_cols);

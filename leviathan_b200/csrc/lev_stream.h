@@ -73,6 +73,7 @@ struct lev_chain_item {
 };
 constexpr int kLevChainMaxOps = 32;
 bool lev_chain_supported(lev_ctx* ctx, int n_ops, const lev_chain_item* items);
+bool lev_chain_preferred(lev_ctx* ctx, int n_ops, const lev_chain_item* items);
 int lev_chain_run(lev_ctx* ctx, int n_ops, const lev_chain_item* items);
 // buffers of the persistent kernel, allocated with the context
 int lev_chain_init(lev_ctx* ctx);
