@@ -112,6 +112,7 @@ SIGNATURES = {
     "lev_act_bf16": (_I, [_P, _P, _L, _P]),
     "lev_moe_weights_upload": (_I, [_P, _P, _P, _Z, _P, _Z, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),
     "lev_moe_weights_free": (_I, [_P, _P]),
+    "lev_moe_weights_release_gguf": (_I, [_P, _P]),
     "lev_moe_route": (_I, [_P, _P, _P, _L, _I, _P, _P, _P, _U]),
     "lev_moe_group": (_I, [_P, _P, _L, _I, _I, _P, _P, _P, _U]),
     "lev_moe_experts": (_I, [_P, _P, _P, _L, _I, _P, _P, _P, _U]),

@@ -59,6 +59,10 @@ class MoEWeights:
         self.experts, self.hidden, self.inter = experts, hidden, inter
         self.local_first, self.local_count = local_first, local_count
 
+    def release_gguf(self):
+        """lev_moe_weights_release_gguf: keep only the repacked copy of the experts (decode-sized calls)."""
+        self.ctx._check(self.ctx.lib.lev_moe_weights_release_gguf(self.ctx.handle, self.handle))
+
     def free(self):
         if self.handle:
             self.ctx.lib.lev_moe_weights_free(self.ctx.handle, self.handle)

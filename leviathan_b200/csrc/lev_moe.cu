@@ -715,6 +715,15 @@ extern "C" int lev_moe_weights_upload(lev_ctx* ctx, const float* router_w, const
     return LEV_OK;
 }
 
+// Drops the GGUF-order copies of the expert tensors.  The decode-sized forms of the layer (below 512 token-slot
+// pairs) read the repacked copies only; the tensor-core form reads the GGUF bytes, so a layer released here
+// runs larger batches through the multi-column stream kernels instead.
+extern "C" int lev_moe_weights_release_gguf(lev_ctx* ctx, lev_moe_weights* w) {
+    if (!ctx || !w || !w->gate_up || !w->down) return LEV_BAD_ARGUMENT;
+    LEV_TRY(lev_weights_release_gguf(ctx, w->gate_up));
+    return lev_weights_release_gguf(ctx, w->down);
+}
+
 extern "C" int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w) {
     if (!ctx || !w) return LEV_BAD_ARGUMENT;
     cudaSetDevice(ctx->device);
@@ -739,6 +748,7 @@ int lev_moe_route_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, in
 
 static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, int32_t* idx,
                           float* weights, float* scores, const GroupArgs* fuse) {
+    if ((tokens + 7) / 8 > 65535) return lev_fail(ctx, LEV_EXCEEDS_WORKLOAD, "%lld tokens in one routing call (at most 524280)", (long long)tokens);
     dim3 grid((unsigned)((w->experts + 7) / 8), (unsigned)((tokens + 7) / 8));
     const size_t stage = (size_t)16 * w->hidden * sizeof(float);
     const bool aligned = w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0;

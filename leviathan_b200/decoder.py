@@ -184,7 +184,10 @@ class SyntheticDecoder:
             self.host[f"blk.{l}.ffn_gate_up_exps"] = gu.cpu().numpy()
             self.host[f"blk.{l}.ffn_down_exps"] = dn.cpu().numpy()
             self.host[f"blk.{l}.ffn_gate_inp"] = router.cpu().numpy()
-        return self.ctx.moe_upload(router, gu, dn, E, H, I, first, per)
+        moe = self.ctx.moe_upload(router, gu, dn, E, H, I, first, per)
+        if self.batch * self.world * c.top_k < 512:
+            moe.release_gguf()   # decode-sized calls read the repacked experts only: one resident copy
+        return moe
 
     def _norm(self, name, n, sigma):
         w = 1.0 + Q.normal_torch(self._next_seed(), (n,), sigma, self.dev)

@@ -210,6 +210,26 @@ def test_prefill_sized_layer_runs_on_the_tensor_cores(ctx, models, tokens):
     assert np.array_equal(out.view(np.uint32), out2.view(np.uint32))
 
 
+def test_layer_after_release_of_the_gguf_copies(ctx, models):
+    """A decode-only host drops the GGUF-order copies of the experts: decode-sized calls give the same bits as
+    before, and a batch of 768 pairs, which would have gone to the tensor cores, runs on the f32-activation
+    stream kernels instead (1e-4 of the f64 oracle instead of 5e-3)."""
+    m = models["gemma"]
+    e, h, i, k = m["dims"]
+    mw = ctx.moe_upload(m["rw"], m["gu"], m["dn"], e, h, i)
+    x1 = torch.from_numpy(Q.normal(801, (3, h), 1.0)).cuda()
+    before = ctx.moe_layer(mw, x1, k).cpu().numpy()
+    mw.release_gguf()
+    after = ctx.moe_layer(mw, x1, k).cpu().numpy()
+    assert np.array_equal(before.view(np.uint32), after.view(np.uint32))
+    x = Q.normal(802, (96, h), 1.0)
+    out = ctx.moe_layer(mw, torch.from_numpy(x).cuda(), k).cpu().numpy()
+    for t in (0, 50, 95):
+        _, _, _, rout64 = O.moe_token(h, i, e, k, m["rw"], m["gu"], m["dn"], x[t])
+        assert float(np.max(np.abs(out[t] - rout64))) / max(1.0, float(np.max(np.abs(rout64)))) < 1e-4, t
+    mw.free()
+
+
 def test_moe_rejections(ctx, models):
     m = models["tail"]
     e, h, i, k = m["dims"]
