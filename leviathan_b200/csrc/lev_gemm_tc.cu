@@ -17,13 +17,17 @@
 //     tcgen05.commit hands the stage back to the producers;
 //   * epilogue: warps 2..9 read the accumulators with tcgen05.ld (warp w owns TMEM lanes
 //     32*(w%4)...) and store Y rows with 16-byte stores.
+// Decode batches (up to 128 tokens) of the 4-bit formats take the STAGED form of the same kernel: the raw
+// bytes reach shared memory by cp.async one 256-column group ahead and two threads share a weight row; the
+// launch then also splits K over gridDim.z, partial products summed in split order by k_gemm_split_sum.
+// The grouped forms further down serve the routed MoE (weights as the MMA's M operand).
 // Every wait is bounded by about a second of SM clocks; on a timeout the CTA sets
 // LEV_DEV_TIMEOUT, skips the remaining work, frees its tensor memory and returns.
 #include <cuda.h>
-
-#include <type_traits>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
+
+#include <type_traits>
 
 #include "lev_internal.h"
 
@@ -41,10 +45,7 @@ constexpr int kWStageBytes = RN * KS * 2;             // 24576
 constexpr int kStageBytes = kXStageBytes + kWStageBytes;
 constexpr int kTmemCols = 512;
 constexpr long long kWaitCycles = 2000000000LL;
-#ifndef LEV_GEMM_AHEAD
-#define LEV_GEMM_AHEAD 3
-#endif
-constexpr int kAhead = LEV_GEMM_AHEAD;  // K-steps of raw weight bytes a decode thread has requested ahead of the one it decodes
+constexpr int kAhead = 3;  // K-steps of raw weight bytes a decode thread has requested ahead of the one it decodes
 
 struct GemmTcArgs {
     const uint8_t* raw;   // GGUF blocks, row-major
@@ -803,18 +804,9 @@ __global__ void __launch_bounds__(GR_THREADS, 3) k_gemm_tc_grouped(const __grid_
 // Decode warps 2..5 take the even K-steps, warps 6..9 the odd ones; jobs hold up to 64 tokens, so two CTAs
 // share an SM: 5 x 8 KB tokens, 2 x 18 KB raw bytes, and 256 TMEM columns each (64 accumulator + 4 x 32 weights).
 // ---------------------------------------------------------------------------
-#ifndef LEV_SG_STAGES
-#define LEV_SG_STAGES 4
-#endif
-#ifndef LEV_SG_XSTAGES
-#define LEV_SG_XSTAGES 5
-#endif
-#ifndef LEV_SG_RAW
-#define LEV_SG_RAW 2
-#endif
-constexpr int SG_STAGES = LEV_SG_STAGES;      // decoded weight tiles in tensor memory (32 columns each)
-constexpr int SG_XSTAGES = LEV_SG_XSTAGES;    // token tiles (8 KB each): a TMA load takes several K-steps to arrive, so this ring is the deeper one
-constexpr int SG_RAW_SLOTS = LEV_SG_RAW;   // groups of raw bytes in shared memory: one being decoded, the others on their way
+constexpr int SG_STAGES = 4;      // decoded weight tiles in tensor memory (32 columns each)
+constexpr int SG_XSTAGES = 5;    // token tiles (8 KB each): a TMA load takes several K-steps to arrive, so this ring is the deeper one
+constexpr int SG_RAW_SLOTS = 2;   // groups of raw bytes in shared memory: one being decoded, the others on their way
 constexpr int SG_X_BYTES = GR_JOB_TOKENS * KS * 2;          // 8192: one TMA box of 64 positions x 64 k
 constexpr int SG_GROUP_COLS = 256;
 constexpr int SG_ROW_BYTES = SG_GROUP_COLS / 32 * LEV_Q4_0_BYTES;   // 144
