@@ -430,9 +430,11 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
 }
 
 // ---------------------------------------------------------------------------
-// Tensor-core form of the split kernel for fp16 caches.  Same staging as k_attn_split (rows of the
-// range to shared memory by asynchronous copies, all requested at once), but the rows are consumed
-// 16 positions at a time by mma.sync m16n8k16 from ldmatrix fragments:
+// Tensor-core form of the split kernel for fp16 caches.  The rows of the range reach shared memory by
+// asynchronous copies in chunks of 32 positions, a fixed number of chunks ahead of the arithmetic, so the
+// stream of a block never drains inside its range (with whole rounds requested at once and a barrier
+// between rounds, 32 sequences ran at 0.61 of the copy bandwidth); the rows are consumed 16 positions at a
+// time by mma.sync m16n8k16 from ldmatrix fragments:
 //   scores:  S[16 positions][8 columns] = K tile [16 x headDim] . Q^T, the columns being the GROUP
 //            query heads of this KV head, each as two fp16 terms (q = hi + lo * 2^-11, exact to 2^-22),
 //   output:  O^T[headDim][8 columns] += V^T tile [headDim x 16] . P, P the softmax weights of the
@@ -442,6 +444,12 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
 // table entry was refused) are zeroed, because 0 * garbage is not 0 in a tensor core.
 // ---------------------------------------------------------------------------
 constexpr int kMmaWarps = 4;
+constexpr int kMmaChunk = 32;   // positions per chunk of the tensor-core kernel: two batches of 16, one copy group
+// chunks in shared memory per block: two blocks share an SM (3 x 32 KB at head_dim 256, 4 x 16 KB at 128)
+template <int HD>
+struct MmaSlots {
+    static constexpr int value = HD >= 256 ? 3 : 4;
+};
 
 __device__ __forceinline__ void ldsm_x4(unsigned addr, unsigned& r0, unsigned& r1, unsigned& r2, unsigned& r3) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr));
@@ -467,14 +475,14 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
     constexpr float kLo = 4.8828125e-4f;  // 2^-11
     extern __shared__ __align__(128) unsigned char attn_smem[];
     __shared__ float sm_m[kMmaWarps][GROUP], sm_l[kMmaWarps][GROUP];
-    __shared__ int sm_tbl[kMaxRoundPages];
-    __shared__ int sm_any_bad;
+    __shared__ unsigned char sm_row_ok[MmaSlots<HD>::value][kMmaChunk];  // 1: the row was copied from the cache
     const int split = blockIdx.x, kvh = blockIdx.y, col = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-    const int round_cap = A.round_cap;  // a multiple of 16
-    unsigned char* ks = attn_smem;
-    unsigned char* vs = attn_smem + (size_t)round_cap * kRowBytes;
-    const unsigned ks_s = smem_u32(ks), vs_s = smem_u32(vs);
+    // The range is walked in chunks of kMmaChunk positions; a chunk's K rows and V rows take one slot of shared memory.
+    // Copies run NS - 1 chunks ahead of the arithmetic and never drain inside a range.
+    constexpr int NS = MmaSlots<HD>::value, CH = kMmaChunk;
+    constexpr unsigned kSlotBytes = 2u * CH * kRowBytes;
+    const unsigned smem_s = smem_u32(attn_smem);
     pdl_wait();
     pdl_launch_dependents();
     int slot, qpos;
@@ -516,135 +524,131 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
     bool bad = false;
     const int page_shift = (A.page & (A.page - 1)) == 0 ? __ffs(A.page) - 1 : -1;
     auto page_of = [&](int p) { return page_shift >= 0 ? p >> page_shift : p / A.page; };
-    if (threadIdx.x == 0) sm_any_bad = 0;
-    for (int r0 = begin; r0 < end; r0 += round_cap) {
-        const int rn = end - r0 < round_cap ? end - r0 : round_cap;  // positions of this round
-        const int rn16 = (rn + 15) & ~15;                            // rows the batches read
-        const int page0 = page_of(r0), pages = page_of(r0 + rn - 1) - page0 + 1;
-        __syncthreads();  // the previous round's rows and table entries are no longer read
-        for (int j = threadIdx.x; j < pages; j += kMmaWarps * 32) {
-            int e = trow[page0 + j];
-            if (e < 0 || e >= A.blocks) {  // an entry outside the pool is recorded and not followed
-                bad = true;
-                e = -1;
-                sm_any_bad = 1;
-            }
-            sm_tbl[j] = e;
-        }
-        __syncthreads();
-        // ---- request every row of the round in four copy groups of whole batches ----
-        const int per_stage = ((rn16 / 16 + kStages - 1) / kStages) * 16;
-#pragma unroll
-        for (int st = 0; st < kStages; st++) {
-            const int j0 = st * per_stage, j1 = j0 + per_stage < rn16 ? j0 + per_stage : rn16;
-            for (int j = j0 + warp; j < j1; j += kMmaWarps) {
-                const int p = r0 + j;
-                int e = -1;
-                int pg = 0;
-                if (j < rn) {
-                    pg = page_of(p);
-                    e = sm_tbl[pg - page0];
-                }
-                const unsigned kd = ks_s + (unsigned)j * kRowBytes, vd = vs_s + (unsigned)j * kRowBytes;
-                if (e >= 0) {
-                    const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
-#pragma unroll
-                    for (int c = lane; c < 2 * kCpr; c += 32) {
-                        const bool is_v = c >= kCpr;
-                        const int cc = is_v ? c - kCpr : c;
-                        cp_async16((is_v ? vd : kd) + ((cc ^ (j & 7)) << 4), (is_v ? vp : kp) + at + cc * 16);
-                    }
-                } else {  // a row no copy fills: zeros
-#pragma unroll
-                    for (int c = lane; c < 2 * kCpr; c += 32) {
-                        const bool is_v = c >= kCpr;
-                        const int cc = is_v ? c - kCpr : c;
-                        asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"((is_v ? vd : kd) + (cc << 4)), "r"(0u) : "memory");
-                    }
+    const int nchunks = (end - begin + CH - 1) / CH;
+    // every warp requests its rows (warp, warp + 4, ...) of chunk c into slot c % NS; lane 0 notes per row whether a
+    // copy fills it (rows past the range and rows whose table entry is refused are zeroed and take no part)
+    auto issue = [&](int c) {
+        const int r0 = begin + c * CH;
+        const int rn = end - r0 < CH ? end - r0 : CH;
+        const int slot_i = c % NS;
+        const unsigned ks_s = smem_s + (unsigned)slot_i * kSlotBytes, vs_s = ks_s + (unsigned)CH * kRowBytes;
+        for (int j = warp; j < CH; j += kMmaWarps) {
+            const int p = r0 + j;
+            int e = -1;
+            int pg = 0;
+            if (j < rn) {
+                pg = page_of(p);
+                e = trow[pg];
+                if (e < 0 || e >= A.blocks) {  // an entry outside the pool is recorded and not followed
+                    bad = true;
+                    e = -1;
                 }
             }
-            cp_async_commit();
+            if (lane == 0) sm_row_ok[slot_i][j] = e >= 0;
+            const unsigned kd = ks_s + (unsigned)j * kRowBytes, vd = vs_s + (unsigned)j * kRowBytes;
+            if (e >= 0) {
+                const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
+#pragma unroll
+                for (int cc0 = lane; cc0 < 2 * kCpr; cc0 += 32) {
+                    const bool is_v = cc0 >= kCpr;
+                    const int cc = is_v ? cc0 - kCpr : cc0;
+                    cp_async16((is_v ? vd : kd) + ((cc ^ (j & 7)) << 4), (is_v ? vp : kp) + at + cc * 16);
+                }
+            } else {
+#pragma unroll
+                for (int cc0 = lane; cc0 < 2 * kCpr; cc0 += 32) {
+                    const bool is_v = cc0 >= kCpr;
+                    const int cc = is_v ? cc0 - kCpr : cc0;
+                    asm volatile("st.shared.v4.u32 [%0], {%1,%1,%1,%1};\n" ::"r"((is_v ? vd : kd) + (cc << 4)), "r"(0u) : "memory");
+                }
+            }
         }
-        // ---- take the groups as they land; batch b (16 positions) belongs to warp b % 4 ----
-        const bool any_bad = sm_any_bad != 0;
+    };
+    // one copy group per chunk, an empty one past the end: "all but the newest NS - 2" then always means chunk c
 #pragma unroll
-        for (int st = 0; st < kStages; st++) {
-            if (st == 0) cp_async_wait<kStages - 1>();
-            if (st == 1) cp_async_wait<kStages - 2>();
-            if (st == 2) cp_async_wait<kStages - 3>();
-            if (st == 3) cp_async_wait<0>();
-            __syncthreads();  // every thread's copies (and zero rows) of this group are visible
-            const int b0 = st * per_stage / 16, b1 = (st * per_stage + per_stage < rn16 ? st * per_stage + per_stage : rn16) / 16;
-            for (int b = b0; b < b1; b++) {
-                if ((b & (kMmaWarps - 1)) != warp) continue;
-                const int j0 = b * 16;
-                // ---- scores of the batch ----
-                float c[4] = {0.f, 0.f, 0.f, 0.f};
-                {
-                    float c2[4] = {0.f, 0.f, 0.f, 0.f};  // odd steps: two shorter dependent chains
-                    const int mi = lane >> 3, r = lane & 7;
-                    const int row = j0 + (mi & 1) * 8 + r;
-                    const unsigned base = ks_s + (unsigned)row * kRowBytes;
+    for (int c = 0; c < NS - 1; c++) {
+        if (c < nchunks) issue(c);
+        cp_async_commit();
+    }
+    for (int c = 0; c < nchunks; c++) {
+        cp_async_wait<NS - 2>();
+        __syncthreads();  // chunk c is there for every warp, and every warp is done with chunk c - 1
+        if (c + NS - 1 < nchunks) issue(c + NS - 1);  // into the slot chunk c - 1 has left
+        cp_async_commit();
+        const int r0 = begin + c * CH;
+        const int rn = end - r0 < CH ? end - r0 : CH;
+        const int slot_i = c % NS;
+        const unsigned ks_s = smem_s + (unsigned)slot_i * kSlotBytes, vs_s = ks_s + (unsigned)CH * kRowBytes;
+        // batch b of the chunk (16 positions) belongs to warp (2 c + b) % 4: the two batches of consecutive chunks go to
+        // different pairs of warps
+        for (int b = 0; b < CH / 16; b++) {
+            if (((2 * c + b) & (kMmaWarps - 1)) != warp) continue;
+            const int j0 = b * 16;
+            if (j0 >= rn) continue;
+            // ---- scores of the batch ----
+            float cacc[4] = {0.f, 0.f, 0.f, 0.f};
+            {
+                float c2[4] = {0.f, 0.f, 0.f, 0.f};  // odd steps: two shorter dependent chains
+                const int mi = lane >> 3, r = lane & 7;
+                const int row = j0 + (mi & 1) * 8 + r;
+                const unsigned base = ks_s + (unsigned)row * kRowBytes;
 #pragma unroll
-                    for (int s = 0; s < kSteps; s++) {
-                        unsigned a0, a1, a2, a3;
-                        ldsm_x4(base + (((2 * s + (mi >> 1)) ^ (row & 7)) << 4), a0, a1, a2, a3);
-                        mma16816((s & 1) ? c2 : c, a0, a1, a2, a3, qb[s][0], qb[s][1]);
-                    }
-#pragma unroll
-                    for (int i = 0; i < 4; i++) c[i] += c2[i];
+                for (int st = 0; st < kSteps; st++) {
+                    unsigned a0, a1, a2, a3;
+                    ldsm_x4(base + (((2 * st + (mi >> 1)) ^ (row & 7)) << 4), a0, a1, a2, a3);
+                    mma16816((st & 1) ? c2 : cacc, a0, a1, a2, a3, qb[st][0], qb[st][1]);
                 }
-                // this lane: positions j0 + g and j0 + g + 8 of head t
-                bool live0 = j0 + g < rn, live1 = j0 + g + 8 < rn;
-                if (any_bad) {
-                    if (live0) live0 = sm_tbl[page_of(r0 + j0 + g) - page0] >= 0;
-                    if (live1) live1 = sm_tbl[page_of(r0 + j0 + g + 8) - page0] >= 0;
-                }
-                const float s0 = live0 ? fmaf(c[1], kLo, c[0]) * A.scale : -INFINITY;
-                const float s1 = live1 ? fmaf(c[3], kLo, c[2]) * A.scale : -INFINITY;
-                float bm = fmaxf(s0, s1);
-                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
-                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
-                bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
-                const float m_new = fmaxf(m, bm);
-                float corr = 1.f, p0 = 0.f, p1 = 0.f;
-                if (m_new != -INFINITY) {
-                    corr = __expf(m - m_new);  // 0 the first time (m = -inf)
-                    p0 = __expf(s0 - m_new);   // dead rows: exp(-inf) = 0
-                    p1 = __expf(s1 - m_new);
-                }
-                m = m_new;
-                l = fmaf(l, corr, p0 + p1);  // this lane's share; summed over g at the end
 #pragma unroll
-                for (int mt = 0; mt < kSteps; mt++)
+                for (int i = 0; i < 4; i++) cacc[i] += c2[i];
+            }
+            // this lane: positions j0 + g and j0 + g + 8 of head t
+            const bool live0 = j0 + g < rn && sm_row_ok[slot_i][j0 + g] != 0;
+            const bool live1 = j0 + g + 8 < rn && sm_row_ok[slot_i][j0 + g + 8] != 0;
+            const float s0 = live0 ? fmaf(cacc[1], kLo, cacc[0]) * A.scale : -INFINITY;
+            const float s1 = live1 ? fmaf(cacc[3], kLo, cacc[2]) * A.scale : -INFINITY;
+            float bm = fmaxf(s0, s1);
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 4));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 8));
+            bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 16));
+            const float m_new = fmaxf(m, bm);
+            float corr = 1.f, p0 = 0.f, p1 = 0.f;
+            if (m_new != -INFINITY) {
+                corr = __expf(m - m_new);  // 0 the first time (m = -inf)
+                p0 = __expf(s0 - m_new);   // dead rows: exp(-inf) = 0
+                p1 = __expf(s1 - m_new);
+            }
+            m = m_new;
+            l = fmaf(l, corr, p0 + p1);  // this lane's share; summed over g at the end
 #pragma unroll
-                    for (int i = 0; i < 4; i++) acc[mt][i] *= corr;
-                // ---- P as a B fragment: column g = (head g / 2, term g % 2), positions 2t, 2t+1, 2t+8, 2t+9 ----
-                unsigned pb0, pb1;
-                {
-                    const int head = g >> 1, term = g & 1;
-                    const int src_a = (2 * t) * 4 + (head & 3), src_b = (2 * t + 1) * 4 + (head & 3);
-                    float pa0 = __shfl_sync(0xffffffffu, p0, src_a), pb_0 = __shfl_sync(0xffffffffu, p0, src_b);
-                    float pa1 = __shfl_sync(0xffffffffu, p1, src_a), pb_1 = __shfl_sync(0xffffffffu, p1, src_b);
-                    if (head >= GROUP) pa0 = pb_0 = pa1 = pb_1 = 0.f;
-                    pb0 = pack_half2(split_half(pa0, term), split_half(pb_0, term));
-                    pb1 = pack_half2(split_half(pa1, term), split_half(pb_1, term));
-                }
-                // ---- O^T += V^T tile . P ----
-                {
-                    const int mi = lane >> 3, r = lane & 7;
-                    const int row = j0 + (mi >> 1) * 8 + r;
-                    const unsigned base = vs_s + (unsigned)row * kRowBytes;
+            for (int mt = 0; mt < kSteps; mt++)
 #pragma unroll
-                    for (int mt = 0; mt < kSteps; mt++) {
-                        unsigned a0, a1, a2, a3;
-                        ldsm_x4_trans(base + (((2 * mt + (mi & 1)) ^ (row & 7)) << 4), a0, a1, a2, a3);
-                        mma16816(acc[mt], a0, a1, a2, a3, pb0, pb1);
-                    }
+                for (int i = 0; i < 4; i++) acc[mt][i] *= corr;
+            // ---- P as a B fragment: column g = (head g / 2, term g % 2), positions 2t, 2t+1, 2t+8, 2t+9 ----
+            unsigned pb0, pb1;
+            {
+                const int head = g >> 1, term = g & 1;
+                const int src_a = (2 * t) * 4 + (head & 3), src_b = (2 * t + 1) * 4 + (head & 3);
+                float pa0 = __shfl_sync(0xffffffffu, p0, src_a), pb_0 = __shfl_sync(0xffffffffu, p0, src_b);
+                float pa1 = __shfl_sync(0xffffffffu, p1, src_a), pb_1 = __shfl_sync(0xffffffffu, p1, src_b);
+                if (head >= GROUP) pa0 = pb_0 = pa1 = pb_1 = 0.f;
+                pb0 = pack_half2(split_half(pa0, term), split_half(pb_0, term));
+                pb1 = pack_half2(split_half(pa1, term), split_half(pb_1, term));
+            }
+            // ---- O^T += V^T tile . P ----
+            {
+                const int mi = lane >> 3, r = lane & 7;
+                const int row = j0 + (mi >> 1) * 8 + r;
+                const unsigned base = vs_s + (unsigned)row * kRowBytes;
+#pragma unroll
+                for (int mt = 0; mt < kSteps; mt++) {
+                    unsigned a0, a1, a2, a3;
+                    ldsm_x4_trans(base + (((2 * mt + (mi & 1)) ^ (row & 7)) << 4), a0, a1, a2, a3);
+                    mma16816(acc[mt], a0, a1, a2, a3, pb0, pb1);
                 }
             }
         }
     }
+    cp_async_wait<0>();
     if (bad) atomicOr(A.status, LEV_DEV_BAD_INDEX);
     // ---- merge the warps (fixed order); the row buffer is free now and holds their sums ----
     l += __shfl_xor_sync(0xffffffffu, l, 4);
@@ -923,17 +927,10 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     int64_t round_cap = (int64_t)(kRoundBytes / (2 * row_bytes));
     if (round_cap > (span + splits - 1) / splits) round_cap = (span + splits - 1) / splits;  // the longest range
     if (round_cap > (int64_t)(kMaxRoundPages - 1) * L->page) round_cap = (int64_t)(kMaxRoundPages - 1) * L->page;
-    // fp16 caches go through the tensor-core kernel: rounds are whole batches of 16 positions
+    // fp16 caches go through the tensor-core kernel: a fixed number of 32-position chunks in shared memory
     const bool use_mma = L->kv_type == LEV_KV_F16;
-    if (use_mma) {
-        round_cap = (int64_t)(kRoundBytesMma / (2 * row_bytes)) & ~(int64_t)15;
-        const int64_t longest = ((span + splits - 1) / splits + 15) & ~(int64_t)15;
-        if (round_cap > longest) round_cap = longest;
-        const int64_t page_cap = ((int64_t)(kMaxRoundPages - 1) * L->page) & ~(int64_t)15;
-        if (round_cap > page_cap) round_cap = page_cap;
-        if (round_cap < 16) return lev_fail(ctx, LEV_UNSUPPORTED, "page size %d too small for the tensor-core attention kernel", L->page);
-    }
     size_t smem = (size_t)round_cap * 2 * row_bytes;
+    if (use_mma) smem = (size_t)(L->head_dim >= 256 ? MmaSlots<256>::value : MmaSlots<128>::value) * kMmaChunk * 2 * row_bytes;
     const size_t merge_bytes = (size_t)kAttnWarps * group * L->head_dim * sizeof(float);
     if (smem < merge_bytes) smem = merge_bytes;
     const int hd = L->head_dim;
