@@ -180,7 +180,8 @@ def run_reference(args):
     line = {
         "impl": "reference", "metric": "Q4/Q6 matvec HBM GB/s", "value": value, "unit": "GB/s",
         "n_gpus": args.gpus, "steps": steps, "warmup": args.warmup, "ms_per_step": ms,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None, "dtype": "f32",
+        "data": "synthetic",
         "config": {"workload": "ffn_matvec_set_b1", "gate_up": "Q4_K 12288x4096 x2", "down": "Q6_K 4096x12288",
                    "columns": 1, "bytes_per_step": STEP_BYTES},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": threads, "kind": "port",
