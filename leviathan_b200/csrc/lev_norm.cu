@@ -390,9 +390,21 @@ static int chain_host(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned
     void *px, *py;
     LEV_TRY(lev_scratch(ctx, LEV_SCR_X, xb_total, &px));
     LEV_TRY(lev_scratch(ctx, LEV_SCR_Y, yb_total, &py));
+    // An output buffer in pinned host memory is mapped into the device's address space: the kernel then stores
+    // its rows there itself (a few posted writes per row tile) and no copy back is queued for that op.
+    bool direct[LEV_MAX_CHAIN_OPS];
     for (int i = 0; i < n_ops; i++) {
         dev[i].x = (const float*)((char*)px + (size_t)dev[i].x);
         dev[i].y = (float*)((char*)py + (size_t)dev[i].y);
+        direct[i] = false;
+        cudaPointerAttributes pa;
+        if (cudaPointerGetAttributes(&pa, ops[i].y) == cudaSuccess && pa.type == cudaMemoryTypeHost && pa.devicePointer != nullptr &&
+            ((uintptr_t)pa.devicePointer & 15) == 0) {
+            dev[i].y = (float*)pa.devicePointer;
+            direct[i] = true;
+        } else {
+            (void)cudaGetLastError();  // an ordinary host pointer is not an error here
+        }
     }
     for (int j = 0; j < n_seen; j++) {
         size_t xb = 0;
@@ -402,7 +414,8 @@ static int chain_host(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned
     }
     LEV_TRY(lev_matvec_chain(ctx, n_ops, dev, 0));
     for (int i = 0; i < n_ops; i++)
-        LEV_CUDA(ctx, cudaMemcpyAsync(ops[i].y, dev[i].y, (size_t)ops[i].rows * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
+        if (!direct[i])
+            LEV_CUDA(ctx, cudaMemcpyAsync(ops[i].y, dev[i].y, (size_t)ops[i].rows * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream));
     LEV_CUDA(ctx, cudaStreamSynchronize(ctx->stream));
     if (flags & LEV_FLAG_CHECK_FINITE)
         for (int i = 0; i < n_ops; i++)

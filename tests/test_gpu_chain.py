@@ -139,6 +139,33 @@ def test_many_small_ops_reuse_table_buffers(ctx):
         h.free()
 
 
+def test_host_buffer_form_with_pinned_and_pageable_outputs(ctx):
+    """LEV_FLAG_HOST_IO: inputs are copied in, one launch, outputs come back -- by the kernel's own stores when the
+    output buffer is pinned host memory, by a copy otherwise.  Both give the bits of the device-pointer call, and
+    the words after a pinned output stay untouched."""
+    specs = [("q4_k", 96, 768), ("q6_k", 48, 3072), ("q4_0", 300, 2816)]
+    hs, xs, refs = [], [], []
+    for i, (name, rows, cols) in enumerate(specs):
+        t = H.TYPES[name]
+        w = H.quantized(t, 1200 + i, rows, cols)
+        hs.append(ctx.upload(w, t, rows, cols))
+        xs.append(Q.normal(1300 + i, (cols,), 1.0))
+    dev_out = ctx.matvec_chain([dict(w=h, x=_dev(x), out=torch.empty(h.rows, device="cuda")) for h, x in zip(hs, xs)])
+    ctx.synchronize()
+    want = [o.cpu().numpy() for o in dev_out]
+    pageable = [np.full(h.rows + 8, 7.0, np.float32) for h in hs]
+    pinned = [torch.full((h.rows + 8,), 7.0).pin_memory() for h in hs]
+    for outs in (pageable, [p.numpy() for p in pinned], [pageable[0], pinned[1].numpy(), pageable[2]]):
+        for o in outs:
+            o[:] = 7.0
+        ctx.matvec_chain([dict(w=h, x=x, out=o[:h.rows]) for h, x, o in zip(hs, xs, outs)])
+        for h, o, ref in zip(hs, outs, want):
+            assert np.array_equal(o[:h.rows].view(np.uint32), ref.view(np.uint32))
+            assert (o[h.rows:] == 7.0).all()
+    for h in hs:
+        h.free()
+
+
 def test_chain_rejections(ctx):
     t = H.TYPES["q4_k"]
     w = H.quantized(t, 1, 32, 256)
