@@ -355,14 +355,18 @@ def run_gpu(args):
             ydp.view(-1).copy_(yd, non_blocking=True)
             torch.cuda.synchronize()
 
-    for i in range(3):
+    # like the device-side figure: the median of `reps` rounds of exactly K steps each, wall clock around a round
+    for i in range(max(3, args.warmup)):
         e2e_step(i)
-    barrier()
-    t0 = time.perf_counter()
-    for i in range(args.steps):
-        e2e_step(i)
-    barrier()
-    e2e_ms = 1000.0 * (time.perf_counter() - t0) / args.steps
+    rounds = []
+    for _ in range(args.reps):
+        barrier()
+        t0 = time.perf_counter()
+        for i in range(args.steps):
+            e2e_step(i)
+        barrier()
+        rounds.append(1000.0 * (time.perf_counter() - t0) / args.steps)
+    e2e_ms = statistics.median(rounds)
 
     if world > 1:
         t = torch.tensor([ms_per_step, e2e_ms], device=dev, dtype=torch.float64)

@@ -313,8 +313,9 @@ int lev_matvec_multi_fused(lev_ctx* ctx, int n_ops, const lev_weights* const* w,
  * the weight stream does not pause between ops; otherwise each op runs as lev_matvec_fused.
  * Device pointers; x has w->cols floats (2 * cols with LEV_PROLOGUE_GELU_UP), y has rows floats.
  * With LEV_FLAG_HOST_IO every x and y is a host buffer (independent plain or gelu-up products only):
- * distinct inputs are copied in once, outputs are copied back (an output in pinned, device-mapped host
- * memory is stored by the kernel itself and needs no copy) and the call synchronises;
+ * distinct inputs are brought in once (those in pinned, device-mapped host memory by one small kernel that
+ * reads them over the bus, the others by a queued copy each), outputs are copied back (an output in pinned,
+ * device-mapped host memory is stored by the kernel itself and needs no copy) and the call synchronises;
  * LEV_FLAG_CHECK_FINITE then checks inputs and outputs on the host like the one-shot entry points. */
 #define LEV_MAX_CHAIN_OPS 32
 typedef struct lev_chain_op {

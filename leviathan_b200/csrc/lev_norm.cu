@@ -74,6 +74,22 @@ __global__ void k_axpy(float alpha, const float* __restrict__ x, const float* r,
         y[i] = fmaf(alpha, x[i], r[i]);
 }
 
+// Inputs of a host-buffer list that lie in pinned, device-mapped host memory: one small kernel reads them over
+// the bus (16 bytes per thread, all requests in flight at once) into the device-side staging area.  It costs one
+// launch where the copy engine costs a queued copy per input plus an engine-to-engine hand-over, and the list's
+// kernel, launched programmatically dependent on it, fills its weight rings while the inputs travel.
+struct PullArgs {
+    const uint4* src[LEV_MAX_CHAIN_OPS];
+    uint4* dst[LEV_MAX_CHAIN_OPS];
+    unsigned n16[LEV_MAX_CHAIN_OPS];
+};
+__global__ void __launch_bounds__(256) k_pull(const __grid_constant__ PullArgs P) {
+    pdl_launch_dependents();
+    const int j = blockIdx.y;
+    const unsigned i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < P.n16[j]) P.dst[j][i] = __ldcv(P.src[j] + i);  // never from a cache: the host rewrites these bytes between calls
+}
+
 int elementwise_grid(lev_ctx* ctx, int64_t n) {
     const int64_t blocks = (n + 255) / 256, cap = (int64_t)ctx->prop.multiProcessorCount * 8;
     return (int)(blocks < cap ? (blocks < 1 ? 1 : blocks) : cap);
@@ -352,7 +368,7 @@ extern "C" int lev_matvec_chain(lev_ctx* ctx, int n_ops, const lev_chain_op* ops
 }
 
 // Host buffers: every op's x and y are host pointers (independent ops only).  Distinct inputs are
-// copied in once, the list runs as one launch, the outputs come back, one synchronisation.
+// brought in once, the list runs as one launch, the outputs come back, one synchronisation.
 static int chain_host(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned flags) {
     lev_chain_op dev[LEV_MAX_CHAIN_OPS];
     const void* seen_x[LEV_MAX_CHAIN_OPS];
@@ -406,11 +422,32 @@ static int chain_host(lev_ctx* ctx, int n_ops, const lev_chain_op* ops, unsigned
             (void)cudaGetLastError();  // an ordinary host pointer is not an error here
         }
     }
+    // Inputs: pinned and mapped ones are fetched by one kernel (k_pull), the others by one queued copy each.
+    PullArgs pull = {};
+    int n_pull = 0;
+    unsigned pull_max = 0;
     for (int j = 0; j < n_seen; j++) {
         size_t xb = 0;
         for (int i = 0; i < n_ops; i++)
             if (ops[i].x == seen_x[j]) xb = (size_t)(ops[i].fusion.prologue == LEV_PROLOGUE_GELU_UP ? 2 : 1) * ops[i].w->cols * sizeof(float);
-        LEV_CUDA(ctx, cudaMemcpyAsync((char*)px + seen_off[j], seen_x[j], xb, cudaMemcpyHostToDevice, ctx->stream));
+        cudaPointerAttributes pa;
+        if (xb % 16 == 0 && xb <= ((size_t)1 << 22) && cudaPointerGetAttributes(&pa, seen_x[j]) == cudaSuccess &&
+            pa.type == cudaMemoryTypeHost && pa.devicePointer != nullptr && ((uintptr_t)pa.devicePointer & 15) == 0) {
+            pull.src[n_pull] = (const uint4*)pa.devicePointer;
+            pull.dst[n_pull] = (uint4*)((char*)px + seen_off[j]);
+            pull.n16[n_pull] = (unsigned)(xb / 16);
+            if (pull.n16[n_pull] > pull_max) pull_max = pull.n16[n_pull];
+            n_pull++;
+        } else {
+            (void)cudaGetLastError();
+            LEV_CUDA(ctx, cudaMemcpyAsync((char*)px + seen_off[j], seen_x[j], xb, cudaMemcpyHostToDevice, ctx->stream));
+        }
+    }
+    if (n_pull) {
+        // an ordinary launch: it starts when everything queued before it (a list still reading the staging area) is over
+        k_pull<<<dim3((pull_max + 255) / 256, (unsigned)n_pull), 256, 0, ctx->stream>>>(pull);
+        LEV_TRY(lev_cuda_check(ctx, cudaGetLastError(), "k_pull"));
+        ctx->launches++;
     }
     LEV_TRY(lev_matvec_chain(ctx, n_ops, dev, 0));
     for (int i = 0; i < n_ops; i++)

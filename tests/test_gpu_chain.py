@@ -162,6 +162,26 @@ def test_host_buffer_form_with_pinned_and_pageable_outputs(ctx):
         for h, o, ref in zip(hs, outs, want):
             assert np.array_equal(o[:h.rows].view(np.uint32), ref.view(np.uint32))
             assert (o[h.rows:] == 7.0).all()
+    # inputs: pinned ones are fetched by one small kernel, pageable ones by a queued copy each; a pinned input
+    # rewritten by the host between two calls is read afresh (nothing is served from a cache)
+    pin_x = [torch.from_numpy(x.copy()).pin_memory() for x in xs]
+    outs = [p.numpy() for p in pinned]
+    for ins in ([p.numpy() for p in pin_x], [pin_x[0].numpy(), xs[1], pin_x[2].numpy()]):
+        for o in outs:
+            o[:] = 7.0
+        l0 = ctx.launch_count()
+        ctx.matvec_chain([dict(w=h, x=x, out=o[:h.rows]) for h, x, o in zip(hs, ins, outs)])
+        assert ctx.launch_count() - l0 == 2  # the fetch and the list
+        for h, o, ref in zip(hs, outs, want):
+            assert np.array_equal(o[:h.rows].view(np.uint32), ref.view(np.uint32))
+    for rep in range(3):
+        for p in pin_x:
+            p.mul_(-0.5)
+        ctx.matvec_chain([dict(w=h, x=p.numpy(), out=o[:h.rows]) for h, p, o in zip(hs, pin_x, outs)])
+        again = ctx.matvec_chain([dict(w=h, x=p.cuda(), out=torch.empty(h.rows, device="cuda")) for h, p in zip(hs, pin_x)])
+        ctx.synchronize()
+        for h, o, ref in zip(hs, outs, again):
+            assert np.array_equal(o[:h.rows].view(np.uint32), ref.cpu().numpy().view(np.uint32))
     for h in hs:
         h.free()
 
