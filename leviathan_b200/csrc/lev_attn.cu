@@ -309,7 +309,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
             for (int j = j0 + warp; j < j1; j += kAttnWarps) {
                 const int p = r0 + j, pg = page_of(p), e = sm_tbl[pg - page0];
                 if (e < 0) continue;
-                const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
+                const int64_t at = LEV_KV_ROW(e, p - pg * A.page, kvh, A.page, A.kv_heads) * (int64_t)kRowBytes;
                 const unsigned kd = smem_u32(ks) + (unsigned)j * kRowBytes, vd = smem_u32(vs) + (unsigned)j * kRowBytes;
 #pragma unroll
                 for (int c = lane; c < 2 * kChunksPerRow; c += 32) {
@@ -525,34 +525,37 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
     const int page_shift = (A.page & (A.page - 1)) == 0 ? __ffs(A.page) - 1 : -1;
     auto page_of = [&](int p) { return page_shift >= 0 ? p >> page_shift : p / A.page; };
     const int nchunks = (end - begin + CH - 1) / CH;
-    // every warp requests its rows (warp, warp + 4, ...) of chunk c into slot c % NS; lane 0 notes per row whether a
-    // copy fills it (rows past the range and rows whose table entry is refused are zeroed and take no part)
+    // Chunk c goes into slot c % NS.  Lane l of every warp looks row l of the chunk up (table entry, byte offset in the
+    // pools: one round of loads per chunk instead of one per row); the warp then requests its rows (warp, warp + 4, ...)
+    // with the offsets handed round by shuffles.  Rows past the range and rows whose table entry is refused are zeroed
+    // and take no part (sm_row_ok).
+    static_assert(CH == 32, "one lane per row of a chunk");
     auto issue = [&](int c) {
         const int r0 = begin + c * CH;
         const int rn = end - r0 < CH ? end - r0 : CH;
         const int slot_i = c % NS;
         const unsigned ks_s = smem_s + (unsigned)slot_i * kSlotBytes, vs_s = ks_s + (unsigned)CH * kRowBytes;
-        for (int j = warp; j < CH; j += kMmaWarps) {
-            const int p = r0 + j;
-            int e = -1;
-            int pg = 0;
-            if (j < rn) {
-                pg = page_of(p);
-                e = trow[pg];
-                if (e < 0 || e >= A.blocks) {  // an entry outside the pool is recorded and not followed
-                    bad = true;
-                    e = -1;
-                }
-            }
-            if (lane == 0) sm_row_ok[slot_i][j] = e >= 0;
+        int64_t at = -1;
+        if (lane < rn) {
+            const int p = r0 + lane, pg = page_of(p);
+            const int e = trow[pg];
+            if (e < 0 || e >= A.blocks) bad = true;  // an entry outside the pool is recorded and not followed
+            else at = LEV_KV_ROW(e, p - pg * A.page, kvh, A.page, A.kv_heads) * (int64_t)kRowBytes;
+        }
+        if (warp == 0) sm_row_ok[slot_i][lane] = at >= 0;
+        const unsigned at_lo = (unsigned)at, at_hi = (unsigned)((uint64_t)at >> 32);
+        const unsigned ok_rows = __ballot_sync(0xffffffffu, at >= 0);
+#pragma unroll
+        for (int i = 0; i < CH / kMmaWarps; i++) {
+            const int j = warp + i * kMmaWarps;
+            const int64_t row_at = (int64_t)(((uint64_t)__shfl_sync(0xffffffffu, at_hi, j) << 32) | __shfl_sync(0xffffffffu, at_lo, j));
             const unsigned kd = ks_s + (unsigned)j * kRowBytes, vd = vs_s + (unsigned)j * kRowBytes;
-            if (e >= 0) {
-                const int64_t at = (((int64_t)e * A.page + (p - pg * A.page)) * A.kv_heads + kvh) * (int64_t)kRowBytes;
+            if ((ok_rows >> j) & 1u) {
 #pragma unroll
                 for (int cc0 = lane; cc0 < 2 * kCpr; cc0 += 32) {
                     const bool is_v = cc0 >= kCpr;
                     const int cc = is_v ? cc0 - kCpr : cc0;
-                    cp_async16((is_v ? vd : kd) + ((cc ^ (j & 7)) << 4), (is_v ? vp : kp) + at + cc * 16);
+                    cp_async16((is_v ? vd : kd) + ((cc ^ (j & 7)) << 4), (is_v ? vp : kp) + row_at + cc * 16);
                 }
             } else {
 #pragma unroll
@@ -619,10 +622,13 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
             }
             m = m_new;
             l = fmaf(l, corr, p0 + p1);  // this lane's share; summed over g at the end
+            // the running maxima rarely move after the first chunks: a factor of one for every head leaves the sums as they are
+            if (__any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll
-            for (int mt = 0; mt < kSteps; mt++)
+                for (int mt = 0; mt < kSteps; mt++)
 #pragma unroll
-                for (int i = 0; i < 4; i++) acc[mt][i] *= corr;
+                    for (int i = 0; i < 4; i++) acc[mt][i] *= corr;
+            }
             // ---- P as a B fragment: column g = (head g / 2, term g % 2), positions 2t, 2t+1, 2t+8, 2t+9 ----
             unsigned pb0, pb1;
             {
@@ -796,7 +802,7 @@ __global__ void k_kv_append(AttnArgs A, void* k_pool, void* v_pool, const float*
         if (threadIdx.x == 0 && kvh == 0) atomicOr(A.status, LEV_DEV_BAD_INDEX);
         return;
     }
-    const int64_t at = ((blk * A.page + pos % A.page) * A.kv_heads + kvh) * hd;
+    const int64_t at = LEV_KV_ROW(blk, pos % A.page, kvh, A.page, A.kv_heads) * hd;
     const int64_t from = ((int64_t)col * A.kv_heads + kvh) * hd;
     for (int i = threadIdx.x; i < hd; i += blockDim.x) {
         static_cast<T*>(k_pool)[at + i] = (T)k[from + i];

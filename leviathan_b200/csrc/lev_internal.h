@@ -21,6 +21,12 @@
 #define LEV_DEV_TIMEOUT 8
 #define LEV_DEV_BAD_INDEX 16  // a slot, position or block-table entry outside the cache layout
 
+// Row (in units of rows of head_dim elements) of (block, position inside the block, KV head) in a paged cache pool.
+#ifdef LEV_KV_HEAD_MAJOR
+#define LEV_KV_ROW(block, in_page, kvh, page, kv_heads) (((int64_t)(block) * (kv_heads) + (kvh)) * (page) + (in_page))
+#else
+#define LEV_KV_ROW(block, in_page, kvh, page, kv_heads) (((int64_t)(block) * (page) + (in_page)) * (kv_heads) + (kvh))
+#endif
 // ints after the status word: counters that kernels leave at zero (ctx->d_status + LEV_COUNTER_OFFSET)
 #define LEV_COUNTER_OFFSET 64
 #define LEV_COUNTERS 65536

@@ -632,7 +632,7 @@ __global__ void __launch_bounds__(128) k_qkv_norm_rope(QkvRows X, int q_heads, i
         int64_t blk = -1;
         if (sl >= 0 && sl < C.slots && ps >= 0 && ps < C.max_blocks * C.page) blk = C.table[(int64_t)sl * C.max_blocks + ps / C.page];
         if (blk >= 0 && blk < C.blocks) {
-            at = ((blk * C.page + ps % C.page) * kv_heads + (is_k ? head - q_heads : head - q_heads - kv_heads)) * hd;
+            at = LEV_KV_ROW(blk, ps % C.page, is_k ? head - q_heads : head - q_heads - kv_heads, C.page, kv_heads) * hd;
         } else if (threadIdx.x == 0) {
             atomicOr(C.status, LEV_DEV_BAD_INDEX);  // recorded, not followed
         }
