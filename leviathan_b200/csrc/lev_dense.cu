@@ -116,6 +116,21 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         return reinterpret_cast<const unsigned char*>(A.wp) +
                (((int64_t)A.job_slice[job] * tpj + tij) * spt + k) * (int64_t)kStepBytes;
     };
+    // sliced form, fetch cursor (lane 0): the K-steps of a job's tiles are contiguous, so the address is formed once
+    // per job (divisions, a table load) and stepped in between
+    const unsigned char* j_ptr = nullptr;
+    int j_run = 0;  // K-steps left at j_ptr before the next job begins
+    auto jobs_next = [&](int q) -> const unsigned char* {
+        if (j_run == 0) {
+            const int tq = q / spt, gt = tile0 + tq;
+            j_ptr = step_src(q);
+            j_run = (tpj - gt % tpj) * spt - (q - tq * spt);
+        }
+        const unsigned char* a = j_ptr;
+        j_ptr += kStepBytes;
+        j_run--;
+        return a;
+    };
     // multi form: the tensor a global tile belongs to
     auto op_of = [&](int gt) -> int {
         int o = 0;
@@ -169,7 +184,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             }
             bulk_copy(dst + done * kStepBytes, a0, run * kStepBytes, bar);
         } else {
-            bulk_load(dst, JOBS ? step_src(f_q) : f_ptr, n * kStepBytes, bar);
+            bulk_load(dst, JOBS ? jobs_next(f_q) : f_ptr, n * kStepBytes, bar);  // sliced form: one K-step per stage
         }
         f_ptr += n * kStepBytes;
         f_q += n;
@@ -370,10 +385,18 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     int orow[CMAX];
 #pragma unroll
     for (int c = 0; c < CMAX; c++) orow[c] = 0;
-    auto enter_tile = [&]() {
+    // first: the warp's first tile; afterwards tiles are entered in order, and only a new job reloads anything
+    auto enter_tile = [&](bool first) {
         if (JOBS) {
-            job = (tile0 + tl) / tpj;
-            tij = tile0 + tl - job * tpj;
+            if (first) {
+                job = (tile0 + tl) / tpj;
+                tij = tile0 + tl - job * tpj;
+            } else if (++tij == tpj) {
+                tij = 0;
+                job++;
+            } else {
+                return;
+            }
             xs = reinterpret_cast<const uint4*>(tables0 + (size_t)(job - job0) * A.table_stride);
             sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
 #pragma unroll
@@ -387,7 +410,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             tij = tile0 + tl;
         }
     };
-    if (s < e) enter_tile();
+    if (s < e) enter_tile(true);
     for (int i0 = s; i0 < e; i0 += sps) {
         if (!mbar_wait(bar_s + 8 * slot, phase)) {
             if (lane == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
@@ -449,7 +472,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
                 tl++;
                 k = 0;
                 seg_k0 = 0;
-                if (i + 1 < e) enter_tile();
+                if (i + 1 < e) enter_tile(false);
             }
         }
         // every lane has consumed its shared-memory reads of this stage: refill it
