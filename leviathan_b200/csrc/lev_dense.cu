@@ -46,6 +46,7 @@ struct DenseArgs {
     int tiles_per_job;
     int gelu_inter;         // > 0: activation e = gelu_tanh(src[e]) * src[gelu_inter + e]
     int table_stride;       // bytes between the tables of consecutive jobs in shared memory
+    int max_tables;         // jobs whose tables the launch has room for in one CTA (<= kMaxJobTables)
     // multi form (MULTI): up to four tensors of one format and K against the same activations;
     // the call's tiles are the tensors' tiles in order
     int n_ops;
@@ -93,7 +94,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     if (ntiles == 0) return;
     const int job0 = JOBS ? tile0 / tpj : 0;
     const int njobs_here = JOBS ? (tile0 + ntiles - 1) / tpj - job0 + 1 : 1;
-    if (JOBS && njobs_here > kMaxJobTables) {
+    if (JOBS && njobs_here > A.max_tables) {
         if (threadIdx.x == 0) atomicOr(A.status, LEV_DEV_TIMEOUT);
         return;
     }
@@ -752,14 +753,29 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     const int64_t tpj = rows_per_job / 16, chunks = lev_stream_chunks(w), spt = chunks / 4;
     const size_t step = step_bytes(w->type);
     const size_t stride = (lev_stream_table_bytes(w, cmax, 2, 1, nullptr) + 255) & ~(size_t)255;
-    const size_t cap = jobs_cap(kMaxJobTables * stride, step);
-    // a CTA that takes the whole SM anyway runs twelve warps
-    const int W = cap > 110 * 1024 && cmax == 4 ? 12 : 8;
     const int sms = ctx->prop.multiProcessorCount;
     const int64_t max_tiles = (int64_t)max_jobs * tpj;
-    const int grid = (int)(max_tiles < sms ? max_tiles : sms);
+    // jobs a CTA's run of tiles can touch when the list's tiles are dealt to `ctas` CTAs
+    auto tables_for = [&](int64_t ctas) -> int64_t {
+        const int64_t g = max_tiles < ctas ? max_tiles : ctas, run = (max_tiles + g - 1) / g;
+        const int64_t n = (run + tpj - 1) / tpj + 1;
+        return n < kMaxJobTables ? n : kMaxJobTables;
+    };
+    // A list is a dependent step of its layer (nothing of the next launch can run beside it): two CTAs of eight
+    // warps per SM when their tables and two ring stages per warp fit half an SM, else one CTA per SM with as many
+    // warps as leave two stages each.
+    int W = 8;
+    int64_t slots = 2 * (int64_t)sms, n_tables = tables_for(slots);
+    size_t cap = 110 * 1024;
+    if (n_tables * stride + 8 * 2 * step > cap) {
+        slots = sms;
+        n_tables = tables_for(slots);
+        cap = 200 * 1024;
+        if (cmax == 4) W = n_tables * stride + 16 * 2 * step <= cap ? 16 : 12;
+    }
+    const int grid = (int)(max_tiles < slots ? max_tiles : slots);
     const int64_t per_warp = (((max_tiles + grid - 1) / grid) * spt + W - 1) / W;
-    int64_t depth = (int64_t)((cap - kMaxJobTables * stride) / ((size_t)W * step));
+    int64_t depth = (int64_t)((cap - n_tables * stride) / ((size_t)W * step));
     if (depth > per_warp) depth = per_warp;
     if (depth > kMaxDepth) depth = kMaxDepth;
     if (depth < 1) depth = 1;
@@ -784,7 +800,8 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
     A.tiles_per_job = (int)tpj;
     A.gelu_inter = gelu_inter;
     A.table_stride = (int)stride;
-    const size_t smem = (size_t)W * depth * step + kMaxJobTables * stride;
+    A.max_tables = (int)n_tables;
+    const size_t smem = (size_t)W * depth * step + n_tables * stride;
     int st;
     if (cmax == 1)
         st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 1, 8, true>(ctx, grid, smem, A)
@@ -794,10 +811,14 @@ int lev_dense_jobs_run(lev_ctx* ctx, const lev_weights* w, int64_t rows_per_job,
         st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, 8, true>(ctx, grid, smem, A)
              : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, 8, true>(ctx, grid, smem, A)
                                         : launch_dense<LEV_GGML_Q4_0, 4, 8, true>(ctx, grid, smem, A);
-    else
+    else if (W == 12)
         st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, 12, true>(ctx, grid, smem, A)
              : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, 12, true>(ctx, grid, smem, A)
                                         : launch_dense<LEV_GGML_Q4_0, 4, 12, true>(ctx, grid, smem, A);
+    else
+        st = w->type == LEV_GGML_Q4_K   ? launch_dense<LEV_GGML_Q4_K, 4, 16, true>(ctx, grid, smem, A)
+             : w->type == LEV_GGML_Q6_K ? launch_dense<LEV_GGML_Q6_K, 4, 16, true>(ctx, grid, smem, A)
+                                        : launch_dense<LEV_GGML_Q4_0, 4, 16, true>(ctx, grid, smem, A);
     if (st) return st;
     ctx->launches++;
     ctx->ev.grid = grid;
