@@ -151,6 +151,16 @@ __device__ __forceinline__ uint2 load8_u16(const uint8_t* p) {
     const unsigned a = ldg2(p), b = ldg2(p + 2), c = ldg2(p + 4), d = ldg2(p + 6);
     return make_uint2(a | (b << 16), c | (d << 16));
 }
+// Eight bytes from a 2-byte aligned address inside a Q6_K block, as the aligned words that cover them: the words
+// may reach two bytes before p and two bytes past p + 8, which the callers keep inside the tensor (a block's
+// quant bytes end 16 bytes before the block does, and a tensor's first block is 4-byte aligned).
+__device__ __forceinline__ uint2 load8_words(const uint8_t* p) {
+    const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+    const unsigned* w = reinterpret_cast<const unsigned*>(a & ~(uintptr_t)3);
+    const unsigned sh = (unsigned)(a & 2u) * 8u;
+    const unsigned x0 = __ldg(w), x1 = __ldg(w + 1), x2 = sh ? __ldg(w + 2) : 0u;
+    return make_uint2(__funnelshift_r(x0, x1, sh), __funnelshift_r(x1, x2, sh));
+}
 // float(byte k of w) without the conversion unit: the byte lands in the mantissa of 2^23
 __device__ __forceinline__ float byte_f(unsigned w, unsigned k) {
     return __uint_as_float(__byte_perm(w, 0x4B000000u, 0x7650u + k)) - 8388608.0f;
@@ -198,9 +208,9 @@ __device__ __forceinline__ void load_raw(const uint8_t* row, int it, int j, bool
     } else {
         const uint8_t* blk = row + (int64_t)(it >> 2) * LEV_Q6_K_BYTES;
         const int c = (it & 3) >> 1, g0 = 2 * (it & 1);
-        R.q0 = load8_u16(blk + 64 * c + 8 * j);
-        R.q1 = load8_u16(blk + 64 * c + 32 + 8 * j);
-        R.qh = load8_u16(blk + 128 + 32 * c + 8 * j);
+        R.q0 = load8_words(blk + 64 * c + 8 * j);
+        R.q1 = load8_words(blk + 64 * c + 32 + 8 * j);
+        R.qh = load8_words(blk + 128 + 32 * c + 8 * j);
         R.hdr.x = ldg2(blk + 208);
         // int8 scales of the two groups for values 8j..8j+7: index 8c + 2*grp + (j >> 1)
         const unsigned s0 = blk[192 + 8 * c + 2 * g0 + (j >> 1)], s1 = blk[192 + 8 * c + 2 * (g0 + 1) + (j >> 1)];
@@ -259,15 +269,20 @@ __device__ __forceinline__ void decode_store(const RowRaw<TYPE>& R, int it, int 
         const float d = h2f(R.hdr.x);
         const float ds0 = __fmul_rn(d, (float)(int)(signed char)(R.hdr.y & 0xffu));
         const float ds1 = __fmul_rn(d, (float)(int)(signed char)((R.hdr.y >> 8) & 0xffu));
+        // four levels per word: the groups of an even K-step take the low nibbles and high-bit pairs 0 and 1, those of
+        // an odd one the high nibbles and pairs 2 and 3; level - 32 is exact in f32, and so is its product with d * scale
         const unsigned a[2] = {R.q0.x, R.q0.y}, b[2] = {R.q1.x, R.q1.y}, h[2] = {R.qh.x, R.qh.y};
+        const unsigned sh = 2u * (unsigned)g0;  // 0 or 4
 #pragma unroll
-        for (int i = 0; i < 8; i++) {
-            const unsigned ba = (a[i >> 2] >> (8 * (i & 3))) & 0xffu, bb = (b[i >> 2] >> (8 * (i & 3))) & 0xffu;
-            const unsigned bh = (h[i >> 2] >> (8 * (i & 3))) & 0xffu;
-            const unsigned na = g0 ? (ba >> 4) : (ba & 15u), nb = g0 ? (bb >> 4) : (bb & 15u);
-            const unsigned ha = (bh >> (2 * g0)) & 3u, hb = (bh >> (2 * g0 + 2)) & 3u;
-            lo[i] = __fmul_rn(ds0, __uint_as_float(0x4B000000u | na | (ha << 4)) - 8388640.0f);
-            hi[i] = __fmul_rn(ds1, __uint_as_float(0x4B000000u | nb | (hb << 4)) - 8388640.0f);
+        for (int wd = 0; wd < 2; wd++) {
+            const unsigned hs = h[wd] >> sh;
+            const unsigned la = ((a[wd] >> sh) & 0x0F0F0F0Fu) | ((hs << 4) & 0x30303030u);
+            const unsigned lb = ((b[wd] >> sh) & 0x0F0F0F0Fu) | ((hs << 2) & 0x30303030u);
+#pragma unroll
+            for (int i = 0; i < 4; i++) {
+                lo[4 * wd + i] = __fmul_rn(ds0, __uint_as_float(__byte_perm(la, 0x4B000000u, 0x7650u + i)) - 8388640.0f);
+                hi[4 * wd + i] = __fmul_rn(ds1, __uint_as_float(__byte_perm(lb, 0x4B000000u, 0x7650u + i)) - 8388640.0f);
+            }
         }
     }
     *reinterpret_cast<uint4*>(wtile + swz(r, ch_lo)) = pack8(lo);
