@@ -167,24 +167,28 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
 }
 
-// Tiled form for 128 tokens or more: a CTA of 8 warps takes 16 experts x 16 tokens and walks the hidden
+// Tiled form for 128 tokens or more: a CTA of 16 warps takes 16 experts x 32 tokens and walks the hidden
 // dimension in chunks (two chunk buffers: the next chunk's bulk copies fly while this one is used); warp w keeps
 // a 4 x 8 tile of double accumulators (experts 4 * (w & 3) ..., tokens 8 * (w >> 2) ...), so twelve conversions to
-// double feed thirty-two FMAs where the 2 x 4 tile above needs six for eight: the kernel is bound by the
-// conversion unit.  A lane still adds its columns lane, lane + 32, ... in ascending order (chunk lengths are
-// multiples of 32), so the bits equal the other forms'.
-constexpr int kRouterChunk = 704;   // floats per row and chunk: 32 rows x 2816 B x 2 buffers = 176 KB
+// double feed thirty-two FMAs where the 2 x 4 tile above needs six for eight.  512 tokens x 128 experts are 128
+// CTAs: one wave, four warps per scheduler (the 16 x 16 tile of eight warps that preceded this form made 256 CTAs of
+// one per SM, a wave and three quarters, and ran 46 us where this one runs 35 us).  A lane still adds
+// its columns lane, lane + 32, ... in ascending order (chunk lengths are multiples of 32), so the bits equal the
+// other forms'.
+constexpr int kRouterChunk = 576;        // floats per row and chunk
+constexpr int kRouterTileTokens = 32;    // 48 rows (16 experts, 32 tokens) x 2304 B x 2 buffers = 216 KB
+constexpr int kRouterTileRows = 16 + kRouterTileTokens;
 
-__global__ void __launch_bounds__(256) k_router_logits_tile(const float* __restrict__ rw, const float* __restrict__ x,
+__global__ void __launch_bounds__(512) k_router_logits_tile(const float* __restrict__ rw, const float* __restrict__ x,
                                                             int64_t tokens, int experts, int hidden,
                                                             float* __restrict__ scores, int* status) {
     extern __shared__ __align__(128) unsigned char rsm[];
     __shared__ __align__(8) unsigned long long bars[2];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int e_base = blockIdx.x * 16;
-    const int64_t t_base = (int64_t)blockIdx.y * 16;
+    const int64_t t_base = (int64_t)blockIdx.y * kRouterTileTokens;
     const int ne = experts - e_base < 16 ? experts - e_base : 16;
-    const int nt = (int)(tokens - t_base < 16 ? tokens - t_base : 16);
+    const int nt = (int)(tokens - t_base < kRouterTileTokens ? tokens - t_base : kRouterTileTokens);
     const int nchunks = (hidden + kRouterChunk - 1) / kRouterChunk;
     float* const base = reinterpret_cast<float*>(rsm);
     if (threadIdx.x == 0) {
@@ -196,26 +200,29 @@ __global__ void __launch_bounds__(256) k_router_logits_tile(const float* __restr
     pdl_launch_dependents();
     pdl_wait();
     __syncthreads();
-    // buffer rows 0..15: the experts' chunk, rows 16..31: the tokens' chunk; lane r of warp 0 requests row r
+    // buffer rows 0..15: the experts' chunk, rows 16..47: the tokens' chunk.  Warp 0 announces the chunk's bytes and
+    // requests the expert rows (lane r: row r), warp 1 requests the token rows.
     auto request = [&](int c) {
         const int len = hidden - c * kRouterChunk < kRouterChunk ? hidden - c * kRouterChunk : kRouterChunk;
         const unsigned bar_s = (unsigned)__cvta_generic_to_shared(&bars[c & 1]);
-        if (lane == 0)
-            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_s), "r"((unsigned)((ne + nt) * len * 4)) : "memory");
-        __syncwarp();
         const float* src = nullptr;
-        if (lane < 16) {
+        int row = 0;
+        if (warp == 0) {
+            if (lane == 0)
+                asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_s), "r"((unsigned)((ne + nt) * len * 4)) : "memory");
+            row = lane;
             if (lane < ne) src = rw + (int64_t)(e_base + lane) * hidden + (int64_t)c * kRouterChunk;
-        } else if (lane - 16 < nt) {
-            src = x + (t_base + lane - 16) * hidden + (int64_t)c * kRouterChunk;
+        } else {
+            row = 16 + lane;
+            if (lane < nt) src = x + (t_base + lane) * hidden + (int64_t)c * kRouterChunk;
         }
         if (src)
             asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
-                             (unsigned)__cvta_generic_to_shared(base + ((size_t)(c & 1) * 32 + lane) * kRouterChunk)),
+                             (unsigned)__cvta_generic_to_shared(base + ((size_t)(c & 1) * kRouterTileRows + row) * kRouterChunk)),
                          "l"(src), "r"((unsigned)len * 4u), "r"(bar_s)
                          : "memory");
     };
-    if (warp == 0) {
+    if (warp < 2) {
         request(0);
         if (nchunks > 1) request(1);
     }
@@ -246,8 +253,8 @@ __global__ void __launch_bounds__(256) k_router_logits_tile(const float* __restr
         }
         if (works) {
             const int len = hidden - c * kRouterChunk < kRouterChunk ? hidden - c * kRouterChunk : kRouterChunk;
-            const float* w0 = base + ((size_t)(c & 1) * 32 + ea) * kRouterChunk;
-            const float* x0 = base + ((size_t)(c & 1) * 32 + 16 + tb) * kRouterChunk;
+            const float* w0 = base + ((size_t)(c & 1) * kRouterTileRows + ea) * kRouterChunk;
+            const float* x0 = base + ((size_t)(c & 1) * kRouterTileRows + 16 + tb) * kRouterChunk;
             for (int i = lane; i < len; i += 32) {
                 double wv[4], xv[8];
 #pragma unroll
@@ -261,7 +268,7 @@ __global__ void __launch_bounds__(256) k_router_logits_tile(const float* __restr
             }
         }
         __syncthreads();  // the buffer is free again
-        if (warp == 0 && c + 2 < nchunks) request(c + 2);
+        if (warp < 2 && c + 2 < nchunks) request(c + 2);
     }
     if (!works) return;
     bool bad = false;
@@ -753,14 +760,14 @@ static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x
     const size_t stage = (size_t)16 * w->hidden * sizeof(float);
     const bool aligned = w->hidden % 4 == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w->router_w & 15) == 0;
     if (aligned && tokens >= 128) {   // below that the tiles are too few to cover the SMs and the 8 x 8 form is the faster one
-        const size_t tile_smem = (size_t)2 * 32 * kRouterChunk * sizeof(float);
+        const size_t tile_smem = (size_t)2 * kRouterTileRows * kRouterChunk * sizeof(float);
         static bool configured_tile[16] = {};
         if (!configured_tile[ctx->device & 15]) {
             LEV_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_tile, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)tile_smem));
             configured_tile[ctx->device & 15] = true;
         }
-        dim3 tgrid((unsigned)((w->experts + 15) / 16), (unsigned)((tokens + 15) / 16));
-        LEV_CUDA(ctx, launch_pdl(k_router_logits_tile, tgrid, dim3(256), tile_smem, ctx->stream, (const float*)w->router_w, x, tokens,
+        dim3 tgrid((unsigned)((w->experts + 15) / 16), (unsigned)((tokens + kRouterTileTokens - 1) / kRouterTileTokens));
+        LEV_CUDA(ctx, launch_pdl(k_router_logits_tile, tgrid, dim3(512), tile_smem, ctx->stream, (const float*)w->router_w, x, tokens,
                                  (int)w->experts, (int)w->hidden, scores, ctx->d_status));
     } else if (stage <= 200 * 1024 && aligned) {
         static bool configured[16] = {};
