@@ -909,10 +909,14 @@ static int experts_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float*
     const bool sliced = moe_sliced(ctx, w, pairs, x);
     // prefill-sized calls: grouped dequant-GEMM on the tensor cores (bf16 operands, f32 accumulate;
     // the 2e-2 bar of tensor-core prefill applies to this form)
+    // Mid-sized calls (one job per expert and four of its tokens) take the one-launch kernel as far as its tables
+    // allow -- 84 tokens of the 128-expert top-8 shape: 180 us at 64 tokens, 222 at 84, where the grouped GEMM costs a
+    // flat 300 us up to about 128 tokens -- and from 1024 pairs on the GEMM is preferred wherever it applies.
+    const bool sliced4_early = !sliced && pairs < 1024 && moe_sliced4(ctx, w, pairs, x);
     const int64_t min_pairs = 512;
-    const bool tensor = !sliced && pairs >= min_pairs && w->hidden % 4 == 0 && lev_gemm_grouped_supported(w->gate_up, (int)gu_rows_) &&
+    const bool tensor = !sliced && !sliced4_early && pairs >= min_pairs && w->hidden % 4 == 0 && lev_gemm_grouped_supported(w->gate_up, (int)gu_rows_) &&
                         lev_gemm_grouped_supported(w->down, w->hidden);
-    const bool sliced4 = !sliced && !tensor && moe_sliced4(ctx, w, pairs, x);
+    const bool sliced4 = sliced4_early || (!sliced && !tensor && moe_sliced4(ctx, w, pairs, x));
     const int cmax = sliced ? 1 : tensor ? lev_gemm_grouped_job_tokens() : sliced4 ? 4 : (pairs <= 2 * (int64_t)w->local_count ? 4 : 8), terms = 2;
     int64_t mj = (int64_t)w->local_count + pairs / cmax;
     if (mj > pairs) mj = pairs;
