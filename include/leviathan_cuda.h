@@ -386,8 +386,8 @@ int lev_moe_weights_upload(lev_ctx* ctx, const float* router_w, const uint8_t* g
                            int local_count, int bytes_on_device, lev_moe_weights** out);
 int lev_moe_weights_free(lev_ctx* ctx, lev_moe_weights* w);
 /* lev_weights_release_gguf for both expert tensors of a layer: a decode-only host keeps one copy of the
- * experts (the repacked one).  Calls of 512 token-slot pairs or more then run on the multi-column stream
- * kernels instead of the tensor-core form, which reads the GGUF-order bytes. */
+ * experts (the repacked one).  Calls the tensor-core form would serve (from 512 token-slot pairs on, where the
+ * job-list form no longer applies; it reads the GGUF-order bytes) then run on the multi-column stream kernels. */
 int lev_moe_weights_release_gguf(lev_ctx* ctx, lev_moe_weights* w);
 
 /* Router decision for `tokens` rows of x [tokens][hidden]: logits in the
