@@ -500,27 +500,6 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
     const unsigned char* kp = static_cast<const unsigned char*>(A.k_pool);
     const unsigned char* vp = static_cast<const unsigned char*>(A.v_pool);
 
-    // B fragments of Q^T: column g is (head g / 2, term g % 2); this lane holds dims 2t, 2t+1, 2t+8, 2t+9 of each step
-    unsigned qb[kSteps][2];
-    {
-        const int head = g >> 1, term = g & 1;
-        const bool used = head < GROUP;
-        const float* qh = A.q + ((int64_t)col * A.q_heads + kvh * GROUP + (used ? head : 0)) * HD;
-#pragma unroll
-        for (int s = 0; s < kSteps; s++) {
-            const float2 a = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t);
-            const float2 b = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t + 8);
-            qb[s][0] = used ? pack_half2(split_half(a.x, term), split_half(a.y, term)) : 0u;
-            qb[s][1] = used ? pack_half2(split_half(b.x, term), split_half(b.y, term)) : 0u;
-        }
-    }
-    // softmax state of head t (lanes t >= GROUP carry a dummy head over zero columns)
-    float m = -INFINITY, l = 0.f;
-    float acc[kSteps][4];  // O^T tile mt: dims mt*16 + g (and + 8), columns 2t (hi), 2t + 1 (lo)
-#pragma unroll
-    for (int mt = 0; mt < kSteps; mt++)
-#pragma unroll
-        for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
     bool bad = false;
     const int page_shift = (A.page & (A.page - 1)) == 0 ? __ffs(A.page) - 1 : -1;
     auto page_of = [&](int p) { return page_shift >= 0 ? p >> page_shift : p / A.page; };
@@ -573,6 +552,28 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
         if (c < nchunks) issue(c);
         cp_async_commit();
     }
+    // (the first chunks are on their way while the query's fragments are formed)
+    // B fragments of Q^T: column g is (head g / 2, term g % 2); this lane holds dims 2t, 2t+1, 2t+8, 2t+9 of each step
+    unsigned qb[kSteps][2];
+    {
+        const int head = g >> 1, term = g & 1;
+        const bool used = head < GROUP;
+        const float* qh = A.q + ((int64_t)col * A.q_heads + kvh * GROUP + (used ? head : 0)) * HD;
+#pragma unroll
+        for (int s = 0; s < kSteps; s++) {
+            const float2 a = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t);
+            const float2 b = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t + 8);
+            qb[s][0] = used ? pack_half2(split_half(a.x, term), split_half(a.y, term)) : 0u;
+            qb[s][1] = used ? pack_half2(split_half(b.x, term), split_half(b.y, term)) : 0u;
+        }
+    }
+    // softmax state of head t (lanes t >= GROUP carry a dummy head over zero columns)
+    float m = -INFINITY, l = 0.f;
+    float acc[kSteps][4];  // O^T tile mt: dims mt*16 + g (and + 8), columns 2t (hi), 2t + 1 (lo)
+#pragma unroll
+    for (int mt = 0; mt < kSteps; mt++)
+#pragma unroll
+        for (int i = 0; i < 4; i++) acc[mt][i] = 0.f;
     for (int c = 0; c < nchunks; c++) {
         cp_async_wait<NS - 2>();
         __syncthreads();  // chunk c is there for every warp, and every warp is done with chunk c - 1
