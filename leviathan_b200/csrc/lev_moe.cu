@@ -167,6 +167,79 @@ __global__ void __launch_bounds__(256) k_router_logits(const float* __restrict__
     if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
 }
 
+// Decode form (up to four tokens): one warp, one expert.  The expert's router row is requested before the
+// dependency wait (it is a constant), the tokens' rows after it; 128 experts then pull their 11 KB rows through 128
+// SMs at once, where the staged form above makes 16 SMs pull 90 KB each and leaves half of its warps without work.
+// Same lane order, same bits.
+constexpr int kRouterWarpTokens = 4;
+
+__global__ void __launch_bounds__(32) k_router_logits_warp(const float* __restrict__ rw, const float* __restrict__ x,
+                                                           int tokens, int experts, int hidden,
+                                                           float* __restrict__ scores, int* status) {
+    extern __shared__ __align__(128) unsigned char rsm[];
+    __shared__ __align__(8) unsigned long long bar;
+    float* ws = reinterpret_cast<float*>(rsm);   // [hidden]
+    float* xs = ws + hidden;                      // [tokens][hidden]
+    const int lane = threadIdx.x, e = blockIdx.x;
+    const unsigned bar_s = (unsigned)__cvta_generic_to_shared(&bar);
+    const unsigned row_bytes = (unsigned)hidden * 4u;
+    if (lane == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(bar_s), "r"(1));
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(bar_s), "r"(row_bytes * (unsigned)(1 + tokens)) : "memory");
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                         (unsigned)__cvta_generic_to_shared(ws)),
+                     "l"(rw + (int64_t)e * hidden), "r"(row_bytes), "r"(bar_s)
+                     : "memory");
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    __syncwarp();
+    if (lane < tokens)
+        asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n" ::"r"(
+                         (unsigned)__cvta_generic_to_shared(xs + (size_t)lane * hidden)),
+                     "l"(x + (int64_t)lane * hidden), "r"(row_bytes), "r"(bar_s)
+                     : "memory");
+    bool landed = false;
+    {
+        const long long t_start = clock64();
+        for (unsigned i = 1; !landed; i++) {
+            unsigned ok;
+            asm volatile(
+                "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}\n"
+                : "=r"(ok)
+                : "r"(bar_s), "r"(0)
+                : "memory");
+            landed = ok != 0;
+            if (!landed && (i & 63u) == 0 && clock64() - t_start > 2000000000LL) break;
+        }
+    }
+    if (!__all_sync(0xffffffffu, landed)) {
+        if (lane == 0) atomicOr(status, LEV_DEV_TIMEOUT);
+        return;
+    }
+    double acc[kRouterWarpTokens];
+#pragma unroll
+    for (int t = 0; t < kRouterWarpTokens; t++) acc[t] = 0.0;
+    for (int i = lane; i < hidden; i += 32) {
+        const double wv = (double)ws[i];
+#pragma unroll
+        for (int t = 0; t < kRouterWarpTokens; t++)
+            if (t < tokens) acc[t] = fma(wv, (double)xs[(size_t)t * hidden + i], acc[t]);
+    }
+    bool bad = false;
+#pragma unroll
+    for (int t = 0; t < kRouterWarpTokens; t++) {
+        if (t < tokens) {
+            const float sv = (float)warp_butterfly(acc[t]);
+            bad |= !isfinite(sv);
+            if (lane == 0) scores[(int64_t)t * experts + e] = sv;
+        }
+    }
+    if (bad && lane == 0) atomicOr(status, LEV_DEV_NONFINITE_OUTPUT);
+}
+
 // Tiled form for 128 tokens or more: a CTA of 16 warps takes 16 experts x 32 tokens and walks the hidden
 // dimension in chunks (two chunk buffers: the next chunk's bulk copies fly while this one is used); warp w keeps
 // a 4 x 8 tile of double accumulators (experts 4 * (w & 3) ..., tokens 8 * (w >> 2) ...), so twelve conversions to
@@ -769,6 +842,15 @@ static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x
         dim3 tgrid((unsigned)((w->experts + 15) / 16), (unsigned)((tokens + kRouterTileTokens - 1) / kRouterTileTokens));
         LEV_CUDA(ctx, launch_pdl(k_router_logits_tile, tgrid, dim3(512), tile_smem, ctx->stream, (const float*)w->router_w, x, tokens,
                                  (int)w->experts, (int)w->hidden, scores, ctx->d_status));
+    } else if (aligned && tokens <= kRouterWarpTokens && (size_t)(1 + tokens) * w->hidden * sizeof(float) <= 200 * 1024) {
+        const size_t warp_smem = (size_t)(1 + tokens) * w->hidden * sizeof(float);
+        static bool configured_warp[16] = {};
+        if (!configured_warp[ctx->device & 15]) {
+            LEV_CUDA(ctx, cudaFuncSetAttribute(k_router_logits_warp, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+            configured_warp[ctx->device & 15] = true;
+        }
+        LEV_CUDA(ctx, launch_pdl(k_router_logits_warp, dim3((unsigned)w->experts), dim3(32), warp_smem, ctx->stream, (const float*)w->router_w, x,
+                                 (int)tokens, (int)w->experts, (int)w->hidden, scores, ctx->d_status));
     } else if (stage <= 200 * 1024 && aligned) {
         static bool configured[16] = {};
         if (!configured[ctx->device & 15]) {
