@@ -388,33 +388,52 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     if (!fuse_group) pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int64_t tok = (int64_t)blockIdx.x * 4 + warp;
-    if (tok < tokens) {
-    double* p = sp + (size_t)warp * experts;
-    const float* s = scores + tok * experts;
-    float m = -INFINITY;
-    for (int i = lane; i < experts; i += 32) m = fmaxf(m, s[i]);
+    // One warp per token.  A call with a single token (decode) spreads that token's exponentials and divisions over
+    // the block's four warps; its sum and its selection stay with warp 0, in the same order.
+    const bool solo = tokens == 1;
+    const int64_t tok = solo ? 0 : (int64_t)blockIdx.x * 4 + warp;
+    const bool has_token = solo || tok < tokens;
+    const bool selects = solo ? warp == 0 : tok < tokens;
+    const int first = solo ? (int)threadIdx.x : lane, step = solo ? (int)blockDim.x : 32;
+    double* p = sp + (solo ? (size_t)0 : (size_t)warp * experts);
+    __shared__ double solo_sum;
+    if (has_token) {
+        const float* s = scores + tok * experts;
+        float m = -INFINITY;
+        for (int i = lane; i < experts; i += 32) m = fmaxf(m, s[i]);
 #pragma unroll
-    for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-    for (int i = lane; i < experts; i += 32) p[i] = exp((double)(s[i] - m));
-    __syncwarp();
+        for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+        for (int i = first; i < experts; i += step) p[i] = exp((double)(s[i] - m));
+    }
+    if (solo) __syncthreads();
+    else __syncwarp();
     // ascending sequential sum like the reference's reduce(0, +); the loads are issued eight at a
     // time so that only the additions are serial
     double sum = 0.0;
-    if (lane == 0) {
-        int i = 0;
-        for (; i + 8 <= experts; i += 8) {
-            double v[8];
+    if (selects) {
+        if (lane == 0) {
+            int i = 0;
+            for (; i + 8 <= experts; i += 8) {
+                double v[8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) v[u] = p[i + u];
+                for (int u = 0; u < 8; u++) v[u] = p[i + u];
 #pragma unroll
-            for (int u = 0; u < 8; u++) sum += v[u];
+                for (int u = 0; u < 8; u++) sum += v[u];
+            }
+            for (; i < experts; i++) sum += p[i];
+            if (solo) solo_sum = sum;
         }
-        for (; i < experts; i++) sum += p[i];
+        sum = __shfl_sync(0xffffffffu, sum, 0);
     }
-    sum = __shfl_sync(0xffffffffu, sum, 0);
-    for (int i = lane; i < experts; i += 32) p[i] = p[i] / sum;
-    __syncwarp();
+    if (solo) {
+        __syncthreads();
+        sum = solo_sum;
+    }
+    if (has_token)
+        for (int i = first; i < experts; i += step) p[i] = p[i] / sum;
+    if (solo) __syncthreads();
+    else __syncwarp();
+    if (selects) {
     double psel = 0.0, prob_sum = 0.0;  // lane k keeps the k-th selected probability (top_k <= 64: two per lane)
     double psel2 = 0.0;
     int isel = -1, isel2 = -1;
@@ -428,14 +447,17 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
                 bi = i;
             }
         }
-#pragma unroll
-        for (int d = 16; d >= 1; d >>= 1) {
-            double ob = __shfl_xor_sync(0xffffffffu, best, d);
-            int oi = __shfl_xor_sync(0xffffffffu, bi, d);
-            if (ob > best || (ob == best && oi < bi)) {
-                best = ob;
-                bi = oi;
-            }
+        // The warp's maximum, ties to the lowest index: candidates are probabilities (>= 0), whose bit patterns order
+        // like unsigned integers, so three warp reductions on the halves of (pattern + 1; 0 = this lane has none) and
+        // on the index replace five rounds of shuffles and compares.
+        {
+            const unsigned long long key = bi != 0x7fffffff ? (unsigned long long)__double_as_longlong(best) + 1ull : 0ull;
+            const unsigned hi = (unsigned)(key >> 32), lo = (unsigned)key;
+            const unsigned mh = __reduce_max_sync(0xffffffffu, hi);
+            const unsigned ml = __reduce_max_sync(0xffffffffu, hi == mh ? lo : 0u);
+            const bool wins = hi == mh && lo == ml;
+            bi = (int)__reduce_min_sync(0xffffffffu, wins ? (unsigned)bi : 0x7fffffffu);
+            best = (mh | ml) != 0u ? __longlong_as_double((long long)((((unsigned long long)mh << 32) | ml) - 1ull)) : -1.0;
         }
         // Non-finite scores make every probability NaN: no comparison above succeeds and bi keeps its
         // sentinel.  Record it and select a valid index (the rank) with weight zero rather than
