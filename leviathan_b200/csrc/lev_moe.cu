@@ -397,6 +397,7 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     const int first = solo ? (int)threadIdx.x : lane, step = solo ? (int)blockDim.x : 32;
     double* p = sp + (solo ? (size_t)0 : (size_t)warp * experts);
     __shared__ double solo_sum;
+    __shared__ int sm_idx[32];
     if (has_token) {
         const float* s = scores + tok * experts;
         float m = -INFINITY;
@@ -483,6 +484,7 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     if (lane < top_k) {
         float sc = expert_scale ? expert_scale[isel] : 1.0f;
         idx[tok * top_k + lane] = isel;
+        if (fuse_group && tok * top_k + lane < 32) sm_idx[tok * top_k + lane] = isel;  // the grouping below reads them here
         weights[tok * top_k + lane] = prob_sum > 0.0 ? __fmul_rn((float)(psel / prob_sum), sc) : 0.0f;
     }
     if (lane + 32 < top_k) {
@@ -495,20 +497,20 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     __syncthreads();  // every token's indices are written (and visible inside the CTA)
     if (warp != 0) return;
     // pair `lane`: stable position among the resident pairs ordered by (expert, pair)
-    const int e = lane < G.pairs ? G.idx[lane] : -1;
+    const int e = lane < G.pairs ? sm_idx[lane] : -1;
     const bool res = e >= G.first && e < G.first + G.count;
     if (lane < G.pairs && (e < 0 || e >= G.experts)) atomicOr(G.status, LEV_DEV_NONFINITE_INPUT);
     int pos = 0;
-    for (int j = 0; j < 32; j++) {
-        const int ej = __shfl_sync(0xffffffffu, e, j);
-        const bool rj = __shfl_sync(0xffffffffu, (int)res, j) != 0;
+    for (int j = 0; j < G.pairs; j++) {
+        const int ej = sm_idx[j];
+        const bool rj = ej >= G.first && ej < G.first + G.count;
         if (rj && (ej < e || (ej == e && j < lane))) pos++;
     }
     const int total = __popc(__ballot_sync(0xffffffffu, res));
     for (int ex = lane; ex < G.experts; ex += 32) {
         int cnt = 0, before = 0;
         for (int j = 0; j < G.pairs; j++) {
-            const int ej = G.idx[j];
+            const int ej = sm_idx[j];
             const bool rj = ej >= G.first && ej < G.first + G.count;
             cnt += rj && ej == ex;
             before += rj && ej < ex;
