@@ -418,6 +418,11 @@ int lev_moe_combine(lev_ctx* ctx, const float* y_slots, const float* weights, in
 /* The whole layer.  idx_out / w_out may be NULL. */
 int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens,
                   int top_k, float* out, int32_t* idx_out, float* w_out, unsigned flags);
+/* out = residual + alpha * layer(x): the whole layer with the decoder loop's residual step (g4_axpy,
+ * Sources/LeviathanCore/Gemma4.swift:3878, :4459-4466) folded into the combine launch; the bits are those of
+ * lev_moe_layer followed by lev_axpy.  Device pointers, no flags; out may be residual, not x. */
+int lev_moe_layer_residual(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                           const float* residual, float alpha, float* out, unsigned flags);
 
 /* ---- Forge op-spec surface ---------------------------------------------
  * Accepts the op JSON of Q4OpIR (Sources/LeviathanCore/Q4Lowering.swift:50-145,

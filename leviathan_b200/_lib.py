@@ -118,6 +118,7 @@ SIGNATURES = {
     "lev_moe_experts": (_I, [_P, _P, _P, _L, _I, _P, _P, _P, _U]),
     "lev_moe_combine": (_I, [_P, _P, _P, _L, _I, _I, _P, _U]),
     "lev_moe_layer": (_I, [_P, _P, _P, _L, _I, _P, _P, _P, _U]),
+    "lev_moe_layer_residual": (_I, [_P, _P, _P, _L, _I, _P, C.c_float, _P, _U]),
     "lev_op_install_json": (_I, [_P, C.c_char_p, _Z, C.POINTER(_P)]),
     "lev_op_uninstall": (_I, [_P, _P]),
     "lev_op_describe": (_I, [_P, C.c_char_p, C.POINTER(_L), C.POINTER(_L), C.POINTER(_I), C.POINTER(_I),

@@ -542,6 +542,16 @@ class Context:
                        self._flags(host, check_finite)))
         return (out, idx, wts) if want_routing else out
 
+    def moe_layer_residual(self, mw: MoEWeights, x, top_k: int, residual, alpha: float = 1.0, out=None):
+        """lev_moe_layer_residual: out = residual + alpha * layer(x) in the layer's own launches (torch CUDA tensors;
+        out may be residual)."""
+        x, residual = x.contiguous(), residual.contiguous()
+        out = residual if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_moe_layer_residual(self.handle, mw.handle, _ptr(x), x.shape[0], top_k, _ptr(residual), float(alpha),
+                                                    _ptr(out), 0))
+        return out
+
     # -- op spec --
     def op_install(self, op_json: str | bytes):
         data = op_json.encode() if isinstance(op_json, str) else op_json

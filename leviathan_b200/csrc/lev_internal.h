@@ -140,3 +140,5 @@ int lev_moe_experts_dev(lev_ctx* ctx, const lev_moe_weights* w, const float* x, 
 int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden, float* out);
 int lev_moe_combine_resident_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden,
                                  float* out, const int32_t* idx, int first, int count);
+int lev_moe_combine_residual_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden,
+                                 float* out, const int32_t* idx, int first, int count, const float* residual, float alpha);

@@ -739,8 +739,10 @@ __global__ void __launch_bounds__(1024) k_group_fast(GroupArgs G, int nchunks) {
 
 // out[t][h] = sum_k w[t][k] * y[t][k][h]: a separate multiply and add per
 // slot in rank order from zero (Sources/LeviathanCore/Gemma4.swift:4459-4466)
+// residual != NULL: out = residual + alpha * sum, the bits of lev_axpy applied to the plain sum (out may be residual)
 __global__ void k_combine(const float* __restrict__ y, const float* __restrict__ w, int64_t tokens, int top_k,
-                          int hidden, float* __restrict__ out, const int32_t* __restrict__ idx, int first, int count) {
+                          int hidden, float* out, const int32_t* __restrict__ idx, int first, int count,
+                          const float* residual, float alpha) {
     pdl_launch_dependents();
     pdl_wait();
     int64_t total = tokens * hidden;
@@ -756,7 +758,7 @@ __global__ void k_combine(const float* __restrict__ y, const float* __restrict__
             }
             acc = __fadd_rn(acc, __fmul_rn(w[t * top_k + k], y[(t * top_k + k) * hidden + h]));
         }
-        out[i] = acc;
+        out[i] = residual ? fmaf(alpha, acc, residual[i]) : acc;
     }
 }
 
@@ -1140,8 +1142,13 @@ int lev_moe_combine_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t 
 // idx != NULL: only the slots routed to experts [first, first + count) enter the sum
 int lev_moe_combine_resident_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden,
                                  float* out, const int32_t* idx, int first, int count) {
+    return lev_moe_combine_residual_dev(ctx, y, wts, tokens, top_k, hidden, out, idx, first, count, nullptr, 1.0f);
+}
+
+int lev_moe_combine_residual_dev(lev_ctx* ctx, const float* y, const float* wts, int64_t tokens, int top_k, int hidden,
+                                 float* out, const int32_t* idx, int first, int count, const float* residual, float alpha) {
     LEV_CUDA(ctx, launch_pdl(k_combine, dim3(grid_for(ctx, tokens * hidden, 256, 8)), dim3(256), (size_t)0, ctx->stream, y, wts,
-                             tokens, top_k, hidden, out, idx, first, count));
+                             tokens, top_k, hidden, out, idx, first, count, residual, alpha));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_combine");
 }
@@ -1316,8 +1323,16 @@ extern "C" int lev_moe_combine(lev_ctx* ctx, const float* y_slots, const float* 
     return LEV_OK;
 }
 
+static int moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, float* out,
+                            int32_t* idx_out, float* w_out, const float* residual, float alpha);
+
 int lev_moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, float* out,
                          int32_t* idx_out, float* w_out) {
+    return moe_layer_device(ctx, w, x, tokens, top_k, out, idx_out, w_out, nullptr, 1.0f);
+}
+
+static int moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k, float* out,
+                            int32_t* idx_out, float* w_out, const float* residual, float alpha) {
     const int64_t pairs = tokens * top_k;
     size_t ib = ((size_t)pairs * 4 + 255) & ~(size_t)255, sb = ((size_t)tokens * w->experts * 4 + 255) & ~(size_t)255;
     void* a;
@@ -1355,7 +1370,26 @@ int lev_moe_layer_device(lev_ctx* ctx, const lev_moe_weights* w, const float* x,
         LEV_TRY(lev_moe_route_dev(ctx, w, x, tokens, top_k, idx, wts, scores));
         LEV_TRY(lev_moe_experts_dev(ctx, w, x, tokens, top_k, idx, (float*)d, nullptr));
     }
-    return lev_moe_combine_dev(ctx, (const float*)d, wts, tokens, top_k, w->hidden, out);
+    return lev_moe_combine_residual_dev(ctx, (const float*)d, wts, tokens, top_k, w->hidden, out, nullptr, 0, 0, residual, alpha);
+}
+
+// out = residual + alpha * layer(x): the layer with the residual step of the decoder loop (g4_axpy,
+// Sources/LeviathanCore/Gemma4.swift:3878) folded into the combine launch.  Device pointers; out may be residual.
+extern "C" int lev_moe_layer_residual(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,
+                                      const float* residual, float alpha, float* out, unsigned flags) {
+    if (!ctx || !w || !x || !out || !residual) return LEV_BAD_ARGUMENT;
+    if (flags & (LEV_FLAG_HOST_IO | LEV_FLAG_CHECK_FINITE))
+        return lev_fail(ctx, LEV_UNSUPPORTED, "the layer with a folded residual takes device pointers and no finite checks");
+    if (!isfinite(alpha)) return lev_fail(ctx, LEV_BAD_ARGUMENT, "alpha %g", (double)alpha);
+    LEV_TRY(check_tokens(ctx, w, tokens, top_k));
+    if (w->local_count != w->experts)
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "experts are sharded on this context: use lev_moe_layer_ep");
+    const size_t xb = (size_t)tokens * w->hidden * sizeof(float);
+    if (out != x && (const char*)out < (const char*)x + xb && (const char*)x < (const char*)out + xb)
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and out overlap");
+    if (out == x) return lev_fail(ctx, LEV_BAD_ARGUMENT, "x and out overlap");
+    LEV_CUDA(ctx, cudaSetDevice(ctx->device));
+    return moe_layer_device(ctx, w, x, tokens, top_k, out, nullptr, nullptr, residual, alpha);
 }
 
 extern "C" int lev_moe_layer(lev_ctx* ctx, const lev_moe_weights* w, const float* x, int64_t tokens, int top_k,

@@ -237,8 +237,11 @@ class SyntheticDecoder:
                 for a, b in self._cols():
                     ctx.matvec_fused(L.wo, self.ao[a:b].view(b - a, qw), None, residual=x[a:b], alpha=1.0, out=x1[a:b])
             ctx.rmsnorm(x1, L.ffn_norm, c.eps, out=self.h)
-            ctx.moe_layer(L.moe, self.h, c.top_k, out=self.mo, expert_parallel=self.world > 1)
-            ctx.axpy(1.0, self.mo, x1, out=x)
+            if self.world > 1:
+                ctx.moe_layer(L.moe, self.h, c.top_k, out=self.mo, expert_parallel=True)
+                ctx.axpy(1.0, self.mo, x1, out=x)
+            else:
+                ctx.moe_layer_residual(L.moe, self.h, c.top_k, x1, 1.0, out=x)  # the residual rides in the combine launch
         self.head_step()
         if advance:
             self.pos.add_(1)

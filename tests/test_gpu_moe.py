@@ -182,6 +182,33 @@ def test_layer_matches_oracle(ctx, models, name, tokens):
     assert O.max_rel_err(hout[0], out[0].astype(np.float64)) < 1e-6
 
 
+@pytest.mark.parametrize("tokens", [1, 3, 32])
+def test_layer_with_folded_residual_gives_the_bits_of_layer_then_axpy(ctx, models, tokens):
+    """lev_moe_layer_residual: out = residual + alpha * layer(x) from the combine launch, in place on the residual
+    too; one launch fewer than the layer followed by lev_axpy, the same bits."""
+    m = models["gemma"]
+    e, h, i, k = m["dims"]
+    x = torch.from_numpy(Q.normal(700 + tokens, (tokens, h), 1.0)).cuda()
+    r = torch.from_numpy(Q.normal(710 + tokens, (tokens, h), 1.0)).cuda()
+    for alpha in (1.0, -0.375):
+        l0 = ctx.launch_count()
+        want = ctx.axpy(alpha, ctx.moe_layer(m["mw"], x, k), r, out=torch.empty_like(r))
+        separate = ctx.launch_count() - l0
+        l0 = ctx.launch_count()
+        got = ctx.moe_layer_residual(m["mw"], x, k, r, alpha, out=torch.empty_like(r))
+        assert ctx.launch_count() - l0 == separate - 1
+        ctx.synchronize()
+        assert torch.equal(got.view(torch.int32), want.view(torch.int32))
+        inplace = r.clone()
+        ctx.moe_layer_residual(m["mw"], x, k, inplace, alpha)
+        ctx.synchronize()
+        assert torch.equal(inplace.view(torch.int32), want.view(torch.int32))
+    with pytest.raises(lev.LevError):
+        ctx.moe_layer_residual(m["mw"], x, k, r, 1.0, out=x)
+    with pytest.raises(lev.LevError):
+        ctx.moe_layer_residual(m["mw"], x, k, r, float("nan"))
+
+
 @pytest.mark.parametrize("tokens", [96, 512])
 def test_prefill_sized_layer_runs_on_the_tensor_cores(ctx, models, tokens):
     """96 tokens x top-8 = 768 pairs and the 512-token batch (4096 pairs): the expert FFN runs as a
