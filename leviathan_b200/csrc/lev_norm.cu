@@ -21,25 +21,59 @@ constexpr int kNormThreads = 256;
 __global__ void __launch_bounds__(kNormThreads) k_rmsnorm(const float* x, int n, const float* __restrict__ w, float eps,
                                                            float* y, float* inverse, const float* cached) {
     __shared__ float part[kNormThreads / 32];
+    // Vectors of up to kNormRegs * 1024 elements whose rows are 16-byte aligned stay in registers between the two
+    // passes, and the weight is requested together with them, not after the reduction.
+    constexpr int kNormRegs = 4;
+    const bool in_regs = (n & 3) == 0 && n <= kNormRegs * kNormThreads * 4 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)y & 15) == 0 &&
+                         (!w || ((uintptr_t)w & 15) == 0);
+    float4 wv[kNormRegs];
     pdl_wait();
     pdl_launch_dependents();
+    if (in_regs && w) {
+#pragma unroll
+        for (int k = 0; k < kNormRegs; k++) {
+            const int i = (threadIdx.x + k * kNormThreads) * 4;
+            wv[k] = i < n ? __ldg(reinterpret_cast<const float4*>(w + i)) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     const float* xv = x + (int64_t)blockIdx.x * n;
     float* yv = y + (int64_t)blockIdx.x * n;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float4 xr[kNormRegs];
     float inv;
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < kNormRegs; k++) {
+            const int i = (threadIdx.x + k * kNormThreads) * 4;
+            xr[k] = i < n ? *reinterpret_cast<const float4*>(xv + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     if (cached) {
         inv = cached[blockIdx.x];
     } else {
         float ss = 0.f;
         const int n4 = n & ~3;
-        for (int i = threadIdx.x * 4; i < n4; i += kNormThreads * 4) {
-            const float4 v = *reinterpret_cast<const float4*>(xv + i);
-            ss = fmaf(v.x, v.x, ss);
-            ss = fmaf(v.y, v.y, ss);
-            ss = fmaf(v.z, v.z, ss);
-            ss = fmaf(v.w, v.w, ss);
+        if (in_regs) {
+            // the same elements in the same order as the loop below: thread t adds its chunks t, t + 256, ...
+#pragma unroll
+            for (int k = 0; k < kNormRegs; k++) {
+                if ((threadIdx.x + k * kNormThreads) * 4 < n) {
+                    ss = fmaf(xr[k].x, xr[k].x, ss);
+                    ss = fmaf(xr[k].y, xr[k].y, ss);
+                    ss = fmaf(xr[k].z, xr[k].z, ss);
+                    ss = fmaf(xr[k].w, xr[k].w, ss);
+                }
+            }
+        } else {
+            for (int i = threadIdx.x * 4; i < n4; i += kNormThreads * 4) {
+                const float4 v = *reinterpret_cast<const float4*>(xv + i);
+                ss = fmaf(v.x, v.x, ss);
+                ss = fmaf(v.y, v.y, ss);
+                ss = fmaf(v.z, v.z, ss);
+                ss = fmaf(v.w, v.w, ss);
+            }
+            if (threadIdx.x < n - n4) ss = fmaf(xv[n4 + threadIdx.x], xv[n4 + threadIdx.x], ss);
         }
-        if (threadIdx.x < n - n4) ss = fmaf(xv[n4 + threadIdx.x], xv[n4 + threadIdx.x], ss);
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
         if (lane == 0) part[warp] = ss;
@@ -49,6 +83,18 @@ __global__ void __launch_bounds__(kNormThreads) k_rmsnorm(const float* x, int n,
         for (int k = 0; k < kNormThreads / 32; k++) tot += part[k];
         inv = 1.0f / sqrtf(tot / (float)n + eps);
         if (inverse && threadIdx.x == 0) inverse[blockIdx.x] = inv;
+    }
+    if (in_regs) {
+#pragma unroll
+        for (int k = 0; k < kNormRegs; k++) {
+            const int i = (threadIdx.x + k * kNormThreads) * 4;
+            if (i < n) {
+                float4 v = make_float4(xr[k].x * inv, xr[k].y * inv, xr[k].z * inv, xr[k].w * inv);
+                if (w) v = make_float4(v.x * wv[k].x, v.y * wv[k].y, v.z * wv[k].z, v.w * wv[k].w);
+                *reinterpret_cast<float4*>(yv + i) = v;
+            }
+        }
+        return;
     }
     for (int i = threadIdx.x; i < n; i += kNormThreads) {
         const float v = xv[i] * inv;
