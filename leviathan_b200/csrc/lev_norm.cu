@@ -652,29 +652,34 @@ __global__ void __launch_bounds__(128) k_qkv_norm_rope(QkvRows X, int q_heads, i
                      : (is_k ? X.k + col * X.kv_stride + (int64_t)(head - q_heads) * hd
                              : X.v + col * X.kv_stride + (int64_t)(head - q_heads - kv_heads) * hd);
     const float* w = is_q ? qw : (is_k ? kw : nullptr);
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < hd; i += 128) {
-        const float v = xv[i];
-        row[i] = v;
-        ss = fmaf(v, v, ss);
+    // Every load that does not wait for the norm is requested up front -- the head's elements, its norm weights, the
+    // rotary frequencies, the column's slot and position and, as soon as those two are there, its block-table entry --
+    // so the kernel pays one round trip to memory plus the table's, not five in a row.  head_dim <= 512: at most four
+    // elements and two rotary pairs per thread.
+    const bool turn = (is_q || is_k) && inv_freq != nullptr;
+    const bool appends = C.k_pool != nullptr && !is_q;
+    const int half = hd >> 1;
+    float xreg[4], wreg[4], freq[2];
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int i = threadIdx.x + 128 * k;
+        xreg[k] = i < hd ? xv[i] : 0.f;
+    }
+    const int ps = (turn || appends) ? pos[col] : 0;
+    const int sl = appends ? C.slot[col] : -1;
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int i = threadIdx.x + 128 * k;
+        wreg[k] = (w && i < hd) ? w[i] : 1.0f;
     }
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
-    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
-    __syncthreads();
-    const float inv = 1.0f / sqrtf((part[0] + part[1] + part[2] + part[3]) / (float)hd + eps);
-    for (int i = threadIdx.x; i < hd; i += 128) {
-        const float v = row[i] * inv;
-        row[i] = w ? v * w[i] : v;
+    for (int k = 0; k < 2; k++) {
+        const int i = threadIdx.x + 128 * k;
+        freq[k] = (turn && i < half) ? inv_freq[i] : 0.f;
     }
-    __syncthreads();
-    const bool turn = (is_q || is_k) && inv_freq != nullptr;
-    const int half = hd >> 1;
-    const float p = turn ? (float)pos[col] : 0.f;
     // cache append of the finished k / v head (optional): the row of this column's position
     int64_t at = -1;
-    if (C.k_pool && !is_q) {
-        const int sl = C.slot[col], ps = pos[col];
+    if (appends) {
         int64_t blk = -1;
         if (sl >= 0 && sl < C.slots && ps >= 0 && ps < C.max_blocks * C.page) blk = C.table[(int64_t)sl * C.max_blocks + ps / C.page];
         if (blk >= 0 && blk < C.blocks) {
@@ -683,12 +688,34 @@ __global__ void __launch_bounds__(128) k_qkv_norm_rope(QkvRows X, int q_heads, i
             atomicOr(C.status, LEV_DEV_BAD_INDEX);  // recorded, not followed
         }
     }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < 4; k++)
+        if (threadIdx.x + 128 * k < hd) ss = fmaf(xreg[k], xreg[k], ss);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    const float inv = 1.0f / sqrtf((part[0] + part[1] + part[2] + part[3]) / (float)hd + eps);
+#pragma unroll
+    for (int k = 0; k < 4; k++) {
+        const int i = threadIdx.x + 128 * k;
+        if (i < hd) {
+            const float v = xreg[k] * inv;
+            row[i] = w ? v * wreg[k] : v;
+        }
+    }
+    __syncthreads();
+    const float p = turn ? (float)ps : 0.f;
     void* pool = is_k ? C.k_pool : C.v_pool;
-    for (int i = threadIdx.x; i < half; i += 128) {
+#pragma unroll
+    for (int k = 0; k < 2; k++) {
+        const int i = threadIdx.x + 128 * k;
+        if (i >= half) break;
         float a = row[i], b = row[i + half];
         if (turn) {
             float sn, cs;
-            sincosf(inv_freq[i] * p, &sn, &cs);
+            sincosf(freq[k] * p, &sn, &cs);
             const float ra = a * cs - b * sn, rb = a * sn + b * cs;
             a = ra;
             b = rb;
