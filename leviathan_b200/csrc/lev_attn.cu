@@ -710,22 +710,33 @@ __global__ void k_attn_merge(AttnArgs A, int hd) {
     pdl_wait();
     pdl_launch_dependents();
     float* o = A.out + ((int64_t)col * A.q_heads + head) * hd;
-    int slot, qpos;
-    if (!column_ok(A, col, &slot, &qpos)) {
-        for (int i = threadIdx.x; i < hd; i += blockDim.x) o[i] = __int_as_float(0x7FC00000);
-        return;
-    }
     const int64_t ph = ((int64_t)col * A.q_heads + head) * A.splits;
-    // statistics: thread s holds range s (splits <= kMaxSplits <= blockDim.x); maxima and the sum go
-    // through warp shuffles and one shared array, always in the same order
-    __shared__ float red[kMaxSplits / 32];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    constexpr int kMergeWarps = 8;
+    // Requested before anything is waited for: the column's slot and position, the ranges' statistics and the first
+    // eight rows this warp will add (they do not depend on the statistics), one round trip to memory instead of three.
+    int slot, qpos;
+    const bool col_ok = column_ok(A, col, &slot, &qpos);
     float ms = -INFINITY, ls = 0.f;
     if ((int)threadIdx.x < A.splits) {
         const float2 v = *reinterpret_cast<const float2*>(A.part_ml + (ph + threadIdx.x) * 2);
         ms = v.x;
         ls = v.y;
     }
+    const int qd = blockIdx.z * 32 + lane;
+    float4 first_rows[8];
+#pragma unroll
+    for (int j = 0; j < 8; j++) {
+        const int s2 = warp + j * kMergeWarps;
+        first_rows[j] = s2 < A.splits ? *reinterpret_cast<const float4*>(A.part_acc + (ph + s2) * hd + qd * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    if (!col_ok) {
+        for (int i = threadIdx.x; i < hd; i += blockDim.x) o[i] = __int_as_float(0x7FC00000);
+        return;
+    }
+    // statistics: thread s holds range s (splits <= kMaxSplits <= blockDim.x); maxima and the sum go
+    // through warp shuffles and one shared array, always in the same order
+    __shared__ float red[kMaxSplits / 32];
     float mm = ms;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
@@ -752,18 +763,17 @@ __global__ void k_attn_merge(AttnArgs A, int hd) {
     // weighted sum of the ranges' rows: warp w takes ranges w, w + warps, ...; a lane holds four
     // consecutive elements, so a row is read in 16-byte loads, eight rows in flight per lane
     // (blockIdx.z selects which 128 elements of the head this block sums)
-    constexpr int kMergeWarps = 8;
     __shared__ float4 sum[kMergeWarps][32];
     const int warps = kMergeWarps;
     {
-        const int qd = blockIdx.z * 32 + lane;
         float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
         for (int sp = warp; sp < A.splits; sp += warps * 8) {
             float4 t[8];
 #pragma unroll
             for (int j = 0; j < 8; j++) {
                 const int s2 = sp + j * warps;
-                t[j] = s2 < A.splits ? *reinterpret_cast<const float4*>(A.part_acc + (ph + s2) * hd + qd * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
+                if (sp == warp) t[j] = first_rows[j];
+                else t[j] = s2 < A.splits ? *reinterpret_cast<const float4*>(A.part_acc + (ph + s2) * hd + qd * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
             }
 #pragma unroll
             for (int j = 0; j < 8; j++) {
