@@ -1017,15 +1017,19 @@ bool lev_chain_supported(lev_ctx* ctx, int n_ops, const lev_chain_item* items) {
 }
 
 // Whether a call that did not ask for a list should take the persistent kernel.  A launch of it fills every SM
-// and cannot overlap its neighbours in the stream, which costs about 5 us; it pays from roughly 48 MB of weight
-// bytes per launch on (the FFN set, the vocabulary head).  Below that the half-SM one-launch kernel, whose blocks
-// become resident beside the previous kernel's, is the faster one (a 28 MB tensor: 9.9 against 12.9 us; the
-// q / k / v and output projections of a decode layer: 9 us per layer less).
+// and cannot overlap its neighbours in the stream, which costs about 5 us; it pays from roughly 40 MB of weight
+// bytes per launch on (the FFN's gate + up pair, its Q6_K down tensor, the vocabulary head).  Below that the half-SM
+// one-launch kernel, whose blocks become resident beside the previous kernel's, is the faster one (a 28 MB tensor:
+// 9.9 against 12.9 us; the q / k / v and output projections of a decode layer: 9 us per layer less).  The line is
+// drawn so that the FFN's two fused launches land on the same side: a persistent launch followed by a half-SM one
+// overlaps with nothing and cost 59 us for the pair where two persistent launches cost 44 (a 41 MB Q6_K tensor alone:
+// 18.2 against 17.6 us).
+static const size_t kChainPreferredBytes = 40000000;
 bool lev_chain_preferred(lev_ctx* ctx, int n_ops, const lev_chain_item* items) {
     size_t bytes = 0;
     for (int i = 0; i < n_ops; i++)
         bytes += (size_t)items[i].rows * (size_t)items[i].w->blocks_per_row * (size_t)lev_block_bytes(items[i].w->type);
-    return bytes >= ((size_t)48 << 20) && lev_chain_supported(ctx, n_ops, items);
+    return bytes >= kChainPreferredBytes && lev_chain_supported(ctx, n_ops, items);
 }
 
 template <int W>
