@@ -16,6 +16,7 @@
 //    order from shared-memory records.  Same call, same bits.
 #include "lev_stream.h"
 #include "lev_stream_math.cuh"
+#include "lev_chain_math.cuh"
 
 namespace {
 
@@ -76,7 +77,9 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long bars[W][kMaxDepth];  // stage filled (bulk copy landed)
     __shared__ float rec[W][2][CMAX][16];  // partial sums of tiles a warp shares with its neighbours
+    __shared__ __align__(16) uint4 zero_block[2];  // one column: the fragments of lanes outside a chunk's column group
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
+    if (CMAX == 1 && threadIdx.x < 2) zero_block[threadIdx.x] = make_uint4(0u, 0u, 0u, 0u);  // read after the table barrier
     // logical position of this warp in the CTA's run: warps of one scheduler (warp % 4) are
     // neighbours, so shares that differ by one step spread evenly over the schedulers
     const int lw = (warp & 3) * (W / 4) + (warp >> 2);
@@ -364,6 +367,20 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
     }
     __syncthreads();
 
+    // One column runs the column-group arithmetic of lev_chain_math.cuh (a third fewer instructions per K-step than
+    // the general form below: one accumulator chain per K-step, block scales applied once): ya / yb are this lane's
+    // sums of rows g and g + 8, the table layout is the same.
+    float ya = 0.f, yb = 0.f;
+    LaneConst LC;
+    LC.q_off = 16u * lane;
+    LC.hdr_off = 16u * g;
+    LC.x_off = (unsigned)(((g & 1) * 4 + t) * 32);
+    LC.grp = (unsigned)(g >> 1);
+    LC.t = (unsigned)t;
+    LC.g = (unsigned)g;
+    LC.sh16 = 16u * (t & 1);
+    LC.zero_s = smem_u32(zero_block);
+    unsigned xs_s = 0, sa_s = 0;  // shared-memory addresses of the tables of the tile being worked on
     float yacc[NT][4];
     float mina[CMAX], minb[CMAX];
 #pragma unroll
@@ -400,6 +417,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
             }
             xs = reinterpret_cast<const uint4*>(tables0 + (size_t)(job - job0) * A.table_stride);
             sa = reinterpret_cast<const float*>(xs + A.chunks * GLT * 8);
+            xs_s = 0;  // (one column) the tables' shared-memory addresses are formed again
 #pragma unroll
             for (int c = 0; c < CMAX; c++) orow[c] = A.job_out[job * CMAX + c];
         } else if (MULTI) {
@@ -420,7 +438,18 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
         const int i1 = i0 + sps < e ? i0 + sps : e;
         for (int i = i0; i < i1; i++) {
             const uint4* st = reinterpret_cast<const uint4*>(ring + slot * stage_bytes + (i - i0) * kStepBytes);
-            stream_step<TYPE, CMAX, true>(st, xs + k * (4 * GLT * 8), sa + k * (4 * kAuxPerChunk), lane, O, yacc, mina, minb);
+            if constexpr (CMAX == 1) {
+                if (xs_s == 0) {
+                    xs_s = smem_u32(xs);
+                    sa_s = smem_u32(sa);
+                    order_after(xs_s);
+                }
+                unsigned st_s = ring_s + (unsigned)slot * stage_bytes + (unsigned)(i - i0) * kStepBytes;
+                order_after(st_s);  // the loads inside are plain asm: this keeps them behind the wait above
+                chain_step<TYPE>(st_s, xs_s + (unsigned)k * 1024u, sa_s + (unsigned)k * (16u * kAuxPerChunk), LC, ya, yb);
+            } else {
+                stream_step<TYPE, CMAX, true>(st, xs + k * (4 * GLT * 8), sa + k * (4 * kAuxPerChunk), lane, O, yacc, mina, minb);
+            }
             k++;
             if (k == spt || i == e - 1) {
                 // ---- this warp's segment of the tile ends: fold to one f32 per (row, column) ----
@@ -429,17 +458,22 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
 #pragma unroll
                 for (int c = 0; c < CMAX; c++) {
                     float va = 0.f, vb = 0.f;
+                    if constexpr (CMAX == 1) {
+                        va = ya;
+                        vb = yb;
+                    } else {
 #pragma unroll
-                    for (int term = 0; term < TERMS; term++) {
-                        constexpr float kScale[2] = {1.0f, 4.8828125e-4f};  // 2^0, 2^-11
-                        const int col = c * TERMS + term, nt = col / 8, jj = col & 1;
-                        const bool mine = t == (col % 8) / 2;
-                        va = fmaf(mine ? yacc[nt][jj] : 0.f, kScale[term], va);
-                        vb = fmaf(mine ? yacc[nt][2 + jj] : 0.f, kScale[term], vb);
-                    }
-                    if (TYPE == LEV_GGML_Q4_K) {
-                        va -= mina[c];
-                        vb -= minb[c];
+                        for (int term = 0; term < TERMS; term++) {
+                            constexpr float kScale[2] = {1.0f, 4.8828125e-4f};  // 2^0, 2^-11
+                            const int col = c * TERMS + term, nt = col / 8, jj = col & 1;
+                            const bool mine = t == (col % 8) / 2;
+                            va = fmaf(mine ? yacc[nt][jj] : 0.f, kScale[term], va);
+                            vb = fmaf(mine ? yacc[nt][2 + jj] : 0.f, kScale[term], vb);
+                        }
+                        if (TYPE == LEV_GGML_Q4_K) {
+                            va -= mina[c];
+                            vb -= minb[c];
+                        }
                     }
                     va += __shfl_xor_sync(0xffffffffu, va, 1);
                     vb += __shfl_xor_sync(0xffffffffu, vb, 1);
@@ -470,6 +504,7 @@ __global__ void __launch_bounds__(W * 32, W <= 8 ? 2 : 1) k_dense(DenseArgs A) {
                     for (int j = 0; j < 4; j++) yacc[nt][j] = 0.f;
 #pragma unroll
                 for (int c = 0; c < CMAX; c++) mina[c] = minb[c] = 0.f;
+                ya = yb = 0.f;
                 tl++;
                 k = 0;
                 seg_k0 = 0;
