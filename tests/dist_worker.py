@@ -109,7 +109,7 @@ def main():
         assert O.max_rel_err(out, mine.astype(np.float64)) < 2e-6, "ep vs single GPU"
         mw_all.free()
 
-    # the layer of BASELINE config 4 at 256 tokens in all (2048 pairs: the tensor-core form)
+    # the 128-expert top-8 layer of the benchmark at 256 tokens in all (2048 pairs: the tensor-core form)
     e2, h2, i2, k2 = 128, 2816, 704, 8
     t2 = 256 // world
     g2 = torch.Generator(device=dev).manual_seed(1234)
