@@ -358,6 +358,13 @@ int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* layout, const void* k_poo
                     const void* v_pool, const int32_t* block_table, const int32_t* slot,
                     const int32_t* pos, int n_cols, int q_heads, const float* q, int window,
                     float scale, float* out);
+/* lev_attn_decode with the columns' query rows q_ld elements apart (even, at least
+ * q_heads * head_dim; q 8-byte aligned): q may be the leading part of each row of a fused
+ * [n_cols][(q_heads + 2 kv_heads) * head_dim] projection output, as lev_qkv_norm_rope_append leaves it. */
+int lev_attn_decode_ld(lev_ctx* ctx, const lev_kv_layout* layout, const void* k_pool,
+                       const void* v_pool, const int32_t* block_table, const int32_t* slot,
+                       const int32_t* pos, int n_cols, int q_heads, const float* q, int64_t q_ld,
+                       int window, float scale, float* out);
 /* lev_qkv_norm_rope whose launch also stores the finished k and v heads at pos[column] of sequence
  * slot[column] of the cache (lev_kv_append without a launch of its own); kv_heads and head_dim come
  * from the layout. */

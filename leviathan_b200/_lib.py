@@ -108,6 +108,7 @@ SIGNATURES = {
     "lev_matvec_multi_fused": (_I, [_P, _I, C.POINTER(_P), _P, _L, _I, C.POINTER(Fusion), C.POINTER(_P), C.POINTER(_L)]),
     "lev_kv_append": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _P, _P]),
     "lev_attn_decode": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _I, _P, _I, C.c_float, _P]),
+    "lev_attn_decode_ld": (_I, [_P, C.POINTER(KVLayout), _P, _P, _P, _P, _P, _I, _I, _P, _L, _I, C.c_float, _P]),
     "lev_gemm_prefill": (_I, [_P, _P, _P, _L, _P, _U]),
     "lev_act_bf16": (_I, [_P, _P, _L, _P]),
     "lev_moe_weights_upload": (_I, [_P, _P, _P, _Z, _P, _Z, _I, _I, _I, _I, _I, _I, C.POINTER(_P)]),

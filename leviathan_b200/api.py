@@ -422,6 +422,20 @@ class Context:
                                              _ptr(slot), _ptr(pos), q.shape[0], q.shape[1], _ptr(q), window, scale, _ptr(out)))
         return out
 
+    def attn_decode_fused_rows(self, cache: "PagedKV", slot, pos, qkv, q_heads: int, window: int = 0, scale: float = 1.0, out=None):
+        """lev_attn_decode_ld: the queries are the leading q_heads * head_dim elements of each row of qkv
+        [n_cols][(q_heads + 2 kv_heads) * head_dim], the fused projection output -> out [n_cols][q_heads][head_dim]."""
+        import torch
+
+        assert qkv.is_contiguous() and qkv.ndim == 2
+        hd = cache.layout.head_dim
+        out = torch.empty((qkv.shape[0], q_heads, hd), device=qkv.device) if out is None else out
+        self._flags(False, False)
+        self._check(self.lib.lev_attn_decode_ld(self.handle, C.byref(cache.layout), _ptr(cache.k), _ptr(cache.v), _ptr(cache.table),
+                                                _ptr(slot), _ptr(pos), qkv.shape[0], q_heads, _ptr(qkv), qkv.shape[1], window, scale,
+                                                _ptr(out)))
+        return out
+
     def _matvec_host(self, fn, blocks, out_dim, in_dim, x):
         blocks = np.ascontiguousarray(blocks, np.uint8)
         x = np.ascontiguousarray(x, np.float32)

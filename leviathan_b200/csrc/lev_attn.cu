@@ -31,7 +31,8 @@ struct AttnArgs {
     const int32_t* table;  // [slots][max_blocks]
     const int32_t* slot;   // [cols]
     const int32_t* pos;    // [cols] query position (attends to 0..pos)
-    const float* q;        // [cols][q_heads][hd]
+    const float* q;        // [cols][q_heads][hd], rows q_ld elements apart
+    int64_t q_ld;
     float* out;            // [cols][q_heads][hd]
     float* part_ml;        // [cols][q_heads][splits][2]
     float* part_acc;       // [cols][q_heads][splits][hd]
@@ -268,7 +269,7 @@ __global__ void __launch_bounds__(kAttnWarps * 32, 2) k_attn_split(AttnArgs A) {
     float qv[GROUP][VEC];
 #pragma unroll
     for (int g = 0; g < GROUP; g++) {
-        const float* qh = A.q + ((int64_t)col * A.q_heads + kvh * GROUP + g) * HD + lane * VEC;
+        const float* qh = A.q + (int64_t)col * A.q_ld + (int64_t)(kvh * GROUP + g) * HD + lane * VEC;
 #pragma unroll
         for (int i = 0; i < VEC; i++) qv[g][i] = qh[i];
     }
@@ -558,7 +559,7 @@ __global__ void __launch_bounds__(kMmaWarps * 32, 2) k_attn_split_mma(AttnArgs A
     {
         const int head = g >> 1, term = g & 1;
         const bool used = head < GROUP;
-        const float* qh = A.q + ((int64_t)col * A.q_heads + kvh * GROUP + (used ? head : 0)) * HD;
+        const float* qh = A.q + (int64_t)col * A.q_ld + (int64_t)(kvh * GROUP + (used ? head : 0)) * HD;
 #pragma unroll
         for (int s = 0; s < kSteps; s++) {
             const float2 a = *reinterpret_cast<const float2*>(qh + s * 16 + 2 * t);
@@ -923,8 +924,21 @@ extern "C" int lev_kv_append(lev_ctx* ctx, const lev_kv_layout* L, void* k_pool,
 extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void* k_pool, const void* v_pool, const int32_t* block_table,
                                const int32_t* slot, const int32_t* pos, int n_cols, int q_heads, const float* q, int window, float scale,
                                float* out) {
+    if (!L) return LEV_BAD_ARGUMENT;
+    return lev_attn_decode_ld(ctx, L, k_pool, v_pool, block_table, slot, pos, n_cols, q_heads, q, (int64_t)q_heads * L->head_dim, window, scale,
+                              out);
+}
+
+// The same with the columns' query rows q_ld elements apart: q may be the leading part of each row of a fused
+// [n_cols][(q_heads + 2 kv_heads) * head_dim] projection output.
+extern "C" int lev_attn_decode_ld(lev_ctx* ctx, const lev_kv_layout* L, const void* k_pool, const void* v_pool, const int32_t* block_table,
+                                  const int32_t* slot, const int32_t* pos, int n_cols, int q_heads, const float* q, int64_t q_ld, int window,
+                                  float scale, float* out) {
     if (!ctx || !k_pool || !v_pool || !block_table || !slot || !pos || !q || !out) return LEV_BAD_ARGUMENT;
     LEV_TRY(check_layout(ctx, L));
+    if (q_ld < (int64_t)q_heads * L->head_dim || q_ld % 2 != 0 || ((uintptr_t)q & 7) != 0)
+        return lev_fail(ctx, LEV_BAD_ARGUMENT, "query rows %lld elements apart (at least %lld, even, 8-byte aligned)", (long long)q_ld,
+                        (long long)q_heads * L->head_dim);
     if (n_cols < 1 || n_cols > 65535) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "columns %d", n_cols);
     if (q_heads <= 0 || q_heads % L->kv_heads != 0) return lev_fail(ctx, LEV_BAD_DIMENSIONS, "%d query heads over %d KV heads", q_heads, L->kv_heads);
     const int group = q_heads / L->kv_heads;
@@ -958,6 +972,7 @@ extern "C" int lev_attn_decode(lev_ctx* ctx, const lev_kv_layout* L, const void*
     A.k_pool = k_pool;
     A.v_pool = v_pool;
     A.q = q;
+    A.q_ld = q_ld;
     A.out = out;
     A.part_acc = (float*)scr;
     A.part_ml = (float*)scr + heads * hd;

@@ -62,9 +62,10 @@ class DecoderConfig:
 
 @dataclass
 class _Layer:
-    wq: object
+    wq: object    # narrow batches: three tensors behind one launch of the decode matvec
     wk: object
     wv: object
+    wqkv: object  # wide batches: the same rows as one [q | k | v] tensor, one GEMM instead of three
     wo: object
     moe: object
     cache: PagedKV
@@ -105,9 +106,18 @@ class SyntheticDecoder:
         blocks_per_seq = (cfg.positions + cfg.page - 1) // cfg.page
         self.layers: list[_Layer] = []
         for l in range(cfg.layers):
-            wq = self._tensor(f"blk.{l}.attn_q", cfg.weight_type, QH * HD, H)
-            wk = self._tensor(f"blk.{l}.attn_k", cfg.weight_type, KVH * HD, H)
-            wv = self._tensor(f"blk.{l}.attn_v", cfg.weight_type, KVH * HD, H)
+            wq = wk = wv = wqkv = None
+            if self.wide:
+                # GGUF rows are independent: the three tensors' bytes one after the other are the fused tensor's
+                parts = [self._blocks(f"blk.{l}.attn_q", cfg.weight_type, QH * HD, H),
+                         self._blocks(f"blk.{l}.attn_k", cfg.weight_type, KVH * HD, H),
+                         self._blocks(f"blk.{l}.attn_v", cfg.weight_type, KVH * HD, H)]
+                wqkv = ctx.upload(torch.cat(parts), cfg.weight_type, (QH + 2 * KVH) * HD, H)
+                del parts
+            else:
+                wq = self._tensor(f"blk.{l}.attn_q", cfg.weight_type, QH * HD, H)
+                wk = self._tensor(f"blk.{l}.attn_k", cfg.weight_type, KVH * HD, H)
+                wv = self._tensor(f"blk.{l}.attn_v", cfg.weight_type, KVH * HD, H)
             wo = self._tensor(f"blk.{l}.attn_output", cfg.weight_type, H, QH * HD)
             if not self.wide:
                 for w in (wq, wk, wv, wo):
@@ -118,7 +128,7 @@ class SyntheticDecoder:
                 cache.ensure(s, cfg.positions - 1)
             self._fill(cache.k, f"blk.{l}.cache_k")
             self._fill(cache.v, f"blk.{l}.cache_v")  # the two fills take their seeds in a per-rank range, see _fill
-            self.layers.append(_Layer(wq, wk, wv, wo, moe, cache,
+            self.layers.append(_Layer(wq, wk, wv, wqkv, wo, moe, cache,
                                       self._norm(f"blk.{l}.attn_norm", H, norm_sigma), self._norm(f"blk.{l}.ffn_norm", H, norm_sigma),
                                       self._norm(f"blk.{l}.attn_q_norm", HD, norm_sigma), self._norm(f"blk.{l}.attn_k_norm", HD, norm_sigma)))
         self.out_norm = self._norm("output_norm", H, norm_sigma)
@@ -138,6 +148,7 @@ class SyntheticDecoder:
         self.ao = torch.empty((B, QH, HD), device=device)
         self.logits = torch.empty((B, cfg.vocab), device=device)
         if self.wide:
+            self.qkv = torch.empty((B, (QH + 2 * KVH) * HD), device=device)
             self.hb = torch.empty((B, H), dtype=torch.bfloat16, device=device)
             self.aob = torch.empty((B, QH * HD), dtype=torch.bfloat16, device=device)
         self.graph = None
@@ -148,6 +159,9 @@ class SyntheticDecoder:
         return self._seed
 
     def _tensor(self, name, t, rows, cols, slab=None):
+        return self.ctx.upload(self._blocks(name, t, rows, cols, slab), t, rows, cols)
+
+    def _blocks(self, name, t, rows, cols, slab=None):
         import torch
 
         slab = rows if slab is None else min(slab, rows)
@@ -158,7 +172,7 @@ class SyntheticDecoder:
         blocks = parts[0] if len(parts) == 1 else torch.cat(parts)
         if self.host is not None:
             self.host[name] = blocks.cpu().numpy()
-        return self.ctx.upload(blocks, t, rows, cols)
+        return blocks
 
     def _experts(self, l):
         import torch
@@ -221,14 +235,14 @@ class SyntheticDecoder:
             if self.wide:
                 ctx.rmsnorm(x, L.attn_norm, c.eps, out=self.h)
                 ctx.act_bf16(self.h, out=self.hb)
-                ctx.gemm_prefill(L.wq, self.hb, out=self.q)
-                ctx.gemm_prefill(L.wk, self.hb, out=self.k)
-                ctx.gemm_prefill(L.wv, self.hb, out=self.v)
+                ctx.gemm_prefill(L.wqkv, self.hb, out=self.qkv)
+                ctx.qkv_norm_rope_append(self.qkv, QH, L.cache, self.slot, self.pos, L.q_norm, L.k_norm, c.eps, self.inv_freq)
+                ctx.attn_decode_fused_rows(L.cache, self.slot, self.pos, self.qkv, QH, 0, c.attn_scale, out=self.ao)
             else:
                 for a, b in self._cols():
                     ctx.matvec_multi_fused([L.wq, L.wk, L.wv], x[a:b], "rmsnorm", L.attn_norm, c.eps, outs=[self.q[a:b], self.k[a:b], self.v[a:b]])
-            ctx.qkv_norm_rope_append_split(self.q, self.k, self.v, QH, L.cache, self.slot, self.pos, L.q_norm, L.k_norm, c.eps, self.inv_freq)
-            ctx.attn_decode(L.cache, self.slot, self.pos, self.q.view(self.batch, QH, HD), 0, c.attn_scale, out=self.ao)
+                ctx.qkv_norm_rope_append_split(self.q, self.k, self.v, QH, L.cache, self.slot, self.pos, L.q_norm, L.k_norm, c.eps, self.inv_freq)
+                ctx.attn_decode(L.cache, self.slot, self.pos, self.q.view(self.batch, QH, HD), 0, c.attn_scale, out=self.ao)
             if self.wide:
                 ctx.act_bf16(self.ao.view(self.batch, qw), out=self.aob)
                 ctx.gemm_prefill(L.wo, self.aob, out=self.mo)
@@ -284,8 +298,9 @@ class SyntheticDecoder:
 
     def free(self):
         for L in self.layers:
-            for w in (L.wq, L.wk, L.wv, L.wo):
-                w.free()
+            for w in (L.wq, L.wk, L.wv, L.wqkv, L.wo):
+                if w is not None:
+                    w.free()
             L.moe.free()
         self.head.free()
         self.layers = []

@@ -83,6 +83,13 @@ def test_columns_of_different_sequences_and_repeat_runs(ctx):
     # one column alone gives the bits it gave inside the batch
     alone = ctx.attn_decode(cache, slot[1:2], pos[1:2], qd[1:2].contiguous(), 0, 1.0).cpu().numpy()
     assert O.max_rel_err(alone[0].reshape(-1), got[1].astype(np.float64).reshape(-1)) < 1e-6
+    # lev_attn_decode_ld: the same queries as the leading part of the rows of a fused [q | k | v] matrix
+    fused = torch.full((len(cols), (q_heads + 2 * kv_heads) * hd), float("nan"), device="cuda")
+    fused[:, :q_heads * hd] = qd.view(len(cols), -1)
+    strided = ctx.attn_decode_fused_rows(cache, slot, pos, fused, q_heads, 0, 1.0).cpu().numpy()
+    assert np.array_equal(strided.view(np.uint32), got.view(np.uint32))
+    with pytest.raises(lev.LevError):
+        ctx.attn_decode_fused_rows(cache, slot, pos, fused[:, :q_heads * hd - 2].contiguous(), q_heads, 0, 1.0)
 
 
 def test_closed_forms_on_the_gpu(ctx):
