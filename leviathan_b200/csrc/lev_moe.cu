@@ -750,15 +750,28 @@ __global__ void k_combine(const float* __restrict__ y, const float* __restrict__
         int64_t t = i / hidden;
         int h = (int)(i - t * hidden);
         float acc = 0.f;
-        for (int k = 0; k < top_k; k++) {
-            // expert-parallel partial: slots whose expert lives on another GPU were never computed here
-            if (idx) {
-                const int e = idx[t * top_k + k];
-                if (e < first || e >= first + count) continue;
+        const float rv = residual ? residual[i] : 0.f;
+        // eight slots at a time: their loads are requested together, the additions stay in slot order
+        for (int k0 = 0; k0 < top_k; k0 += 8) {
+            float wv[8], yv[8];
+            bool use[8];
+#pragma unroll
+            for (int j = 0; j < 8; j++) {
+                const int k = k0 + j;
+                // expert-parallel partial: slots whose expert lives on another GPU were never computed here
+                use[j] = k < top_k;
+                if (use[j] && idx) {
+                    const int e = idx[t * top_k + k];
+                    use[j] = e >= first && e < first + count;
+                }
+                wv[j] = use[j] ? w[t * top_k + k] : 0.f;
+                yv[j] = use[j] ? y[(t * top_k + k) * hidden + h] : 0.f;
             }
-            acc = __fadd_rn(acc, __fmul_rn(w[t * top_k + k], y[(t * top_k + k) * hidden + h]));
+#pragma unroll
+            for (int j = 0; j < 8; j++)
+                if (use[j]) acc = __fadd_rn(acc, __fmul_rn(wv[j], yv[j]));
         }
-        out[i] = residual ? fmaf(alpha, acc, residual[i]) : acc;
+        out[i] = residual ? fmaf(alpha, acc, rv) : acc;
     }
 }
 
