@@ -222,7 +222,22 @@ __global__ void __launch_bounds__(32) k_router_logits_warp(const float* __restri
     double acc[kRouterWarpTokens];
 #pragma unroll
     for (int t = 0; t < kRouterWarpTokens; t++) acc[t] = 0.0;
-    for (int i = lane; i < hidden; i += 32) {
+    // A single token: eight columns of the lane at a time, their loads and conversions issued together, the additions
+    // in ascending order (with more tokens the conversion unit is busy either way and the plain loop is as fast).
+    int i = lane;
+    if (tokens == 1) {
+        for (; i + 7 * 32 < hidden; i += 8 * 32) {
+            double wv[8], xv[8];
+#pragma unroll
+            for (int u = 0; u < 8; u++) {
+                wv[u] = (double)ws[i + 32 * u];
+                xv[u] = (double)xs[i + 32 * u];
+            }
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc[0] = fma(wv[u], xv[u], acc[0]);
+        }
+    }
+    for (; i < hidden; i += 32) {
         const double wv = (double)ws[i];
 #pragma unroll
         for (int t = 0; t < kRouterWarpTokens; t++)
@@ -401,7 +416,13 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     if (has_token) {
         const float* s = scores + tok * experts;
         float m = -INFINITY;
-        for (int i = lane; i < experts; i += 32) m = fmaxf(m, s[i]);
+        for (int i0 = lane; i0 < experts; i0 += 128) {  // four scores per round, requested together
+            float v[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) v[j] = i0 + 32 * j < experts ? s[i0 + 32 * j] : -INFINITY;
+#pragma unroll
+            for (int j = 0; j < 4; j++) m = fmaxf(m, v[j]);
+        }
 #pragma unroll
         for (int d = 16; d >= 1; d >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
         for (int i = first; i < experts; i += step) p[i] = exp((double)(s[i] - m));
