@@ -400,13 +400,15 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     extern __shared__ double sp[];  // [warps][experts] probabilities; selected ones are set to -1
     // With the grouping fused in, the kernels that follow read the job table before their own
     // dependency wait: they may only start when this grid has completed.
-    if (!fuse_group) pdl_launch_dependents();
+    const bool fuse = (fuse_group & 1) != 0;
+    if (!fuse) pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    // One warp per token.  A call with a single token (decode) spreads that token's exponentials and divisions over
-    // the block's four warps; its sum and its selection stay with warp 0, in the same order.
-    const bool solo = tokens == 1;
-    const int64_t tok = solo ? 0 : (int64_t)blockIdx.x * 4 + warp;
+    // One block per token (fuse_group bit 1): the token's exponentials and divisions are spread over the block's four
+    // warps; its sum and its selection stay with warp 0, in the same order.  Otherwise one warp per token, four tokens
+    // per block: the form the fused grouping of two to four decode tokens needs, which wants them in one block.
+    const bool solo = (fuse_group & 2) != 0;
+    const int64_t tok = solo ? (int64_t)blockIdx.x : (int64_t)blockIdx.x * 4 + warp;
     const bool has_token = solo || tok < tokens;
     const bool selects = solo ? warp == 0 : tok < tokens;
     const int first = solo ? (int)threadIdx.x : lane, step = solo ? (int)blockDim.x : 32;
@@ -505,7 +507,7 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
     if (lane < top_k) {
         float sc = expert_scale ? expert_scale[isel] : 1.0f;
         idx[tok * top_k + lane] = isel;
-        if (fuse_group && tok * top_k + lane < 32) sm_idx[tok * top_k + lane] = isel;  // the grouping below reads them here
+        if (fuse && tok * top_k + lane < 32) sm_idx[tok * top_k + lane] = isel;  // the grouping below reads them here
         weights[tok * top_k + lane] = prob_sum > 0.0 ? __fmul_rn((float)(psel / prob_sum), sc) : 0.0f;
     }
     if (lane + 32 < top_k) {
@@ -514,7 +516,7 @@ __global__ void __launch_bounds__(128) k_router_topk(const float* __restrict__ s
         weights[tok * top_k + lane + 32] = prob_sum > 0.0 ? __fmul_rn((float)(psel2 / prob_sum), sc) : 0.0f;
     }
     }
-    if (!fuse_group) return;
+    if (!fuse) return;
     __syncthreads();  // every token's indices are written (and visible inside the CTA)
     if (warp != 0) return;
     // pair `lane`: stable position among the resident pairs ordered by (expert, pair)
@@ -929,8 +931,11 @@ static int route_dev_impl(lev_ctx* ctx, const lev_moe_weights* w, const float* x
     if (fuse) G = *fuse;
     G.status = ctx->d_status;  // the selection loop reports non-finite scores there
     static_assert((size_t)4 * LEV_MAX_EXPERTS * sizeof(double) <= 48 * 1024, "k_router_topk runs without a shared-memory opt-in");
-    LEV_CUDA(ctx, launch_pdl(k_router_topk, dim3((unsigned)((tokens + 3) / 4)), dim3(128), smem, ctx->stream, (const float*)scores,
-                             tokens, (int)w->experts, top_k, (const float*)nullptr, idx, weights, G, fuse ? 1 : 0));
+    // one block per token, except where the fused grouping needs two to four tokens in one block
+    const bool per_token = tokens == 1 || !fuse;
+    LEV_CUDA(ctx, launch_pdl(k_router_topk, dim3((unsigned)(per_token ? tokens : (tokens + 3) / 4)), dim3(128), smem, ctx->stream,
+                             (const float*)scores, tokens, (int)w->experts, top_k, (const float*)nullptr, idx, weights, G,
+                             (fuse ? 1 : 0) | (per_token ? 2 : 0)));
     ctx->launches++;
     return lev_cuda_check(ctx, cudaGetLastError(), "k_router_topk");
 }
