@@ -981,9 +981,9 @@ extern "C" int lev_attn_decode_ld(lev_ctx* ctx, const lev_kv_layout* L, const vo
     A.round_cap = (int)round_cap;
     A.window = window;
     A.scale = scale;
-    // LEV_ATTN_ONE_LAUNCH=1: the last block of each (column, KV head) merges the ranges itself.  Off by
-    // default: at 4096 positions the serial tail of that block cost more than the second launch
-    // (19.7 us against 17.6 us per call).
+    // The kernels can also let the last block of each (column, KV head) merge the ranges itself (A.counters).  No
+    // call takes that form: at 4096 positions the serial tail of that block costs more than the second launch
+    // (18.4 us against 16.9 us per call).
     A.direct = splits == 1;  // short windows, or enough columns to fill the GPU: no partials at all
     const bool one_launch = A.direct;
     A.counters = one_launch && !A.direct ? ctx->d_status + LEV_COUNTER_OFFSET : nullptr;
